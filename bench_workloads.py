@@ -1,0 +1,295 @@
+"""Synthetic workloads of bench.py (shapes and distributions of the benchmark configs).
+
+Device tensors are created with torch (memory + streams only); every timed operation is a call
+into libtatara_b200.so through the C ABI.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+import tatara_b200 as tb
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+
+def measured_peaks():
+    """Roofline denominators: the driver-measured peaks of this pool, else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def decode_bytes(n_keys: int) -> int:
+    """Algorithmic bytes of one decode-attention step: K+V rows of n keys + q, gate, out."""
+    return n_keys * 2048 + 3 * 8192
+
+
+def prefill_flops(rows: int, base: int = 0) -> float:
+    """Causal QK^T + PV flops: 4 * 256 * 16 heads * visible (row, key) pairs."""
+    pairs = rows * base + rows * (rows + 1) // 2
+    return 4.0 * 256 * 16 * pairs
+
+
+def _rope_rows(torch, x, positions):
+    """Rotate dims 0..63 of x [n, heads, 256] (f32) at `positions` (theta base 1e7)."""
+    div = torch.pow(torch.tensor(1.0e7, dtype=torch.float64, device=x.device),
+                    torch.arange(32, dtype=torch.float64, device=x.device) / 32).float()
+    theta = positions.float()[:, None] / div[None, :]
+    c, s = torch.cos(theta)[:, None, :], torch.sin(theta)[:, None, :]
+    lo, hi = x[..., :32].clone(), x[..., 32:64].clone()
+    x[..., :32] = lo * c - hi * s
+    x[..., 32:64] = hi * c + lo * s
+    return x
+
+
+def device_cache(torch, n_keys, capacity, seed):
+    """K, V planes [2][capacity][256] bf16: unit-RMS rotated keys, N(0,1) values."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    keys = torch.zeros((2, capacity, 256), dtype=torch.bfloat16, device="cuda")
+    values = torch.zeros((2, capacity, 256), dtype=torch.bfloat16, device="cuda")
+    chunk = 32768
+    for start in range(0, n_keys, chunk):
+        stop = min(start + chunk, n_keys)
+        x = torch.randn((stop - start, 2, 256), generator=g, device="cuda")
+        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6)
+        x = _rope_rows(torch, x.to(torch.bfloat16).float(), torch.arange(start, stop, device="cuda"))
+        keys[:, start:stop] = x.to(torch.bfloat16).transpose(0, 1)
+        values[:, start:stop] = torch.randn((2, stop - start, 256), generator=g, device="cuda").to(torch.bfloat16)
+    return keys, values
+
+
+def device_query(torch, positions, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pos = torch.as_tensor(positions, device="cuda")
+    x = torch.randn((len(positions), 16, 256), generator=g, device="cuda")
+    x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-6)
+    q = _rope_rows(torch, x.to(torch.bfloat16).float(), pos).to(torch.bfloat16)
+    gate = torch.randn((len(positions), 16, 256), generator=g, device="cuda").to(torch.bfloat16)
+    return q, gate
+
+
+class DecodeCase:
+    def __init__(self, ctx, torch, n_keys, seed=0):
+        self.ctx, self.torch, self.n = ctx, torch, n_keys
+        self.capacity = n_keys
+        self.keys, self.values = device_cache(torch, n_keys, n_keys, seed)
+        q, gate = device_query(torch, [n_keys - 1], seed + 1)
+        self.q, self.gate = q[0].contiguous(), gate[0].contiguous()
+        self.out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
+        self.scratch = torch.empty(tb.decode_scratch_bytes(n_keys, 1) // 4, dtype=torch.float32, device="cuda")
+        # end-to-end leg: the token's projection row lives in pinned host memory
+        g = torch.Generator().manual_seed(seed + 2)
+        self.h_proj = torch.randn((1, 9216), generator=g).to(torch.bfloat16).pin_memory()
+        self.d_proj = torch.zeros((1, 9216), dtype=torch.bfloat16, device="cuda")
+        self.h_out = torch.zeros((16, 256), dtype=torch.bfloat16).pin_memory()
+        self.q2 = torch.zeros((1, 16, 256), dtype=torch.bfloat16, device="cuda")
+        self.g2 = torch.zeros_like(self.q2)
+        self.ones = torch.ones(256, dtype=torch.bfloat16, device="cuda")
+
+    def step(self):
+        self.ctx.attn_decode(self.q, self.gate, self.keys, self.values, self.n - 1, self.capacity,
+                             self.out, self.scratch)
+
+    def step_e2e(self):
+        self.d_proj.copy_(self.h_proj, non_blocking=True)
+        self.ctx.attn_qk_rope(self.d_proj, self.ones, self.ones, self.q2, self.g2, self.keys, self.values,
+                              self.n - 1, self.capacity, 1)
+        self.ctx.attn_decode(self.q2, self.g2, self.keys, self.values, self.n - 1, self.capacity,
+                             self.out, self.scratch)
+        self.h_out.copy_(self.out, non_blocking=True)
+
+    def free(self):
+        del self.keys, self.values, self.scratch
+        self.torch.cuda.empty_cache()
+
+
+class Workloads:
+    def __init__(self, ctx, torch, rank=0, world=1):
+        self.ctx, self.torch, self.rank, self.world = ctx, torch, rank, world
+        self._flush = None
+
+    def flush_l2(self):
+        if self._flush is None:
+            self._flush = self.torch.empty(256 * 1024 * 1024, dtype=self.torch.uint8, device="cuda")
+        self._flush.zero_()
+
+    def traffic_hint(self):
+        """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+        path = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                return json.load(f).get("attn_decode_partition_kernel_ctx262144")
+        return None
+
+    def decode_setup(self, n_keys):
+        return DecodeCase(self.ctx, self.torch, n_keys, seed=self.rank * 100)
+
+    # ---- config 4b: 32 independent lanes, contexts uniform in [4096, 32768]
+    def lanes32(self, timed, steps, warmup):
+        torch = self.torch
+        rng = np.random.default_rng(0)
+        contexts = [int(c) for c in rng.integers(4096, 32769, size=32)]
+        # greedy longest-first assignment of whole lanes to GPUs
+        loads = [0] * self.world
+        mine = []
+        for lane in sorted(range(32), key=lambda i: -contexts[i]):
+            r = loads.index(min(loads))
+            loads[r] += contexts[lane]
+            if r == self.rank:
+                mine.append(lane)
+        cap = 32768
+        n = len(mine)
+        kpool = torch.randn((n, 2, cap, 256), device="cuda", dtype=torch.float32).to(torch.bfloat16) if n else None
+        vpool = torch.randn((n, 2, cap, 256), device="cuda", dtype=torch.float32).to(torch.bfloat16) if n else None
+        q, gate = device_query(torch, [contexts[i] - 1 for i in mine], 7)
+        out = torch.zeros((n, 16, 256), dtype=torch.bfloat16, device="cuda")
+        scratch = torch.empty(tb.decode_scratch_bytes(cap, n) // 4, dtype=torch.float32, device="cuda")
+        lanes = tb.Context.attn_lanes([(i * 2 * cap * 256, contexts[lane] - 1) for i, lane in enumerate(mine)])
+
+        def step():
+            self.ctx.attn_decode_batch(q, gate, kpool, vpool, lanes, cap, out, scratch)
+
+        ms = timed(step, steps, warmup)
+        total_bytes = sum(c * 2048 + 3 * 8192 for c in contexts)
+        res = {"lanes": 32, "contexts": "uniform[4096,32768] seed 0", "ms": ms, "lanes_per_s": 32 / (ms * 1e-3),
+               "gbs": total_bytes / (ms * 1e-3) / 1e9, "total_kv_bytes": total_bytes,
+               "max_rank_keys": max(loads)}
+        # bit-identity: the first local lane alone gives the bits it got inside the batch
+        if n:
+            solo = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
+            step()
+            self.ctx.attn_decode(q[0], gate[0], kpool[0], vpool[0], contexts[mine[0]] - 1, cap, solo, scratch)
+            torch.cuda.synchronize()
+            step()
+            torch.cuda.synchronize()
+            res["lane_bits_identical_alone_vs_batched"] = bool(torch.equal(solo, out[0]))
+        del kpool, vpool
+        torch.cuda.empty_cache()
+        return res
+
+    # ---- config 1: GDN decode step, 4 lanes
+    def gdn_step(self, timed, steps, warmup, n=4):
+        torch = self.torch
+        g = torch.Generator(device="cuda").manual_seed(11)
+        bf = torch.bfloat16
+        proj = torch.randn((n, 12352), generator=g, device="cuda").to(bf)
+        conv_w = (0.5 * torch.randn((8192, 4), generator=g, device="cuda")).to(bf)
+        a_log = torch.log(1 + 15 * torch.rand(32, generator=g, device="cuda")).to(bf)
+        dt_bias = (0.5 * torch.randn(32, generator=g, device="cuda")).to(bf)
+        norm_w = torch.ones(128, device="cuda").to(bf)
+        conv_pool = torch.randn((n, 2, 3, 8192), generator=g, device="cuda").to(bf)
+        rec_pool = 0.02 * torch.randn((n, 2, 32, 128, 128), generator=g, device="cuda")
+        y = torch.zeros((n, 4096), dtype=bf, device="cuda")
+        gated = torch.zeros_like(y)
+        cs, rs = 3 * 8192, 32 * 128 * 128
+        tables = [tb.Context.gdn_lanes([((2 * i + a) * cs, (2 * i + b) * cs, (2 * i + a) * rs, (2 * i + b) * rs)
+                                        for i in range(n)]) for a, b in ((0, 1), (1, 0))]
+        state = {"t": 0}
+
+        def step():
+            self.ctx.gdn_decode_batch(proj, conv_w, a_log, dt_bias, norm_w, conv_pool, rec_pool,
+                                      tables[state["t"] & 1], y, gated)
+            state["t"] += 1
+
+        ms = timed(step, max(steps, 20), warmup, self.flush_l2)
+        nbytes = n * (2 * 2097152 + 2 * 49152 + 24704 + 8192) + 65536
+        return {"lanes": n, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                "l2": "flushed between steps", "kernel": "gdn_decode_fused_kernel (1 launch per step)"}
+
+    # ---- config 3: GDN prefill, 16384 rows
+    def gdn_prefill(self, timed, rows=16384):
+        torch = self.torch
+        g = torch.Generator(device="cuda").manual_seed(12)
+        bf = torch.bfloat16
+        x = torch.randn((rows, 32, 128), generator=g, device="cuda")
+        x = x / x.norm(dim=-1, keepdim=True)
+        qk = torch.cat([(x[:, :16] / 128 ** 0.5).reshape(rows, 2048), x[:, 16:].reshape(rows, 2048)], 1).to(bf).contiguous()
+        v = torch.randn((rows, 4096), generator=g, device="cuda").to(bf)
+        a = torch.randn((rows, 32), generator=g, device="cuda")
+        a_log = torch.log(1 + 15 * torch.rand(32, generator=g, device="cuda"))
+        decay = torch.exp(-torch.exp(a_log)[None, :] * torch.nn.functional.softplus(a)).contiguous()
+        beta = torch.sigmoid(torch.randn((rows, 32), generator=g, device="cuda")).contiguous()
+        s0 = torch.zeros((32, 128, 128), device="cuda")
+        s1 = torch.zeros_like(s0)
+        y = torch.zeros((rows, 4096), dtype=bf, device="cuda")
+        out = {}
+        for chunk, name in ((64, "chunk64"), (1, "sequential_scan")):
+            try:
+                ms = timed(lambda: self.ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk), 5, 3)
+                out[name] = {"ms": ms, "tokens_per_s": rows / (ms * 1e-3),
+                             "tflops_chunked_form": 94.5e9 / (ms * 1e-3) / 1e12,
+                             "gbs_algorithmic": 406913024 / (ms * 1e-3) / 1e9}
+            except tb.TataraError as e:
+                out[name] = {"unavailable": str(e)}
+        out["rows"] = rows
+        return out
+
+    # ---- config 2: causal prefill attention, 16384 rows from position 0
+    def prefill(self, timed, peaks, rows=16384, steps=5):
+        torch = self.torch
+        try:
+            keys, values = device_cache(torch, rows, rows, 21)
+            q, gate = device_query(torch, list(range(rows)), 22)
+            out = torch.zeros((rows, 16, 256), dtype=torch.bfloat16, device="cuda")
+            ms = timed(lambda: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
+        except tb.TataraError as e:
+            return {"unavailable": str(e)}
+        tf = prefill_flops(rows) / (ms * 1e-3) / 1e12
+        return {"rows": rows, "ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
+                "l2": "Q/gate/out 402 MB > L2"}
+
+    # ---- config 4a: one lane at 262144 split along KV over the ranks, LSE merge over NCCL
+    def split_kv(self, dist, n_keys, timed, steps, warmup):
+        torch = self.torch
+        w, r = self.world, self.rank
+        local = n_keys // w
+        keys, values = device_cache(torch, local, local, 31 + r)
+        q, gate = device_query(torch, [n_keys - 1], 32)
+        q, gate = q[0].contiguous(), gate[0].contiguous()
+        rec = torch.zeros((16, 258), device="cuda")
+        allrec = torch.zeros((w, 16, 258), device="cuda")
+        out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
+        scratch = torch.empty(tb.decode_scratch_bytes(local, 1) // 4, dtype=torch.float32, device="cuda")
+
+        def kernel_only():
+            self.ctx.attn_decode_partial(q, keys, values, 0, local, local, rec, scratch)
+
+        def full():
+            self.ctx.attn_decode_partial(q, keys, values, 0, local, local, rec, scratch)
+            dist.all_gather_into_tensor(allrec, rec)
+            self.ctx.attn_combine(allrec, w, 258, 16 * 258, gate, out)
+
+        def collective_only():
+            dist.all_gather_into_tensor(allrec, rec)
+
+        k_ms = timed(kernel_only, steps, warmup)
+        c_ms = timed(collective_only, steps, warmup)
+        f_ms = timed(full, steps, warmup)
+        total = n_keys * 2048 + 3 * 8192
+        return {"context": n_keys, "gpus": w, "keys_per_gpu": local, "kernel_us": k_ms * 1e3,
+                "collective_us": c_ms * 1e3, "end_to_end_us": f_ms * 1e3,
+                "aggregate_gbs": total / (f_ms * 1e-3) / 1e9, "message_bytes_per_rank": 16 * 258 * 4,
+                "scaling": "strong"}
+
+    # ---- single-workload runs (profiling)
+    def run_only(self, which, args, timed, steps, warmup):
+        if which == "decode":
+            d = self.decode_setup(args.context)
+            ms = timed(d.step, steps, warmup, None if args.context * 2048 > 126e6 else self.flush_l2)
+            return {"workload": f"decode_attn_ctx{args.context}", "us": ms * 1e3,
+                    "gbs": (args.context * 2048 + 24576) / (ms * 1e-3) / 1e9}
+        if which == "gdn_step":
+            return self.gdn_step(timed, steps, warmup)
+        if which == "gdn_prefill":
+            return self.gdn_prefill(timed, rows=args.rows)
+        if which == "prefill":
+            return self.prefill(timed, measured_peaks(), rows=args.rows, steps=steps)
+        raise ValueError(which)

@@ -1,0 +1,207 @@
+/*
+ * tatara_b200 -- C ABI of the B200 (sm_100a) attention + Gated DeltaNet operators.
+ *
+ * This header is the drop-in boundary for the reference engine's attention hot path.
+ * The reference talks to its GPU through (pipeline name, buffer-slot bindings, u32
+ * constants, grid) tuples; every entry point below replaces one such dispatch and cites
+ * the reference call site whose slot order it keeps.  Conventions shared by all calls:
+ *
+ *   - Plain C, int status return, caller-owned DEVICE pointers, explicit CUDA stream
+ *     (passed as void* == cudaStream_t; NULL is the default stream).
+ *   - Nothing is allocated after tatara_ctx_create ("the per-token walk allocates
+ *     nothing", include/tatara/runtime/decode_step.h:110-114).
+ *   - bf16 storage / f32 arithmetic.  Tensor layouts are the reference's:
+ *       attention projection  [row][9216] = per head h: q(256)|gate(256), k(2x256), v(2x256)
+ *       q / gate / attended   [row][16][256] bf16
+ *       KV cache planes K, V  [kv_head][capacity][256] bf16   (attention.metal:108-111)
+ *       partial record        258 f32 = [numerator(256) | max | sum]  (decode_geometry.h:111)
+ *       GDN projection        [row][12352] = q 2048|k 2048|v 4096|z 4096|b 32|a 32
+ *       GDN conv state        [3][8192] bf16 oldest first; conv weights [8192][4] bf16
+ *       GDN recurrent state   [32 v-head][128 v-dim][128 k-dim] f32 (in/out ping-pong)
+ *   - Arguments are validated on the host BEFORE anything is enqueued
+ *     (src/runtime/decode_step.cpp:812-824); a failing call enqueues nothing.
+ *   - Calls are asynchronous on `stream`; errors of earlier asynchronous work surface
+ *     as TATARA_CUDA_ERROR from a later call or from tatara_ctx_sync.
+ */
+#ifndef TATARA_B200_H_
+#define TATARA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; names mirror MetalCommandError
+ * (include/tatara/backend/metal/commands.h:232-262). */
+typedef enum tatara_status {
+    TATARA_OK = 0,
+    TATARA_INVALID_BUFFER = 1,          /* null / misaligned pointer            */
+    TATARA_CONTEXT_OUT_OF_RANGE = 2,    /* context >= capacity, empty key range */
+    TATARA_STATE_SLOT_MISMATCH = 3,     /* aliasing in/out state slots          */
+    TATARA_INVALID_STREAM_GROUP = 4,    /* lane count 0 or above the maximum    */
+    TATARA_INVALID_DISPATCH_EXTENT = 5, /* rows == 0, bad chunk size, ...       */
+    TATARA_INVALID_DEVICE = 6,
+    TATARA_SCRATCH_TOO_SMALL = 7,
+    TATARA_DEVICE_WAIT_TIMEOUT = 8,     /* a bounded device-side wait gave up   */
+    TATARA_CUDA_ERROR = 9
+} tatara_status;
+
+typedef struct tatara_ctx tatara_ctx;
+
+#define TATARA_MAX_LANES 256u            /* lanes per batched call            */
+#define TATARA_MAX_CONTEXT 262144u       /* prefill_geometry.h:14             */
+#define TATARA_RECORD_FLOATS 258u        /* decode_geometry.h:111             */
+
+/* One row of the per-layer lane table (the reference's state_table rows,
+ * src/runtime/decode_step.cpp:1037-1062).  Offsets are in ELEMENTS of the pool's type. */
+typedef struct tatara_attn_lane {
+    uint64_t kv_offset; /* element offset of this lane's stripe in the K and V pools */
+    uint32_t context;   /* position of the token being decoded; attends 0..context    */
+    uint32_t reserved;
+} tatara_attn_lane;
+
+typedef struct tatara_gdn_lane {
+    uint64_t conv_in, conv_out; /* element offsets into the conv pool (bf16)      */
+    uint64_t rec_in, rec_out;   /* element offsets into the recurrent pool (f32)  */
+} tatara_gdn_lane;
+
+/* ---- context ----------------------------------------------------------------------- */
+/* Replaces device/queue/library/pipeline creation (tools/native/decode_harness.cpp:148-337). */
+tatara_status tatara_ctx_create(int device, tatara_ctx** out);
+void tatara_ctx_destroy(tatara_ctx* ctx);
+/* Waits for `stream` and returns the first latched device-side error, if any
+ * (MetalExecutionResult, include/tatara/backend/metal/commands.h:374-387). */
+tatara_status tatara_ctx_sync(tatara_ctx* ctx, void* stream);
+const char* tatara_last_error_string(const tatara_ctx* ctx);
+const char* tatara_status_name(tatara_status status);
+int tatara_abi_version(void);
+/* Kernels launched through this context since creation (for benchmark accounting). */
+uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx);
+
+/* ---- geometry (pure functions; include/tatara/runtime/decode_geometry.h:133-135, 165-273) */
+/* Keys per partition and partition count of the split-KV decode for `n_keys` attended
+ * keys.  Depends on n_keys only, never on the batch: this is what keeps a lane's output
+ * bit-identical alone vs batched (src/runtime/decode_step.cpp:15-19). */
+uint32_t tatara_attn_partition_keys(uint32_t n_keys);
+uint32_t tatara_attn_partitions(uint32_t n_keys);
+/* Scratch bytes that decode of `lanes` lanes, each attending at most `max_keys` keys, needs
+ * (attn_record_scratch_bytes, decode_geometry.h:256-262). */
+uint64_t tatara_attn_decode_scratch_bytes(uint32_t max_keys, uint32_t lanes);
+
+/* ---- gated full attention ------------------------------------------------------------ */
+/* attn_qk_rope / attn_qk_rope_blk: slots 0 projection, 1 q_norm w, 2 k_norm w, 3 q out,
+ * 4 gate out, 5 K cache, 6 V cache, 7 context, 8 capacity; grid.y = rows
+ * (src/runtime/decode_step.cpp:713-723, src/runtime/prefill_step.cpp:1450-1465).
+ * Normalises and rotates q/k for `rows` positions starting at `position` and appends K, V
+ * to the cache at those positions. */
+tatara_status tatara_attn_qk_rope(tatara_ctx* ctx, void* stream, const void* projection,
+                                  const void* q_weight, const void* k_weight, void* q_out,
+                                  void* gate_out, void* keys, void* values, uint32_t position,
+                                  uint32_t capacity, uint32_t rows);
+
+/* attn_qk_rope_ms: one row per lane over pooled caches; strides in elements
+ * (src/backend/metal/kernels/attention.metal:119-198). */
+tatara_status tatara_attn_qk_rope_batch(tatara_ctx* ctx, void* stream, const void* projection,
+                                        const void* q_weight, const void* k_weight, void* q_out,
+                                        void* gate_out, void* keys_pool, void* values_pool,
+                                        uint32_t capacity, const tatara_attn_lane* lanes,
+                                        uint32_t n_lanes, uint32_t projection_stride,
+                                        uint32_t query_stride);
+
+/* Decode attention of one lane: slots 0 q, 1 gate, 2 K, 3 V, 4 context, 5 out, 6 capacity,
+ * plus the record scratch of the partitioned family
+ * (src/runtime/decode_step.cpp:239-247, 296-337).  Attends keys 0..context inclusive. */
+tatara_status tatara_attn_decode(tatara_ctx* ctx, void* stream, const void* q, const void* gate,
+                                 const void* keys, const void* values, uint32_t context,
+                                 uint32_t capacity, void* out, void* scratch,
+                                 uint64_t scratch_bytes);
+
+/* Lane-batched decode: slots 0 q slab, 1 gate slab, 2 K pool, 3 V pool, 4 state_table,
+ * 5 out slab, 6 capacity, 8 query_stride (src/runtime/decode_step.cpp:1261-1272).  One
+ * varlen launch for every lane; each lane's arithmetic is exactly its solo call's. */
+tatara_status tatara_attn_decode_batch(tatara_ctx* ctx, void* stream, const void* q,
+                                       const void* gate, const void* keys_pool,
+                                       const void* values_pool, const tatara_attn_lane* lanes,
+                                       uint32_t n_lanes, uint32_t capacity, uint32_t query_stride,
+                                       void* out, void* scratch, uint64_t scratch_bytes);
+
+/* Split-KV building block: one merged record per head over keys [key_begin, key_end) of a
+ * cache slice -> records_out [16][258] f32, un-normalised, no gate
+ * (scores/values record family, src/runtime/decode_step.cpp:296-330). */
+tatara_status tatara_attn_decode_partial(tatara_ctx* ctx, void* stream, const void* q,
+                                         const void* keys, const void* values,
+                                         uint32_t key_begin, uint32_t key_end, uint32_t capacity,
+                                         void* records_out, void* scratch, uint64_t scratch_bytes);
+
+/* attention_decode_combine: slots records, gate, nparts, out
+ * (src/runtime/decode_step.cpp:331-337; attention.metal:1086-1108).
+ * Record (head h, part p) sits at records + h*head_stride + p*part_stride (in floats);
+ * the reference layout is head_stride = nparts*258, part_stride = 258. */
+tatara_status tatara_attn_combine(tatara_ctx* ctx, void* stream, const void* records,
+                                  uint32_t nparts, uint64_t head_stride, uint64_t part_stride,
+                                  const void* gate, void* out);
+
+/* Causal block prefill: slots 0 query, 1 K, 2 V, 3 gate, 4 out, 5 visible, 6 capacity,
+ * 7 tile_rows, 8 tile_context (src/runtime/prefill_step.cpp:1661-1683).  Row r sits at
+ * position context_base + r and attends keys 0..context_base + r of the lane cache (which
+ * tatara_attn_qk_rope has filled). */
+tatara_status tatara_attn_prefill(tatara_ctx* ctx, void* stream, const void* query,
+                                  const void* gate, const void* keys, const void* values,
+                                  uint32_t context_base, uint32_t rows, uint32_t capacity,
+                                  void* out);
+
+/* The numerical-control prefill family (attention_partial_blk + attention_combine_blk,
+ * src/backend/metal/kernels/prefill_attention.metal:97-254): every row runs the decode
+ * kernels' arithmetic.  Needs tatara_attn_decode_scratch_bytes(context_base+rows, rows). */
+tatara_status tatara_attn_prefill_control(tatara_ctx* ctx, void* stream, const void* query,
+                                          const void* gate, const void* keys, const void* values,
+                                          uint32_t context_base, uint32_t rows, uint32_t capacity,
+                                          void* out, void* scratch, uint64_t scratch_bytes);
+
+/* ---- gated deltanet ------------------------------------------------------------------- */
+/* gdn_prepare / gdn_conv_blk: slots 0 projection, 1 conv_in, 2 conv w, 3 qk, 4 value, 5 z,
+ * 6 conv_out [, 7 rows] (src/runtime/decode_step.cpp:666-674, prefill_step.cpp:1936-1943). */
+tatara_status tatara_gdn_prepare(tatara_ctx* ctx, void* stream, const void* projection,
+                                 const void* conv_in, const void* conv_weights, void* qk,
+                                 void* value, void* z, void* conv_out, uint32_t rows);
+
+/* gdn_gates_blk: decay/beta planes [rows][32] f32
+ * (src/backend/metal/kernels/prefill_gdn.metal:94-135). */
+tatara_status tatara_gdn_gates(tatara_ctx* ctx, void* stream, const void* projection,
+                               uint32_t projection_stride, const void* a_log, const void* dt_bias,
+                               void* decay, void* beta, uint32_t rows);
+
+/* gdn_recurrence: slots 0 qk, 1 value, 2 projection, 3 a_log, 4 dt_bias, 5 state_in, 6 y,
+ * 7 state_out (src/runtime/decode_step.cpp:676-690).  state_in != state_out. */
+tatara_status tatara_gdn_step(tatara_ctx* ctx, void* stream, const void* qk, const void* value,
+                              const void* projection, const void* a_log, const void* dt_bias,
+                              const void* state_in, void* y, void* state_out);
+
+/* gdn_gate_norm(_blk): slots 0 y, 1 z, 2 norm w, 3 out (src/runtime/decode_step.cpp:692-697). */
+tatara_status tatara_gdn_gate_norm(tatara_ctx* ctx, void* stream, const void* y, const void* z,
+                                   const void* weight, void* out, uint32_t rows);
+
+/* Lane-batched fused decode step (gdn_prepare_ms + gdn_recurrence_ms + gdn_gate_norm,
+ * src/backend/metal/kernels/gdn.metal:231-378, src/runtime/decode_step.cpp:1037-1062):
+ * one row per lane; conv and recurrent state live in pools addressed by the lane table.
+ * Outputs: gated [lane][4096] bf16 (the o-proj input); y [lane][4096] bf16 optional. */
+tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, const void* projection,
+                                      uint32_t projection_stride, const void* conv_weights,
+                                      const void* a_log, const void* dt_bias,
+                                      const void* norm_weight, void* conv_pool, void* rec_pool,
+                                      const tatara_gdn_lane* lanes, uint32_t n_lanes, void* y,
+                                      void* gated);
+
+/* gdn_recurrence_gates_blk: slots 0 qk, 1 value, 2 decay, 4 beta, 5 state_in, 6 y,
+ * 7 state_out, 8 rows (src/runtime/prefill_step.cpp:2003-2024).  Chunked (WY/UT) evaluation
+ * of the same recurrence; chunk must be 64.  rows need not be a multiple of the chunk. */
+tatara_status tatara_gdn_prefill(tatara_ctx* ctx, void* stream, const void* qk, const void* value,
+                                 const void* decay, const void* beta, const void* state_in,
+                                 void* y, void* state_out, uint32_t rows, uint32_t chunk);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TATARA_B200_H_ */

@@ -1,0 +1,226 @@
+"""tatara_b200 -- B200 (sm_100a) attention + Gated DeltaNet operators behind a C ABI.
+
+The product is ``libtatara_b200.so`` (hand-written CUDA, C ABI declared in
+``include/tatara_b200.h``).  This module is only the loader plus a thin ctypes wrapper used by
+the tests and the benchmark; torch appears solely as the owner of device memory and streams.
+There is no CPU path: if the library is missing, importing :func:`lib` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtatara_b200.so")
+HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "tatara_b200.h")
+
+Q_HEADS, KV_HEADS, HEAD_DIM = 16, 2, 256
+ATTN_PROJ = 9216
+GDN_PROJ, GDN_CONV, GDN_QK, GDN_V, GDN_HEADS, GDN_DIM = 12352, 8192, 4096, 4096, 32, 128
+RECORD_FLOATS = 258
+MAX_LANES = 256
+
+STATUS_NAMES = ["None", "InvalidBuffer", "ContextOutOfRange", "StateSlotMismatch",
+                "InvalidStreamGroup", "InvalidDispatchExtent", "InvalidDevice", "ScratchTooSmall",
+                "DeviceWaitTimeout", "CudaError"]
+
+
+class TataraError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"tatara_b200 status {status} ({STATUS_NAMES[status] if status < len(STATUS_NAMES) else '?'}): {message}")
+        self.status = status
+
+
+class AttnLane(ctypes.Structure):
+    _fields_ = [("kv_offset", ctypes.c_uint64), ("context", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+
+class GdnLane(ctypes.Structure):
+    _fields_ = [("conv_in", ctypes.c_uint64), ("conv_out", ctypes.c_uint64),
+                ("rec_in", ctypes.c_uint64), ("rec_out", ctypes.c_uint64)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libtatara_b200.so; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m tatara_b200.build` "
+                "(nvcc, sm_100a).  tatara_b200 has no CPU or PyTorch fallback.")
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.tatara_status_name.restype = ctypes.c_char_p
+        _lib.tatara_last_error_string.restype = ctypes.c_char_p
+        _lib.tatara_last_error_string.argtypes = [ctypes.c_void_p]
+        _lib.tatara_attn_decode_scratch_bytes.restype = ctypes.c_uint64
+        _lib.tatara_ctx_launch_count.restype = ctypes.c_uint64
+        _lib.tatara_ctx_launch_count.argtypes = [ctypes.c_void_p]
+        _lib.tatara_attn_partition_keys.restype = ctypes.c_uint32
+        _lib.tatara_attn_partitions.restype = ctypes.c_uint32
+    return _lib
+
+
+def partition_keys(n_keys: int) -> int:
+    return int(lib().tatara_attn_partition_keys(ctypes.c_uint32(n_keys)))
+
+
+def partitions(n_keys: int) -> int:
+    return int(lib().tatara_attn_partitions(ctypes.c_uint32(n_keys)))
+
+
+def decode_scratch_bytes(max_keys: int, lanes: int = 1) -> int:
+    return int(lib().tatara_attn_decode_scratch_bytes(ctypes.c_uint32(max_keys), ctypes.c_uint32(lanes)))
+
+
+def _ptr(t):
+    """Device pointer of a torch tensor (or None / int passthrough)."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    if isinstance(t, int):
+        return ctypes.c_void_p(t)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+_u32 = ctypes.c_uint32
+_u64 = ctypes.c_uint64
+
+
+class Context:
+    """One tatara_ctx on one device.  Methods mirror the C entry points one to one and raise
+    :class:`TataraError` on a non-zero status; tensor arguments are torch CUDA tensors."""
+
+    def __init__(self, device: int = 0):
+        self._h = ctypes.c_void_p()
+        st = lib().tatara_ctx_create(ctypes.c_int(device), ctypes.byref(self._h))
+        if st != 0:
+            raise TataraError(st, f"tatara_ctx_create(device={device})")
+        self.device = device
+
+    def close(self):
+        if self._h:
+            lib().tatara_ctx_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st: int):
+        if st != 0:
+            raise TataraError(st, lib().tatara_last_error_string(self._h).decode())
+
+    @staticmethod
+    def _stream(stream):
+        if stream is None:
+            import torch
+            stream = torch.cuda.current_stream()
+        return ctypes.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
+
+    @property
+    def launches(self) -> int:
+        return int(lib().tatara_ctx_launch_count(self._h))
+
+    def sync(self, stream=None):
+        self._check(lib().tatara_ctx_sync(self._h, self._stream(stream)))
+
+    # ---- attention
+    def attn_qk_rope(self, projection, q_weight, k_weight, q_out, gate_out, keys, values, position,
+                     capacity, rows, stream=None):
+        self._check(lib().tatara_attn_qk_rope(self._h, self._stream(stream), _ptr(projection),
+                                              _ptr(q_weight), _ptr(k_weight), _ptr(q_out), _ptr(gate_out),
+                                              _ptr(keys), _ptr(values), _u32(position), _u32(capacity),
+                                              _u32(rows)))
+
+    @staticmethod
+    def attn_lanes(entries):
+        arr = (AttnLane * len(entries))()
+        for i, (off, ctxt) in enumerate(entries):
+            arr[i].kv_offset, arr[i].context, arr[i].reserved = off, ctxt, 0
+        return arr
+
+    @staticmethod
+    def gdn_lanes(entries):
+        arr = (GdnLane * len(entries))()
+        for i, (ci, co, ri, ro) in enumerate(entries):
+            arr[i].conv_in, arr[i].conv_out, arr[i].rec_in, arr[i].rec_out = ci, co, ri, ro
+        return arr
+
+    def attn_qk_rope_batch(self, projection, q_weight, k_weight, q_out, gate_out, keys_pool,
+                           values_pool, capacity, lanes, projection_stride=ATTN_PROJ,
+                           query_stride=Q_HEADS * HEAD_DIM, stream=None):
+        self._check(lib().tatara_attn_qk_rope_batch(
+            self._h, self._stream(stream), _ptr(projection), _ptr(q_weight), _ptr(k_weight), _ptr(q_out),
+            _ptr(gate_out), _ptr(keys_pool), _ptr(values_pool), _u32(capacity), lanes, _u32(len(lanes)),
+            _u32(projection_stride), _u32(query_stride)))
+
+    def attn_decode(self, q, gate, keys, values, context, capacity, out, scratch, stream=None):
+        self._check(lib().tatara_attn_decode(self._h, self._stream(stream), _ptr(q), _ptr(gate), _ptr(keys),
+                                             _ptr(values), _u32(context), _u32(capacity), _ptr(out),
+                                             _ptr(scratch), _u64(scratch.numel() * scratch.element_size())))
+
+    def attn_decode_batch(self, q, gate, keys_pool, values_pool, lanes, capacity, out, scratch,
+                          query_stride=Q_HEADS * HEAD_DIM, stream=None):
+        self._check(lib().tatara_attn_decode_batch(
+            self._h, self._stream(stream), _ptr(q), _ptr(gate), _ptr(keys_pool), _ptr(values_pool), lanes,
+            _u32(len(lanes)), _u32(capacity), _u32(query_stride), _ptr(out), _ptr(scratch),
+            _u64(scratch.numel() * scratch.element_size())))
+
+    def attn_decode_partial(self, q, keys, values, key_begin, key_end, capacity, records_out, scratch,
+                            stream=None):
+        self._check(lib().tatara_attn_decode_partial(
+            self._h, self._stream(stream), _ptr(q), _ptr(keys), _ptr(values), _u32(key_begin), _u32(key_end),
+            _u32(capacity), _ptr(records_out), _ptr(scratch), _u64(scratch.numel() * scratch.element_size())))
+
+    def attn_combine(self, records, nparts, head_stride, part_stride, gate, out, stream=None):
+        self._check(lib().tatara_attn_combine(self._h, self._stream(stream), _ptr(records), _u32(nparts),
+                                              _u64(head_stride), _u64(part_stride), _ptr(gate), _ptr(out)))
+
+    def attn_prefill(self, query, gate, keys, values, context_base, rows, capacity, out, stream=None):
+        self._check(lib().tatara_attn_prefill(self._h, self._stream(stream), _ptr(query), _ptr(gate),
+                                              _ptr(keys), _ptr(values), _u32(context_base), _u32(rows),
+                                              _u32(capacity), _ptr(out)))
+
+    def attn_prefill_control(self, query, gate, keys, values, context_base, rows, capacity, out, scratch,
+                             stream=None):
+        self._check(lib().tatara_attn_prefill_control(
+            self._h, self._stream(stream), _ptr(query), _ptr(gate), _ptr(keys), _ptr(values),
+            _u32(context_base), _u32(rows), _u32(capacity), _ptr(out), _ptr(scratch),
+            _u64(scratch.numel() * scratch.element_size())))
+
+    # ---- gated deltanet
+    def gdn_prepare(self, projection, conv_in, conv_weights, qk, value, z, conv_out, rows, stream=None):
+        self._check(lib().tatara_gdn_prepare(self._h, self._stream(stream), _ptr(projection), _ptr(conv_in),
+                                             _ptr(conv_weights), _ptr(qk), _ptr(value), _ptr(z),
+                                             _ptr(conv_out), _u32(rows)))
+
+    def gdn_gates(self, projection, a_log, dt_bias, decay, beta, rows, projection_stride=GDN_PROJ,
+                  stream=None):
+        self._check(lib().tatara_gdn_gates(self._h, self._stream(stream), _ptr(projection),
+                                           _u32(projection_stride), _ptr(a_log), _ptr(dt_bias), _ptr(decay),
+                                           _ptr(beta), _u32(rows)))
+
+    def gdn_step(self, qk, value, projection, a_log, dt_bias, state_in, y, state_out, stream=None):
+        self._check(lib().tatara_gdn_step(self._h, self._stream(stream), _ptr(qk), _ptr(value),
+                                          _ptr(projection), _ptr(a_log), _ptr(dt_bias), _ptr(state_in),
+                                          _ptr(y), _ptr(state_out)))
+
+    def gdn_gate_norm(self, y, z, weight, out, rows, stream=None):
+        self._check(lib().tatara_gdn_gate_norm(self._h, self._stream(stream), _ptr(y), _ptr(z), _ptr(weight),
+                                               _ptr(out), _u32(rows)))
+
+    def gdn_decode_batch(self, projection, conv_weights, a_log, dt_bias, norm_weight, conv_pool, rec_pool,
+                         lanes, y, gated, projection_stride=GDN_PROJ, stream=None):
+        self._check(lib().tatara_gdn_decode_batch(
+            self._h, self._stream(stream), _ptr(projection), _u32(projection_stride), _ptr(conv_weights),
+            _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), _ptr(conv_pool), _ptr(rec_pool), lanes,
+            _u32(len(lanes)), _ptr(y), _ptr(gated)))
+
+    def gdn_prefill(self, qk, value, decay, beta, state_in, y, state_out, rows, chunk=64, stream=None):
+        self._check(lib().tatara_gdn_prefill(self._h, self._stream(stream), _ptr(qk), _ptr(value),
+                                             _ptr(decay), _ptr(beta), _ptr(state_in), _ptr(y),
+                                             _ptr(state_out), _u32(rows), _u32(chunk)))

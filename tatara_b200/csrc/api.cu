@@ -1,0 +1,133 @@
+// Context, status and geometry entry points of the C ABI.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace tb {
+
+tatara_status fail(tatara_ctx* ctx, tatara_status status, const char* what) {
+    if (ctx != nullptr) {
+        std::snprintf(ctx->error, sizeof(ctx->error), "%s: %s", tatara_status_name(status), what);
+    }
+    return status;
+}
+
+tatara_status check_launch(tatara_ctx* ctx, const char* what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        std::snprintf(ctx->error, sizeof(ctx->error), "CudaError: %s: %s", what,
+                      cudaGetErrorString(err));
+        return TATARA_CUDA_ERROR;
+    }
+    ++ctx->launches;
+    return TATARA_OK;
+}
+
+} // namespace tb
+
+extern "C" {
+
+int tatara_abi_version(void) { return 1; }
+
+const char* tatara_status_name(tatara_status status) {
+    switch (status) {
+    case TATARA_OK: return "None";
+    case TATARA_INVALID_BUFFER: return "InvalidBuffer";
+    case TATARA_CONTEXT_OUT_OF_RANGE: return "ContextOutOfRange";
+    case TATARA_STATE_SLOT_MISMATCH: return "StateSlotMismatch";
+    case TATARA_INVALID_STREAM_GROUP: return "InvalidStreamGroup";
+    case TATARA_INVALID_DISPATCH_EXTENT: return "InvalidDispatchExtent";
+    case TATARA_INVALID_DEVICE: return "InvalidDevice";
+    case TATARA_SCRATCH_TOO_SMALL: return "ScratchTooSmall";
+    case TATARA_DEVICE_WAIT_TIMEOUT: return "DeviceWaitTimeout";
+    case TATARA_CUDA_ERROR: return "CudaError";
+    }
+    return "Unknown";
+}
+
+tatara_status tatara_ctx_create(int device, tatara_ctx** out) {
+    if (out == nullptr) return TATARA_INVALID_BUFFER;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return TATARA_INVALID_DEVICE;
+    }
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return TATARA_INVALID_DEVICE;
+    if (prop.major != 10) return TATARA_INVALID_DEVICE; // sm_100a binaries only
+    if (cudaSetDevice(device) != cudaSuccess) return TATARA_INVALID_DEVICE;
+    auto* ctx = new tatara_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(&ctx->device_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(ctx->device_status, 0, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMallocHost(&ctx->host_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        tatara_ctx_destroy(ctx);
+        return TATARA_CUDA_ERROR;
+    }
+    std::memset(ctx->host_status, 0, tb::kStatusWords * sizeof(uint32_t));
+    *out = ctx;
+    return TATARA_OK;
+}
+
+void tatara_ctx_destroy(tatara_ctx* ctx) {
+    if (ctx == nullptr) return;
+    if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
+    if (ctx->host_status != nullptr) cudaFreeHost(ctx->host_status);
+    delete ctx;
+}
+
+tatara_status tatara_ctx_sync(tatara_ctx* ctx, void* stream) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    auto s = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaMemcpyAsync(ctx->host_status, ctx->device_status,
+                                      tb::kStatusWords * sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) {
+        std::snprintf(ctx->error, sizeof(ctx->error), "CudaError: sync: %s", cudaGetErrorString(err));
+        return TATARA_CUDA_ERROR;
+    }
+    const uint32_t code = ctx->host_status[tb::kStatusCode];
+    if (code != 0) {
+        std::snprintf(ctx->error, sizeof(ctx->error), "%s: device status detail %u",
+                      tatara_status_name(static_cast<tatara_status>(code)),
+                      ctx->host_status[tb::kStatusDetail]);
+        cudaMemsetAsync(ctx->device_status, 0, tb::kStatusWords * sizeof(uint32_t), s);
+        return static_cast<tatara_status>(code);
+    }
+    return TATARA_OK;
+}
+
+const char* tatara_last_error_string(const tatara_ctx* ctx) {
+    return ctx == nullptr ? "null context" : ctx->error;
+}
+
+uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx) { return ctx == nullptr ? 0 : ctx->launches; }
+
+uint32_t tatara_attn_partition_keys(uint32_t n_keys) {
+    return n_keys == 0 ? 0 : tb::partition_keys(n_keys);
+}
+uint32_t tatara_attn_partitions(uint32_t n_keys) {
+    return n_keys == 0 ? 0 : tb::partition_count(n_keys);
+}
+
+uint64_t tatara_attn_decode_scratch_bytes(uint32_t max_keys, uint32_t lanes) {
+    // The partition count is not monotonic in n (the partition size grows in steps), so take
+    // the bound that holds for every n <= max_keys: partitions never hold fewer than 64 keys
+    // below 4736 keys and never fewer than 112 above, and the count peaks at a wave boundary.
+    uint32_t worst = 0;
+    const uint32_t probe[] = {max_keys, 74u * 64u, 98303u};
+    for (uint32_t n : probe) {
+        if (n == 0 || n > max_keys) continue;
+        const uint32_t c = tb::partition_count(n);
+        if (c > worst) worst = c;
+    }
+    // conservative closed bound: n/112 + 74 covers every wave rounding
+    const uint32_t bound = max_keys / 112u + 75u;
+    if (bound > worst) worst = bound;
+    return static_cast<uint64_t>(lanes) * worst * tb::kQHeads * tb::kRecordFloats * sizeof(float);
+}
+
+} // extern "C"

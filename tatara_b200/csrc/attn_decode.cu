@@ -1,0 +1,602 @@
+// Split-KV decode attention for the gated GQA layers (reference semantics:
+// attention.metal:200-276 single kernel, :373-1108 partitioned families + combine).
+//
+// Two kernels:
+//   1. attn_decode_partition_kernel -- persistent CTAs walk work items (lane, kv head,
+//      key partition).  One K/V read serves all 8 query heads of the GQA group: scores and
+//      P.V are mma.sync m16n8k16 tiles with the 8 heads in the M dimension.  Each warp owns a
+//      private cp.async ring of 16-key K and V slices (16-byte coalesced loads, XOR-swizzled
+//      rows, ldmatrix reads) that runs ahead across item boundaries, so HBM stays busy while
+//      a finished item is merged and its 258-float records are written.
+//   2. attn_combine_kernel -- log-sum-exp merge of a lane's records, normalisation and the
+//      sigmoid output gate (or, for split-KV across GPUs, one merged un-normalised record).
+//
+// Lossless concurrency: the partition size is a function of the lane's own key count only
+// (tb::partition_keys), every record is computed by one warp-order-fixed procedure and the
+// combine walks records in index order, so a lane's output bits do not depend on which other
+// lanes share the launch or on which CTA ran which item.
+#include "common.cuh"
+
+namespace tb {
+
+constexpr uint32_t kDecWarps = 4;
+constexpr uint32_t kDecThreads = kDecWarps * 32;
+constexpr uint32_t kDecStages = 3;
+constexpr uint32_t kSliceKeys = 16;
+constexpr uint32_t kRowBytes = kHeadDim * 2;                 // 512
+constexpr uint32_t kSliceBytes = kSliceKeys * kRowBytes;     // 8 KiB per plane
+constexpr uint32_t kStageBytes = 2 * kSliceBytes;            // K then V
+constexpr uint32_t kRingBytes = kDecStages * kStageBytes;    // per warp
+constexpr uint32_t kMergeFloats = kDecWarps * kHeadsPerKv * kHeadDim;
+constexpr uint32_t kDecSmemBytes = kDecWarps * kRingBytes + kMergeFloats * 4 +
+                                   kDecWarps * kHeadsPerKv * 2 * 4 + (TATARA_MAX_LANES + 1) * 4;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecLane {
+    uint64_t kv_offset;  // elements into the K / V pools
+    uint64_t rec_offset; // floats into the record scratch
+    uint32_t key_begin, key_end;
+    uint32_t part_keys, nparts;
+    uint32_t item_start; // first work item of this lane
+    uint32_t row;        // q / gate / out row
+};
+
+template <uint32_t N>
+struct DecParams {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* keys;
+    const __nv_bfloat16* values;
+    float* records;
+    uint64_t query_stride;
+    uint32_t capacity;
+    uint32_t n_lanes;
+    uint32_t total_items;
+    DecLane lane[N];
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                            uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// D(16x8) = A(16x16) * B(16x8) + C with rows 8..15 of A zero: only rows 0..7 are kept.
+__device__ __forceinline__ void mma_top_rows(float& d0, float& d1, uint32_t a0, uint32_t a2,
+                                             uint32_t b0, uint32_t b1) {
+    float z0, z1;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%10,%10};\n"
+        : "+f"(d0), "+f"(d1), "=f"(z0), "=f"(z1)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Position of one warp in its stream of 16-key slices.
+struct SliceCursor {
+    uint32_t item, slice, nkeys, lane, kv, part;
+    const uint8_t* kbase;
+    const uint8_t* vbase;
+    bool valid;
+};
+
+template <uint32_t N>
+__device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams<N>& p,
+                                                 const uint32_t* item_start) {
+    uint32_t lo = 0, hi = p.n_lanes; // last lane with item_start <= item
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (item_start[mid] <= c.item) lo = mid; else hi = mid;
+    }
+    const DecLane& l = p.lane[lo];
+    const uint32_t local = c.item - l.item_start;
+    c.lane = lo;
+    c.part = local >> 1;
+    c.kv = local & 1u;
+    const uint32_t begin = l.key_begin + c.part * l.part_keys;
+    const uint32_t end = min(l.key_end, begin + l.part_keys);
+    c.nkeys = end - begin;
+    const uint64_t first = (l.kv_offset + (uint64_t(c.kv) * p.capacity + begin) * kHeadDim) * 2ull;
+    c.kbase = reinterpret_cast<const uint8_t*>(p.keys) + first;
+    c.vbase = reinterpret_cast<const uint8_t*>(p.values) + first;
+}
+
+template <uint32_t N>
+__device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>& p,
+                                              const uint32_t* item_start, uint32_t warp) {
+    while (c.valid && c.slice * kSliceKeys >= c.nkeys) {
+        c.item += gridDim.x;
+        if (c.item >= p.total_items) {
+            c.valid = false;
+            break;
+        }
+        cursor_load_item(c, p, item_start);
+        c.slice = warp;
+    }
+}
+
+// Issues the 16-key K and V slice under the cursor into one ring stage (rows past the
+// partition end are zero-filled), 32 x 16-byte cp.async per lane.
+__device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage_addr, uint32_t lane) {
+    const uint32_t first = c.slice * kSliceKeys;
+    const uint32_t rows = min(kSliceKeys, c.nkeys - first);
+    const uint8_t* ksrc = c.kbase + uint64_t(first) * kRowBytes + lane * 16u;
+    const uint8_t* vsrc = c.vbase + uint64_t(first) * kRowBytes + lane * 16u;
+#pragma unroll
+    for (uint32_t row = 0; row < kSliceKeys; ++row) {
+        const bool live = row < rows;
+        const uint32_t off = live ? row * kRowBytes : 0u;
+        const uint32_t dst = stage_addr + row * kRowBytes + ((lane ^ (row & 7u)) << 4);
+        cp_async_16(dst, ksrc + off, live ? 16u : 0u);
+        cp_async_16(dst + kSliceBytes, vsrc + off, live ? 16u : 0u);
+    }
+}
+
+template <uint32_t N>
+__global__ void __launch_bounds__(kDecThreads, 1)
+attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    float* merge_o = reinterpret_cast<float*>(smem + kDecWarps * kRingBytes);
+    float* merge_ml = merge_o + kMergeFloats;
+    uint32_t* item_start = reinterpret_cast<uint32_t*>(merge_ml + kDecWarps * kHeadsPerKv * 2);
+    for (uint32_t i = threadIdx.x; i <= p.n_lanes; i += kDecThreads)
+        item_start[i] = i < p.n_lanes ? p.lane[i].item_start : p.total_items;
+    __syncthreads();
+
+    const uint32_t ring = smem_u32(smem + warp * kRingBytes);
+
+    // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
+    SliceCursor pc{};
+    pc.item = blockIdx.x;
+    pc.valid = pc.item < p.total_items;
+    if (pc.valid) {
+        cursor_load_item(pc, p, item_start);
+        pc.slice = warp;
+        cursor_settle(pc, p, item_start, warp);
+    }
+    uint32_t issued = 0, consumed = 0;
+#pragma unroll
+    for (uint32_t i = 0; i + 1 < kDecStages; ++i) {
+        if (pc.valid) {
+            issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
+            pc.slice += kDecWarps;
+            cursor_settle(pc, p, item_start, warp);
+        }
+        cp_async_commit();
+        ++issued;
+    }
+
+    // Per-lane ldmatrix address pieces (see the fragment layouts of mma.m16n8k16).
+    const uint32_t lm_j = lane >> 3, lm_r = lane & 7u;
+    const uint32_t k_row_off = ((lm_j >> 1) * 8u + lm_r) * kRowBytes; // K: matrices (keys lo/hi) x (dims lo/hi)
+    const uint32_t k_chunk_lo = lm_j & 1u;
+    const uint32_t v_row_off = ((lm_j & 1u) * 8u + lm_r) * kRowBytes; // V: matrices (keys lo/hi) x (d lo/hi)
+    const uint32_t v_chunk_lo = lm_j >> 1;
+    const float score_scale = kAttnScale * kLog2e;
+
+    SliceCursor cc{};
+    for (cc.item = blockIdx.x; cc.item < p.total_items; cc.item += gridDim.x) {
+        cursor_load_item(cc, p, item_start);
+        const DecLane& dl = p.lane[cc.lane];
+        // Q fragments of head (kv*8 + g): A rows 0..7 of every k-step.
+        uint32_t qa[16][2];
+        {
+            const __nv_bfloat16* qrow =
+                p.q + dl.row * p.query_stride + (cc.kv * kHeadsPerKv + g) * kHeadDim;
+#pragma unroll
+            for (uint32_t ks = 0; ks < 16; ++ks) {
+                qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16u + 2u * t);
+                qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16u + 8u + 2u * t);
+            }
+        }
+        float o[32][2];
+#pragma unroll
+        for (uint32_t nt = 0; nt < 32; ++nt) o[nt][0] = o[nt][1] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+
+        for (uint32_t slice = warp; slice * kSliceKeys < cc.nkeys; slice += kDecWarps) {
+            // keep the ring full, then wait for the oldest slice
+            if (pc.valid) {
+                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
+                pc.slice += kDecWarps;
+                cursor_settle(pc, p, item_start, warp);
+            }
+            cp_async_commit();
+            ++issued;
+            cp_async_wait<kDecStages - 1>();
+            __syncwarp();
+            const uint32_t kst = ring + (consumed % kDecStages) * kStageBytes;
+            const uint32_t vst = kst + kSliceBytes;
+
+            float s0a = 0.0f, s0b = 0.0f, s1a = 0.0f, s1b = 0.0f;
+#pragma unroll
+            for (uint32_t ks = 0; ks < 16; ++ks) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(kst + k_row_off + (((ks * 2u + k_chunk_lo) ^ lm_r) << 4), b0, b1, b2, b3);
+                mma_top_rows(s0a, s0b, qa[ks][0], qa[ks][1], b0, b1);
+                mma_top_rows(s1a, s1b, qa[ks][0], qa[ks][1], b2, b3);
+            }
+            // thread (g, t): head g, keys 2t, 2t+1 (tile 0) and 8+2t, 8+2t+1 (tile 1)
+            const uint32_t key0 = slice * kSliceKeys + 2u * t;
+            s0a = key0 < cc.nkeys ? s0a * score_scale : -INFINITY;
+            s0b = key0 + 1u < cc.nkeys ? s0b * score_scale : -INFINITY;
+            s1a = key0 + 8u < cc.nkeys ? s1a * score_scale : -INFINITY;
+            s1b = key0 + 9u < cc.nkeys ? s1b * score_scale : -INFINITY;
+            float mx = fmaxf(fmaxf(s0a, s0b), fmaxf(s1a, s1b));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m, mx); // finite: key 0 of every slice is live
+            const float alpha = exp2f(m - m_new);
+            const float p0a = exp2f(s0a - m_new), p0b = exp2f(s0b - m_new);
+            const float p1a = exp2f(s1a - m_new), p1b = exp2f(s1b - m_new);
+            l = l * alpha + ((p0a + p0b) + (p1a + p1b));
+            m = m_new;
+            const uint32_t pa0 = pack_bf16x2(p0a, p0b), pa2 = pack_bf16x2(p1a, p1b);
+#pragma unroll
+            for (uint32_t pr = 0; pr < 16; ++pr) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(vst + v_row_off + (((pr * 2u + v_chunk_lo) ^ lm_r) << 4), b0, b1, b2, b3);
+                o[2 * pr][0] *= alpha;
+                o[2 * pr][1] *= alpha;
+                o[2 * pr + 1][0] *= alpha;
+                o[2 * pr + 1][1] *= alpha;
+                mma_top_rows(o[2 * pr][0], o[2 * pr][1], pa0, pa2, b0, b1);
+                mma_top_rows(o[2 * pr + 1][0], o[2 * pr + 1][1], pa0, pa2, b2, b3);
+            }
+            __syncwarp(); // every lane is done with this stage before it is refilled
+            ++consumed;
+        }
+
+        // ---- merge the four warps of this item and write its 8 records --------------------
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        float* mo = merge_o + (warp * kHeadsPerKv + g) * kHeadDim;
+#pragma unroll
+        for (uint32_t nt = 0; nt < 32; ++nt)
+            *reinterpret_cast<float2*>(mo + nt * 8u + 2u * t) = make_float2(o[nt][0], o[nt][1]);
+        if (t == 0) {
+            merge_ml[(warp * kHeadsPerKv + g) * 2u] = m;
+            merge_ml[(warp * kHeadsPerKv + g) * 2u + 1u] = l;
+        }
+        __syncthreads();
+        {
+            const uint32_t h = threadIdx.x >> 4, d0 = (threadIdx.x & 15u) * 16u;
+            float mw[kDecWarps], big = -INFINITY;
+#pragma unroll
+            for (uint32_t w = 0; w < kDecWarps; ++w) {
+                mw[w] = merge_ml[(w * kHeadsPerKv + h) * 2u];
+                big = fmaxf(big, mw[w]);
+            }
+            float acc[16], lsum = 0.0f;
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) acc[i] = 0.0f;
+#pragma unroll
+            for (uint32_t w = 0; w < kDecWarps; ++w) {
+                const float wt = mw[w] == -INFINITY ? 0.0f : exp2f(mw[w] - big);
+                lsum = fmaf(wt, merge_ml[(w * kHeadsPerKv + h) * 2u + 1u], lsum);
+                const float4* src =
+                    reinterpret_cast<const float4*>(merge_o + (w * kHeadsPerKv + h) * kHeadDim + d0);
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const float4 v = src[i];
+                    acc[4 * i] = fmaf(wt, v.x, acc[4 * i]);
+                    acc[4 * i + 1] = fmaf(wt, v.y, acc[4 * i + 1]);
+                    acc[4 * i + 2] = fmaf(wt, v.z, acc[4 * i + 2]);
+                    acc[4 * i + 3] = fmaf(wt, v.w, acc[4 * i + 3]);
+                }
+            }
+            float* rec = p.records + dl.rec_offset +
+                         (uint64_t(cc.kv * kHeadsPerKv + h) * dl.nparts + cc.part) * kRecordFloats;
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i)
+                *reinterpret_cast<float2*>(rec + d0 + 2u * i) = make_float2(acc[2 * i], acc[2 * i + 1]);
+            if ((threadIdx.x & 15u) == 0u) {
+                rec[kHeadDim] = big * kLn2; // stored in natural-log units, as the reference record
+                rec[kHeadDim + 1u] = lsum;
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+}
+
+// ---- combine ---------------------------------------------------------------------------
+struct CombineLane {
+    const float* records; // record (h, p) at records + h*head_stride + p*part_stride
+    uint64_t head_stride, part_stride;
+    uint32_t nparts;
+    uint32_t row;
+};
+template <uint32_t N>
+struct CombineParams {
+    const __nv_bfloat16* gate;
+    __nv_bfloat16* out;  // [row][16][256] gated output, or null
+    float* record_out;   // [lane][16][258] merged un-normalised record, or null
+    uint64_t query_stride;
+    CombineLane lane[N];
+};
+
+constexpr uint32_t kCombineThreads = 256, kCombinePhases = 8, kCombineDims = 64;
+
+template <uint32_t N>
+__global__ void __launch_bounds__(kCombineThreads)
+attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
+    __shared__ float red_max[kCombineThreads / 32];
+    __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
+    const CombineLane& cl = p.lane[blockIdx.y];
+    const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
+    const uint32_t lane = threadIdx.x & 31u, phase = threadIdx.x >> 5;
+    const float* base = cl.records + head * cl.head_stride;
+    float big = -INFINITY;
+    for (uint32_t part = threadIdx.x; part < cl.nparts; part += kCombineThreads)
+        big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    if (lane == 0) red_max[phase] = big;
+    __syncthreads();
+    big = red_max[0];
+#pragma unroll
+    for (uint32_t i = 1; i < kCombineThreads / 32; ++i) big = fmaxf(big, red_max[i]);
+
+    const uint32_t d = quarter * kCombineDims + lane * 2u;
+    float a0 = 0.0f, a1 = 0.0f, denom = 0.0f;
+    for (uint32_t part = phase; part < cl.nparts; part += kCombinePhases) {
+        const float* rec = base + part * cl.part_stride;
+        const float local = rec[kHeadDim];
+        const float w = local == -INFINITY ? 0.0f : expf(local - big);
+        const float2 v = *reinterpret_cast<const float2*>(rec + d);
+        a0 = fmaf(w, v.x, a0);
+        a1 = fmaf(w, v.y, a1);
+        denom = fmaf(w, rec[kHeadDim + 1u], denom);
+    }
+    red_acc[phase][lane * 2u] = a0;
+    red_acc[phase][lane * 2u + 1u] = a1;
+    if (lane == 0) red_acc[phase][kCombineDims] = denom;
+    __syncthreads();
+    if (threadIdx.x < kCombineDims + 1u) {
+        float total = 0.0f;
+#pragma unroll
+        for (uint32_t ph = 0; ph < kCombinePhases; ++ph) total += red_acc[ph][threadIdx.x];
+        red_acc[0][threadIdx.x] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x < kCombineDims) {
+        const uint32_t dd = quarter * kCombineDims + threadIdx.x;
+        const float acc = red_acc[0][threadIdx.x], total = red_acc[0][kCombineDims];
+        if (p.record_out != nullptr) {
+            float* ro = p.record_out + (uint64_t(blockIdx.y) * kQHeads + head) * kRecordFloats;
+            ro[dd] = acc;
+            if (dd == 0) {
+                ro[kHeadDim] = big;
+                ro[kHeadDim + 1u] = total;
+            }
+        } else {
+            const uint64_t at = cl.row * p.query_stride + head * kHeadDim + dd;
+            const float gate = bf2f(p.gate[at]);
+            p.out[at] = f2bf((acc / total) * (1.0f / (1.0f + expf(-gate))));
+        }
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+struct DecodeRequest {
+    const void* q;
+    const void* gate;
+    const void* keys;
+    const void* values;
+    void* out;        // gated output rows, or null
+    void* record_out; // merged records, or null
+    void* scratch;
+    uint64_t scratch_bytes;
+    uint64_t query_stride;
+    uint32_t capacity;
+};
+
+template <uint32_t N>
+static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const DecodeRequest& r,
+                                   const tatara_attn_lane* lanes, const uint32_t* key_begin,
+                                   const uint32_t* key_end, const uint32_t* rows, uint32_t n_lanes,
+                                   const char* what) {
+    DecParams<N> dp{};
+    CombineParams<N> cp{};
+    dp.q = static_cast<const __nv_bfloat16*>(r.q);
+    dp.keys = static_cast<const __nv_bfloat16*>(r.keys);
+    dp.values = static_cast<const __nv_bfloat16*>(r.values);
+    dp.records = static_cast<float*>(r.scratch);
+    dp.query_stride = r.query_stride;
+    dp.capacity = r.capacity;
+    dp.n_lanes = n_lanes;
+    uint64_t rec_floats = 0;
+    uint32_t items = 0;
+    for (uint32_t i = 0; i < n_lanes; ++i) {
+        DecLane& l = dp.lane[i];
+        l.kv_offset = lanes[i].kv_offset;
+        l.key_begin = key_begin[i];
+        l.key_end = key_end[i];
+        const uint32_t n = l.key_end - l.key_begin;
+        l.part_keys = partition_keys(n);
+        l.nparts = partition_count(n);
+        l.item_start = items;
+        l.rec_offset = rec_floats;
+        l.row = rows[i];
+        items += l.nparts * kKvHeads;
+        cp.lane[i].records = dp.records + rec_floats;
+        cp.lane[i].head_stride = uint64_t(l.nparts) * kRecordFloats;
+        cp.lane[i].part_stride = kRecordFloats;
+        cp.lane[i].nparts = l.nparts;
+        cp.lane[i].row = rows[i];
+        rec_floats += uint64_t(l.nparts) * kQHeads * kRecordFloats;
+    }
+    if (rec_floats * sizeof(float) > r.scratch_bytes) return fail(ctx, TATARA_SCRATCH_TOO_SMALL, what);
+    dp.total_items = items;
+    cp.gate = static_cast<const __nv_bfloat16*>(r.gate);
+    cp.out = static_cast<__nv_bfloat16*>(r.out);
+    cp.record_out = static_cast<float*>(r.record_out);
+    cp.query_stride = r.query_stride;
+
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(attn_decode_partition_kernel<1>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_decode_partition_kernel<TATARA_MAX_LANES>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess)
+            return check_launch(ctx, "attn_decode: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    const uint32_t grid = items < uint32_t(ctx->sm_count) ? items : uint32_t(ctx->sm_count);
+    attn_decode_partition_kernel<N><<<grid, kDecThreads, kDecSmemBytes, stream>>>(dp);
+    tatara_status st = check_launch(ctx, what);
+    if (st != TATARA_OK) return st;
+    attn_combine_kernel<N><<<dim3(kQHeads * 4, n_lanes), kCombineThreads, 0, stream>>>(cp);
+    return check_launch(ctx, what);
+}
+
+} // namespace tb
+
+using namespace tb;
+
+extern "C" tatara_status tatara_attn_decode(tatara_ctx* ctx, void* stream, const void* q,
+                                            const void* gate, const void* keys, const void* values,
+                                            uint32_t context, uint32_t capacity, void* out,
+                                            void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !gate || !keys || !values || !out || !scratch)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode: null buffer");
+    if (!aligned(q, 4) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(scratch, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode: misaligned buffer");
+    if (capacity == 0 || context >= capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode: context >= capacity");
+    const DecodeRequest r{q, gate, keys, values, out, nullptr, scratch, scratch_bytes,
+                          kQHeads * kHeadDim, capacity};
+    const tatara_attn_lane lane{0, context, 0};
+    const uint32_t begin = 0, end = context + 1u, row = 0;
+    return launch_decode<1>(ctx, static_cast<cudaStream_t>(stream), r, &lane, &begin, &end, &row, 1,
+                            "attn_decode");
+}
+
+extern "C" tatara_status tatara_attn_decode_batch(tatara_ctx* ctx, void* stream, const void* q,
+                                                  const void* gate, const void* keys_pool,
+                                                  const void* values_pool,
+                                                  const tatara_attn_lane* lanes, uint32_t n_lanes,
+                                                  uint32_t capacity, uint32_t query_stride,
+                                                  void* out, void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !gate || !keys_pool || !values_pool || !out || !scratch || !lanes)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_batch: null buffer");
+    if (!aligned(q, 4) || !aligned(keys_pool, 16) || !aligned(values_pool, 16) || !aligned(scratch, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_batch: misaligned buffer");
+    if (n_lanes == 0 || n_lanes > TATARA_MAX_LANES)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_decode_batch: lane count");
+    if (query_stride < kQHeads * kHeadDim || (query_stride & 1u))
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_decode_batch: query_stride");
+    uint32_t begin[TATARA_MAX_LANES], end[TATARA_MAX_LANES], rows[TATARA_MAX_LANES];
+    for (uint32_t i = 0; i < n_lanes; ++i) {
+        if (capacity == 0 || lanes[i].context >= capacity)
+            return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_batch: context >= capacity");
+        if (lanes[i].kv_offset % 8u)
+            return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_batch: kv_offset not 16-byte aligned");
+        begin[i] = 0;
+        end[i] = lanes[i].context + 1u;
+        rows[i] = i;
+    }
+    const DecodeRequest r{q, gate, keys_pool, values_pool, out, nullptr, scratch, scratch_bytes,
+                          query_stride, capacity};
+    return launch_decode<TATARA_MAX_LANES>(ctx, static_cast<cudaStream_t>(stream), r, lanes, begin, end,
+                                           rows, n_lanes, "attn_decode_batch");
+}
+
+extern "C" tatara_status tatara_attn_decode_partial(tatara_ctx* ctx, void* stream, const void* q,
+                                                    const void* keys, const void* values,
+                                                    uint32_t key_begin, uint32_t key_end,
+                                                    uint32_t capacity, void* records_out,
+                                                    void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !keys || !values || !records_out || !scratch)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_partial: null buffer");
+    if (!aligned(q, 4) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(scratch, 16) ||
+        !aligned(records_out, 8))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_partial: misaligned buffer");
+    if (capacity == 0 || key_begin >= key_end || key_end > capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_partial: key range");
+    const DecodeRequest r{q, nullptr, keys, values, nullptr, records_out, scratch, scratch_bytes,
+                          kQHeads * kHeadDim, capacity};
+    const tatara_attn_lane lane{0, key_end - 1u, 0};
+    const uint32_t row = 0;
+    return launch_decode<1>(ctx, static_cast<cudaStream_t>(stream), r, &lane, &key_begin, &key_end, &row,
+                            1, "attn_decode_partial");
+}
+
+extern "C" tatara_status tatara_attn_combine(tatara_ctx* ctx, void* stream, const void* records,
+                                             uint32_t nparts, uint64_t head_stride,
+                                             uint64_t part_stride, const void* gate, void* out) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!records || !gate || !out) return fail(ctx, TATARA_INVALID_BUFFER, "attn_combine: null buffer");
+    if (!aligned(records, 8) || (head_stride & 1u) || (part_stride & 1u))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_combine: records must be 8-byte aligned");
+    if (nparts == 0) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_combine: nparts");
+    CombineParams<1> cp{};
+    cp.gate = static_cast<const __nv_bfloat16*>(gate);
+    cp.out = static_cast<__nv_bfloat16*>(out);
+    cp.record_out = nullptr;
+    cp.query_stride = kQHeads * kHeadDim;
+    cp.lane[0] = CombineLane{static_cast<const float*>(records), head_stride, part_stride, nparts, 0};
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(cp);
+    return check_launch(ctx, "attn_combine");
+}
+
+extern "C" tatara_status tatara_attn_prefill_control(tatara_ctx* ctx, void* stream, const void* query,
+                                                     const void* gate, const void* keys,
+                                                     const void* values, uint32_t context_base,
+                                                     uint32_t rows, uint32_t capacity, void* out,
+                                                     void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!query || !gate || !keys || !values || !out || !scratch)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_prefill_control: null buffer");
+    if (!aligned(query, 4) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(scratch, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_prefill_control: misaligned buffer");
+    if (rows == 0) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_prefill_control: rows");
+    if (capacity == 0 || uint64_t(context_base) + rows > capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_prefill_control: rows past capacity");
+    const DecodeRequest r{query, gate, keys, values, out, nullptr, scratch, scratch_bytes,
+                          kQHeads * kHeadDim, capacity};
+    tatara_attn_lane lanes[TATARA_MAX_LANES];
+    uint32_t begin[TATARA_MAX_LANES], end[TATARA_MAX_LANES], row_index[TATARA_MAX_LANES];
+    for (uint32_t first = 0; first < rows; first += TATARA_MAX_LANES) {
+        const uint32_t n = rows - first < TATARA_MAX_LANES ? rows - first : TATARA_MAX_LANES;
+        for (uint32_t i = 0; i < n; ++i) {
+            lanes[i] = tatara_attn_lane{0, context_base + first + i, 0};
+            begin[i] = 0;
+            end[i] = context_base + first + i + 1u;
+            row_index[i] = first + i;
+        }
+        const tatara_status st = launch_decode<TATARA_MAX_LANES>(
+            ctx, static_cast<cudaStream_t>(stream), r, lanes, begin, end, row_index, n, "attn_prefill_control");
+        if (st != TATARA_OK) return st;
+    }
+    return TATARA_OK;
+}

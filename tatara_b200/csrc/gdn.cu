@@ -1,0 +1,408 @@
+// Gated DeltaNet decode-side operators (reference: gdn.metal:48-207, 231-378;
+// prefill_gdn.metal:4-135, 283-320).
+//
+// The recurrent state is f32 [32 v-head][128 v-dim][128 k-dim] = 2 MiB per lane and layer; a
+// decode step reads and rewrites all of it, so the step is HBM-bound.  Each warp owns whole
+// state rows: a lane holds 4 contiguous k-dim elements (one coalesced 512-byte float4 row per
+// warp), four rows are in flight per warp, and the two dot products per row are
+// adjacent-pairs shuffle trees -- the reference's reduction order.
+#include "common.cuh"
+
+namespace tb {
+
+// ---- conv + SiLU + q/k normalisation -----------------------------------------------------
+// One activated conv channel: 4-tap causal conv (f32), bf16, SiLU with per-op bf16 rounding
+// (gdn.metal:66-80).  Position `row` of a block taps the logical sequence
+// [3 state rows | projection rows] at row..row+3 (prefill_gdn.metal:24-32).
+__device__ __forceinline__ __nv_bfloat16 conv_channel(const __nv_bfloat16* projection,
+                                                      uint64_t projection_stride,
+                                                      const __nv_bfloat16* conv_state,
+                                                      const __nv_bfloat16* conv_weights,
+                                                      uint32_t row, uint32_t channel, float taps[4]) {
+#pragma unroll
+    for (uint32_t t = 0; t < 4; ++t) {
+        const uint32_t logical = row + t;
+        taps[t] = logical < 3u ? bf2f(conv_state[logical * kGdnConv + channel])
+                               : bf2f(projection[uint64_t(logical - 3u) * projection_stride + channel]);
+    }
+    const uint2 wraw = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(channel) * 4u);
+    const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
+    const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
+    float acc = __fmul_rn(bf2f(w01.x), taps[0]);
+    acc = __fadd_rn(acc, __fmul_rn(bf2f(w01.y), taps[1]));
+    acc = __fadd_rn(acc, __fmul_rn(bf2f(w23.x), taps[2]));
+    acc = __fadd_rn(acc, __fmul_rn(bf2f(w23.y), taps[3]));
+    const __nv_bfloat16 c = f2bf(acc);
+    return bmul(c, sigmoid_bf16(c));
+}
+
+// l2-normalise one 128-channel head held one channel per thread of a 128-thread group:
+// 32 lanes x 4 contiguous squares, adjacent-pairs tree (gdn.metal:84-104).
+__device__ __forceinline__ __nv_bfloat16 head_normalise(float* head_smem, uint32_t lane128,
+                                                        float activated, bool is_query) {
+    head_smem[lane128] = activated;
+    __syncthreads();
+    float acc = 0.0f;
+    const uint32_t l = lane128 & 31u;
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const float v = head_smem[l * 4u + i];
+        acc += v * v;
+    }
+    acc = warp_sum(acc);
+    const float inverse = 1.0f / sqrtf(acc / float(kGdnDim) + kRmsEps);
+    const __nv_bfloat16 scale = is_query ? f2bf(1.0f / 128.0f) : f2bf(0.08838834764831845f);
+    return bmul(f2bf(activated * inverse), scale);
+}
+
+// grid (96, rows) x 128 threads, exactly the reference's decomposition.
+__global__ void __launch_bounds__(128)
+gdn_prepare_kernel(const __nv_bfloat16* __restrict__ projection,
+                   const __nv_bfloat16* __restrict__ conv_state,
+                   const __nv_bfloat16* __restrict__ conv_weights, __nv_bfloat16* __restrict__ qk,
+                   __nv_bfloat16* __restrict__ value, __nv_bfloat16* __restrict__ z,
+                   __nv_bfloat16* __restrict__ new_conv_state, uint32_t rows) {
+    __shared__ float head_smem[kGdnDim];
+    const uint32_t group = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
+    if (group < kGdnConv / kGdnDim) {
+        const uint32_t channel = group * kGdnDim + lane;
+        float taps[4];
+        const __nv_bfloat16 act = conv_channel(projection, kGdnProj, conv_state, conv_weights, row, channel, taps);
+        if (row + 1u == rows) {
+#pragma unroll
+            for (uint32_t t = 0; t < 3; ++t) new_conv_state[t * kGdnConv + channel] = f2bf(taps[t + 1u]);
+        }
+        if (group < kGdnQk / kGdnDim) {
+            qk[uint64_t(row) * kGdnQk + channel] =
+                head_normalise(head_smem, lane, bf2f(act), group < kGdnKeyHeads);
+        } else {
+            value[uint64_t(row) * kGdnV + channel - kGdnQk] = act;
+        }
+    } else {
+        const uint32_t index = (group - kGdnConv / kGdnDim) * kGdnDim + lane;
+        z[uint64_t(row) * kGdnV + index] = projection[uint64_t(row) * kGdnProj + kGdnZOff + index];
+    }
+}
+
+__global__ void gdn_gates_kernel(const __nv_bfloat16* __restrict__ projection,
+                                 uint64_t projection_stride, const __nv_bfloat16* __restrict__ a_log,
+                                 const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ decay,
+                                 float* __restrict__ beta, uint32_t rows) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * kGdnValueHeads) return;
+    const uint32_t row = idx / kGdnValueHeads, head = idx % kGdnValueHeads;
+    const __nv_bfloat16* proj = projection + row * projection_stride;
+    decay[idx] = gdn_decay(proj[kGdnAOff + head], dt_bias[head], a_log[head]);
+    beta[idx] = gdn_beta(proj[kGdnBOff + head]);
+}
+
+// ---- recurrence --------------------------------------------------------------------------
+// Four state rows of one warp through one delta-rule step (gdn.metal:151-171).
+// kf / qf: this lane's 4 key / query elements.  Returns the 4 row outputs (all lanes).
+struct Rows4 {
+    float4 s[4];
+};
+__device__ __forceinline__ void delta_rule_rows4(Rows4& r, const float kf[4], const float qf[4],
+                                                 const float v[4], float decay, float beta,
+                                                 float out[4]) {
+    float kv[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        r.s[j].x *= decay; r.s[j].y *= decay; r.s[j].z *= decay; r.s[j].w *= decay;
+        float a = r.s[j].x * kf[0];
+        a = fmaf(r.s[j].y, kf[1], a);
+        a = fmaf(r.s[j].z, kf[2], a);
+        kv[j] = fmaf(r.s[j].w, kf[3], a);
+    }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) kv[j] += __shfl_xor_sync(0xffffffffu, kv[j], off);
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        const float delta = (v[j] - kv[j]) * beta;
+        r.s[j].x = fmaf(kf[0], delta, r.s[j].x);
+        r.s[j].y = fmaf(kf[1], delta, r.s[j].y);
+        r.s[j].z = fmaf(kf[2], delta, r.s[j].z);
+        r.s[j].w = fmaf(kf[3], delta, r.s[j].w);
+        float a = r.s[j].x * qf[0];
+        a = fmaf(r.s[j].y, qf[1], a);
+        a = fmaf(r.s[j].z, qf[2], a);
+        out[j] = fmaf(r.s[j].w, qf[3], a);
+    }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) out[j] += __shfl_xor_sync(0xffffffffu, out[j], off);
+    }
+}
+
+__device__ __forceinline__ void load_bf16x4(const __nv_bfloat16* p, float out[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    out[0] = bf2f(a.x); out[1] = bf2f(a.y); out[2] = bf2f(b.x); out[3] = bf2f(b.y);
+}
+
+// Standalone recurrence step: grid (4 quarters, 32 v-heads), 256 threads = 8 warps x 4 rows.
+__global__ void __launch_bounds__(256)
+gdn_step_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __restrict__ value,
+                const __nv_bfloat16* __restrict__ projection, const __nv_bfloat16* __restrict__ a_log,
+                const __nv_bfloat16* __restrict__ dt_bias, const float* __restrict__ state_in,
+                __nv_bfloat16* __restrict__ y, float* __restrict__ state_out) {
+    const uint32_t head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row0 = blockIdx.x * 32u + warp * 4u;
+    const uint64_t base = (uint64_t(head) * kGdnDim + row0) * kGdnDim + lane * 4u;
+    Rows4 r;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+        r.s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + base + j * kGdnDim));
+    const float decay = gdn_decay(projection[kGdnAOff + head], dt_bias[head], a_log[head]);
+    const float beta = gdn_beta(projection[kGdnBOff + head]);
+    float kf[4], qf[4], v[4], out[4];
+    load_bf16x4(qk + (head >> 1) * kGdnDim + lane * 4u, qf);
+    load_bf16x4(qk + kGdnKOff + (head >> 1) * kGdnDim + lane * 4u, kf);
+    load_bf16x4(value + head * kGdnDim + row0, v);
+    delta_rule_rows4(r, kf, qf, v, decay, beta, out);
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+        __stcs(reinterpret_cast<float4*>(state_out + base + j * kGdnDim), r.s[j]);
+    if (lane < 4u) {
+        const float mine = lane == 0 ? out[0] : lane == 1 ? out[1] : lane == 2 ? out[2] : out[3];
+        y[head * kGdnDim + row0 + lane] = f2bf(mine);
+    }
+}
+
+// Weighted per-head RMSNorm of y times SiLU(z) (gdn.metal:174-207): one warp per head.
+__device__ __forceinline__ void gate_norm_head(const float yv[4], const __nv_bfloat16* z,
+                                               const __nv_bfloat16* weight, __nv_bfloat16* out,
+                                               uint32_t lane) {
+    float acc = 0.0f;
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) acc += yv[i] * yv[i];
+    acc = warp_sum(acc);
+    const float inverse = 1.0f / sqrtf(acc / float(kGdnDim) + kRmsEps);
+    float zf[4];
+    load_bf16x4(z + lane * 4u, zf);
+    const uint2 wraw = *reinterpret_cast<const uint2*>(weight + lane * 4u);
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(&wraw);
+    __nv_bfloat16 res[4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const __nv_bfloat16 normed = bmul(w[i], f2bf(yv[i] * inverse));
+        res[i] = f2bf((zf[i] * sigmoid_f32(zf[i])) * bf2f(normed));
+    }
+    *reinterpret_cast<uint2*>(out + lane * 4u) = *reinterpret_cast<const uint2*>(res);
+}
+
+__global__ void __launch_bounds__(128)
+gdn_gate_norm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
+                     const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out) {
+    const uint32_t head = blockIdx.x * 4u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    const uint64_t base = uint64_t(blockIdx.y) * kGdnV + head * kGdnDim;
+    float yv[4];
+    load_bf16x4(y + base + lane * 4u, yv);
+    gate_norm_head(yv, z + base, weight, out + base, lane);
+}
+
+// ---- fused lane-batched decode step ------------------------------------------------------
+// One CTA per (v-head, lane): conv + SiLU + l2-norm for this head's q, k and v channels,
+// gates, the 128-row state update and the gated RMSNorm, with the first state rows already in
+// flight while the prologue computes.  256 threads = 8 warps x 16 rows.
+struct GdnLanes {
+    tatara_gdn_lane lane[TATARA_MAX_LANES];
+};
+
+__global__ void __launch_bounds__(256)
+gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t projection_stride,
+                        const __nv_bfloat16* __restrict__ conv_weights,
+                        const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
+                        const __nv_bfloat16* __restrict__ norm_weight, __nv_bfloat16* conv_pool,
+                        float* rec_pool, __nv_bfloat16* __restrict__ y_out,
+                        __nv_bfloat16* __restrict__ gated, const __grid_constant__ GdnLanes lanes) {
+    __shared__ float head_q[kGdnDim], head_k[kGdnDim];
+    __shared__ float qn[kGdnDim], kn[kGdnDim], vn[kGdnDim], ys[kGdnDim];
+    const uint32_t head = blockIdx.x, row_lane = blockIdx.y;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const tatara_gdn_lane gl = lanes.lane[row_lane];
+    const __nv_bfloat16* proj = projection + row_lane * projection_stride;
+    const __nv_bfloat16* conv_in = conv_pool + gl.conv_in;
+    __nv_bfloat16* conv_out = conv_pool + gl.conv_out;
+    const float* state_in = rec_pool + gl.rec_in;
+    float* state_out = rec_pool + gl.rec_out;
+
+    // state rows of batch 0 go in flight first
+    const uint32_t row_base = warp * 16u;
+    const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
+    Rows4 r;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+        r.s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + j * kGdnDim));
+
+    // prologue: threads 0..127 -> q channel, 128..255 -> k channel; then v channel on 0..127
+    const uint32_t l128 = threadIdx.x & 127u;
+    const bool is_q = threadIdx.x < 128u;
+    const uint32_t qk_channel = (is_q ? 0u : kGdnKOff) + (head >> 1) * kGdnDim + l128;
+    float taps[4];
+    const __nv_bfloat16 act = conv_channel(proj, 0, conv_in, conv_weights, 0, qk_channel, taps);
+    if ((head & 1u) == 0u) {
+#pragma unroll
+        for (uint32_t t = 0; t < 3; ++t) conv_out[t * kGdnConv + qk_channel] = f2bf(taps[t + 1u]);
+    }
+    const __nv_bfloat16 normed = head_normalise(is_q ? head_q : head_k, l128, bf2f(act), is_q);
+    (is_q ? qn : kn)[l128] = bf2f(normed);
+    if (is_q) {
+        const uint32_t v_channel = kGdnQk + head * kGdnDim + l128;
+        const __nv_bfloat16 va = conv_channel(proj, 0, conv_in, conv_weights, 0, v_channel, taps);
+#pragma unroll
+        for (uint32_t t = 0; t < 3; ++t) conv_out[t * kGdnConv + v_channel] = f2bf(taps[t + 1u]);
+        vn[l128] = bf2f(va);
+    }
+    const float decay = gdn_decay(proj[kGdnAOff + head], dt_bias[head], a_log[head]);
+    const float beta = gdn_beta(proj[kGdnBOff + head]);
+    __syncthreads();
+
+    float kf[4], qf[4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        kf[i] = kn[lane * 4u + i];
+        qf[i] = qn[lane * 4u + i];
+    }
+#pragma unroll
+    for (uint32_t batch = 0; batch < 4; ++batch) {
+        Rows4 next;
+        if (batch + 1u < 4u) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j)
+                next.s[j] = __ldcs(reinterpret_cast<const float4*>(
+                    state_in + sbase + ((batch + 1u) * 4u + j) * kGdnDim));
+        }
+        float v[4], out[4];
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) v[j] = vn[row_base + batch * 4u + j];
+        delta_rule_rows4(r, kf, qf, v, decay, beta, out);
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j)
+            __stcs(reinterpret_cast<float4*>(state_out + sbase + (batch * 4u + j) * kGdnDim), r.s[j]);
+        if (lane < 4u) {
+            const float mine = lane == 0 ? out[0] : lane == 1 ? out[1] : lane == 2 ? out[2] : out[3];
+            ys[row_base + batch * 4u + lane] = bf2f(f2bf(mine));
+        }
+        if (batch + 1u < 4u) r = next;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const uint64_t obase = uint64_t(row_lane) * kGdnV + head * kGdnDim;
+        float yv[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) yv[i] = ys[lane * 4u + i];
+        if (y_out != nullptr) {
+            __nv_bfloat16 yb[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) yb[i] = f2bf(yv[i]);
+            *reinterpret_cast<uint2*>(y_out + obase + lane * 4u) = *reinterpret_cast<const uint2*>(yb);
+        }
+        gate_norm_head(yv, proj + kGdnZOff + head * kGdnDim, norm_weight, gated + obase, lane);
+    }
+}
+
+} // namespace tb
+
+using namespace tb;
+using bf16 = __nv_bfloat16;
+
+extern "C" tatara_status tatara_gdn_prepare(tatara_ctx* ctx, void* stream, const void* projection,
+                                            const void* conv_in, const void* conv_weights, void* qk,
+                                            void* value, void* z, void* conv_out, uint32_t rows) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !conv_in || !conv_weights || !qk || !value || !z || !conv_out)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare: null buffer");
+    if (!aligned(conv_weights, 8)) return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare: conv weights alignment");
+    if (conv_in == conv_out) return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_prepare: conv_in aliases conv_out");
+    if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_prepare: rows");
+    gdn_prepare_kernel<<<dim3(96, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(projection), static_cast<const bf16*>(conv_in),
+        static_cast<const bf16*>(conv_weights), static_cast<bf16*>(qk), static_cast<bf16*>(value),
+        static_cast<bf16*>(z), static_cast<bf16*>(conv_out), rows);
+    return check_launch(ctx, "gdn_prepare");
+}
+
+extern "C" tatara_status tatara_gdn_gates(tatara_ctx* ctx, void* stream, const void* projection,
+                                          uint32_t projection_stride, const void* a_log,
+                                          const void* dt_bias, void* decay, void* beta, uint32_t rows) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !a_log || !dt_bias || !decay || !beta)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_gates: null buffer");
+    if (rows == 0 || projection_stride < kGdnProj)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_gates: rows / stride");
+    const uint32_t total = rows * kGdnValueHeads;
+    gdn_gates_kernel<<<(total + 255u) / 256u, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(projection), projection_stride, static_cast<const bf16*>(a_log),
+        static_cast<const bf16*>(dt_bias), static_cast<float*>(decay), static_cast<float*>(beta), rows);
+    return check_launch(ctx, "gdn_gates");
+}
+
+extern "C" tatara_status tatara_gdn_step(tatara_ctx* ctx, void* stream, const void* qk,
+                                         const void* value, const void* projection, const void* a_log,
+                                         const void* dt_bias, const void* state_in, void* y,
+                                         void* state_out) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!qk || !value || !projection || !a_log || !dt_bias || !state_in || !y || !state_out)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_step: null buffer");
+    if (!aligned(state_in, 16) || !aligned(state_out, 16) || !aligned(qk, 8) || !aligned(value, 8))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_step: misaligned buffer");
+    if (state_in == state_out) return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_step: state_in aliases state_out");
+    gdn_step_kernel<<<dim3(4, kGdnValueHeads), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(qk), static_cast<const bf16*>(value), static_cast<const bf16*>(projection),
+        static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
+        static_cast<const float*>(state_in), static_cast<bf16*>(y), static_cast<float*>(state_out));
+    return check_launch(ctx, "gdn_step");
+}
+
+extern "C" tatara_status tatara_gdn_gate_norm(tatara_ctx* ctx, void* stream, const void* y, const void* z,
+                                              const void* weight, void* out, uint32_t rows) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!y || !z || !weight || !out) return fail(ctx, TATARA_INVALID_BUFFER, "gdn_gate_norm: null buffer");
+    if (!aligned(y, 8) || !aligned(z, 8) || !aligned(weight, 8) || !aligned(out, 8))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_gate_norm: misaligned buffer");
+    if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_gate_norm: rows");
+    gdn_gate_norm_kernel<<<dim3(kGdnValueHeads / 4, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(y), static_cast<const bf16*>(z), static_cast<const bf16*>(weight),
+        static_cast<bf16*>(out));
+    return check_launch(ctx, "gdn_gate_norm");
+}
+
+extern "C" tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, const void* projection,
+                                                 uint32_t projection_stride, const void* conv_weights,
+                                                 const void* a_log, const void* dt_bias,
+                                                 const void* norm_weight, void* conv_pool, void* rec_pool,
+                                                 const tatara_gdn_lane* lanes, uint32_t n_lanes, void* y,
+                                                 void* gated) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !conv_weights || !a_log || !dt_bias || !norm_weight || !conv_pool || !rec_pool ||
+        !lanes || !gated)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch: null buffer");
+    if (!aligned(rec_pool, 16) || !aligned(conv_weights, 8) || !aligned(norm_weight, 8) ||
+        !aligned(gated, 8) || !aligned(projection, 8) || (y && !aligned(y, 8)))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch: misaligned buffer");
+    if (n_lanes == 0 || n_lanes > TATARA_MAX_LANES)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "gdn_decode_batch: lane count");
+    if (projection_stride < kGdnProj || (projection_stride & 3u))
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_decode_batch: projection stride");
+    GdnLanes table{};
+    for (uint32_t i = 0; i < n_lanes; ++i) {
+        const tatara_gdn_lane& l = lanes[i];
+        if (l.conv_in == l.conv_out || l.rec_in == l.rec_out)
+            return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_decode_batch: in slot aliases out slot");
+        if ((l.rec_in & 3u) || (l.rec_out & 3u))
+            return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch: recurrent offset alignment");
+        table.lane[i] = l;
+    }
+    gdn_decode_fused_kernel<<<dim3(kGdnValueHeads, n_lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(projection), projection_stride, static_cast<const bf16*>(conv_weights),
+        static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
+        static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool), static_cast<float*>(rec_pool),
+        static_cast<bf16*>(y), static_cast<bf16*>(gated), table);
+    return check_launch(ctx, "gdn_decode_batch");
+}

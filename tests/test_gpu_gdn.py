@@ -1,0 +1,203 @@
+"""GPU parity of the Gated DeltaNet operators against the CPU oracle, through the C ABI."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import tatara_b200 as tb
+from tatara_b200 import synthetic as syn
+from gpu_util import assert_close_bf16, bf16_ulp_distance, dev_bf16, dev_f32, host_f32, host_u16
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import cases  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = tb.Context(0)
+    yield c
+    c.close()
+
+
+def bf(shape):
+    return torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+
+
+def gpu_prepare(ctx, proj, conv, conv_w):
+    rows = proj.shape[0]
+    qk, v, z, new_conv = bf((rows, 4096)), bf((rows, 4096)), bf((rows, 4096)), bf((3, 8192))
+    ctx.gdn_prepare(dev_bf16(proj), dev_bf16(conv), dev_bf16(conv_w), qk, v, z, new_conv, rows)
+    ctx.sync()
+    return host_u16(qk), host_u16(v), host_u16(z), host_u16(new_conv)
+
+
+def assert_bf16_steps(got, want, what, max_steps=1, max_frac=5e-3):
+    dist = bf16_ulp_distance(got, want)
+    assert dist.max() <= max_steps, f"{what}: {dist.max()} bf16 steps"
+    assert (dist > 0).mean() <= max_frac, f"{what}: {(dist > 0).mean():.3%} elements differ"
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 7, 64])
+def test_prepare_matches_oracle(ctx, rows):
+    rng = np.random.default_rng(rows)
+    conv_w, *_ = syn.gdn_weights(rng)
+    conv, _ = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    qk, v, z, new_conv = gpu_prepare(ctx, proj, conv, conv_w)
+    oqk, ov, oz, oconv = oracle.gdn_prepare(proj, conv, conv_w)
+    assert np.array_equal(z, oz) and np.array_equal(new_conv, oconv)
+    assert_bf16_steps(v, ov, "value")
+    assert_bf16_steps(qk, oqk, "qk")
+    assert_close_bf16(qk, oqk, "qk"); assert_close_bf16(v, ov, "value", max_abs=4e-2)
+
+
+def test_gates_match_oracle(ctx):
+    rng = np.random.default_rng(21)
+    _, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    proj = syn.gdn_projection(rng, 50)
+    decay = torch.zeros((50, 32), device="cuda"); beta = torch.zeros((50, 32), device="cuda")
+    ctx.gdn_gates(dev_bf16(proj), dev_bf16(a_log), dev_bf16(dt_bias), decay, beta, 50)
+    ctx.sync()
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    np.testing.assert_allclose(host_f32(decay), od, rtol=2e-5, atol=1e-7)
+    np.testing.assert_allclose(host_f32(beta), ob, rtol=0, atol=0.0079)  # one bf16 step below 1
+    assert (host_f32(beta) != ob).mean() < 0.02
+
+
+def test_step_and_gate_norm_match_oracle(ctx):
+    rng = np.random.default_rng(22)
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, 1)
+    oqk, ov, oz, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
+    y = bf((1, 4096)); state_out = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_step(dev_bf16(oqk), dev_bf16(ov), dev_bf16(proj), dev_bf16(a_log), dev_bf16(dt_bias),
+                 dev_f32(state), y, state_out)
+    ctx.sync()
+    assert_close_bf16(host_u16(y), oy, "gdn step y")
+    np.testing.assert_allclose(host_f32(state_out), ostate, rtol=1e-4, atol=1e-6)
+    out = bf((1, 4096))
+    ctx.gdn_gate_norm(dev_bf16(oy), dev_bf16(oz), dev_bf16(norm_w), out, 1)
+    ctx.sync()
+    want = oracle.gdn_gate_norm(oy, oz, norm_w)
+    assert_bf16_steps(host_u16(out), want, "gate_norm")
+    # in/out slot aliasing is rejected before anything is enqueued
+    st = dev_f32(state)
+    with pytest.raises(tb.TataraError) as e:
+        ctx.gdn_step(dev_bf16(oqk), dev_bf16(ov), dev_bf16(proj), dev_bf16(a_log), dev_bf16(dt_bias), st, y, st)
+    assert e.value.status == tb.STATUS_NAMES.index("StateSlotMismatch")
+
+
+def make_pools(rng, n):
+    convs, states = zip(*[syn.gdn_state(rng) for _ in range(n)])
+    conv_pool = torch.zeros((n, 2, 3, 8192), dtype=torch.bfloat16, device="cuda")
+    rec_pool = torch.zeros((n, 2, 32, 128, 128), dtype=torch.float32, device="cuda")
+    for i in range(n):
+        conv_pool[i, 0] = dev_bf16(convs[i]); rec_pool[i, 0] = dev_f32(states[i])
+    return convs, states, conv_pool, rec_pool
+
+
+def lane_table(n, swapped):
+    cs, rs = 3 * 8192, 32 * 128 * 128
+    a, b = (1, 0) if swapped else (0, 1)
+    return tb.Context.gdn_lanes([((2 * i + a) * cs, (2 * i + b) * cs, (2 * i + a) * rs, (2 * i + b) * rs)
+                                 for i in range(n)])
+
+
+def test_fused_decode_batch_4_lanes(ctx):
+    """Benchmark config 1: 4 lanes, two consecutive tokens (ping-pong), vs the oracle chain, and
+    bit-identical to each lane run alone."""
+    rng = np.random.default_rng(23)
+    n = 4
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    convs, states, conv_pool, rec_pool = make_pools(rng, n)
+    solo_conv, solo_rec = conv_pool.clone(), rec_pool.clone()
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    o_conv, o_state = list(convs), list(states)
+    for token in range(2):
+        proj = syn.gdn_projection(rng, n)
+        y, gated = bf((n, 4096)), bf((n, 4096))
+        ctx.gdn_decode_batch(dev_bf16(proj), w[0], w[1], w[2], w[3], conv_pool, rec_pool,
+                             lane_table(n, token % 2 == 1), y, gated)
+        ctx.sync()
+        for i in range(n):
+            oqk, ov, oz, o_conv[i] = oracle.gdn_prepare(proj[i:i + 1], o_conv[i], conv_w)
+            od, ob = oracle.gdn_gates(proj[i:i + 1], a_log, dt_bias)
+            oy, o_state[i] = oracle.gdn_scan(oqk, ov, od, ob, o_state[i], threads=8)
+            og = oracle.gdn_gate_norm(oy, oz, norm_w)
+            assert_close_bf16(host_u16(y[i]), oy[0], f"token {token} lane {i} y")
+            assert_close_bf16(host_u16(gated[i]), og[0], f"token {token} lane {i} gated", max_abs=4e-2)
+            slot = (token + 1) % 2
+            np.testing.assert_allclose(host_f32(rec_pool[i, slot]), o_state[i], rtol=2e-4, atol=2e-6)
+            assert np.array_equal(host_u16(conv_pool[i, slot]), o_conv[i])
+            # solo run of the same lane: same bits
+            ys, gs = bf((1, 4096)), bf((1, 4096))
+            cs, rs = 3 * 8192, 32 * 128 * 128
+            a, b = (1, 0) if token % 2 else (0, 1)
+            lane = tb.Context.gdn_lanes([((2 * i + a) * cs, (2 * i + b) * cs, (2 * i + a) * rs, (2 * i + b) * rs)])
+            ctx.gdn_decode_batch(dev_bf16(proj[i:i + 1]), w[0], w[1], w[2], w[3], solo_conv, solo_rec, lane, ys, gs)
+            ctx.sync()
+            assert torch.equal(ys[0], y[i]) and torch.equal(gs[0], gated[i])
+            assert torch.equal(solo_rec[i, slot], rec_pool[i, slot])
+
+
+def test_fused_equals_unfused_ops(ctx):
+    rng = np.random.default_rng(24)
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    convs, states, conv_pool, rec_pool = make_pools(rng, 1)
+    proj = syn.gdn_projection(rng, 1)
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    y, gated = bf((1, 4096)), bf((1, 4096))
+    ctx.gdn_decode_batch(dev_bf16(proj), w[0], w[1], w[2], w[3], conv_pool, rec_pool, lane_table(1, False), y, gated)
+    qk, v, z, new_conv = bf((1, 4096)), bf((1, 4096)), bf((1, 4096)), bf((3, 8192))
+    ctx.gdn_prepare(dev_bf16(proj), dev_bf16(convs[0]), w[0], qk, v, z, new_conv, 1)
+    y2 = bf((1, 4096)); s2 = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_step(qk, v, dev_bf16(proj), w[1], w[2], dev_f32(states[0]), y2, s2)
+    g2 = bf((1, 4096))
+    ctx.gdn_gate_norm(y2, z, w[3], g2, 1)
+    ctx.sync()
+    assert torch.equal(y, y2) and torch.equal(gated, g2)
+    assert torch.equal(rec_pool[0, 1], s2) and torch.equal(conv_pool[0, 1], new_conv)
+
+
+@pytest.mark.parametrize("rows", [1, 5, 200])
+def test_sequential_scan_prefill_matches_oracle(ctx, rows):
+    rng = np.random.default_rng(30 + rows)
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    oqk, ov, _, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
+    y = bf((rows, 4096)); s = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_prefill(dev_bf16(oqk), dev_bf16(ov), dev_f32(od), dev_f32(ob), dev_f32(state), y, s, rows, chunk=1)
+    ctx.sync()
+    assert_close_bf16(host_u16(y), oy, f"scan rows={rows}")
+    np.testing.assert_allclose(host_f32(s), ostate, rtol=5e-4, atol=5e-6)
+
+
+def test_gdn_chain_matches_reference_golden(ctx):
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.npz"))
+    weights, conv, state, projections = cases.gdn_chain()
+    conv_w, a_log, dt_bias, norm_w = weights
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    conv_pool = torch.zeros((2, 3, 8192), dtype=torch.bfloat16, device="cuda")
+    rec_pool = torch.zeros((2, 32, 128, 128), dtype=torch.float32, device="cuda")
+    conv_pool[0] = dev_bf16(conv); rec_pool[0] = dev_f32(state)
+    for step, proj in enumerate(projections):
+        y, gated = bf((1, 4096)), bf((1, 4096))
+        ctx.gdn_decode_batch(dev_bf16(proj[None]), w[0], w[1], w[2], w[3], conv_pool, rec_pool,
+                             lane_table(1, step % 2 == 1), y, gated)
+        ctx.sync()
+        assert_close_bf16(host_u16(y[0]), gold[f"gdn/{step}/y"], f"golden y step {step}")
+        assert_close_bf16(host_u16(gated[0]), gold[f"gdn/{step}/gated"], f"golden gated step {step}", max_abs=4e-2)
+    final = host_f32(rec_pool[len(projections) % 2])
+    np.testing.assert_allclose(final[3], gold["gdn/final_state_head3"], rtol=1e-3, atol=1e-5)
+    assert np.array_equal(host_u16(conv_pool[len(projections) % 2]), gold["gdn/final_conv"])
