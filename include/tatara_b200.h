@@ -127,6 +127,28 @@ tatara_status tatara_attn_decode_batch(tatara_ctx* ctx, void* stream, const void
                                        uint32_t n_lanes, uint32_t capacity, uint32_t query_stride,
                                        void* out, void* scratch, uint64_t scratch_bytes);
 
+/* Decode attention of one lane for callers that must not allocate device memory: a serving
+ * loop that has frozen its memory plan after boot, a plug-in running inside a host framework
+ * whose allocator it may not touch, or any code path where cudaMalloc (a synchronising call
+ * that can fail under memory pressure) is off limits.  It has no counterpart in the reference,
+ * whose record scratch is always a caller-owned buffer.  Same arithmetic and output as
+ * tatara_attn_decode, but the partial records go to a 4 MiB array built into the library, so
+ * no scratch pointer is passed and this call never calls cudaMalloc, cudaFree or any routine
+ * that allocates.  Limits and sharing:
+ *   - at most 65536 attended keys (context <= 65535); longer lanes return
+ *     TATARA_SCRATCH_TOO_SMALL and must use tatara_attn_decode with caller scratch;
+ *   - every call on a device shares the one array: calls that may overlap on the GPU
+ *     (different streams, or several host threads) race on it; serialise them.  The array
+ *     keeps the previous call's records, which is harmless: each call rewrites every record it
+ *     later reads, so nothing has to start at zero;
+ *   - the first call on each device (with that device current) looks up the array's device
+ *     address and configures the kernel; make that first call before any stream capture;
+ *   - every GPU that loads the library holds the 4 MiB until the process exits;
+ *   - ctx may be NULL (it only receives the error text and the launch count). */
+tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream, const void* q,
+                                        const void* gate, const void* keys, const void* values,
+                                        uint32_t context, uint32_t capacity, void* out);
+
 /* Split-KV building block: one merged record per head over keys [key_begin, key_end) of a
  * cache slice -> records_out [16][258] f32, un-normalised, no gate
  * (scores/values record family, src/runtime/decode_step.cpp:296-330). */

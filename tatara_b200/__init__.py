@@ -163,6 +163,12 @@ class Context:
                                              _ptr(values), _u32(context), _u32(capacity), _ptr(out),
                                              _ptr(scratch), _u64(scratch.numel() * scratch.element_size())))
 
+    def attn_decode_static(self, q, gate, keys, values, context, capacity, out, stream=None):
+        """Decode attention with the library's built-in record scratch (no allocation, <= 65536 keys)."""
+        self._check(lib().tatara_attn_decode_static(self._h, self._stream(stream), _ptr(q), _ptr(gate),
+                                                    _ptr(keys), _ptr(values), _u32(context), _u32(capacity),
+                                                    _ptr(out)))
+
     def attn_decode_batch(self, q, gate, keys_pool, values_pool, lanes, capacity, out, scratch,
                           query_stride=Q_HEADS * HEAD_DIM, stream=None):
         self._check(lib().tatara_attn_decode_batch(

@@ -600,3 +600,90 @@ extern "C" tatara_status tatara_attn_prefill_control(tatara_ctx* ctx, void* stre
     }
     return TATARA_OK;
 }
+
+// ---- allocation-free decode ---------------------------------------------------------------
+// Record scratch that lives inside the library image instead of in caller memory.  Every GPU
+// that loads the library holds these 4 MiB until the process exits.
+namespace tb {
+constexpr uint32_t kStaticMaxKeys = 65536;
+constexpr uint32_t kStaticMaxParts = 256; // partition_count(n) <= 222 for every n <= 65536
+static __device__ __align__(256) float g_static_records[kStaticMaxParts * kQHeads * kRecordFloats];
+
+struct StaticSetup {
+    bool ready;
+    float* records; // device address of g_static_records on that device
+    int sm_count;
+};
+static StaticSetup g_static_setup[64] = {};
+} // namespace tb
+
+extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream, const void* q,
+                                                   const void* gate, const void* keys,
+                                                   const void* values, uint32_t context,
+                                                   uint32_t capacity, void* out) {
+    // ctx may be null: it is used for the error text and the launch counter only.
+    if (!q || !gate || !keys || !values || !out)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_static: null buffer");
+    if (!aligned(q, 4) || !aligned(keys, 16) || !aligned(values, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_static: misaligned buffer");
+    if (capacity == 0 || context >= capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_static: context >= capacity");
+    const uint32_t n = context + 1u;
+    if (n > kStaticMaxKeys || partition_count(n) > kStaticMaxParts)
+        return fail(ctx, TATARA_SCRATCH_TOO_SMALL,
+                    "attn_decode_static: the built-in scratch covers at most 65536 attended keys; "
+                    "use tatara_attn_decode with caller scratch beyond that");
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
+        return fail(ctx, TATARA_INVALID_DEVICE, "attn_decode_static: no current device");
+    StaticSetup& setup = g_static_setup[device];
+    if (!setup.ready) {
+        // Once per device, with that device current.  In host code the array's name is only a
+        // stand-in for the symbol; the address a kernel may use comes from the runtime.
+        float* address = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_records);
+        if (err == cudaSuccess)
+            err = cudaDeviceGetAttribute(&setup.sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(attn_decode_partition_kernel<1>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
+        if (err != cudaSuccess || address == nullptr) {
+            (void)cudaGetLastError();
+            return fail(ctx, TATARA_CUDA_ERROR, "attn_decode_static: set-up of the built-in scratch failed");
+        }
+        setup.records = address;
+        setup.ready = true;
+    }
+    DecParams<1> dp{};
+    dp.q = static_cast<const __nv_bfloat16*>(q);
+    dp.keys = static_cast<const __nv_bfloat16*>(keys);
+    dp.values = static_cast<const __nv_bfloat16*>(values);
+    dp.records = setup.records;
+    dp.query_stride = kQHeads * kHeadDim;
+    dp.capacity = capacity;
+    dp.n_lanes = 1;
+    DecLane& l = dp.lane[0];
+    l.kv_offset = 0;
+    l.rec_offset = 0;
+    l.key_begin = 0;
+    l.key_end = n;
+    l.part_keys = partition_keys(n);
+    l.nparts = partition_count(n);
+    l.item_start = 0;
+    l.row = 0;
+    dp.total_items = l.nparts * kKvHeads;
+    CombineParams<1> cp{};
+    cp.gate = static_cast<const __nv_bfloat16*>(gate);
+    cp.out = static_cast<__nv_bfloat16*>(out);
+    cp.record_out = nullptr;
+    cp.query_stride = kQHeads * kHeadDim;
+    cp.lane[0] = CombineLane{setup.records, uint64_t(l.nparts) * kRecordFloats, kRecordFloats, l.nparts, 0};
+    const uint32_t grid = dp.total_items < uint32_t(setup.sm_count) ? dp.total_items : uint32_t(setup.sm_count);
+    auto s = static_cast<cudaStream_t>(stream);
+    attn_decode_partition_kernel<1><<<grid, kDecThreads, kDecSmemBytes, s>>>(dp);
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, s>>>(cp);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return fail(ctx, TATARA_CUDA_ERROR, cudaGetErrorString(err));
+    if (ctx != nullptr) ctx->launches += 2;
+    return TATARA_OK;
+}
