@@ -58,7 +58,7 @@ def build(verbose: bool = False) -> str:
         for _, log in results:
             sys.stderr.write(log)
     if _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcuda"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

@@ -1,11 +1,461 @@
-// Causal block prefill attention (tcgen05 / TMEM / TMA).
+// Causal block prefill of the gated GQA attention layers on the 5th-generation tensor cores
+// (reference semantics: attention_partial_blk + attention_combine_blk,
+// prefill_attention.metal:97-254; shipped pair of GEMMs + softmax + gate, host
+// src/runtime/prefill_step.cpp:1467-1819).
+//
+// One CTA owns 128 query rows of one head (a 128 x 256 bf16 Q tile) and streams the visible
+// keys in tiles of 64:
+//     S = Q K^T      tcgen05.mma  M128 N64  K256   (A, B K-major from 128B-swizzled smem)
+//     P = exp2(S*c - m)  in registers, one thread per query row (tcgen05.ld of its TMEM lane)
+//     O += P V       tcgen05.mma  M128 N256 K64    (A = P from smem, B = V, MN-major)
+// S is double-buffered in TMEM (2 x 64 columns) and O lives in 256 TMEM columns for the whole
+// tile; K and V tiles arrive through a two-stage TMA ring (tiled tensor maps, 128-byte swizzle).
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 softmax + epilogue.  The
+// running maximum is updated lazily (O and l are rescaled only when the maximum grows by more
+// than 2^8), which keeps the TMEM round trip of O off the steady-state path.
+// Every mbarrier wait is bounded; on a timeout the CTA latches TATARA_DEVICE_WAIT_TIMEOUT in the
+// context's status word, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
+
+namespace tb {
+
+constexpr uint32_t kBM = 128, kBN = 64;
+constexpr uint32_t kAtomBytesQ = kBM * 128;          // one 64-dim swizzle atom of the Q tile
+constexpr uint32_t kAtomBytesKV = kBN * 128;         // one 64-dim atom of a K or V tile
+constexpr uint32_t kQBytes = 4 * kAtomBytesQ;        // 64 KiB
+constexpr uint32_t kKVBytes = 4 * kAtomBytesKV;      // 32 KiB
+constexpr uint32_t kPBytes = kBM * kBN * 2;          // 16 KiB
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = kOffQ + kQBytes;          // 2 stages
+constexpr uint32_t kOffV = kOffK + 2 * kKVBytes;     // 2 stages
+constexpr uint32_t kOffP = kOffV + 2 * kKVBytes;     // 2 buffers
+constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
+constexpr uint32_t kPrefillSmem = kOffBar + 256;
+constexpr uint32_t kPrefillThreads = 192;
+constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 128;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
+
+// barrier slots
+enum : uint32_t { kBarQ = 0, kBarKFull = 1, kBarKEmpty = 3, kBarVFull = 5, kBarVEmpty = 7,
+                  kBarSFull = 9, kBarPFull = 11, kBarPvDone = 13, kBarCount = 15 };
+
+struct PrefillParams {
+    const __nv_bfloat16* gate;
+    __nv_bfloat16* out;
+    uint32_t* status;
+    uint32_t context_base, rows, n_qtiles;
+};
+
+__device__ __forceinline__ uint32_t s2u(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false once the CTA has been told to abort or the time limit passed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = now_ns();
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if (now_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1u;
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+          "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+          "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100):
+// start address, leading byte offset and stride byte offset in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return uint64_t((addr >> 4) & 0x3FFFu) | (uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           (uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// kind::f16 instruction descriptor: f32 accumulate, bf16 A and B.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t m, uint32_t n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((n >> 3) << 17) |
+           ((m >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t base = s2u(smem);
+    const uint32_t bars = base + kOffBar;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kOffBar + 8 * kBarCount);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + 8 * kBarCount + 8);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+
+    // longest tiles first; the 16 heads of one query tile are adjacent (K/V stay hot in L2)
+    const uint32_t qt = p.n_qtiles - 1u - (blockIdx.x >> 4);
+    const uint32_t head = blockIdx.x & 15u, kv = head >> 3;
+    const uint32_t r0 = qt * kBM;
+    const uint32_t rows_here = min(kBM, p.rows - r0);
+    const uint32_t visible = p.context_base + r0 + rows_here; // keys [0, visible)
+    const uint32_t ntiles = (visible + kBN - 1u) / kBN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(kBarQ), 1);
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar(kBarKFull + s), 1);
+            mbar_init(bar(kBarKEmpty + s), 1);
+            mbar_init(bar(kBarVFull + s), 1);
+            mbar_init(bar(kBarVEmpty + s), 1);
+            mbar_init(bar(kBarSFull + s), 1);
+            mbar_init(bar(kBarPFull + s), 128);
+            mbar_init(bar(kBarPvDone + s), 1);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(bar(kBarQ), kQBytes);
+            for (uint32_t a = 0; a < 4; ++a)
+                tma_load_3d(base + kOffQ + a * kAtomBytesQ, &map_q, bar(kBarQ), int(a * 64), int(head), int(r0));
+            for (uint32_t j = 0; j < ntiles; ++j) {
+                const uint32_t s = j & 1u, use = j >> 1;
+                if (use > 0 && !mbar_wait(bar(kBarKEmpty + s), (use - 1u) & 1u, abort_flag)) break;
+                mbar_expect_tx(bar(kBarKFull + s), kKVBytes);
+                for (uint32_t a = 0; a < 4; ++a)
+                    tma_load_3d(base + kOffK + s * kKVBytes + a * kAtomBytesKV, &map_k, bar(kBarKFull + s),
+                                int(a * 64), int(j * kBN), int(kv));
+                if (use > 0 && !mbar_wait(bar(kBarVEmpty + s), (use - 1u) & 1u, abort_flag)) break;
+                mbar_expect_tx(bar(kBarVFull + s), kKVBytes);
+                for (uint32_t a = 0; a < 4; ++a)
+                    tma_load_3d(base + kOffV + s * kKVBytes + a * kAtomBytesKV, &map_v, bar(kBarVFull + s),
+                                int(a * 64), int(j * kBN), int(kv));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc(kBM, kBN, false);
+            constexpr uint32_t idesc_pv = instr_desc(kBM, kHeadDim, true);
+            bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
+            auto issue_pv = [&](uint32_t i) {
+                const uint32_t t = i & 1u, par = (i >> 1) & 1u;
+                if (!mbar_wait(bar(kBarVFull + t), par, abort_flag)) return false;
+                if (!mbar_wait(bar(kBarPFull + t), par, abort_flag)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
+                    // A = P tile [128 x 64] K-major: +32 B per 16-key step inside the swizzle atom
+                    const uint64_t ad = smem_desc(base + kOffP + t * kPBytes + kk * 32u, 16, 1024);
+                    // B = V tile [64 keys x 256 d] MN-major: atoms of 64 d are kAtomBytesKV apart
+                    // (leading offset), groups of 8 keys 1024 B apart (stride offset); 16 keys = 2048 B
+                    const uint64_t bd = smem_desc(base + kOffV + t * kKVBytes + kk * 2048u, kAtomBytesKV, 1024);
+                    tc_mma(tmem + kColO, ad, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(bar(kBarVEmpty + t));
+                tc_commit(bar(kBarPvDone + t));
+                return true;
+            };
+            for (uint32_t j = 0; ok && j < ntiles; ++j) {
+                const uint32_t s = j & 1u, par = (j >> 1) & 1u;
+                if (!mbar_wait(bar(kBarKFull + s), par, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t ks = 0; ks < kHeadDim / 16; ++ks) {
+                    const uint32_t atom = ks >> 2, inner = (ks & 3u) * 32u;
+                    const uint64_t ad = smem_desc(base + kOffQ + atom * kAtomBytesQ + inner, 16, 1024);
+                    const uint64_t bd = smem_desc(base + kOffK + s * kKVBytes + atom * kAtomBytesKV + inner, 16, 1024);
+                    tc_mma(tmem + kColS + s * kBN, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(kBarKEmpty + s));
+                tc_commit(bar(kBarSFull + s));
+                if (j > 0 && !issue_pv(j - 1u)) { ok = false; break; }
+            }
+            if (ok) issue_pv(ntiles - 1u);
+        }
+    } else {
+        // ---------------- softmax + epilogue: one thread per query row ----------------
+        const uint32_t quarter = warp & 3u;
+        const uint32_t row = quarter * 32u + lane;
+        const uint32_t tlane = (quarter * 32u) << 16;
+        const uint32_t pos = p.context_base + r0 + row; // keys 0..pos are visible to this row
+        const float c = kAttnScale * 1.4426950408889634f;
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (uint32_t j = 0; ok && j < ntiles; ++j) {
+            const uint32_t s = j & 1u, par = (j >> 1) & 1u;
+            if (!mbar_wait(bar(kBarSFull + s), par, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            float sv[64];
+            tmem_ld32(tmem + tlane + kColS + s * kBN, sv);
+            tmem_ld32(tmem + tlane + kColS + s * kBN + 32u, sv + 32);
+            tmem_wait_ld();
+            const uint32_t key0 = j * kBN;
+            float mx = -INFINITY;
+            if (key0 + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
+#pragma unroll
+                for (uint32_t i = 0; i < 64; ++i) {
+                    sv[i] = key0 + i <= pos ? sv[i] * c : -INFINITY;
+                    mx = fmaxf(mx, sv[i]);
+                }
+            } else {
+#pragma unroll
+                for (uint32_t i = 0; i < 64; ++i) {
+                    sv[i] *= c;
+                    mx = fmaxf(mx, sv[i]);
+                }
+            }
+            if (j == 0) {
+                m_used = mx; // key 0 is visible to every row, so this is finite
+            } else {
+                const bool grow = mx > m_used + 8.0f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O holds P.V of tiles < j: wait for tile j-1, then rescale this row in TMEM
+                    const uint32_t jp = j - 1u;
+                    if (!mbar_wait(bar(kBarPvDone + (jp & 1u)), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const float f = grow ? exp2f(m_used - mx) : 1.0f;
+                    for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
+                        float ov[32];
+                        tmem_ld32(tmem + tlane + kColO + ch * 32u, ov);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) ov[i] *= f;
+                        tmem_st32(tmem + tlane + kColO + ch * 32u, ov);
+                    }
+                    tmem_wait_st();
+                    l *= f;
+                    if (grow) m_used = mx;
+                }
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (uint32_t i = 0; i < 64; ++i) {
+                sv[i] = exp2f(sv[i] - m_used);
+                sum += sv[i];
+            }
+            l += sum;
+            if (j >= 2) { // P buffer s was read by the P.V of tile j-2
+                const uint32_t jp = j - 2u;
+                if (!mbar_wait(bar(kBarPvDone + s), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }
+            }
+            // P row -> smem, K-major with the 128-byte swizzle: 16-byte chunk ^ (row & 7)
+            uint8_t* prow = smem + kOffP + s * kPBytes + row * 128u;
+#pragma unroll
+            for (uint32_t ch = 0; ch < 8; ++ch) {
+                uint4 packed;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(sv[ch * 8 + 0], sv[ch * 8 + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(sv[ch * 8 + 2], sv[ch * 8 + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(sv[ch * 8 + 4], sv[ch * 8 + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(sv[ch * 8 + 6], sv[ch * 8 + 7]);
+                packed.x = *reinterpret_cast<uint32_t*>(&h0);
+                packed.y = *reinterpret_cast<uint32_t*>(&h1);
+                packed.z = *reinterpret_cast<uint32_t*>(&h2);
+                packed.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7u)) << 4)) = packed;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(kBarPFull + s));
+        }
+        if (ok) {
+            const uint32_t jl = ntiles - 1u;
+            ok = mbar_wait(bar(kBarPvDone + (jl & 1u)), (jl >> 1) & 1u, abort_flag);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv_l = 1.0f / l;
+            const bool live = row < rows_here;
+            const uint64_t at = (uint64_t(r0 + row) * kQHeads + head) * kHeadDim;
+            for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
+                float ov[32];
+                tmem_ld32(tmem + tlane + kColO + ch * 32u, ov);
+                tmem_wait_ld();
+                if (live) {
+#pragma unroll
+                    for (uint32_t q4 = 0; q4 < 4; ++q4) {
+                        const uint4 graw = *reinterpret_cast<const uint4*>(p.gate + at + ch * 32u + q4 * 8u);
+                        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&graw);
+                        __nv_bfloat16 res[8];
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            const float gate = bf2f(g[i]);
+                            res[i] = f2bf((ov[q4 * 8 + i] * inv_l) * (1.0f / (1.0f + __expf(-gate))));
+                        }
+                        *reinterpret_cast<uint4*>(p.out + at + ch * 32u + q4 * 8u) = *reinterpret_cast<const uint4*>(res);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000); // let copies still in flight land before the shared memory is released
+        __syncthreads();
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled_entry() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+// 3-D bf16 tensor map {256 dims, d1, d2} with a {64, box1, 1} box and the 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* ptr, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                     uint64_t stride2_bytes, uint32_t box1, uint32_t box2) {
+    EncodeTiled fn = encode_tiled_entry();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[3] = {kHeadDim, d1, d2};
+    const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    const cuuint32_t box[3] = {64, box1, box2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace tb
 
 using namespace tb;
 
-extern "C" tatara_status tatara_attn_prefill(tatara_ctx* ctx, void*, const void*, const void*,
-                                             const void*, const void*, uint32_t, uint32_t, uint32_t,
-                                             void*) {
+extern "C" tatara_status tatara_attn_prefill(tatara_ctx* ctx, void* stream, const void* query,
+                                             const void* gate, const void* keys, const void* values,
+                                             uint32_t context_base, uint32_t rows, uint32_t capacity,
+                                             void* out) {
     if (ctx == nullptr) return TATARA_INVALID_BUFFER;
-    return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_prefill: kernel not built in this revision");
+    if (!query || !gate || !keys || !values || !out)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_prefill: null buffer");
+    if (!aligned(query, 16) || !aligned(gate, 16) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(out, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_prefill: buffers must be 16-byte aligned");
+    if (rows == 0) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_prefill: rows");
+    if (capacity == 0 || uint64_t(context_base) + rows > capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_prefill: rows past capacity");
+    const uint32_t visible = context_base + rows;
+    CUtensorMap map_q, map_k, map_v;
+    // Q [rows][16 heads][256]: box = 64 dims x 1 head x 128 rows
+    if (!make_map(&map_q, query, kQHeads, rows, kHeadDim * 2ull, uint64_t(kQHeads) * kHeadDim * 2ull, 1, kBM) ||
+        // K, V [2][capacity][256], extent clipped to the visible keys so the tail reads as zero
+        !make_map(&map_k, keys, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, kBN, 1) ||
+        !make_map(&map_v, values, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, kBN, 1))
+        return fail(ctx, TATARA_CUDA_ERROR, "attn_prefill: tensor map encoding failed");
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kPrefillSmem) != cudaSuccess)
+            return check_launch(ctx, "attn_prefill: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    PrefillParams pp{};
+    pp.gate = static_cast<const __nv_bfloat16*>(gate);
+    pp.out = static_cast<__nv_bfloat16*>(out);
+    pp.status = ctx->device_status;
+    pp.context_base = context_base;
+    pp.rows = rows;
+    pp.n_qtiles = (rows + kBM - 1u) / kBM;
+    attn_prefill_kernel<<<pp.n_qtiles * kQHeads, kPrefillThreads, kPrefillSmem, static_cast<cudaStream_t>(stream)>>>(
+        map_q, map_k, map_v, pp);
+    return check_launch(ctx, "attn_prefill");
 }
