@@ -168,6 +168,8 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         item_start[i] = i < p.n_lanes ? p.lane[i].item_start : p.total_items;
     __syncthreads();
 
+    // Let a programmatic dependent (the combine) be staged; it still waits for this grid to finish.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t ring = smem_u32(smem + warp * kRingBytes);
 
     // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
@@ -341,19 +343,25 @@ struct CombineParams {
     CombineLane lane[N];
 };
 
-constexpr uint32_t kCombineThreads = 256, kCombinePhases = 8, kCombineDims = 64;
+// One CTA per (head, 64-dim quarter, lane): 32 warps, warp w merges records w, w+32, ... (four
+// in flight per thread), lane owns a float2 of the quarter; then the 32 warp partials are summed
+// in warp order.  Every order is fixed by nparts alone.
+constexpr uint32_t kCombineThreads = 1024, kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
 
 template <uint32_t N>
 __global__ void __launch_bounds__(kCombineThreads)
 attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
-    __shared__ float red_max[kCombineThreads / 32];
+    __shared__ float red_max[kCombinePhases];
     __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
+    // When launched as a programmatic dependent of the partition kernel: wait for its records.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const CombineLane& cl = p.lane[blockIdx.y];
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, phase = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride;
+    const uint32_t nparts = cl.nparts;
     float big = -INFINITY;
-    for (uint32_t part = threadIdx.x; part < cl.nparts; part += kCombineThreads)
+    for (uint32_t part = threadIdx.x; part < nparts; part += kCombineThreads)
         big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
 #pragma unroll
     for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
@@ -361,18 +369,29 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     __syncthreads();
     big = red_max[0];
 #pragma unroll
-    for (uint32_t i = 1; i < kCombineThreads / 32; ++i) big = fmaxf(big, red_max[i]);
+    for (uint32_t i = 1; i < kCombinePhases; ++i) big = fmaxf(big, red_max[i]);
 
     const uint32_t d = quarter * kCombineDims + lane * 2u;
     float a0 = 0.0f, a1 = 0.0f, denom = 0.0f;
-    for (uint32_t part = phase; part < cl.nparts; part += kCombinePhases) {
-        const float* rec = base + part * cl.part_stride;
-        const float local = rec[kHeadDim];
-        const float w = local == -INFINITY ? 0.0f : expf(local - big);
-        const float2 v = *reinterpret_cast<const float2*>(rec + d);
-        a0 = fmaf(w, v.x, a0);
-        a1 = fmaf(w, v.y, a1);
-        denom = fmaf(w, rec[kHeadDim + 1u], denom);
+    for (uint32_t first = phase; first < nparts; first += kCombinePhases * kCombineUnroll) {
+        float lm[kCombineUnroll], ls[kCombineUnroll];
+        float2 v[kCombineUnroll];
+#pragma unroll
+        for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+            const uint32_t part = first + u * kCombinePhases;
+            const bool live = part < nparts;
+            const float* rec = base + (live ? part : first) * cl.part_stride;
+            lm[u] = live ? rec[kHeadDim] : -INFINITY;
+            ls[u] = rec[kHeadDim + 1u];
+            v[u] = *reinterpret_cast<const float2*>(rec + d);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+            const float w = lm[u] == -INFINITY ? 0.0f : expf(lm[u] - big);
+            a0 = fmaf(w, v[u].x, a0);
+            a1 = fmaf(w, v[u].y, a1);
+            denom = fmaf(w, ls[u], denom);
+        }
     }
     red_acc[phase][lane * 2u] = a0;
     red_acc[phase][lane * 2u + 1u] = a1;
@@ -472,7 +491,20 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     attn_decode_partition_kernel<N><<<grid, kDecThreads, kDecSmemBytes, stream>>>(dp);
     tatara_status st = check_launch(ctx, what);
     if (st != TATARA_OK) return st;
-    attn_combine_kernel<N><<<dim3(kQHeads * 4, n_lanes), kCombineThreads, 0, stream>>>(cp);
+    // The combine is a programmatic dependent of the partition kernel: its CTAs are staged
+    // while the partitions drain and block in griddepcontrol.wait until every record is visible.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kQHeads * 4, n_lanes);
+    cfg.blockDim = dim3(kCombineThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp) != cudaSuccess)
+        return check_launch(ctx, what);
     return check_launch(ctx, what);
 }
 

@@ -51,7 +51,7 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 __host__ __device__ inline uint32_t partition_keys(uint32_t n) {
     constexpr uint32_t per_wave = kSmCount / kKvHeads; // 74
     if (n <= per_wave * 64u) return 64u;
-    const uint32_t target_keys = n < 98304u ? 256u : 512u;
+    const uint32_t target_keys = n < 49152u ? 256u : (n < 196608u ? 512u : 1024u);
     uint32_t waves = (n + per_wave * target_keys / 2u) / (per_wave * target_keys);
     if (waves == 0) waves = 1;
     const uint32_t parts = per_wave * waves;
