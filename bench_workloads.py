@@ -11,6 +11,7 @@ import os
 import numpy as np
 
 import tatara_b200 as tb
+from tatara_b200 import sharding
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
@@ -151,14 +152,9 @@ class Workloads:
         torch = self.torch
         rng = np.random.default_rng(0)
         contexts = [int(c) for c in rng.integers(4096, 32769, size=32)]
-        # greedy longest-first assignment of whole lanes to GPUs
-        loads = [0] * self.world
-        mine = []
-        for lane in sorted(range(32), key=lambda i: -contexts[i]):
-            r = loads.index(min(loads))
-            loads[r] += contexts[lane]
-            if r == self.rank:
-                mine.append(lane)
+        owned = sharding.assign_lanes(contexts, self.world)      # greedy longest-first, whole lanes
+        mine = owned[self.rank]
+        loads = [sum(contexts[l] for l in r) for r in owned]
         cap = 32768
         n = len(mine)
         kpool = torch.randn((n, 2, cap, 256), device="cuda", dtype=torch.float32).to(torch.bfloat16) if n else None
@@ -265,8 +261,9 @@ class Workloads:
     def split_kv(self, dist, n_keys, timed, steps, warmup):
         torch = self.torch
         w, r = self.world, self.rank
-        local = n_keys // w
-        keys, values = device_cache(torch, local, local, 31 + r)
+        begin, end = sharding.split_kv_ranges(n_keys, w)[r]
+        local = end - begin
+        keys, values = device_cache(torch, local, local, 31 + r)   # this rank's slice of the lane
         q, gate = device_query(torch, [n_keys - 1], 32)
         q, gate = q[0].contiguous(), gate[0].contiguous()
         rec = torch.zeros((16, 258), device="cuda")
@@ -274,16 +271,22 @@ class Workloads:
         out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
         scratch = torch.empty(tb.decode_scratch_bytes(local, 1) // 4, dtype=torch.float32, device="cuda")
 
-        def kernel_only(i=0):
+        def partial():
             self.ctx.attn_decode_partial(q, keys, values, 0, local, local, rec, scratch)
+            return rec
+
+        def combine(gathered):
+            # all-gather layout [rank][head][258]: head stride 258, part stride 16*258
+            self.ctx.attn_combine(gathered, w, 258, 16 * 258, gate, out)
+
+        def kernel_only(i=0):
+            partial()
 
         def full(i=0):
-            self.ctx.attn_decode_partial(q, keys, values, 0, local, local, rec, scratch)
-            dist.all_gather_into_tensor(allrec, rec)
-            self.ctx.attn_combine(allrec, w, 258, 16 * 258, gate, out)
+            sharding.split_kv_decode(dist, w, partial, allrec, combine)
 
         def collective_only(i=0):
-            dist.all_gather_into_tensor(allrec, rec)
+            dist.all_gather_into_tensor(allrec.view(-1), rec.view(-1))
 
         k_ms = timed(kernel_only, steps, warmup)
         c_ms = timed(collective_only, steps, warmup, eager=True)
@@ -291,8 +294,10 @@ class Workloads:
         total = n_keys * 2048 + 3 * 8192
         return {"context": n_keys, "gpus": w, "keys_per_gpu": local, "kernel_us": k_ms * 1e3,
                 "collective_us": c_ms * 1e3, "end_to_end_us": f_ms * 1e3,
-                "aggregate_gbs": total / (f_ms * 1e-3) / 1e9, "message_bytes_per_rank": 16 * 258 * 4,
-                "scaling": "strong"}
+                "aggregate_gbs": total / (f_ms * 1e-3) / 1e9,
+                "kernel_gbs_per_gpu": (local * 2048) / (k_ms * 1e-3) / 1e9,
+                "message_bytes_per_rank": 16 * 258 * 4, "scaling": "strong",
+                "timing": "kernel: CUDA graph; collective and end-to-end: host-issued, CUDA events, max over ranks"}
 
     # ---- single-workload runs (profiling)
     def run_only(self, which, args, timed, steps, warmup):

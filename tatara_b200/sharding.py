@@ -1,0 +1,63 @@
+"""Host-side sharding of the attention path over the GPUs of one box.
+
+Two ways the path shards (one process per GPU, torch.distributed for the plumbing):
+
+* lane-parallel -- whole request lanes are assigned to GPUs and each GPU runs the ordinary
+  batched decode; there is no data-path collective.  Because the split-KV partition function
+  depends only on a lane's own context, every lane's output is bit-identical to its solo run on
+  any GPU.
+* split-KV -- one long lane's keys are cut into contiguous ranges, one per GPU; each GPU reduces
+  its range to one 258-float record per head ([numerator | max | sum], the reference's partition
+  record, src/backend/metal/kernels/attention.metal:1086-1108), the records are all-gathered
+  (16 x 258 x 4 = 16512 bytes per rank) and every rank runs the same log-sum-exp combine.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Sequence, Tuple
+
+RECORD_FLOATS = 258
+Q_HEADS = 16
+
+
+def assign_lanes(contexts: Sequence[int], world: int) -> List[List[int]]:
+    """Greedy longest-first assignment of whole lanes to `world` GPUs.
+
+    Returns, per rank, the lane indices it owns (in assignment order).  Deterministic: ties go
+    to the lower lane index and the lower rank."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    loads = [0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for lane in sorted(range(len(contexts)), key=lambda i: (-contexts[i], i)):
+        rank = loads.index(min(loads))
+        loads[rank] += contexts[lane]
+        owned[rank].append(lane)
+    return owned
+
+
+def split_kv_ranges(n_keys: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous key ranges [begin, end) per rank, 16-key aligned except the last end."""
+    if n_keys <= 0 or world <= 0:
+        raise ValueError("n_keys and world must be positive")
+    per = -(-n_keys // world)
+    per = (per + 15) // 16 * 16
+    ranges = []
+    for r in range(world):
+        begin = min(r * per, n_keys)
+        ranges.append((begin, min(begin + per, n_keys)))
+    return ranges
+
+
+def split_kv_decode(dist, world: int, partial: Callable[[], "object"], gathered, combine: Callable[[object], None]):
+    """One split-KV decode step on this rank: local partial records -> all-gather -> combine.
+
+    `partial()` returns this rank's record tensor [16][258] f32 (a rank whose range is empty
+    returns max = -inf, sum = 0 records, which the combine weighs with 0); `gathered` is the
+    [world][16][258] receive buffer; `combine(gathered)` merges in rank order."""
+    rec = partial()
+    if world > 1:
+        dist.all_gather_into_tensor(gathered.view(-1), rec.reshape(-1))
+    else:
+        gathered.view(-1).copy_(rec.reshape(-1))
+    combine(gathered)
+    return gathered
