@@ -231,9 +231,10 @@ class Workloads:
         s1 = torch.zeros_like(s0)
         y = torch.zeros((rows, 4096), dtype=bf, device="cuda")
         out = {}
+        scratch = torch.empty(tb.gdn_prefill_scratch_bytes(rows), dtype=torch.uint8, device="cuda")
         for chunk, name in ((64, "chunk64"), (1, "sequential_scan")):
             try:
-                ms = timed(lambda i=0: self.ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk), 5, 3)
+                ms = timed(lambda i=0: self.ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk, scratch), 5, 3)
                 out[name] = {"ms": ms, "tokens_per_s": rows / (ms * 1e-3),
                              "tflops_chunked_form": 94.5e9 / (ms * 1e-3) / 1e12,
                              "gbs_algorithmic": 406913024 / (ms * 1e-3) / 1e9}

@@ -217,11 +217,16 @@ tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, const void*
                                       void* gated);
 
 /* gdn_recurrence_gates_blk: slots 0 qk, 1 value, 2 decay, 4 beta, 5 state_in, 6 y,
- * 7 state_out, 8 rows (src/runtime/prefill_step.cpp:2003-2024).  Chunked (WY/UT) evaluation
- * of the same recurrence; chunk must be 64.  rows need not be a multiple of the chunk. */
+ * 7 state_out, 8 rows (src/runtime/prefill_step.cpp:2003-2024).
+ *   chunk == 64: chunked (WY / UT transform) evaluation of the same recurrence on the tensor
+ *                cores; needs tatara_gdn_prefill_scratch_bytes(rows) bytes of scratch.
+ *   chunk == 1 : the reference's own sequential scan (scratch may be NULL).
+ * rows need not be a multiple of the chunk.  state_in != state_out. */
 tatara_status tatara_gdn_prefill(tatara_ctx* ctx, void* stream, const void* qk, const void* value,
                                  const void* decay, const void* beta, const void* state_in,
-                                 void* y, void* state_out, uint32_t rows, uint32_t chunk);
+                                 void* y, void* state_out, uint32_t rows, uint32_t chunk,
+                                 void* scratch, uint64_t scratch_bytes);
+uint64_t tatara_gdn_prefill_scratch_bytes(uint32_t rows);
 
 #ifdef __cplusplus
 }

@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
         _lib.tatara_ctx_launch_count.restype = ctypes.c_uint64
         _lib.tatara_ctx_launch_count.argtypes = [ctypes.c_void_p]
         _lib.tatara_attn_partition_keys.restype = ctypes.c_uint32
+        _lib.tatara_gdn_prefill_scratch_bytes.restype = ctypes.c_uint64
         _lib.tatara_attn_partitions.restype = ctypes.c_uint32
     return _lib
 
@@ -226,7 +227,14 @@ class Context:
             _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), _ptr(conv_pool), _ptr(rec_pool), lanes,
             _u32(len(lanes)), _ptr(y), _ptr(gated)))
 
-    def gdn_prefill(self, qk, value, decay, beta, state_in, y, state_out, rows, chunk=64, stream=None):
+    def gdn_prefill(self, qk, value, decay, beta, state_in, y, state_out, rows, chunk=64, scratch=None,
+                    stream=None):
+        nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
         self._check(lib().tatara_gdn_prefill(self._h, self._stream(stream), _ptr(qk), _ptr(value),
                                              _ptr(decay), _ptr(beta), _ptr(state_in), _ptr(y),
-                                             _ptr(state_out), _u32(rows), _u32(chunk)))
+                                             _ptr(state_out), _u32(rows), _u32(chunk), _ptr(scratch),
+                                             _u64(nbytes)))
+
+
+def gdn_prefill_scratch_bytes(rows: int) -> int:
+    return int(lib().tatara_gdn_prefill_scratch_bytes(ctypes.c_uint32(rows)))

@@ -1,6 +1,7 @@
 // Gated DeltaNet block prefill (reference: prefill_gdn.metal:137-196,
 // gdn_recurrence_gates_blk; host src/runtime/prefill_step.cpp:1958-2038).
 //
+// chunk == 64 runs the chunked (WY / UT transform) form on the tensor cores (gdn_chunked.cu).
 // chunk == 1 selects the sequential scan: the reference's own algorithm, one warp per four
 // state rows held in registers for the whole block, one state write at the end.
 #include "common.cuh"
@@ -87,7 +88,7 @@ gdn_scan_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __res
 tatara_status launch_gdn_chunked(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
                                  const __nv_bfloat16* value, const float* decay, const float* beta,
                                  const float* state_in, __nv_bfloat16* y, float* state_out,
-                                 uint32_t rows);
+                                 uint32_t rows, void* scratch, uint64_t scratch_bytes);
 
 } // namespace tb
 
@@ -96,7 +97,8 @@ using namespace tb;
 extern "C" tatara_status tatara_gdn_prefill(tatara_ctx* ctx, void* stream, const void* qk,
                                             const void* value, const void* decay, const void* beta,
                                             const void* state_in, void* y, void* state_out,
-                                            uint32_t rows, uint32_t chunk) {
+                                            uint32_t rows, uint32_t chunk, void* scratch,
+                                            uint64_t scratch_bytes) {
     if (ctx == nullptr) return TATARA_INVALID_BUFFER;
     if (!qk || !value || !decay || !beta || !state_in || !y || !state_out)
         return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prefill: null buffer");
@@ -110,7 +112,8 @@ extern "C" tatara_status tatara_gdn_prefill(tatara_ctx* ctx, void* stream, const
         return launch_gdn_chunked(ctx, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(qk),
                                   static_cast<const __nv_bfloat16*>(value), static_cast<const float*>(decay),
                                   static_cast<const float*>(beta), static_cast<const float*>(state_in),
-                                  static_cast<__nv_bfloat16*>(y), static_cast<float*>(state_out), rows);
+                                  static_cast<__nv_bfloat16*>(y), static_cast<float*>(state_out), rows, scratch,
+                                  scratch_bytes);
     gdn_scan_kernel<<<dim3(4, kGdnValueHeads), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(qk), static_cast<const __nv_bfloat16*>(value),
         static_cast<const float*>(decay), static_cast<const float*>(beta),

@@ -201,3 +201,96 @@ def test_gdn_chain_matches_reference_golden(ctx):
     final = host_f32(rec_pool[len(projections) % 2])
     np.testing.assert_allclose(final[3], gold["gdn/final_state_head3"], rtol=1e-3, atol=1e-5)
     assert np.array_equal(host_u16(conv_pool[len(projections) % 2]), gold["gdn/final_conv"])
+
+
+def chunk_scratch(rows):
+    return torch.empty(tb.gdn_prefill_scratch_bytes(rows), dtype=torch.uint8, device="cuda")
+
+
+def state_close(got, want, what):
+    from gpu_util import cosine
+    err = float(np.max(np.abs(got - want)))
+    assert np.isfinite(got).all(), f"{what}: non-finite state"
+    assert err <= 2e-2, f"{what}: state max-abs {err:.4g}"
+    assert cosine(got, want) >= 0.9999, f"{what}: state cosine {cosine(got, want):.6f}"
+
+
+@pytest.mark.parametrize("rows,zero_state", [(1, False), (63, False), (64, True), (65, False), (200, False),
+                                              (1000, True)])
+def test_chunked_prefill_matches_sequential_oracle(ctx, rows, zero_state):
+    """Chunk-64 WY form on the tensor cores against the oracle's sequential scan (the reference
+    has only the sequential form, prefill_gdn.metal:137-196)."""
+    rng = np.random.default_rng(50 + rows)
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng, zero=zero_state)
+    proj = syn.gdn_projection(rng, rows)
+    oqk, ov, _, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
+    y = torch.full((rows + 2, 4096), 3.0, dtype=torch.bfloat16, device="cuda")
+    s = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_prefill(dev_bf16(oqk), dev_bf16(ov), dev_f32(od), dev_f32(ob), dev_f32(state), y, s, rows, chunk=64,
+                    scratch=chunk_scratch(rows))
+    ctx.sync()
+    assert torch.all(y[rows:] == 3.0), "rows past the block were written"
+    assert_close_bf16(host_u16(y[:rows]), oy, f"chunked rows={rows}")
+    state_close(host_f32(s), ostate, f"chunked rows={rows}")
+
+
+def test_chunked_prefill_slow_decay_and_split_blocks(ctx):
+    """Slowly forgetting heads (decay near 1) stress the intra-chunk solve; two consecutive
+    blocks must equal one block (state hand-over), and the chunked form must agree with the
+    device's own sequential scan."""
+    rng = np.random.default_rng(61)
+    rows = 384
+    conv_w, _, _, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    oqk, ov, _, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od = (1.0 - 0.02 * rng.random((rows, 32))).astype(np.float32)       # decay in [0.98, 1]
+    ob = (0.2 + 0.8 * rng.random((rows, 32))).astype(np.float32)
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
+    dq, dv, dd, db = dev_bf16(oqk), dev_bf16(ov), dev_f32(od), dev_f32(ob)
+    y = bf((rows, 4096)); s = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_prefill(dq, dv, dd, db, dev_f32(state), y, s, rows, chunk=64, scratch=chunk_scratch(rows))
+    ctx.sync()
+    assert_close_bf16(host_u16(y), oy, "slow decay chunked")
+    state_close(host_f32(s), ostate, "slow decay chunked")
+    # two blocks of 200 + 184 rows
+    y2 = bf((rows, 4096)); mid = torch.zeros_like(s); s2 = torch.zeros_like(s)
+    ctx.gdn_prefill(dq, dv, dd, db, dev_f32(state), y2, mid, 200, chunk=64, scratch=chunk_scratch(200))
+    ctx.gdn_prefill(dq[200:], dv[200:], dd[200:], db[200:], mid, y2[200:], s2, 184, chunk=64,
+                    scratch=chunk_scratch(184))
+    ctx.sync()
+    assert_close_bf16(host_u16(y2), oy, "two blocks")
+    state_close(host_f32(s2), ostate, "two blocks")
+    # device sequential scan
+    y3 = bf((rows, 4096)); s3 = torch.zeros_like(s)
+    ctx.gdn_prefill(dq, dv, dd, db, dev_f32(state), y3, s3, rows, chunk=1)
+    ctx.sync()
+    assert_close_bf16(host_u16(y), host_u16(y3), "chunked vs device scan")
+    with pytest.raises(tb.TataraError) as e:
+        ctx.gdn_prefill(dq, dv, dd, db, dev_f32(state), y, s, rows, chunk=64, scratch=chunk_scratch(64))
+    assert e.value.status == tb.STATUS_NAMES.index("ScratchTooSmall")
+    with pytest.raises(tb.TataraError) as e:
+        ctx.gdn_prefill(dq, dv, dd, db, dev_f32(state), y, s, rows, chunk=32, scratch=chunk_scratch(rows))
+    assert e.value.status == tb.STATUS_NAMES.index("InvalidDispatchExtent")
+
+
+def test_chunked_prefill_config3_full_size(ctx):
+    """Benchmark config 3: 16384 rows, chunk 64, initial state zero; per-token outputs and the
+    final f32 state against the sequential oracle."""
+    rng = np.random.default_rng(70)
+    rows = 16384
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng, zero=True)
+    proj = syn.gdn_projection(rng, rows)
+    oqk, ov, _, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=16)
+    y = bf((rows, 4096)); s = torch.zeros((32, 128, 128), device="cuda")
+    ctx.gdn_prefill(dev_bf16(oqk), dev_bf16(ov), dev_f32(od), dev_f32(ob), dev_f32(state), y, s, rows, chunk=64,
+                    scratch=chunk_scratch(rows))
+    ctx.sync()
+    assert_close_bf16(host_u16(y), oy, "config 3 outputs")
+    state_close(host_f32(s), ostate, "config 3 final state")
