@@ -74,18 +74,24 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false once the CTA has been told to abort or the time limit passed.
+// Bounded wait: false once the CTA has been told to abort or the time limit passed.  The timer
+// and the abort flag are looked at once per burst of polls (try_wait itself suspends the thread
+// for a hardware-defined time), so a waiting thread costs few issue slots.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
     if (mbar_try(bar, parity)) return true;
-    const unsigned long long t0 = now_ns();
-    while (!mbar_try(bar, parity)) {
+    unsigned long long t0 = 0;
+    for (;;) {
+#pragma unroll 1
+        for (uint32_t i = 0; i < 32u; ++i)
+            if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (now_ns() - t0 > kWaitLimitNs) {
+        const unsigned long long t = now_ns();
+        if (t0 == 0) t0 = t;
+        if (t - t0 > kWaitLimitNs) {
             *abort_flag = 1u;
             return false;
         }
     }
-    return true;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1, int c2) {
@@ -132,6 +138,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
           "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
           "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -271,20 +282,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tmem_ld32(tmem + tlane + kColS + s * kBN + 32u, sv + 32);
             tmem_wait_ld();
             const uint32_t key0 = j * kBN;
-            float mx = -INFINITY;
             if (key0 + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
 #pragma unroll
-                for (uint32_t i = 0; i < 64; ++i) {
-                    sv[i] = key0 + i <= pos ? sv[i] * c : -INFINITY;
-                    mx = fmaxf(mx, sv[i]);
-                }
-            } else {
-#pragma unroll
-                for (uint32_t i = 0; i < 64; ++i) {
-                    sv[i] *= c;
-                    mx = fmaxf(mx, sv[i]);
-                }
+                for (uint32_t i = 0; i < 64; ++i) sv[i] = key0 + i <= pos ? sv[i] : -INFINITY;
             }
+            // row maximum of the raw scores (c > 0), four independent chains
+            float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]), m2 = fmaxf(sv[4], sv[5]), m3 = fmaxf(sv[6], sv[7]);
+#pragma unroll
+            for (uint32_t i = 8; i < 64; i += 8) {
+                m0 = fmaxf(m0, fmaxf(sv[i], sv[i + 1]));
+                m1 = fmaxf(m1, fmaxf(sv[i + 2], sv[i + 3]));
+                m2 = fmaxf(m2, fmaxf(sv[i + 4], sv[i + 5]));
+                m3 = fmaxf(m3, fmaxf(sv[i + 6], sv[i + 7]));
+            }
+            const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
             if (j == 0) {
                 m_used = mx; // key 0 is visible to every row, so this is finite
             } else {
@@ -294,7 +305,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const uint32_t jp = j - 1u;
                     if (!mbar_wait(bar(kBarPvDone + (jp & 1u)), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const float f = grow ? exp2f(m_used - mx) : 1.0f;
+                    const float f = grow ? ex2(m_used - mx) : 1.0f;
                     for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
                         float ov[32];
                         tmem_ld32(tmem + tlane + kColO + ch * 32u, ov);
@@ -308,13 +319,18 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     if (grow) m_used = mx;
                 }
             }
-            float sum = 0.0f;
+            // p = 2^(s*c - m): one FFMA + one MUFU per score; four independent sums
+            const float neg_m = -m_used;
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (uint32_t i = 0; i < 64; ++i) {
-                sv[i] = exp2f(sv[i] - m_used);
-                sum += sv[i];
+            for (uint32_t i = 0; i < 64; i += 4) {
+                sv[i] = ex2(fmaf(sv[i], c, neg_m));
+                sv[i + 1] = ex2(fmaf(sv[i + 1], c, neg_m));
+                sv[i + 2] = ex2(fmaf(sv[i + 2], c, neg_m));
+                sv[i + 3] = ex2(fmaf(sv[i + 3], c, neg_m));
+                s0 += sv[i]; s1 += sv[i + 1]; s2 += sv[i + 2]; s3 += sv[i + 3];
             }
-            l += sum;
+            l += (s0 + s1) + (s2 + s3);
             if (j >= 2) { // P buffer s was read by the P.V of tile j-2
                 const uint32_t jp = j - 2u;
                 if (!mbar_wait(bar(kBarPvDone + s), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }

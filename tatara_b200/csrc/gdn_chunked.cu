@@ -64,7 +64,7 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) {
 }
 
 // ---- kernel 1: per (chunk, v-head) ------------------------------------------------------
-constexpr uint32_t kPrepSmem = 2u * kChunk * 256u + kChunk * (kChunk + 1u) * 4u + 2u * kChunk * 4u;
+constexpr uint32_t kPrepSmem = 2u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u + 2u * kChunk * 4u;
 __global__ void __launch_bounds__(256)
 gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __restrict__ value,
                          const float* __restrict__ decay, const float* __restrict__ beta,
@@ -72,8 +72,8 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
     extern __shared__ __align__(1024) uint8_t prep_smem[];
     uint8_t* k_tile = prep_smem;
     uint8_t* q_tile = prep_smem + kChunk * 256u;
-    float (*a_mat)[kChunk + 1] = reinterpret_cast<float (*)[kChunk + 1]>(prep_smem + 2u * kChunk * 256u);
-    float* g_cum = reinterpret_cast<float*>(prep_smem + 2u * kChunk * 256u + kChunk * (kChunk + 1u) * 4u);
+    float (*a_mat)[kChunk + 4] = reinterpret_cast<float (*)[kChunk + 4]>(prep_smem + 2u * kChunk * 256u);
+    float* g_cum = reinterpret_cast<float*>(prep_smem + 2u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u);
     float* beta_s = g_cum + kChunk;
     const uint32_t chunk = blockIdx.x, head = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -165,14 +165,14 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
             }
             float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (uint32_t i = 0; i + 3 < r; i += 4) {
-                s0 = fmaf(a_mat[r][i], x[i], s0);
-                s1 = fmaf(a_mat[r][i + 1], x[i + 1], s1);
-                s2 = fmaf(a_mat[r][i + 2], x[i + 2], s2);
-                s3 = fmaf(a_mat[r][i + 3], x[i + 3], s3);
+            for (uint32_t i = 0; i < r; i += 4) {
+                // A is strictly lower triangular and zero elsewhere, so whole float4 groups are safe
+                const float4 a = *reinterpret_cast<const float4*>(&a_mat[r][i]);
+                s0 = fmaf(a.x, x[i], s0);
+                if (i + 1 < r) s1 = fmaf(a.y, x[i + 1], s1);
+                if (i + 2 < r) s2 = fmaf(a.z, x[i + 2], s2);
+                if (i + 3 < r) s3 = fmaf(a.w, x[i + 3], s3);
             }
-#pragma unroll
-            for (uint32_t i = r & ~3u; i < r; ++i) s0 = fmaf(a_mat[r][i], x[i], s0);
             x[r] = rhs - ((s0 + s1) + (s2 + s3));
         }
         if (is_u) {
