@@ -137,12 +137,11 @@ class Workloads:
         self._flush = None
 
     def traffic_hint(self):
-        """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
-        path = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(path):
-            with open(path) as f:
-                return json.load(f).get("attn_decode_partition_kernel_ctx262144")
-        return None
+        """DRAM bytes (read + write) per launch of attn_decode_partition_kernel at the headline
+        context, from the ncu capture summarised in
+        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.261248 + 6.488832) MB at
+        65 536 keys, scaled by keys (traffic is proportional to keys) to 262 144."""
+        return int((134.261248e6 + 6.488832e6) * 4)
 
     def decode_setup(self, n_keys):
         return DecodeCase(self.ctx, self.torch, n_keys, seed=self.rank * 100)

@@ -166,6 +166,10 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     uint32_t* item_start = reinterpret_cast<uint32_t*>(merge_ml + kDecWarps * kHeadsPerKv * 2);
     for (uint32_t i = threadIdx.x; i <= p.n_lanes; i += kDecThreads)
         item_start[i] = i < p.n_lanes ? p.lane[i].item_start : p.total_items;
+    // Launched with programmatic stream serialization: everything above overlapped the tail of
+    // the previous kernel in the stream; nothing below (which reads q, K, V and writes records)
+    // runs until that kernel has completed and its writes are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
 
     // Let a programmatic dependent (the combine) be staged; it still waits for this grid to finish.
@@ -355,6 +359,7 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
     // When launched as a programmatic dependent of the partition kernel: wait for its records.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const CombineLane& cl = p.lane[blockIdx.y];
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, phase = threadIdx.x >> 5;
@@ -488,23 +493,26 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
         configured[ctx->device & 63] = true;
     }
     const uint32_t grid = items < uint32_t(ctx->sm_count) ? items : uint32_t(ctx->sm_count);
-    attn_decode_partition_kernel<N><<<grid, kDecThreads, kDecSmemBytes, stream>>>(dp);
-    tatara_status st = check_launch(ctx, what);
-    if (st != TATARA_OK) return st;
-    // The combine is a programmatic dependent of the partition kernel: its CTAs are staged
-    // while the partitions drain and block in griddepcontrol.wait until every record is visible.
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(kQHeads * 4, n_lanes);
-    cfg.blockDim = dim3(kCombineThreads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
+    // Both kernels are launched with programmatic stream serialization: each may be staged while
+    // its predecessor in the stream drains and blocks in griddepcontrol.wait until that
+    // predecessor has finished (a predecessor that never signals simply finishes first).
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = kDecSmemBytes;
+    cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp) != cudaSuccess)
-        return check_launch(ctx, what);
+    (void)cudaLaunchKernelEx(&cfg, attn_decode_partition_kernel<N>, dp);
+    tatara_status st = check_launch(ctx, what);
+    if (st != TATARA_OK) return st;
+    cfg.gridDim = dim3(kQHeads * 4, n_lanes);
+    cfg.blockDim = dim3(kCombineThreads);
+    cfg.dynamicSmemBytes = 0;
+    (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp);
     return check_launch(ctx, what);
 }
 

@@ -3,16 +3,21 @@
 // prefill_attention.metal:97-254; shipped pair of GEMMs + softmax + gate, host
 // src/runtime/prefill_step.cpp:1467-1819).
 //
-// One CTA owns 128 query rows of one head (a 128 x 256 bf16 Q tile) and streams the visible
-// keys in tiles of 64:
-//     S = Q K^T      tcgen05.mma  M128 N64  K256   (A, B K-major from 128B-swizzled smem)
+// One CTA owns 128 query rows of one head and streams the visible keys in tiles of 128:
+//     S = Q K^T      tcgen05.mma  M128 N128 K256   (A = Q, B = K tile, both K-major swizzled smem)
 //     P = exp2(S*c - m)  in registers, one thread per query row (tcgen05.ld of its TMEM lane)
-//     O += P V       tcgen05.mma  M128 N256 K64    (A = P from smem, B = V, MN-major)
-// S is double-buffered in TMEM (2 x 64 columns) and O lives in 256 TMEM columns for the whole
-// tile; K and V tiles arrive through a two-stage TMA ring (tiled tensor maps, 128-byte swizzle).
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 softmax + epilogue.  The
-// running maximum is updated lazily (O and l are rescaled only when the maximum grows by more
-// than 2^8), which keeps the TMEM round trip of O off the steady-state path.
+//     O += P V       tcgen05.mma  M128 N256 K128   (A = P from TMEM, B = V tile, MN-major smem)
+// An M128 MMA costs about 64 cycles whatever its N up to 128 (measured: N = 64 tiles ran the
+// tensor pipe at half rate), so the score tile is 128 keys wide.  A 128-key K or V tile is
+// 64 KiB, too large to double-buffer next to the 64 KiB Q tile, so K and V stream through rings
+// of 16 KiB slots that are released and refilled INSIDE a tile: a K slot holds 64 of the 256 dims
+// (the operand of four consecutive k-steps), a V slot holds 32 of the 128 keys (two k-steps);
+// a tcgen05.commit after each slot's MMAs hands the slot back to the TMA producer.
+// TMEM map (512 columns): S/P buffer 0 at 0..127, buffer 1 at 128..255, O at 256..511; P (bf16
+// pairs per 32-bit column) overwrites the first 64 columns of the S buffer it was computed from
+// and is consumed from TMEM.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5
+// softmax + epilogue.  The running maximum is updated lazily (O and l are rescaled only when the
+// maximum grows by more than 2^8), which keeps the TMEM round trip of O off the steady-state path.
 // Every mbarrier wait is bounded; on a timeout the CTA latches TATARA_DEVICE_WAIT_TIMEOUT in the
 // context's status word, frees its TMEM and returns.
 #include <cuda.h>
@@ -21,25 +26,25 @@
 
 namespace tb {
 
-constexpr uint32_t kBM = 128, kBN = 64;
+constexpr uint32_t kBM = 128, kBN = 128, kKSlots = 6, kVSlots = 4, kSBufs = 2;
 constexpr uint32_t kAtomBytesQ = kBM * 128;          // one 64-dim swizzle atom of the Q tile
-constexpr uint32_t kAtomBytesKV = kBN * 128;         // one 64-dim atom of a K or V tile
 constexpr uint32_t kQBytes = 4 * kAtomBytesQ;        // 64 KiB
-constexpr uint32_t kKVBytes = 4 * kAtomBytesKV;      // 32 KiB
-constexpr uint32_t kPBytes = kBM * kBN * 2;          // 16 KiB
+constexpr uint32_t kSlotBytes = 16384;               // K slot: 128 keys x 64 dims; V slot: 32 keys x 256 d
+constexpr uint32_t kVAtomBytes = 32 * 128;           // one 64-d atom of a V slot (32 keys x 128 B)
 constexpr uint32_t kOffQ = 0;
-constexpr uint32_t kOffK = kOffQ + kQBytes;          // 2 stages
-constexpr uint32_t kOffV = kOffK + 2 * kKVBytes;     // 2 stages
-constexpr uint32_t kOffP = kOffV + 2 * kKVBytes;     // 2 buffers
-constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
+constexpr uint32_t kOffK = kOffQ + kQBytes;
+constexpr uint32_t kOffV = kOffK + kKSlots * kSlotBytes;
+constexpr uint32_t kOffBar = kOffV + kVSlots * kSlotBytes;
 constexpr uint32_t kPrefillSmem = kOffBar + 256;
 constexpr uint32_t kPrefillThreads = 192;
-constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 128;
+constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 256;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
 
 // barrier slots
-enum : uint32_t { kBarQ = 0, kBarKFull = 1, kBarKEmpty = 3, kBarVFull = 5, kBarVEmpty = 7,
-                  kBarSFull = 9, kBarPFull = 11, kBarPvDone = 13, kBarCount = 15 };
+enum : uint32_t { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kKSlots, kBarVFull = kBarKEmpty + kKSlots,
+                  kBarVEmpty = kBarVFull + kVSlots, kBarSFull = kBarVEmpty + kVSlots, kBarPFull = kBarSFull + kSBufs,
+                  kBarPvDone = kBarPFull + kSBufs, kBarCount = kBarPvDone + kSBufs };
+static_assert(8 * kBarCount + 16 <= 256, "barrier block");
 
 struct PrefillParams {
     const __nv_bfloat16* gate;
@@ -113,6 +118,15 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// A operand from tensor memory (lane = row, bf16 pairs per 32-bit column, K contiguous).
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
@@ -180,11 +194,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (threadIdx.x == 0) {
         mbar_init(bar(kBarQ), 1);
-        for (uint32_t s = 0; s < 2; ++s) {
+        for (uint32_t s = 0; s < kKSlots; ++s) {
             mbar_init(bar(kBarKFull + s), 1);
             mbar_init(bar(kBarKEmpty + s), 1);
+        }
+        for (uint32_t s = 0; s < kVSlots; ++s) {
             mbar_init(bar(kBarVFull + s), 1);
             mbar_init(bar(kBarVEmpty + s), 1);
+        }
+        for (uint32_t s = 0; s < kSBufs; ++s) {
             mbar_init(bar(kBarSFull + s), 1);
             mbar_init(bar(kBarPFull + s), 128);
             mbar_init(bar(kBarPvDone + s), 1);
@@ -209,18 +227,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_expect_tx(bar(kBarQ), kQBytes);
             for (uint32_t a = 0; a < 4; ++a)
                 tma_load_3d(base + kOffQ + a * kAtomBytesQ, &map_q, bar(kBarQ), int(a * 64), int(head), int(r0));
-            for (uint32_t j = 0; j < ntiles; ++j) {
-                const uint32_t s = j & 1u, use = j >> 1;
-                if (use > 0 && !mbar_wait(bar(kBarKEmpty + s), (use - 1u) & 1u, abort_flag)) break;
-                mbar_expect_tx(bar(kBarKFull + s), kKVBytes);
-                for (uint32_t a = 0; a < 4; ++a)
-                    tma_load_3d(base + kOffK + s * kKVBytes + a * kAtomBytesKV, &map_k, bar(kBarKFull + s),
-                                int(a * 64), int(j * kBN), int(kv));
-                if (use > 0 && !mbar_wait(bar(kBarVEmpty + s), (use - 1u) & 1u, abort_flag)) break;
-                mbar_expect_tx(bar(kBarVFull + s), kKVBytes);
-                for (uint32_t a = 0; a < 4; ++a)
-                    tma_load_3d(base + kOffV + s * kKVBytes + a * kAtomBytesKV, &map_v, bar(kBarVFull + s),
-                                int(a * 64), int(j * kBN), int(kv));
+            // consumption order of the MMA thread: S_0, S_1, P.V_0, S_2, P.V_1, ...
+            auto load_k = [&](uint32_t j) {                 // four 64-dim atoms of key tile j
+                for (uint32_t a = 0; a < 4; ++a) {
+                    const uint32_t n = j * 4u + a, slot = n % kKSlots, use = n / kKSlots;
+                    if (use > 0 && !mbar_wait(bar(kBarKEmpty + slot), (use - 1u) & 1u, abort_flag)) return false;
+                    mbar_expect_tx(bar(kBarKFull + slot), kSlotBytes);
+                    tma_load_3d(base + kOffK + slot * kSlotBytes, &map_k, bar(kBarKFull + slot), int(a * 64),
+                                int(j * kBN), int(kv));
+                }
+                return true;
+            };
+            auto load_v = [&](uint32_t j) {                 // four 32-key groups of key tile j
+                for (uint32_t g = 0; g < 4; ++g) {
+                    const uint32_t n = j * 4u + g, slot = n % kVSlots, use = n / kVSlots;
+                    if (use > 0 && !mbar_wait(bar(kBarVEmpty + slot), (use - 1u) & 1u, abort_flag)) return false;
+                    mbar_expect_tx(bar(kBarVFull + slot), kSlotBytes);
+                    for (uint32_t a = 0; a < 4; ++a)
+                        tma_load_3d(base + kOffV + slot * kSlotBytes + a * kVAtomBytes, &map_v, bar(kBarVFull + slot),
+                                    int(a * 64), int(j * kBN + g * 32u), int(kv));
+                }
+                return true;
+            };
+            bool ok = load_k(0);
+            for (uint32_t j = 0; ok && j < ntiles; ++j) {
+                if (j + 1u < ntiles) ok = load_k(j + 1u);
+                if (ok) ok = load_v(j);
             }
         }
     } else if (warp == 1) {
@@ -229,38 +261,49 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             constexpr uint32_t idesc_s = instr_desc(kBM, kBN, false);
             constexpr uint32_t idesc_pv = instr_desc(kBM, kHeadDim, true);
             bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
-            auto issue_pv = [&](uint32_t i) {
-                const uint32_t t = i & 1u, par = (i >> 1) & 1u;
-                if (!mbar_wait(bar(kBarVFull + t), par, abort_flag)) return false;
-                if (!mbar_wait(bar(kBarPFull + t), par, abort_flag)) return false;
-                tc_fence_after();
+            auto issue_s = [&](uint32_t j) {
+                const uint32_t b = j % kSBufs;
+                // Buffer b held P of tile j-2: its P.V was issued before this point and the
+                // tcgen05.mma instructions of one thread execute in issue order.
+                for (uint32_t a = 0; a < 4; ++a) {
+                    const uint32_t n = j * 4u + a, slot = n % kKSlots;
+                    if (!mbar_wait(bar(kBarKFull + slot), (n / kKSlots) & 1u, abort_flag)) return false;
+                    tc_fence_after();
 #pragma unroll
-                for (uint32_t kk = 0; kk < kBN / 16; ++kk) {
-                    // A = P tile [128 x 64] K-major: +32 B per 16-key step inside the swizzle atom
-                    const uint64_t ad = smem_desc(base + kOffP + t * kPBytes + kk * 32u, 16, 1024);
-                    // B = V tile [64 keys x 256 d] MN-major: atoms of 64 d are kAtomBytesKV apart
-                    // (leading offset), groups of 8 keys 1024 B apart (stride offset); 16 keys = 2048 B
-                    const uint64_t bd = smem_desc(base + kOffV + t * kKVBytes + kk * 2048u, kAtomBytesKV, 1024);
-                    tc_mma(tmem + kColO, ad, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                    for (uint32_t q4 = 0; q4 < 4; ++q4) {
+                        const uint64_t ad = smem_desc(base + kOffQ + a * kAtomBytesQ + q4 * 32u, 16, 1024);
+                        const uint64_t bd = smem_desc(base + kOffK + slot * kSlotBytes + q4 * 32u, 16, 1024);
+                        tc_mma(tmem + kColS + b * kBN, ad, bd, idesc_s, (a | q4) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarKEmpty + slot));
                 }
-                tc_commit(bar(kBarVEmpty + t));
-                tc_commit(bar(kBarPvDone + t));
+                tc_commit(bar(kBarSFull + b));
+                return true;
+            };
+            auto issue_pv = [&](uint32_t i) {
+                const uint32_t b = i % kSBufs;
+                if (!mbar_wait(bar(kBarPFull + b), (i / kSBufs) & 1u, abort_flag)) return false;
+                for (uint32_t g = 0; g < 4; ++g) {
+                    const uint32_t n = i * 4u + g, slot = n % kVSlots;
+                    if (!mbar_wait(bar(kBarVFull + slot), (n / kVSlots) & 1u, abort_flag)) return false;
+                    tc_fence_after();
+#pragma unroll
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        // A = P [128 x 128] in TMEM: 8 columns per 16-key step.
+                        // B = V slot [32 keys x 256 d] MN-major: atoms of 64 d are kVAtomBytes apart
+                        // (leading offset), groups of 8 keys 1024 B apart (stride offset); 16 keys = 2048 B
+                        const uint64_t bd = smem_desc(base + kOffV + slot * kSlotBytes + h * 2048u, kVAtomBytes, 1024);
+                        tc_mma_ts(tmem + kColO, tmem + kColS + b * kBN + (g * 2u + h) * 8u, bd, idesc_pv,
+                                  (i | g | h) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarVEmpty + slot));
+                }
+                tc_commit(bar(kBarPvDone + b));
                 return true;
             };
             for (uint32_t j = 0; ok && j < ntiles; ++j) {
-                const uint32_t s = j & 1u, par = (j >> 1) & 1u;
-                if (!mbar_wait(bar(kBarKFull + s), par, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (uint32_t ks = 0; ks < kHeadDim / 16; ++ks) {
-                    const uint32_t atom = ks >> 2, inner = (ks & 3u) * 32u;
-                    const uint64_t ad = smem_desc(base + kOffQ + atom * kAtomBytesQ + inner, 16, 1024);
-                    const uint64_t bd = smem_desc(base + kOffK + s * kKVBytes + atom * kAtomBytesKV + inner, 16, 1024);
-                    tc_mma(tmem + kColS + s * kBN, ad, bd, idesc_s, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(bar(kBarKEmpty + s));
-                tc_commit(bar(kBarSFull + s));
-                if (j > 0 && !issue_pv(j - 1u)) { ok = false; break; }
+                ok = issue_s(j);
+                if (ok && j > 0) ok = issue_pv(j - 1u);
             }
             if (ok) issue_pv(ntiles - 1u);
         }
@@ -274,22 +317,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         for (uint32_t j = 0; ok && j < ntiles; ++j) {
-            const uint32_t s = j & 1u, par = (j >> 1) & 1u;
+            const uint32_t s = j % kSBufs, par = (j / kSBufs) & 1u;
             if (!mbar_wait(bar(kBarSFull + s), par, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float sv[64];
-            tmem_ld32(tmem + tlane + kColS + s * kBN, sv);
-            tmem_ld32(tmem + tlane + kColS + s * kBN + 32u, sv + 32);
+            float sv[128];
+#pragma unroll
+            for (uint32_t ch = 0; ch < 4; ++ch) tmem_ld32(tmem + tlane + kColS + s * kBN + ch * 32u, sv + ch * 32);
             tmem_wait_ld();
             const uint32_t key0 = j * kBN;
             if (key0 + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
 #pragma unroll
-                for (uint32_t i = 0; i < 64; ++i) sv[i] = key0 + i <= pos ? sv[i] : -INFINITY;
+                for (uint32_t i = 0; i < 128; ++i) sv[i] = key0 + i <= pos ? sv[i] : -INFINITY;
             }
             // row maximum of the raw scores (c > 0), four independent chains
             float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]), m2 = fmaxf(sv[4], sv[5]), m3 = fmaxf(sv[6], sv[7]);
 #pragma unroll
-            for (uint32_t i = 8; i < 64; i += 8) {
+            for (uint32_t i = 8; i < 128; i += 8) {
                 m0 = fmaxf(m0, fmaxf(sv[i], sv[i + 1]));
                 m1 = fmaxf(m1, fmaxf(sv[i + 2], sv[i + 3]));
                 m2 = fmaxf(m2, fmaxf(sv[i + 4], sv[i + 5]));
@@ -303,7 +346,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (__any_sync(0xffffffffu, grow)) {
                     // O holds P.V of tiles < j: wait for tile j-1, then rescale this row in TMEM
                     const uint32_t jp = j - 1u;
-                    if (!mbar_wait(bar(kBarPvDone + (jp & 1u)), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(kBarPvDone + jp % kSBufs), (jp / kSBufs) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const float f = grow ? ex2(m_used - mx) : 1.0f;
                     for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
@@ -323,7 +366,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float neg_m = -m_used;
             float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (uint32_t i = 0; i < 64; i += 4) {
+            for (uint32_t i = 0; i < 128; i += 4) {
                 sv[i] = ex2(fmaf(sv[i], c, neg_m));
                 sv[i + 1] = ex2(fmaf(sv[i + 1], c, neg_m));
                 sv[i + 2] = ex2(fmaf(sv[i + 2], c, neg_m));
@@ -331,32 +374,24 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 s0 += sv[i]; s1 += sv[i + 1]; s2 += sv[i + 2]; s3 += sv[i + 3];
             }
             l += (s0 + s1) + (s2 + s3);
-            if (j >= 2) { // P buffer s was read by the P.V of tile j-2
-                const uint32_t jp = j - 2u;
-                if (!mbar_wait(bar(kBarPvDone + s), (jp >> 1) & 1u, abort_flag)) { ok = false; break; }
-            }
-            // P row -> smem, K-major with the 128-byte swizzle: 16-byte chunk ^ (row & 7)
-            uint8_t* prow = smem + kOffP + s * kPBytes + row * 128u;
+            // P row (bf16 pairs) overwrites the first 64 columns of the S buffer it came from
 #pragma unroll
-            for (uint32_t ch = 0; ch < 8; ++ch) {
-                uint4 packed;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(sv[ch * 8 + 0], sv[ch * 8 + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(sv[ch * 8 + 2], sv[ch * 8 + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(sv[ch * 8 + 4], sv[ch * 8 + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(sv[ch * 8 + 6], sv[ch * 8 + 7]);
-                packed.x = *reinterpret_cast<uint32_t*>(&h0);
-                packed.y = *reinterpret_cast<uint32_t*>(&h1);
-                packed.z = *reinterpret_cast<uint32_t*>(&h2);
-                packed.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7u)) << 4)) = packed;
+            for (uint32_t ch = 0; ch < 2; ++ch) {
+                uint32_t packed[32];
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(sv[ch * 64 + 2 * i], sv[ch * 64 + 2 * i + 1]);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                tmem_st32(tmem + tlane + kColS + s * kBN + ch * 32u, reinterpret_cast<const float*>(packed));
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar(kBarPFull + s));
         }
         if (ok) {
             const uint32_t jl = ntiles - 1u;
-            ok = mbar_wait(bar(kBarPvDone + (jl & 1u)), (jl >> 1) & 1u, abort_flag);
+            ok = mbar_wait(bar(kBarPvDone + jl % kSBufs), (jl / kSBufs) & 1u, abort_flag);
         }
         if (ok) {
             tc_fence_after();
@@ -455,7 +490,7 @@ extern "C" tatara_status tatara_attn_prefill(tatara_ctx* ctx, void* stream, cons
     if (!make_map(&map_q, query, kQHeads, rows, kHeadDim * 2ull, uint64_t(kQHeads) * kHeadDim * 2ull, 1, kBM) ||
         // K, V [2][capacity][256], extent clipped to the visible keys so the tail reads as zero
         !make_map(&map_k, keys, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, kBN, 1) ||
-        !make_map(&map_v, values, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, kBN, 1))
+        !make_map(&map_v, values, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, 32, 1))
         return fail(ctx, TATARA_CUDA_ERROR, "attn_prefill: tensor map encoding failed");
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {

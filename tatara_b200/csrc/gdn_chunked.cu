@@ -154,15 +154,18 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
         const bool is_u = threadIdx.x >= 128u;
         const uint32_t jcol = threadIdx.x & 127u;
         float x[kChunk];
+        // right-hand sides first (64 independent loads in flight), then the in-place solve
 #pragma unroll
         for (uint32_t r = 0; r < kChunk; ++r) {
-            float rhs;
             if (is_u) {
-                rhs = r < live_rows ? beta_s[r] * bf2f(value[uint64_t(row0 + r) * kGdnV + head * kGdnDim + jcol]) : 0.0f;
+                x[r] = r < live_rows ? bf2f(value[uint64_t(row0 + r) * kGdnV + head * kGdnDim + jcol]) : 0.0f;
             } else {
-                const __nv_bfloat16 kv = *reinterpret_cast<const __nv_bfloat16*>(k_tile + swz<128>(r, jcol >> 3) + (jcol & 7u) * 2u);
-                rhs = beta_s[r] * __expf(g_cum[r]) * bf2f(kv);
+                x[r] = bf2f(*reinterpret_cast<const __nv_bfloat16*>(k_tile + swz<128>(r, jcol >> 3) + (jcol & 7u) * 2u));
             }
+        }
+#pragma unroll
+        for (uint32_t r = 0; r < kChunk; ++r) {
+            const float rhs = is_u ? beta_s[r] * x[r] : beta_s[r] * __expf(g_cum[r]) * x[r];
             float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
             for (uint32_t i = 0; i < r; i += 4) {
