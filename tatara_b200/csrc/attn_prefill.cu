@@ -15,8 +15,9 @@
 // a tcgen05.commit after each slot's MMAs hands the slot back to the TMA producer.
 // TMEM map (512 columns): S/P buffer 0 at 0..127, buffer 1 at 128..255, O at 256..511; P (bf16
 // pairs per 32-bit column) overwrites the first 64 columns of the S buffer it was computed from
-// and is consumed from TMEM.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5
-// softmax + epilogue.  The running maximum is updated lazily (O and l are rescaled only when the
+// and is consumed from TMEM.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9
+// softmax + epilogue (two warps per 32-row TMEM lane quarter, each owning one 64-key half of the
+// score tile; the halves exchange their row maxima through shared memory).  The running maximum is updated lazily (O and l are rescaled only when the
 // maximum grows by more than 2^8), which keeps the TMEM round trip of O off the steady-state path.
 // Every mbarrier wait is bounded; on a timeout the CTA latches TATARA_DEVICE_WAIT_TIMEOUT in the
 // context's status word, frees its TMEM and returns.
@@ -35,8 +36,10 @@ constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + kKSlots * kSlotBytes;
 constexpr uint32_t kOffBar = kOffV + kVSlots * kSlotBytes;
-constexpr uint32_t kPrefillSmem = kOffBar + 256;
-constexpr uint32_t kPrefillThreads = 192;
+constexpr uint32_t kPrefillSmem = kOffBar + 256 + 2 * 256 * 4;  // + row-max exchange (2 phases)
+static_assert(kPrefillSmem <= 232448, "shared memory budget");
+constexpr uint32_t kPrefillThreads = 320;   // TMA warp, MMA warp, 8 softmax warps
+constexpr uint32_t kSoftmaxThreads = 256;
 constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 256;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull; // 2 s
 
@@ -45,6 +48,8 @@ enum : uint32_t { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kKSlots, kB
                   kBarVEmpty = kBarVFull + kVSlots, kBarSFull = kBarVEmpty + kVSlots, kBarPFull = kBarSFull + kSBufs,
                   kBarPvDone = kBarPFull + kSBufs, kBarCount = kBarPvDone + kSBufs };
 static_assert(8 * kBarCount + 16 <= 256, "barrier block");
+constexpr uint32_t kOffPair = kOffBar + 256;       // [2 halves][128 rows] f32 exchange between the two warps of a row
+
 
 struct PrefillParams {
     const __nv_bfloat16* gate;
@@ -204,7 +209,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         for (uint32_t s = 0; s < kSBufs; ++s) {
             mbar_init(bar(kBarSFull + s), 1);
-            mbar_init(bar(kBarPFull + s), 128);
+            mbar_init(bar(kBarPFull + s), kSoftmaxThreads);
             mbar_init(bar(kBarPvDone + s), 1);
         }
         *abort_flag = 0u;
@@ -308,54 +313,67 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (ok) issue_pv(ntiles - 1u);
         }
     } else {
-        // ---------------- softmax + epilogue: one thread per query row ----------------
-        const uint32_t quarter = warp & 3u;
+        // ---------------- softmax + epilogue: two threads per query row ----------------
+        const uint32_t quarter = warp & 3u;            // TMEM lanes 32*quarter .. +31
+        const uint32_t half = (warp - 2u) >> 2;        // which 64 keys of the tile / 128 dims of O
         const uint32_t row = quarter * 32u + lane;
         const uint32_t tlane = (quarter * 32u) << 16;
         const uint32_t pos = p.context_base + r0 + row; // keys 0..pos are visible to this row
         const float c = kAttnScale * 1.4426950408889634f;
+        float* pair_x = reinterpret_cast<float*>(smem + kOffPair);
+        const uint32_t pair_bar = 1u + quarter;        // named barrier of the two warps of this quarter
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (uint32_t j = 0; ok && j < ntiles; ++j) {
+        for (uint32_t j = 0; j < ntiles; ++j) {
             const uint32_t s = j % kSBufs, par = (j / kSBufs) & 1u;
-            if (!mbar_wait(bar(kBarSFull + s), par, abort_flag)) { ok = false; break; }
+            // After a failed wait a thread keeps walking the tiles but only meets its partner at
+            // the pair barrier, so the partner can never be left waiting there.
+            if (ok && !mbar_wait(bar(kBarSFull + s), par, abort_flag)) ok = false;
+            if (!ok) {
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                continue;
+            }
             tc_fence_after();
-            float sv[128];
-#pragma unroll
-            for (uint32_t ch = 0; ch < 4; ++ch) tmem_ld32(tmem + tlane + kColS + s * kBN + ch * 32u, sv + ch * 32);
+            float sv[64];
+            tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u, sv);
+            tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u + 32u, sv + 32);
             tmem_wait_ld();
-            const uint32_t key0 = j * kBN;
-            if (key0 + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
+            const uint32_t key0 = j * kBN + half * 64u;
+            if (j * kBN + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
 #pragma unroll
-                for (uint32_t i = 0; i < 128; ++i) sv[i] = key0 + i <= pos ? sv[i] : -INFINITY;
+                for (uint32_t i = 0; i < 64; ++i) sv[i] = key0 + i <= pos ? sv[i] : -INFINITY;
             }
             // row maximum of the raw scores (c > 0), four independent chains
             float m0 = fmaxf(sv[0], sv[1]), m1 = fmaxf(sv[2], sv[3]), m2 = fmaxf(sv[4], sv[5]), m3 = fmaxf(sv[6], sv[7]);
 #pragma unroll
-            for (uint32_t i = 8; i < 128; i += 8) {
+            for (uint32_t i = 8; i < 64; i += 8) {
                 m0 = fmaxf(m0, fmaxf(sv[i], sv[i + 1]));
                 m1 = fmaxf(m1, fmaxf(sv[i + 2], sv[i + 3]));
                 m2 = fmaxf(m2, fmaxf(sv[i + 4], sv[i + 5]));
                 m3 = fmaxf(m3, fmaxf(sv[i + 6], sv[i + 7]));
             }
-            const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
+            float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c;
+            // both halves of the row must agree on the maximum: exchange through shared memory
+            pair_x[(j & 1u) * 256u + half * 128u + row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, pair_x[(j & 1u) * 256u + (half ^ 1u) * 128u + row]);
             if (j == 0) {
                 m_used = mx; // key 0 is visible to every row, so this is finite
             } else {
                 const bool grow = mx > m_used + 8.0f;
                 if (__any_sync(0xffffffffu, grow)) {
-                    // O holds P.V of tiles < j: wait for tile j-1, then rescale this row in TMEM
+                    // O holds P.V of tiles < j: wait for tile j-1, then rescale this row's half of O
                     const uint32_t jp = j - 1u;
-                    if (!mbar_wait(bar(kBarPvDone + jp % kSBufs), (jp / kSBufs) & 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(kBarPvDone + jp % kSBufs), (jp / kSBufs) & 1u, abort_flag)) { ok = false; continue; }
                     tc_fence_after();
                     const float f = grow ? ex2(m_used - mx) : 1.0f;
-                    for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
+                    for (uint32_t ch = 0; ch < 4; ++ch) {
                         float ov[32];
-                        tmem_ld32(tmem + tlane + kColO + ch * 32u, ov);
+                        tmem_ld32(tmem + tlane + kColO + half * 128u + ch * 32u, ov);
                         tmem_wait_ld();
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i) ov[i] *= f;
-                        tmem_st32(tmem + tlane + kColO + ch * 32u, ov);
+                        tmem_st32(tmem + tlane + kColO + half * 128u + ch * 32u, ov);
                     }
                     tmem_wait_st();
                     l *= f;
@@ -366,7 +384,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float neg_m = -m_used;
             float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (uint32_t i = 0; i < 128; i += 4) {
+            for (uint32_t i = 0; i < 64; i += 4) {
                 sv[i] = ex2(fmaf(sv[i], c, neg_m));
                 sv[i + 1] = ex2(fmaf(sv[i + 1], c, neg_m));
                 sv[i + 2] = ex2(fmaf(sv[i + 2], c, neg_m));
@@ -374,18 +392,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 s0 += sv[i]; s1 += sv[i + 1]; s2 += sv[i + 2]; s3 += sv[i + 3];
             }
             l += (s0 + s1) + (s2 + s3);
-            // P row (bf16 pairs) overwrites the first 64 columns of the S buffer it came from
+            // P (bf16 pairs) overwrites the first 64 columns of the S buffer: this half's 64 keys
+            // are columns 32*half .. 32*half+31.  The partner may still be reading its S half
+            // (columns 64.. for half 1) -- the pair barrier above ordered both loads before this store.
+            uint32_t packed[32];
 #pragma unroll
-            for (uint32_t ch = 0; ch < 2; ++ch) {
-                uint32_t packed[32];
-#pragma unroll
-                for (uint32_t i = 0; i < 32; ++i) {
-                    const __nv_bfloat162 h = __floats2bfloat162_rn(sv[ch * 64 + 2 * i], sv[ch * 64 + 2 * i + 1]);
-                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-                tmem_st32(tmem + tlane + kColS + s * kBN + ch * 32u, reinterpret_cast<const float*>(packed));
+            for (uint32_t i = 0; i < 32; ++i) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(sv[2 * i], sv[2 * i + 1]);
+                packed[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
+            tmem_st32(tmem + tlane + kColS + s * kBN + half * 32u, reinterpret_cast<const float*>(packed));
             tmem_wait_st();
+            if (j + 1u == ntiles) {   // the partner reads this half's row sum after the last P.V completes
+                reinterpret_cast<float*>(smem + kOffQ)[half * 128u + row] = l; // Q is dead: every S MMA has completed
+                __threadfence_block();
+            }
             tc_fence_before();
             mbar_arrive(bar(kBarPFull + s));
         }
@@ -395,12 +416,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         if (ok) {
             tc_fence_after();
+            l += reinterpret_cast<const float*>(smem + kOffQ)[(half ^ 1u) * 128u + row]; // + the partner's half
             const float inv_l = 1.0f / l;
             const bool live = row < rows_here;
-            const uint64_t at = (uint64_t(r0 + row) * kQHeads + head) * kHeadDim;
-            for (uint32_t ch = 0; ch < kHeadDim / 32; ++ch) {
+            const uint64_t at = (uint64_t(r0 + row) * kQHeads + head) * kHeadDim + half * 128u;
+            for (uint32_t ch = 0; ch < 4; ++ch) {
                 float ov[32];
-                tmem_ld32(tmem + tlane + kColO + ch * 32u, ov);
+                tmem_ld32(tmem + tlane + kColO + half * 128u + ch * 32u, ov);
                 tmem_wait_ld();
                 if (live) {
 #pragma unroll

@@ -64,7 +64,7 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) {
 }
 
 // ---- kernel 1: per (chunk, v-head) ------------------------------------------------------
-constexpr uint32_t kPrepSmem = 2u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u + 2u * kChunk * 4u;
+constexpr uint32_t kPrepSmem = 3u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u + 2u * kChunk * 4u;
 __global__ void __launch_bounds__(256)
 gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __restrict__ value,
                          const float* __restrict__ decay, const float* __restrict__ beta,
@@ -72,8 +72,9 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
     extern __shared__ __align__(1024) uint8_t prep_smem[];
     uint8_t* k_tile = prep_smem;
     uint8_t* q_tile = prep_smem + kChunk * 256u;
-    float (*a_mat)[kChunk + 4] = reinterpret_cast<float (*)[kChunk + 4]>(prep_smem + 2u * kChunk * 256u);
-    float* g_cum = reinterpret_cast<float*>(prep_smem + 2u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u);
+    uint8_t* v_tile = prep_smem + 2u * kChunk * 256u;
+    float (*a_mat)[kChunk + 4] = reinterpret_cast<float (*)[kChunk + 4]>(prep_smem + 3u * kChunk * 256u);
+    float* g_cum = reinterpret_cast<float*>(prep_smem + 3u * kChunk * 256u + kChunk * (kChunk + 4u) * 4u);
     float* beta_s = g_cum + kChunk;
     const uint32_t chunk = blockIdx.x, head = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -88,6 +89,13 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
         const bool live = r < live_rows;
         const __nv_bfloat16* src = qk + uint64_t(row0 + (live ? r : 0u)) * kGdnQk + (which ? qcol : kGdnKOff + qcol) + c * 8u;
         cpa16z(sm_u32(which ? q_tile : k_tile) + swz<128>(r, c), src, live);
+    }
+    // this head's V rows (plain row-major tile; read back one column per thread)
+    for (uint32_t idx = threadIdx.x; idx < kChunk * 16u; idx += 256u) {
+        const uint32_t r = idx >> 4, c = idx & 15u;
+        const bool live = r < live_rows;
+        cpa16z(sm_u32(v_tile) + r * 256u + c * 16u,
+               value + uint64_t(row0 + (live ? r : 0u)) * kGdnV + head * kGdnDim + c * 8u, live);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     if (warp == 0) {
@@ -158,7 +166,7 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
 #pragma unroll
         for (uint32_t r = 0; r < kChunk; ++r) {
             if (is_u) {
-                x[r] = r < live_rows ? bf2f(value[uint64_t(row0 + r) * kGdnV + head * kGdnDim + jcol]) : 0.0f;
+                x[r] = bf2f(*reinterpret_cast<const __nv_bfloat16*>(v_tile + r * 256u + jcol * 2u));
             } else {
                 x[r] = bf2f(*reinterpret_cast<const __nv_bfloat16*>(k_tile + swz<128>(r, jcol >> 3) + (jcol & 7u) * 2u));
             }
