@@ -165,6 +165,33 @@ tatara_status tatara_attn_combine(tatara_ctx* ctx, void* stream, const void* rec
                                   uint32_t nparts, uint64_t head_stride, uint64_t part_stride,
                                   const void* gate, void* out);
 
+/* ---- split-KV of one lane across the GPUs of a box, over peer memory (no counterpart in the
+ * reference, which is single-device).  One process per GPU.  Every rank owns a gather buffer
+ * [2 parities][world][16][258] f32 and a flag array [2 parities][world] u32 inside one peer
+ * buffer that the other ranks map through CUDA IPC. */
+/* Allocates (cudaMalloc, zero-filled) a buffer and exports its 64-byte IPC handle; the other
+ * ranks open it.  Set-up time only. */
+tatara_status tatara_peer_buffer_create(tatara_ctx* ctx, uint64_t bytes, void** ptr, void* handle64);
+tatara_status tatara_peer_buffer_open(tatara_ctx* ctx, const void* handle64, void** ptr);
+tatara_status tatara_peer_buffer_close(tatara_ctx* ctx, void* ptr, int owned);
+/* tatara_attn_decode_partial whose merged record ([16][258]) is stored by the kernel itself into
+ * slot `rank` of EVERY rank's gather buffer (peer stores over NVLink), after which word `rank` of
+ * every rank's flag array is set to `epoch` (release, system scope).  peer_gather / peer_flags:
+ * `world` device pointers (this rank's own buffer at index rank), already offset to the parity
+ * in use.  epoch > 0 and different from the previous call's on the same parity. */
+tatara_status tatara_attn_decode_partial_push(tatara_ctx* ctx, void* stream, const void* q,
+                                              const void* keys, const void* values,
+                                              uint32_t key_begin, uint32_t key_end, uint32_t capacity,
+                                              void* const* peer_gather, void* const* peer_flags,
+                                              uint32_t rank, uint32_t world, uint32_t epoch,
+                                              void* scratch, uint64_t scratch_bytes);
+/* tatara_attn_combine over this rank's gather buffer ([world][16][258]) that first waits until
+ * all `world` flags equal `epoch`.  The wait is bounded by wait_limit_us (<= 2 000 000); when it
+ * runs out the kernel writes nothing and tatara_ctx_sync returns TATARA_DEVICE_WAIT_TIMEOUT. */
+tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream, const void* gather,
+                                       const void* flags, uint32_t world, uint32_t epoch,
+                                       uint32_t wait_limit_us, const void* gate, void* out);
+
 /* Causal block prefill: slots 0 query, 1 K, 2 V, 3 gate, 4 out, 5 visible, 6 capacity,
  * 7 tile_rows, 8 tile_context (src/runtime/prefill_step.cpp:1661-1683).  Row r sits at
  * position context_base + r and attends keys 0..context_base + r of the lane cache (which

@@ -187,6 +187,37 @@ class Context:
         self._check(lib().tatara_attn_combine(self._h, self._stream(stream), _ptr(records), _u32(nparts),
                                               _u64(head_stride), _u64(part_stride), _ptr(gate), _ptr(out)))
 
+    # ---- split-KV over peer memory
+    def peer_buffer_create(self, nbytes):
+        """Returns (device pointer, 64-byte IPC handle) of a zero-filled peer buffer."""
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        self._check(lib().tatara_peer_buffer_create(self._h, _u64(nbytes), ctypes.byref(ptr), handle))
+        return ptr.value, handle.raw
+
+    def peer_buffer_open(self, handle):
+        ptr = ctypes.c_void_p()
+        self._check(lib().tatara_peer_buffer_open(self._h, ctypes.c_char_p(handle), ctypes.byref(ptr)))
+        return ptr.value
+
+    def peer_buffer_close(self, ptr, owned):
+        self._check(lib().tatara_peer_buffer_close(self._h, ctypes.c_void_p(ptr), ctypes.c_int(1 if owned else 0)))
+
+    def attn_decode_partial_push(self, q, keys, values, key_begin, key_end, capacity, peer_gather, peer_flags,
+                                 rank, epoch, scratch, stream=None):
+        world = len(peer_gather)
+        pg = (ctypes.c_void_p * world)(*peer_gather)
+        pf = (ctypes.c_void_p * world)(*peer_flags)
+        self._check(lib().tatara_attn_decode_partial_push(
+            self._h, self._stream(stream), _ptr(q), _ptr(keys), _ptr(values), _u32(key_begin), _u32(key_end),
+            _u32(capacity), pg, pf, _u32(rank), _u32(world), _u32(epoch), _ptr(scratch),
+            _u64(scratch.numel() * scratch.element_size())))
+
+    def attn_combine_wait(self, gather_ptr, flags_ptr, world, epoch, gate, out, wait_limit_us=1000000, stream=None):
+        self._check(lib().tatara_attn_combine_wait(self._h, self._stream(stream), ctypes.c_void_p(gather_ptr),
+                                                   ctypes.c_void_p(flags_ptr), _u32(world), _u32(epoch),
+                                                   _u32(wait_limit_us), _ptr(gate), _ptr(out)))
+
     def attn_prefill(self, query, gate, keys, values, context_base, rows, capacity, out, stream=None):
         self._check(lib().tatara_attn_prefill(self._h, self._stream(stream), _ptr(query), _ptr(gate),
                                               _ptr(keys), _ptr(values), _u32(context_base), _u32(rows),

@@ -114,19 +114,10 @@ uint32_t tatara_attn_partitions(uint32_t n_keys) {
 }
 
 uint64_t tatara_attn_decode_scratch_bytes(uint32_t max_keys, uint32_t lanes) {
-    // The partition count is not monotonic in n (the partition size grows in steps), so take
-    // the bound that holds for every n <= max_keys: partitions never hold fewer than 64 keys
-    // below 4736 keys and never fewer than 112 above, and the count peaks at a wave boundary.
-    uint32_t worst = 0;
-    const uint32_t probe[] = {max_keys, 74u * 64u, 98303u};
-    for (uint32_t n : probe) {
-        if (n == 0 || n > max_keys) continue;
-        const uint32_t c = tb::partition_count(n);
-        if (c > worst) worst = c;
-    }
-    // conservative closed bound: n/112 + 74 covers every wave rounding
-    const uint32_t bound = max_keys / 112u + 75u;
-    if (bound > worst) worst = bound;
+    // The partition count is not monotonic in n (the partition size grows in steps); n/112 + 75
+    // bounds it for every n <= max_keys (partitions hold at least 128 keys up to 9472 keys, and
+    // at least n/148 rounded up to 16 beyond).
+    const uint32_t worst = max_keys / 112u + 75u;
     return static_cast<uint64_t>(lanes) * worst * tb::kQHeads * tb::kRecordFloats * sizeof(float);
 }
 

@@ -17,6 +17,8 @@
 // lanes share the launch or on which CTA ran which item.
 #include "common.cuh"
 
+#include <cstring>
+
 namespace tb {
 
 constexpr uint32_t kDecWarps = 4;
@@ -338,14 +340,30 @@ struct CombineLane {
     uint32_t nparts;
     uint32_t row;
 };
+constexpr uint32_t kMaxPeers = 8;
+// Peer exchange of the split-KV merge (one process per GPU, buffers mapped through CUDA IPC).
+struct PeerExchange {
+    float* peer_out[kMaxPeers];      // push: slot [rank] of every rank's gather buffer ([16][258] f32)
+    uint32_t* peer_flag[kMaxPeers];  // push: word [rank] of every rank's flag array
+    const uint32_t* wait_flags;      // wait: this rank's flag array, or null
+    uint32_t* done_counter;          // push: local counter of finished CTAs (self-resetting)
+    uint32_t* status;                // device status word of the context
+    uint32_t world, epoch, wait_limit_us;
+};
 template <uint32_t N>
 struct CombineParams {
     const __nv_bfloat16* gate;
     __nv_bfloat16* out;  // [row][16][256] gated output, or null
     float* record_out;   // [lane][16][258] merged un-normalised record, or null
     uint64_t query_stride;
+    PeerExchange px;     // all null / zero outside the multi-GPU split-KV calls
     CombineLane lane[N];
 };
+__device__ __forceinline__ unsigned long long combine_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 // One CTA per (head, 64-dim quarter, lane): 32 warps, warp w merges records w, w+32, ... (four
 // in flight per thread), lane owns a float2 of the quarter; then the 32 warp partials are summed
@@ -360,6 +378,33 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     // When launched as a programmatic dependent of the partition kernel: wait for its records.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (p.px.wait_flags != nullptr) {
+        // Split-KV merge: the records of the other ranks are pushed into this GPU's memory by
+        // kernels running on THEIR GPUs; wait, with a time limit, until every rank's flag carries
+        // this step's epoch.  On expiry the CTA latches DeviceWaitTimeout and writes nothing.
+        __shared__ uint32_t arrived;
+        if (threadIdx.x == 0) {
+            const unsigned long long t0 = combine_now_ns();
+            uint32_t ok = 1u;
+            for (uint32_t r = 0; r < p.px.world && ok; ++r) {
+                for (;;) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.px.wait_flags + r) : "memory");
+                    if (v == p.px.epoch) break;
+                    if (combine_now_ns() - t0 > 1000ull * p.px.wait_limit_us) {
+                        ok = 0u;
+                        atomicCAS(p.px.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+                        p.px.status[kStatusDetail] = r;
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            arrived = ok;
+        }
+        __syncthreads();
+        if (arrived == 0u) return;
+    }
     const CombineLane& cl = p.lane[blockIdx.y];
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, phase = threadIdx.x >> 5;
@@ -412,7 +457,17 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     if (threadIdx.x < kCombineDims) {
         const uint32_t dd = quarter * kCombineDims + threadIdx.x;
         const float acc = red_acc[0][threadIdx.x], total = red_acc[0][kCombineDims];
-        if (p.record_out != nullptr) {
+        if (p.px.world != 0u && p.px.wait_flags == nullptr) {
+            // push this head's slice of the merged record into every rank's gather buffer
+            for (uint32_t r = 0; r < p.px.world; ++r) {
+                float* ro = p.px.peer_out[r] + head * kRecordFloats;
+                ro[dd] = acc;
+                if (dd == 0) {
+                    ro[kHeadDim] = big;
+                    ro[kHeadDim + 1u] = total;
+                }
+            }
+        } else if (p.record_out != nullptr) {
             float* ro = p.record_out + (uint64_t(blockIdx.y) * kQHeads + head) * kRecordFloats;
             ro[dd] = acc;
             if (dd == 0) {
@@ -423,6 +478,21 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
             const uint64_t at = cl.row * p.query_stride + head * kHeadDim + dd;
             const float gate = bf2f(p.gate[at]);
             p.out[at] = f2bf((acc / total) * (1.0f / (1.0f + expf(-gate))));
+        }
+    }
+    if (p.px.world != 0u && p.px.wait_flags == nullptr) {
+        // The CTA that finishes last raises this rank's flag on every rank: each CTA makes its
+        // peer stores visible system-wide, then counts itself; the counter resets for the next call.
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t total_ctas = gridDim.x * gridDim.y;
+            if (atomicAdd(p.px.done_counter, 1u) == total_ctas - 1u) {
+                *p.px.done_counter = 0u;
+                __threadfence_system();
+                for (uint32_t r = 0; r < p.px.world; ++r)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.px.peer_flag[r]), "r"(p.px.epoch) : "memory");
+            }
         }
     }
 }
@@ -439,6 +509,7 @@ struct DecodeRequest {
     uint64_t scratch_bytes;
     uint64_t query_stride;
     uint32_t capacity;
+    const PeerExchange* px = nullptr;
 };
 
 template <uint32_t N>
@@ -482,6 +553,7 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     cp.out = static_cast<__nv_bfloat16*>(r.out);
     cp.record_out = static_cast<float*>(r.record_out);
     cp.query_stride = r.query_stride;
+    if (r.px != nullptr) cp.px = *r.px;
 
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
@@ -726,4 +798,100 @@ extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream
     if (err != cudaSuccess) return fail(ctx, TATARA_CUDA_ERROR, cudaGetErrorString(err));
     if (ctx != nullptr) ctx->launches += 2;
     return TATARA_OK;
+}
+
+// ---- split-KV across GPUs over peer memory -----------------------------------------------
+extern "C" tatara_status tatara_peer_buffer_create(tatara_ctx* ctx, uint64_t bytes, void** ptr, void* handle64) {
+    if (ctx == nullptr || ptr == nullptr || handle64 == nullptr) return TATARA_INVALID_BUFFER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess || cudaMemset(p, 0, bytes) != cudaSuccess ||
+        cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (p != nullptr) cudaFree(p);
+        return fail(ctx, TATARA_CUDA_ERROR, "peer_buffer_create: allocation or IPC export failed");
+    }
+    cudaDeviceSynchronize();
+    *ptr = p;
+    return TATARA_OK;
+}
+
+extern "C" tatara_status tatara_peer_buffer_open(tatara_ctx* ctx, const void* handle64, void** ptr) {
+    if (ctx == nullptr || ptr == nullptr || handle64 == nullptr) return TATARA_INVALID_BUFFER;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(ctx, TATARA_CUDA_ERROR, "peer_buffer_open: cudaIpcOpenMemHandle failed");
+    }
+    return TATARA_OK;
+}
+
+extern "C" tatara_status tatara_peer_buffer_close(tatara_ctx* ctx, void* ptr, int owned) {
+    if (ctx == nullptr || ptr == nullptr) return TATARA_INVALID_BUFFER;
+    const cudaError_t err = owned ? cudaFree(ptr) : cudaIpcCloseMemHandle(ptr);
+    if (err != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(ctx, TATARA_CUDA_ERROR, "peer_buffer_close failed");
+    }
+    return TATARA_OK;
+}
+
+extern "C" tatara_status tatara_attn_decode_partial_push(tatara_ctx* ctx, void* stream, const void* q,
+                                                         const void* keys, const void* values,
+                                                         uint32_t key_begin, uint32_t key_end,
+                                                         uint32_t capacity, void* const* peer_gather,
+                                                         void* const* peer_flags, uint32_t rank,
+                                                         uint32_t world, uint32_t epoch, void* scratch,
+                                                         uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !keys || !values || !scratch || !peer_gather || !peer_flags)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_partial_push: null buffer");
+    if (!aligned(q, 4) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(scratch, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_partial_push: misaligned buffer");
+    if (world == 0 || world > kMaxPeers || rank >= world || epoch == 0)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_decode_partial_push: rank / world / epoch");
+    if (capacity == 0 || key_begin >= key_end || key_end > capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_partial_push: key range");
+    PeerExchange px{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!peer_gather[r] || !peer_flags[r] || !aligned(peer_gather[r], 8))
+            return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_partial_push: peer pointer");
+        px.peer_out[r] = static_cast<float*>(peer_gather[r]) + uint64_t(rank) * kQHeads * kRecordFloats;
+        px.peer_flag[r] = static_cast<uint32_t*>(peer_flags[r]) + rank;
+    }
+    px.done_counter = ctx->device_status + 2;
+    px.status = ctx->device_status;
+    px.world = world;
+    px.epoch = epoch;
+    DecodeRequest r{q, nullptr, keys, values, nullptr, nullptr, scratch, scratch_bytes, kQHeads * kHeadDim, capacity};
+    r.px = &px;
+    const tatara_attn_lane lane{0, key_end - 1u, 0};
+    const uint32_t row = 0;
+    return launch_decode<1>(ctx, static_cast<cudaStream_t>(stream), r, &lane, &key_begin, &key_end, &row, 1,
+                            "attn_decode_partial_push");
+}
+
+extern "C" tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream, const void* gather,
+                                                  const void* flags, uint32_t world, uint32_t epoch,
+                                                  uint32_t wait_limit_us, const void* gate, void* out) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!gather || !flags || !gate || !out) return fail(ctx, TATARA_INVALID_BUFFER, "attn_combine_wait: null buffer");
+    if (!aligned(gather, 8) || !aligned(flags, 4))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_combine_wait: misaligned buffer");
+    if (world == 0 || world > kMaxPeers || epoch == 0 || wait_limit_us == 0 || wait_limit_us > 2000000u)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_combine_wait: world / epoch / time limit");
+    CombineParams<1> cp{};
+    cp.gate = static_cast<const __nv_bfloat16*>(gate);
+    cp.out = static_cast<__nv_bfloat16*>(out);
+    cp.query_stride = kQHeads * kHeadDim;
+    // gather layout [rank][head][258]: head stride 258, part (= rank) stride 16*258
+    cp.lane[0] = CombineLane{static_cast<const float*>(gather), kRecordFloats, uint64_t(kQHeads) * kRecordFloats, world, 0};
+    cp.px.wait_flags = static_cast<const uint32_t*>(flags);
+    cp.px.status = ctx->device_status;
+    cp.px.world = world;
+    cp.px.epoch = epoch;
+    cp.px.wait_limit_us = wait_limit_us;
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(cp);
+    return check_launch(ctx, "attn_combine_wait");
 }

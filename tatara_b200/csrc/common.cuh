@@ -50,7 +50,7 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // (kv head, partition): 2 per partition, so 74*k partitions fill k waves of 148 SMs.
 __host__ __device__ inline uint32_t partition_keys(uint32_t n) {
     constexpr uint32_t per_wave = kSmCount / kKvHeads; // 74
-    if (n <= per_wave * 64u) return 64u;
+    if (n <= per_wave * 128u) return 128u;   // short lanes: at least 128 keys per item
     const uint32_t target_keys = n < 49152u ? 256u : (n < 196608u ? 512u : 1024u);
     uint32_t waves = (n + per_wave * target_keys / 2u) / (per_wave * target_keys);
     if (waves == 0) waves = 1;

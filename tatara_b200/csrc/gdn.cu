@@ -232,13 +232,16 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
     const float* state_in = rec_pool + gl.rec_in;
     float* state_out = rec_pool + gl.rec_out;
 
-    // state rows of batch 0 go in flight first
+    // all 16 state rows of this warp go in flight first (4 batches x 4 rows, 64 KiB per CTA),
+    // so the whole state read overlaps the conv / norm prologue
     const uint32_t row_base = warp * 16u;
     const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
-    Rows4 r;
+    Rows4 rows[4];
 #pragma unroll
-    for (uint32_t j = 0; j < 4; ++j)
-        r.s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + j * kGdnDim));
+    for (uint32_t batch = 0; batch < 4; ++batch)
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j)
+            rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
 
     // prologue: threads 0..127 -> q channel, 128..255 -> k channel; then v channel on 0..127
     const uint32_t l128 = threadIdx.x & 127u;
@@ -271,13 +274,7 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
     }
 #pragma unroll
     for (uint32_t batch = 0; batch < 4; ++batch) {
-        Rows4 next;
-        if (batch + 1u < 4u) {
-#pragma unroll
-            for (uint32_t j = 0; j < 4; ++j)
-                next.s[j] = __ldcs(reinterpret_cast<const float4*>(
-                    state_in + sbase + ((batch + 1u) * 4u + j) * kGdnDim));
-        }
+        Rows4& r = rows[batch];
         float v[4], out[4];
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) v[j] = vn[row_base + batch * 4u + j];
@@ -289,7 +286,6 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
             const float mine = lane == 0 ? out[0] : lane == 1 ? out[1] : lane == 2 ? out[2] : out[3];
             ys[row_base + batch * 4u + lane] = bf2f(f2bf(mine));
         }
-        if (batch + 1u < 4u) r = next;
     }
     __syncthreads();
     if (warp == 0) {

@@ -61,3 +61,39 @@ def split_kv_decode(dist, world: int, partial: Callable[[], "object"], gathered,
         gathered.view(-1).copy_(rec.reshape(-1))
     combine(gathered)
     return gathered
+
+
+class PeerExchange:
+    """Peer buffers of the collective-free split-KV merge: per rank one buffer holding
+    [2 parities][world][16][258] f32 records followed by [2][world] u32 flags, mapped into every
+    process through CUDA IPC (handles exchanged once with all_gather_object)."""
+
+    RECORD_BYTES = Q_HEADS * RECORD_FLOATS * 4
+
+    def __init__(self, ctx, dist, rank: int, world: int):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.gather_bytes = world * self.RECORD_BYTES
+        self.flags_offset = 2 * self.gather_bytes
+        nbytes = self.flags_offset + 2 * world * 4
+        self.own_ptr, handle = ctx.peer_buffer_create(nbytes)
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle)
+        else:
+            handles[0] = handle
+        self.ptrs = [self.own_ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)]
+        self.epoch = 0
+
+    def step(self, push, combine_wait):
+        """push(peer_gather, peer_flags, epoch) then combine_wait(gather_ptr, flags_ptr, epoch)."""
+        self.epoch += 1
+        parity = self.epoch & 1
+        gathers = [p + parity * self.gather_bytes for p in self.ptrs]
+        flags = [p + self.flags_offset + parity * self.world * 4 for p in self.ptrs]
+        push(gathers, flags, self.epoch)
+        combine_wait(gathers[self.rank], flags[self.rank], self.epoch)
+
+    def close(self):
+        for r, p in enumerate(self.ptrs):
+            self.ctx.peer_buffer_close(p, owned=(r == self.rank))
+        self.ptrs = []
