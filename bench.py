@@ -277,7 +277,7 @@ def main():
         extra["lanes32"] = wl.lanes32(timed, steps, warmup)
         extra["gdn_step"] = wl.gdn_step(timed, steps, warmup)
         extra["gdn_prefill"] = wl.gdn_prefill(timed)
-        extra["prefill_attn"] = wl.prefill(timed, peaks)
+        extra["prefill_attn"] = wl.prefill(timed, peaks, sampler=ClockSampler(local))
     else:
         extra["split_kv"] = wl.split_kv(dist, n, timed, steps, warmup)
         extra["lanes32"] = wl.lanes32(timed, steps, warmup)

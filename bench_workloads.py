@@ -243,17 +243,24 @@ class Workloads:
         return out
 
     # ---- config 2: causal prefill attention, 16384 rows from position 0
-    def prefill(self, timed, peaks, rows=16384, steps=5):
+    def prefill(self, timed, peaks, rows=16384, steps=5, sampler=None):
         torch = self.torch
         try:
             keys, values = device_cache(torch, rows, rows, 21)
             q, gate = device_query(torch, list(range(rows)), 22)
             out = torch.zeros((rows, 16, 256), dtype=torch.bfloat16, device="cuda")
-            ms = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
+            clocks = None
+            if sampler is not None:
+                with sampler as cs:
+                    ms = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3,
+                               hold_s=1.0)
+                clocks = cs.summary()
+            else:
+                ms = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
         except tb.TataraError as e:
             return {"unavailable": str(e)}
         tf = prefill_flops(rows) / (ms * 1e-3) / 1e12
-        return {"rows": rows, "ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+        return {"rows": rows, "ms": ms, "tflops": tf, "clocks": clocks, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                 "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
                 "l2": "Q/gate/out 402 MB > L2"}
 
