@@ -1,0 +1,221 @@
+// Native test of the C++ host layer (tatara_b200/host/hybrid_layers.hpp) over the C ABI, in the
+// style of the reference's tests (tests/native/*_test.cpp: plain main(), a distinct non-zero exit
+// code per failed check).  Host-only checks always run; the device checks run when a B200 is
+// present: a two-layer slice (gated delta + full attention), three lanes at different contexts,
+// three decode tokens batched, compared with the CPU oracle and, bit for bit, with solo runs.
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "../../tatara_b200/host/hybrid_layers.hpp"
+
+using namespace tatara::runtime;
+using u16 = std::uint16_t;
+
+extern "C" {  // oracle/tatara_oracle.cpp (test infrastructure)
+void orc_attn_qk_rope(const u16*, const u16*, const u16*, u16*, u16*, u16*, u16*, std::uint32_t, std::uint32_t, std::uint32_t);
+void orc_attn_decode(const u16*, const u16*, const u16*, const u16*, std::uint32_t, std::uint32_t, u16*, int);
+void orc_gdn_prepare(const u16*, const u16*, const u16*, u16*, u16*, u16*, u16*, std::uint32_t);
+void orc_gdn_gates(const u16*, std::uint32_t, const u16*, const u16*, float*, float*, std::uint32_t);
+void orc_gdn_scan(const u16*, const u16*, const float*, const float*, const float*, u16*, float*, std::uint32_t, int);
+void orc_gdn_gate_norm(const u16*, const u16*, const u16*, u16*, std::uint32_t);
+}
+
+namespace {
+
+u16 to_bf16(float v) {
+    std::uint32_t b;
+    std::memcpy(&b, &v, 4);
+    return static_cast<u16>((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+}
+float from_bf16(u16 h) {
+    const std::uint32_t b = static_cast<std::uint32_t>(h) << 16;
+    float v;
+    std::memcpy(&v, &b, 4);
+    return v;
+}
+struct Rng {
+    std::uint64_t s;
+    std::uint64_t next() { s ^= s >> 12; s ^= s << 25; s ^= s >> 27; return s * 0x2545F4914F6CDD1Dull; }
+    float uniform() { return static_cast<float>(next() >> 40) / 16777216.0f; }
+    float normal() { float a = 0; for (int i = 0; i < 12; ++i) a += uniform(); return a - 6.0f; }
+    void fill(std::vector<u16>& v, float scale = 1.0f, float shift = 0.0f) { for (auto& x : v) x = to_bf16(shift + scale * normal()); }
+};
+template <class T>
+bool upload(void* dst, const std::vector<T>& src) { return cudaMemcpy(dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice) == cudaSuccess; }
+bool close_enough(const std::vector<u16>& got, const u16* want, std::size_t n, float max_abs) {
+    double dot = 0, na = 0, nb = 0;
+    float worst = 0;
+    for (std::size_t i = 0; i < n; ++i) {
+        const float a = from_bf16(got[i]), b = from_bf16(want[i]);
+        if (!std::isfinite(a)) return false;
+        worst = std::fmax(worst, std::fabs(a - b));
+        dot += double(a) * b; na += double(a) * a; nb += double(b) * b;
+    }
+    const double cosine = (na == 0 && nb == 0) ? 1.0 : dot / std::sqrt(na * nb);
+    return worst <= max_abs && cosine >= 0.9999;
+}
+
+int host_only_checks() {
+    if (context_in_capacity(0, 0) || !context_in_capacity(7, 8) || context_in_capacity(8, 8)) return 10;
+    if (std::strcmp(to_string(CommandError::ContextOutOfRange), "ContextOutOfRange") != 0) return 11;
+    if (std::strcmp(to_string(CommandError::StateSlotMismatch), "StateSlotMismatch") != 0) return 12;
+    if (std::strcmp(to_string(CommandError::None), "None") != 0) return 13;
+    LayerPass pass(nullptr, nullptr);
+    if (pass.error() != CommandError::InvalidDevice) return 14;
+    DecodeStatePool pool;
+    DecodeBatchScratch scratch;
+    if (pass.encode_attention(pool, 0, AttentionWeights{}, {}, nullptr, scratch) != CommandError::InvalidDevice) return 15;
+    if (pass.encode_gated_delta(pool, 0, GatedDeltaWeights{}, {}, nullptr, scratch) != CommandError::InvalidDevice) return 16;
+    if (tatara_attn_partition_keys(1) != 128 || tatara_attn_partitions(9472) != 74) return 17;
+    if (tatara_attn_decode_scratch_bytes(4097, 2) != 2 * tatara_attn_decode_scratch_bytes(4097, 1)) return 18;
+    return 0;
+}
+
+int device_checks(tatara_ctx* ctx) {
+    constexpr std::uint32_t kSlots = 3, kCapacity = 512, kTokens = 3;
+    const std::vector<LayerKind> schedule{LayerKind::GatedDelta, LayerKind::FullAttention};
+    const std::uint32_t start_context[kSlots] = {5, 200, 300};
+    Rng rng{0x51A7E5ull};
+
+    // weights
+    std::vector<u16> qn(256), kn(256), conv_w(8192 * 4), a_log(32), dt_bias(32), gnorm(128);
+    rng.fill(qn, 0.1f, 1.0f); rng.fill(kn, 0.1f, 1.0f); rng.fill(conv_w, 0.5f); rng.fill(dt_bias, 0.5f); rng.fill(gnorm, 0.1f, 1.0f);
+    for (auto& x : a_log) x = to_bf16(std::log(1.0f + 15.0f * rng.uniform()));
+    DeviceBuffer d_qn(512), d_kn(512), d_conv(8192 * 8), d_alog(64), d_dt(64), d_gn(256);
+    if (!upload(d_qn.data(), qn) || !upload(d_kn.data(), kn) || !upload(d_conv.data(), conv_w) ||
+        !upload(d_alog.data(), a_log) || !upload(d_dt.data(), dt_bias) || !upload(d_gn.data(), gnorm)) return 20;
+    const AttentionWeights aw{d_qn.data(), d_kn.data()};
+    const GatedDeltaWeights gw{d_conv.data(), d_alog.data(), d_dt.data(), d_gn.data()};
+
+    // two identical pools: one driven batched, one driven lane by lane
+    DecodeStatePool pool[2];
+    std::vector<DecodeStateSlot> slots[2];
+    DecodeBatchScratch scratch[2];
+    for (int p = 0; p < 2; ++p)
+        if (!create_state_pool(kSlots, kCapacity, schedule, pool[p], slots[p]) ||
+            !create_batch_scratch(kSlots, kCapacity, scratch[p])) return 21;
+
+    // host mirrors for the oracle
+    struct HostLane {
+        std::vector<u16> keys, values, conv;
+        std::vector<float> state;
+    };
+    std::vector<HostLane> host(kSlots);
+    for (std::uint32_t s = 0; s < kSlots; ++s) {
+        HostLane& h = host[s];
+        h.keys.assign(2 * kCapacity * 256, 0); h.values.assign(2 * kCapacity * 256, 0);
+        h.conv.resize(3 * 8192); rng.fill(h.conv);
+        h.state.resize(32 * 128 * 128);
+        for (auto& x : h.state) x = 0.02f * rng.normal();
+        // history: fill positions 0..context-1 through the library, mirror with the oracle
+        std::vector<u16> hist(std::size_t{start_context[s]} * 9216); rng.fill(hist);
+        DeviceBuffer d_hist(hist.size() * 2), d_q(std::size_t{start_context[s]} * 4096 * 2), d_g(std::size_t{start_context[s]} * 4096 * 2);
+        if (!upload(d_hist.data(), hist)) return 22;
+        std::vector<u16> oq(std::size_t{start_context[s]} * 4096), og(oq.size());
+        orc_attn_qk_rope(hist.data(), qn.data(), kn.data(), oq.data(), og.data(), h.keys.data(), h.values.data(), 0, kCapacity, start_context[s]);
+        for (int p = 0; p < 2; ++p) {
+            const DecodeStatePoolLayer& al = pool[p].layers[1];
+            u16* k = static_cast<u16*>(al.first.data()) + s * al.first_stride;
+            u16* v = static_cast<u16*>(al.second.data()) + s * al.second_stride;
+            if (tatara_attn_qk_rope(ctx, nullptr, d_hist.data(), d_qn.data(), d_kn.data(), d_q.data(), d_g.data(), k, v, 0,
+                                    kCapacity, start_context[s]) != TATARA_OK) return 23;
+            const DecodeStatePoolLayer& gl = pool[p].layers[0];
+            if (!upload(static_cast<u16*>(gl.first.data()) + 2 * s * gl.first_stride, h.conv) ||
+                !upload(static_cast<float*>(gl.second.data()) + 2 * s * gl.second_stride, h.state)) return 24;
+        }
+    }
+    if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 25;
+
+    DeviceBuffer d_gproj(kSlots * 12352 * 2), d_aproj(kSlots * 9216 * 2);
+    std::vector<u16> batched_attn(kSlots * 4096), batched_gdn(kSlots * 4096), solo(4096);
+    for (std::uint32_t token = 0; token < kTokens; ++token) {
+        std::vector<u16> gproj(kSlots * 12352), aproj(kSlots * 9216);
+        rng.fill(gproj); rng.fill(aproj);
+        if (!upload(d_gproj.data(), gproj) || !upload(d_aproj.data(), aproj)) return 30;
+        std::vector<DecodeStream> streams;
+        for (std::uint32_t s = 0; s < kSlots; ++s) streams.push_back(DecodeStream{&slots[0][s], start_context[s] + token});
+        LayerPass pass(ctx, nullptr);
+        if (pass.encode_gated_delta(pool[0], 0, gw, streams, d_gproj.data(), scratch[0]) != CommandError::None) return 31;
+        if (pass.encode_attention(pool[0], 1, aw, streams, d_aproj.data(), scratch[0]) != CommandError::None) return 32;
+        if (pass.commit_and_wait() != CommandError::None) return 33;
+        cudaMemcpy(batched_gdn.data(), scratch[0].gdn_gated.data(), batched_gdn.size() * 2, cudaMemcpyDeviceToHost);
+        cudaMemcpy(batched_attn.data(), scratch[0].attended.data(), batched_attn.size() * 2, cudaMemcpyDeviceToHost);
+        advance_decode_state(pool[0], streams);
+
+        for (std::uint32_t s = 0; s < kSlots; ++s) {
+            // oracle for this lane and token
+            HostLane& h = host[s];
+            const std::uint32_t context = start_context[s] + token;
+            std::vector<u16> qk(4096), v(4096), z(4096), conv_out(3 * 8192), y(4096), gated(4096);
+            std::vector<float> decay(32), beta(32), state_out(h.state.size());
+            orc_gdn_prepare(&gproj[s * 12352], h.conv.data(), conv_w.data(), qk.data(), v.data(), z.data(), conv_out.data(), 1);
+            orc_gdn_gates(&gproj[s * 12352], 12352, a_log.data(), dt_bias.data(), decay.data(), beta.data(), 1);
+            orc_gdn_scan(qk.data(), v.data(), decay.data(), beta.data(), h.state.data(), y.data(), state_out.data(), 1, 4);
+            orc_gdn_gate_norm(y.data(), z.data(), gnorm.data(), gated.data(), 1);
+            h.conv = conv_out; h.state = state_out;
+            std::vector<u16> oq(4096), og(4096), want(4096);
+            orc_attn_qk_rope(&aproj[s * 9216], qn.data(), kn.data(), oq.data(), og.data(), h.keys.data(), h.values.data(), context, kCapacity, 1);
+            orc_attn_decode(oq.data(), og.data(), h.keys.data(), h.values.data(), context, kCapacity, want.data(), 4);
+            const std::vector<u16> got_attn(batched_attn.begin() + s * 4096, batched_attn.begin() + (s + 1) * 4096);
+            const std::vector<u16> got_gdn(batched_gdn.begin() + s * 4096, batched_gdn.begin() + (s + 1) * 4096);
+            if (!close_enough(got_attn, want.data(), 4096, 2e-2f)) return 40 + int(s);
+            if (!close_enough(got_gdn, gated.data(), 4096, 4e-2f)) return 50 + int(s);
+
+            // the same lane alone on the second pool: bit-identical (lossless concurrency)
+            DeviceBuffer d_g1(12352 * 2), d_a1(9216 * 2);
+            cudaMemcpy(d_g1.data(), &gproj[s * 12352], 12352 * 2, cudaMemcpyHostToDevice);
+            cudaMemcpy(d_a1.data(), &aproj[s * 9216], 9216 * 2, cudaMemcpyHostToDevice);
+            const std::vector<DecodeStream> one{DecodeStream{&slots[1][s], context}};
+            LayerPass solo_pass(ctx, nullptr);
+            if (solo_pass.encode_gated_delta(pool[1], 0, gw, one, d_g1.data(), scratch[1]) != CommandError::None) return 60;
+            if (solo_pass.encode_attention(pool[1], 1, aw, one, d_a1.data(), scratch[1]) != CommandError::None) return 61;
+            if (solo_pass.commit_and_wait() != CommandError::None) return 62;
+            cudaMemcpy(solo.data(), scratch[1].attended.data(), 4096 * 2, cudaMemcpyDeviceToHost);
+            if (std::memcmp(solo.data(), got_attn.data(), 4096 * 2) != 0) return 70 + int(s);
+            cudaMemcpy(solo.data(), scratch[1].gdn_gated.data(), 4096 * 2, cudaMemcpyDeviceToHost);
+            if (std::memcmp(solo.data(), got_gdn.data(), 4096 * 2) != 0) return 80 + int(s);
+            advance_decode_state(pool[1], one);
+        }
+    }
+
+    // error behaviour: out-of-range context is refused before anything is enqueued, latches, and
+    // gates the rest of the pass
+    {
+        const std::uint64_t before = tatara_ctx_launch_count(ctx);
+        std::vector<DecodeStream> streams{DecodeStream{&slots[0][0], kCapacity}};
+        LayerPass pass(ctx, nullptr);
+        if (pass.encode_attention(pool[0], 1, aw, streams, d_aproj.data(), scratch[0]) != CommandError::ContextOutOfRange) return 90;
+        streams[0].context = 1;
+        if (pass.encode_attention(pool[0], 1, aw, streams, d_aproj.data(), scratch[0]) != CommandError::ContextOutOfRange) return 91;
+        if (pass.commit_and_wait() != CommandError::ContextOutOfRange) return 92;
+        if (tatara_ctx_launch_count(ctx) != before) return 93;
+        LayerPass wrong(ctx, nullptr);
+        if (wrong.encode_attention(pool[0], 0, aw, streams, d_aproj.data(), scratch[0]) != CommandError::StateSlotMismatch) return 94;
+        LayerPass dup(ctx, nullptr);
+        std::vector<DecodeStream> twice{DecodeStream{&slots[0][0], 1}, DecodeStream{&slots[0][0], 2}};
+        if (dup.encode_gated_delta(pool[0], 0, gw, twice, d_gproj.data(), scratch[0]) != CommandError::InvalidStreamGroup) return 95;
+        slots[0][1].status = DecodeStateSlotStatus::Poisoned;
+        LayerPass poisoned(ctx, nullptr);
+        std::vector<DecodeStream> bad{DecodeStream{&slots[0][1], 1}};
+        if (poisoned.encode_gated_delta(pool[0], 0, gw, bad, d_gproj.data(), scratch[0]) != CommandError::StateSlotMismatch) return 96;
+    }
+    return 0;
+}
+
+} // namespace
+
+int main() {
+    if (const int rc = host_only_checks(); rc != 0) { std::printf("host check failed: %d\n", rc); return rc; }
+    tatara_ctx* ctx = nullptr;
+    const tatara_status st = tatara_ctx_create(0, &ctx);
+    if (st == TATARA_INVALID_DEVICE) { std::printf("host checks passed; no B200 present, device checks skipped\n"); return 0; }
+    if (st != TATARA_OK) return 2;
+    const int rc = device_checks(ctx);
+    tatara_ctx_destroy(ctx);
+    if (rc != 0) { std::printf("device check failed: %d\n", rc); return rc; }
+    std::printf("host and device checks passed\n");
+    return 0;
+}
