@@ -214,36 +214,47 @@ gdn_chunk_prepare_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat
 }
 
 // ---- kernel 2: serial over chunks --------------------------------------------------------
-constexpr uint32_t kScanThreads = 64;
+// CTA = (32 v-dims, v-head): two groups of four warps.  A group owns 16 v-dims; its state slice
+// Z [16][128] is split by k-dim quarter over the four warps (4 accumulator tiles each).  Per chunk:
+//   1. every warp multiplies ITS k-dim quarter of Z into all 64 steps (split-K partials of
+//      E = Z W^T and OQ = Z Q^T), the partials meet in shared memory;
+//   2. warp w sums the four partials for ITS 16 steps, forms Delta^T = U^T - E there, and publishes
+//      it (plain and scaled by e^{G_C-G_i}) as bf16;
+//   3. every warp reads all of Delta^T as an A operand: O^T quarter += Delta^T P^T (its 16 steps),
+//      Z quarter = e^{G_C} Z + (scaled Delta^T) K (its 32 k-dims).
+// 56 MMAs per warp per chunk on the dependent chain instead of 224, at the price of two
+// 128-thread named barriers.
+constexpr uint32_t kScanThreads = 256;
 constexpr uint32_t kStW = 0, kStQ = kStW + kWBytes, kStK = kStQ + kWBytes, kStP = kStK + kWBytes,
                    kStU = kStP + kPBytesC, kStG = kStU + 32u * kChunk * 2u, kStageScan = kStG + kGFloats * 4u;
-constexpr uint32_t kScanSmem = 2u * kStageScan + kChunk * 32u * 2u; // two stages + output staging
+constexpr uint32_t kPartStride = 72u, kDeltaStride = 72u;            // padded rows: no bank conflicts
+constexpr uint32_t kPartFloats = 16u * kPartStride;                  // one [16][64] f32 partial
+constexpr uint32_t kOffPart = 2u * kStageScan;                       // [group 2][warp 4][E|OQ][16][64] f32
+constexpr uint32_t kOffDelta = kOffPart + 2u * 4u * 2u * kPartFloats * 4u;  // [group 2][plain|scaled][16][64] bf16
+constexpr uint32_t kOffOut = kOffDelta + 2u * 2u * 16u * kDeltaStride * 2u; // [64 steps][32 v-dims] bf16
+constexpr uint32_t kScanSmem = kOffOut + kChunk * 32u * 2u;
 
 __device__ __forceinline__ void scan_issue(uint32_t stage, const uint8_t* chunk_scratch,
                                            const __nv_bfloat16* qk_rows, uint32_t live_rows, uint32_t qcol,
                                            uint32_t slice) {
     const uint32_t tid = threadIdx.x;
-    // W [64][128] (swizzled rows of 16 chunks)
-    for (uint32_t idx = tid; idx < kChunk * 16u; idx += kScanThreads) {
+    for (uint32_t idx = tid; idx < kChunk * 16u; idx += kScanThreads) {      // W [64][128]
         const uint32_t r = idx >> 4, c = idx & 15u;
         cpa16(stage + kStW + swz<128>(r, c), chunk_scratch + idx * 16u);
     }
-    // Q and K rows from the qk tensor
-    for (uint32_t idx = tid; idx < 2u * kChunk * 16u; idx += kScanThreads) {
+    for (uint32_t idx = tid; idx < 2u * kChunk * 16u; idx += kScanThreads) { // Q and K rows of the qk tensor
         const uint32_t which = idx >> 10, rem = idx & 1023u, r = rem >> 4, c = rem & 15u;
         const bool live = r < live_rows;
         const __nv_bfloat16* src = qk_rows + uint64_t(live ? r : 0u) * kGdnQk + (which ? kGdnKOff + qcol : qcol) + c * 8u;
         cpa16z(stage + (which ? kStK : kStQ) + swz<128>(r, c), src, live);
     }
-    // P [64][64] (rows of 8 chunks)
-    for (uint32_t idx = tid; idx < kChunk * 8u; idx += kScanThreads) {
+    for (uint32_t idx = tid; idx < kChunk * 8u; idx += kScanThreads) {       // P [64][64]
         const uint32_t r = idx >> 3, c = idx & 7u;
         cpa16(stage + kStP + swz<64>(r, c), chunk_scratch + kWBytes + kUtBytes + idx * 16u);
     }
-    // U^T rows of this CTA's 32 v-dims, and the decay vectors
-    for (uint32_t idx = tid; idx < 32u * 8u; idx += kScanThreads)
+    for (uint32_t idx = tid; idx < 32u * 8u; idx += kScanThreads)            // U^T rows of this CTA's 32 v-dims
         cpa16(stage + kStU + idx * 16u, chunk_scratch + kWBytes + slice * (32u * kChunk * 2u) + idx * 16u);
-    for (uint32_t idx = tid; idx < kGFloats / 4u; idx += kScanThreads)
+    for (uint32_t idx = tid; idx < kGFloats / 4u; idx += kScanThreads)       // decay vectors
         cpa16(stage + kStG + idx * 16u, chunk_scratch + kWBytes + kUtBytes + kPBytesC + idx * 16u);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
 }
@@ -255,18 +266,22 @@ gdn_chunk_scan_kernel(const __nv_bfloat16* __restrict__ qk, const uint8_t* __res
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t slice = blockIdx.x, head = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t group = warp >> 2, wq = warp & 3u;   // v-dim half of the CTA, quarter within the group
     const uint32_t g = lane >> 2, t = lane & 3u, j = lane >> 3, r8 = lane & 7u;
     const uint32_t qcol = (head >> 1) * kGdnDim;
-    const uint32_t vrow = slice * 32u + warp * 16u; // first v-dim of this warp
+    const uint32_t vrow = slice * 32u + group * 16u;     // first v-dim of this group
     const uint32_t sbase = sm_u32(smem);
-    uint8_t* o_stage = smem + 2u * kStageScan;
+    const uint32_t group_bar = 1u + group;
+    float* part = reinterpret_cast<float*>(smem + kOffPart) + group * (4u * 2u * kPartFloats);
+    __nv_bfloat16* delta = reinterpret_cast<__nv_bfloat16*>(smem + kOffDelta) + group * (2u * 16u * kDeltaStride);
+    __nv_bfloat16* ost = reinterpret_cast<__nv_bfloat16*>(smem + kOffOut);
 
-    // state slice Z [16 v-dims][128 k-dims] as 16 accumulator tiles
-    float z[16][4];
+    // this warp's quarter of the state slice: Z[16 v-dims][k-dims 32*wq .. +31] as 4 accumulator tiles
+    float z[4][4];
     {
-        const float* src = state_in + (uint64_t(head) * kGdnDim + vrow) * kGdnDim;
+        const float* src = state_in + (uint64_t(head) * kGdnDim + vrow) * kGdnDim + wq * 32u;
 #pragma unroll
-        for (uint32_t nt = 0; nt < 16; ++nt) {
+        for (uint32_t nt = 0; nt < 4; ++nt) {
             const float2 lo = *reinterpret_cast<const float2*>(src + uint64_t(g) * kGdnDim + nt * 8u + 2u * t);
             const float2 hi = *reinterpret_cast<const float2*>(src + uint64_t(g + 8u) * kGdnDim + nt * 8u + 2u * t);
             z[nt][0] = lo.x; z[nt][1] = lo.y; z[nt][2] = hi.x; z[nt][3] = hi.y;
@@ -289,16 +304,15 @@ gdn_chunk_scan_kernel(const __nv_bfloat16* __restrict__ qk, const uint8_t* __res
         __syncthreads();
         const float* gvec = reinterpret_cast<const float*>(stage_ptr + kStG);
 
-        // bf16 A fragments of the state (accumulator tiles 2ks, 2ks+1 -> k-step ks)
-        uint32_t za[8][4];
+        // ---- 1. split-K partials over this warp's 32 k-dims, all 64 steps
+        uint32_t za[2][4];
 #pragma unroll
-        for (uint32_t ks = 0; ks < 8; ++ks) {
+        for (uint32_t ks = 0; ks < 2; ++ks) {
             za[ks][0] = pack2(z[2 * ks][0], z[2 * ks][1]);
             za[ks][1] = pack2(z[2 * ks][2], z[2 * ks][3]);
             za[ks][2] = pack2(z[2 * ks + 1][0], z[2 * ks + 1][1]);
             za[ks][3] = pack2(z[2 * ks + 1][2], z[2 * ks + 1][3]);
         }
-        // E = Z W^T and OQ = Z Q^T   ([16 v-dims][64 steps] each)
         float e[8][4], o[8][4];
 #pragma unroll
         for (uint32_t nt = 0; nt < 8; ++nt) {
@@ -306,11 +320,11 @@ gdn_chunk_scan_kernel(const __nv_bfloat16* __restrict__ qk, const uint8_t* __res
             o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
         }
 #pragma unroll
-        for (uint32_t ks = 0; ks < 8; ++ks) {
+        for (uint32_t ks = 0; ks < 2; ++ks) {
 #pragma unroll
             for (uint32_t np = 0; np < 4; ++np) {
                 uint32_t b0, b1, b2, b3;
-                const uint32_t off = swz<128>(np * 16u + (j >> 1) * 8u + r8, ks * 2u + (j & 1u));
+                const uint32_t off = swz<128>(np * 16u + (j >> 1) * 8u + r8, (wq * 2u + ks) * 2u + (j & 1u));
                 ldsm_x4(stage + kStW + off, b0, b1, b2, b3);
                 mma16816(e[2 * np], za[ks][0], za[ks][1], za[ks][2], za[ks][3], b0, b1);
                 mma16816(e[2 * np + 1], za[ks][0], za[ks][1], za[ks][2], za[ks][3], b2, b3);
@@ -319,74 +333,112 @@ gdn_chunk_scan_kernel(const __nv_bfloat16* __restrict__ qk, const uint8_t* __res
                 mma16816(o[2 * np + 1], za[ks][0], za[ks][1], za[ks][2], za[ks][3], b2, b3);
             }
         }
-        // Delta^T = U^T - E;  O^T = diag-scale(OQ, e^{G_r}) + Delta^T P^T
-        const __nv_bfloat16* ut = reinterpret_cast<const __nv_bfloat16*>(stage_ptr + kStU) + (warp * 16u) * kChunk;
-        uint32_t da[4][4], ds[4][4]; // Delta^T as A fragments: plain, and scaled by e^{G_C-G_i}
+        {
+            float* pe = part + (wq * 2u) * kPartFloats;
+            float* po = pe + kPartFloats;
 #pragma unroll
-        for (uint32_t nt = 0; nt < 8; ++nt) {
-            const uint32_t col = nt * 8u + 2u * t;
-            const __nv_bfloat162 ulo = *reinterpret_cast<const __nv_bfloat162*>(ut + g * kChunk + col);
-            const __nv_bfloat162 uhi = *reinterpret_cast<const __nv_bfloat162*>(ut + (g + 8u) * kChunk + col);
-            const float d0 = bf2f(ulo.x) - e[nt][0], d1 = bf2f(ulo.y) - e[nt][1];
-            const float d2 = bf2f(uhi.x) - e[nt][2], d3 = bf2f(uhi.y) - e[nt][3];
-            const float gr0 = gvec[col], gr1 = gvec[col + 1u];
-            const float gc0 = gvec[kChunk + col], gc1 = gvec[kChunk + col + 1u];
-            o[nt][0] *= gr0; o[nt][1] *= gr1; o[nt][2] *= gr0; o[nt][3] *= gr1;
-            const uint32_t ks = nt >> 1, half = (nt & 1u) * 2u;
-            da[ks][half] = pack2(d0, d1);
-            da[ks][half + 1u] = pack2(d2, d3);
-            ds[ks][half] = pack2(d0 * gc0, d1 * gc1);
-            ds[ks][half + 1u] = pack2(d2 * gc0, d3 * gc1);
+            for (uint32_t nt = 0; nt < 8; ++nt) {
+                const uint32_t col = nt * 8u + 2u * t;
+                *reinterpret_cast<float2*>(pe + g * kPartStride + col) = make_float2(e[nt][0], e[nt][1]);
+                *reinterpret_cast<float2*>(pe + (g + 8u) * kPartStride + col) = make_float2(e[nt][2], e[nt][3]);
+                *reinterpret_cast<float2*>(po + g * kPartStride + col) = make_float2(o[nt][0], o[nt][1]);
+                *reinterpret_cast<float2*>(po + (g + 8u) * kPartStride + col) = make_float2(o[nt][2], o[nt][3]);
+            }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
+
+        // ---- 2. this warp's 16 steps: sum the four partials (warp order), Delta^T, scaled OQ
+        float oq[2][4];
+        {
+            const __nv_bfloat16* ut = reinterpret_cast<const __nv_bfloat16*>(stage_ptr + kStU) + (group * 16u) * kChunk;
+#pragma unroll
+            for (uint32_t nt = 0; nt < 2; ++nt) {
+                const uint32_t col = wq * 16u + nt * 8u + 2u * t;
+                float2 elo = make_float2(0.0f, 0.0f), ehi = elo, olo = elo, ohi = elo;
+#pragma unroll
+                for (uint32_t w = 0; w < 4; ++w) {
+                    const float* pe = part + (w * 2u) * kPartFloats;
+                    const float* po = pe + kPartFloats;
+                    const float2 a = *reinterpret_cast<const float2*>(pe + g * kPartStride + col);
+                    const float2 b = *reinterpret_cast<const float2*>(pe + (g + 8u) * kPartStride + col);
+                    const float2 cc = *reinterpret_cast<const float2*>(po + g * kPartStride + col);
+                    const float2 d = *reinterpret_cast<const float2*>(po + (g + 8u) * kPartStride + col);
+                    elo.x += a.x; elo.y += a.y; ehi.x += b.x; ehi.y += b.y;
+                    olo.x += cc.x; olo.y += cc.y; ohi.x += d.x; ohi.y += d.y;
+                }
+                const __nv_bfloat162 ulo = *reinterpret_cast<const __nv_bfloat162*>(ut + g * kChunk + col);
+                const __nv_bfloat162 uhi = *reinterpret_cast<const __nv_bfloat162*>(ut + (g + 8u) * kChunk + col);
+                const float d0 = bf2f(ulo.x) - elo.x, d1 = bf2f(ulo.y) - elo.y;
+                const float d2 = bf2f(uhi.x) - ehi.x, d3 = bf2f(uhi.y) - ehi.y;
+                const float gr0 = gvec[col], gr1 = gvec[col + 1u];
+                const float gc0 = gvec[kChunk + col], gc1 = gvec[kChunk + col + 1u];
+                oq[nt][0] = olo.x * gr0; oq[nt][1] = olo.y * gr1; oq[nt][2] = ohi.x * gr0; oq[nt][3] = ohi.y * gr1;
+                *reinterpret_cast<uint32_t*>(delta + g * kDeltaStride + col) = pack2(d0, d1);
+                *reinterpret_cast<uint32_t*>(delta + (g + 8u) * kDeltaStride + col) = pack2(d2, d3);
+                *reinterpret_cast<uint32_t*>(delta + 16u * kDeltaStride + g * kDeltaStride + col) = pack2(d0 * gc0, d1 * gc1);
+                *reinterpret_cast<uint32_t*>(delta + 16u * kDeltaStride + (g + 8u) * kDeltaStride + col) = pack2(d2 * gc0, d3 * gc1);
+            }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(group_bar) : "memory");
+
+        // ---- 3. all of Delta^T as A fragments; O^T quarter and Z quarter
+        uint32_t da[4][4], ds[4][4];
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks) {
+            const uint32_t col = ks * 16u + 2u * t;
+            da[ks][0] = *reinterpret_cast<const uint32_t*>(delta + g * kDeltaStride + col);
+            da[ks][1] = *reinterpret_cast<const uint32_t*>(delta + (g + 8u) * kDeltaStride + col);
+            da[ks][2] = *reinterpret_cast<const uint32_t*>(delta + g * kDeltaStride + col + 8u);
+            da[ks][3] = *reinterpret_cast<const uint32_t*>(delta + (g + 8u) * kDeltaStride + col + 8u);
+            ds[ks][0] = *reinterpret_cast<const uint32_t*>(delta + 16u * kDeltaStride + g * kDeltaStride + col);
+            ds[ks][1] = *reinterpret_cast<const uint32_t*>(delta + 16u * kDeltaStride + (g + 8u) * kDeltaStride + col);
+            ds[ks][2] = *reinterpret_cast<const uint32_t*>(delta + 16u * kDeltaStride + g * kDeltaStride + col + 8u);
+            ds[ks][3] = *reinterpret_cast<const uint32_t*>(delta + 16u * kDeltaStride + (g + 8u) * kDeltaStride + col + 8u);
         }
 #pragma unroll
         for (uint32_t ks = 0; ks < 4; ++ks) {
-#pragma unroll
-            for (uint32_t np = 0; np < 4; ++np) {
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4(stage + kStP + swz<64>(np * 16u + (j >> 1) * 8u + r8, ks * 2u + (j & 1u)), b0, b1, b2, b3);
-                mma16816(o[2 * np], da[ks][0], da[ks][1], da[ks][2], da[ks][3], b0, b1);
-                mma16816(o[2 * np + 1], da[ks][0], da[ks][1], da[ks][2], da[ks][3], b2, b3);
-            }
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(stage + kStP + swz<64>(wq * 16u + (j >> 1) * 8u + r8, ks * 2u + (j & 1u)), b0, b1, b2, b3);
+            mma16816(oq[0], da[ks][0], da[ks][1], da[ks][2], da[ks][3], b0, b1);
+            mma16816(oq[1], da[ks][0], da[ks][1], da[ks][2], da[ks][3], b2, b3);
         }
-        // Z = e^{G_C} Z + (Delta^T scaled) K
         const float gend = gvec[2u * kChunk];
 #pragma unroll
-        for (uint32_t nt = 0; nt < 16; ++nt) {
+        for (uint32_t nt = 0; nt < 4; ++nt) {
             z[nt][0] *= gend; z[nt][1] *= gend; z[nt][2] *= gend; z[nt][3] *= gend;
         }
 #pragma unroll
         for (uint32_t ks = 0; ks < 4; ++ks) {
 #pragma unroll
-            for (uint32_t np = 0; np < 8; ++np) {
+            for (uint32_t np = 0; np < 2; ++np) {
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4_t(stage + kStK + swz<128>(ks * 16u + (j & 1u) * 8u + r8, np * 2u + (j >> 1)), b0, b1, b2, b3);
+                ldsm_x4_t(stage + kStK + swz<128>(ks * 16u + (j & 1u) * 8u + r8, (wq * 2u + np) * 2u + (j >> 1)), b0, b1, b2, b3);
                 mma16816(z[2 * np], ds[ks][0], ds[ks][1], ds[ks][2], ds[ks][3], b0, b1);
                 mma16816(z[2 * np + 1], ds[ks][0], ds[ks][1], ds[ks][2], ds[ks][3], b2, b3);
             }
         }
         // outputs: O^T [v-dim][step] -> staging [step][32 v-dims] -> y rows (64 bytes per row)
-        __nv_bfloat16* ost = reinterpret_cast<__nv_bfloat16*>(o_stage);
 #pragma unroll
-        for (uint32_t nt = 0; nt < 8; ++nt) {
-            const uint32_t col = nt * 8u + 2u * t;
-            ost[col * 32u + warp * 16u + g] = f2bf(o[nt][0]);
-            ost[(col + 1u) * 32u + warp * 16u + g] = f2bf(o[nt][1]);
-            ost[col * 32u + warp * 16u + g + 8u] = f2bf(o[nt][2]);
-            ost[(col + 1u) * 32u + warp * 16u + g + 8u] = f2bf(o[nt][3]);
+        for (uint32_t nt = 0; nt < 2; ++nt) {
+            const uint32_t col = wq * 16u + nt * 8u + 2u * t;
+            ost[col * 32u + group * 16u + g] = f2bf(oq[nt][0]);
+            ost[(col + 1u) * 32u + group * 16u + g] = f2bf(oq[nt][1]);
+            ost[col * 32u + group * 16u + g + 8u] = f2bf(oq[nt][2]);
+            ost[(col + 1u) * 32u + group * 16u + g + 8u] = f2bf(oq[nt][3]);
         }
         __syncthreads();
         const uint32_t live_rows = min(kChunk, rows - c * kChunk);
-        for (uint32_t idx = threadIdx.x; idx < kChunk * 4u; idx += kScanThreads) {
-            const uint32_t r = idx >> 2, q4 = idx & 3u;
+        {
+            const uint32_t r = threadIdx.x >> 2, q4 = threadIdx.x & 3u;   // 256 threads = 64 rows x 4 x 16 B
             if (r < live_rows)
                 *reinterpret_cast<uint4*>(y + uint64_t(c * kChunk + r) * kGdnV + head * kGdnDim + slice * 32u + q4 * 8u) =
-                    *reinterpret_cast<const uint4*>(o_stage + r * 64u + q4 * 16u);
+                    *reinterpret_cast<const uint4*>(smem + kOffOut + r * 64u + q4 * 16u);
         }
-        __syncthreads(); // the other stage and the output staging are free again
+        __syncthreads(); // the other stage, the exchange buffers and the output staging are free again
     }
-    float* dst = state_out + (uint64_t(head) * kGdnDim + vrow) * kGdnDim;
+    float* dst = state_out + (uint64_t(head) * kGdnDim + vrow) * kGdnDim + wq * 32u;
 #pragma unroll
-    for (uint32_t nt = 0; nt < 16; ++nt) {
+    for (uint32_t nt = 0; nt < 4; ++nt) {
         *reinterpret_cast<float2*>(dst + uint64_t(g) * kGdnDim + nt * 8u + 2u * t) = make_float2(z[nt][0], z[nt][1]);
         *reinterpret_cast<float2*>(dst + uint64_t(g + 8u) * kGdnDim + nt * 8u + 2u * t) = make_float2(z[nt][2], z[nt][3]);
     }
