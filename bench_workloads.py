@@ -335,6 +335,8 @@ class Workloads:
                     "gbs": (args.context * 2048 + 24576) / (ms * 1e-3) / 1e9}
         if which == "gdn_step":
             return self.gdn_step(timed, steps, warmup)
+        if which == "lanes32":
+            return self.lanes32(timed, steps, warmup)
         if which == "gdn_prefill":
             return self.gdn_prefill(timed, rows=args.rows)
         if which == "prefill":
