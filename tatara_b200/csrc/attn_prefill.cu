@@ -10,8 +10,8 @@
 // An M128 MMA costs about 64 cycles whatever its N up to 128 (measured: N = 64 tiles ran the
 // tensor pipe at half rate), so the score tile is 128 keys wide.  A 128-key K or V tile is
 // 64 KiB, too large to double-buffer next to the 64 KiB Q tile, so K and V stream through rings
-// of 16 KiB slots that are released and refilled INSIDE a tile: a K slot holds 64 of the 256 dims
-// (the operand of four consecutive k-steps), a V slot holds 32 of the 128 keys (two k-steps);
+// of 32 KiB slots that are released and refilled INSIDE a tile: a K slot holds 128 of the 256 dims
+// (the operand of eight consecutive k-steps), a V slot holds 64 of the 128 keys (four k-steps);
 // a tcgen05.commit after each slot's MMAs hands the slot back to the TMA producer.
 // TMEM map (512 columns): S/P buffer 0 at 0..127, buffer 1 at 128..255, O at 256..511; P (bf16
 // pairs per 32-bit column) overwrites the first 64 columns of the S buffer it was computed from
@@ -27,11 +27,12 @@
 
 namespace tb {
 
-constexpr uint32_t kBM = 128, kBN = 128, kKSlots = 6, kVSlots = 4, kSBufs = 2;
+constexpr uint32_t kBM = 128, kBN = 128, kKSlots = 3, kVSlots = 2, kSBufs = 2;
 constexpr uint32_t kAtomBytesQ = kBM * 128;          // one 64-dim swizzle atom of the Q tile
 constexpr uint32_t kQBytes = 4 * kAtomBytesQ;        // 64 KiB
-constexpr uint32_t kSlotBytes = 16384;               // K slot: 128 keys x 64 dims; V slot: 32 keys x 256 d
-constexpr uint32_t kVAtomBytes = 32 * 128;           // one 64-d atom of a V slot (32 keys x 128 B)
+constexpr uint32_t kSlotBytes = 32768;               // K slot: 128 keys x 128 dims; V slot: 64 keys x 256 d
+constexpr uint32_t kKAtomBytes = 128 * 128;          // one 64-dim atom of a K slot (128 keys x 128 B)
+constexpr uint32_t kVAtomBytes = 64 * 128;           // one 64-d atom of a V slot (64 keys x 128 B)
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + kKSlots * kSlotBytes;
@@ -233,24 +234,25 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (uint32_t a = 0; a < 4; ++a)
                 tma_load_3d(base + kOffQ + a * kAtomBytesQ, &map_q, bar(kBarQ), int(a * 64), int(head), int(r0));
             // consumption order of the MMA thread: S_0, S_1, P.V_0, S_2, P.V_1, ...
-            auto load_k = [&](uint32_t j) {                 // four 64-dim atoms of key tile j
-                for (uint32_t a = 0; a < 4; ++a) {
-                    const uint32_t n = j * 4u + a, slot = n % kKSlots, use = n / kKSlots;
+            auto load_k = [&](uint32_t j) {                 // two 128-dim halves of key tile j
+                for (uint32_t h = 0; h < 2; ++h) {
+                    const uint32_t n = j * 2u + h, slot = n % kKSlots, use = n / kKSlots;
                     if (use > 0 && !mbar_wait(bar(kBarKEmpty + slot), (use - 1u) & 1u, abort_flag)) return false;
                     mbar_expect_tx(bar(kBarKFull + slot), kSlotBytes);
-                    tma_load_3d(base + kOffK + slot * kSlotBytes, &map_k, bar(kBarKFull + slot), int(a * 64),
-                                int(j * kBN), int(kv));
+                    for (uint32_t a = 0; a < 2; ++a)
+                        tma_load_3d(base + kOffK + slot * kSlotBytes + a * kKAtomBytes, &map_k, bar(kBarKFull + slot),
+                                    int((h * 2u + a) * 64u), int(j * kBN), int(kv));
                 }
                 return true;
             };
-            auto load_v = [&](uint32_t j) {                 // four 32-key groups of key tile j
-                for (uint32_t g = 0; g < 4; ++g) {
-                    const uint32_t n = j * 4u + g, slot = n % kVSlots, use = n / kVSlots;
+            auto load_v = [&](uint32_t j) {                 // two 64-key halves of key tile j
+                for (uint32_t g = 0; g < 2; ++g) {
+                    const uint32_t n = j * 2u + g, slot = n % kVSlots, use = n / kVSlots;
                     if (use > 0 && !mbar_wait(bar(kBarVEmpty + slot), (use - 1u) & 1u, abort_flag)) return false;
                     mbar_expect_tx(bar(kBarVFull + slot), kSlotBytes);
                     for (uint32_t a = 0; a < 4; ++a)
                         tma_load_3d(base + kOffV + slot * kSlotBytes + a * kVAtomBytes, &map_v, bar(kBarVFull + slot),
-                                    int(a * 64), int(j * kBN + g * 32u), int(kv));
+                                    int(a * 64), int(j * kBN + g * 64u), int(kv));
                 }
                 return true;
             };
@@ -270,15 +272,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const uint32_t b = j % kSBufs;
                 // Buffer b held P of tile j-2: its P.V was issued before this point and the
                 // tcgen05.mma instructions of one thread execute in issue order.
-                for (uint32_t a = 0; a < 4; ++a) {
-                    const uint32_t n = j * 4u + a, slot = n % kKSlots;
+                for (uint32_t h = 0; h < 2; ++h) {
+                    const uint32_t n = j * 2u + h, slot = n % kKSlots;
                     if (!mbar_wait(bar(kBarKFull + slot), (n / kKSlots) & 1u, abort_flag)) return false;
                     tc_fence_after();
 #pragma unroll
-                    for (uint32_t q4 = 0; q4 < 4; ++q4) {
-                        const uint64_t ad = smem_desc(base + kOffQ + a * kAtomBytesQ + q4 * 32u, 16, 1024);
-                        const uint64_t bd = smem_desc(base + kOffK + slot * kSlotBytes + q4 * 32u, 16, 1024);
-                        tc_mma(tmem + kColS + b * kBN, ad, bd, idesc_s, (a | q4) ? 1u : 0u);
+                    for (uint32_t ks = 0; ks < 8; ++ks) {
+                        const uint32_t atom = ks >> 2, inner = (ks & 3u) * 32u;
+                        const uint64_t ad = smem_desc(base + kOffQ + (h * 2u + atom) * kAtomBytesQ + inner, 16, 1024);
+                        const uint64_t bd = smem_desc(base + kOffK + slot * kSlotBytes + atom * kKAtomBytes + inner, 16, 1024);
+                        tc_mma(tmem + kColS + b * kBN, ad, bd, idesc_s, (h | ks) ? 1u : 0u);
                     }
                     tc_commit(bar(kBarKEmpty + slot));
                 }
@@ -288,17 +291,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             auto issue_pv = [&](uint32_t i) {
                 const uint32_t b = i % kSBufs;
                 if (!mbar_wait(bar(kBarPFull + b), (i / kSBufs) & 1u, abort_flag)) return false;
-                for (uint32_t g = 0; g < 4; ++g) {
-                    const uint32_t n = i * 4u + g, slot = n % kVSlots;
+                for (uint32_t g = 0; g < 2; ++g) {
+                    const uint32_t n = i * 2u + g, slot = n % kVSlots;
                     if (!mbar_wait(bar(kBarVFull + slot), (n / kVSlots) & 1u, abort_flag)) return false;
                     tc_fence_after();
 #pragma unroll
-                    for (uint32_t h = 0; h < 2; ++h) {
+                    for (uint32_t h = 0; h < 4; ++h) {
                         // A = P [128 x 128] in TMEM: 8 columns per 16-key step.
-                        // B = V slot [32 keys x 256 d] MN-major: atoms of 64 d are kVAtomBytes apart
+                        // B = V slot [64 keys x 256 d] MN-major: atoms of 64 d are kVAtomBytes apart
                         // (leading offset), groups of 8 keys 1024 B apart (stride offset); 16 keys = 2048 B
                         const uint64_t bd = smem_desc(base + kOffV + slot * kSlotBytes + h * 2048u, kVAtomBytes, 1024);
-                        tc_mma_ts(tmem + kColO, tmem + kColS + b * kBN + (g * 2u + h) * 8u, bd, idesc_pv,
+                        tc_mma_ts(tmem + kColO, tmem + kColS + b * kBN + (g * 4u + h) * 8u, bd, idesc_pv,
                                   (i | g | h) ? 1u : 0u);
                     }
                     tc_commit(bar(kBarVEmpty + slot));
@@ -512,7 +515,7 @@ extern "C" tatara_status tatara_attn_prefill(tatara_ctx* ctx, void* stream, cons
     if (!make_map(&map_q, query, kQHeads, rows, kHeadDim * 2ull, uint64_t(kQHeads) * kHeadDim * 2ull, 1, kBM) ||
         // K, V [2][capacity][256], extent clipped to the visible keys so the tail reads as zero
         !make_map(&map_k, keys, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, kBN, 1) ||
-        !make_map(&map_v, values, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, 32, 1))
+        !make_map(&map_v, values, visible, kKvHeads, kHeadDim * 2ull, uint64_t(capacity) * kHeadDim * 2ull, 64, 1))
         return fail(ctx, TATARA_CUDA_ERROR, "attn_prefill: tensor map encoding failed");
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
