@@ -153,6 +153,7 @@ def main():
                     help="run one workload only (small profiling runs)")
     ap.add_argument("--context", type=int, default=HEADLINE_CONTEXT)
     ap.add_argument("--rows", type=int, default=PREFILL_ROWS)
+    ap.add_argument("--lanes", type=int, default=4, help="lanes of --only gdn_step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -276,6 +277,7 @@ def main():
         extra["decode_sweep"] = sweep
         extra["lanes32"] = wl.lanes32(timed, steps, warmup)
         extra["gdn_step"] = wl.gdn_step(timed, steps, warmup)
+        extra["gdn_step_lanes32"] = wl.gdn_step(timed, steps, warmup, n=32)
         extra["gdn_prefill"] = wl.gdn_prefill(timed)
         extra["prefill_attn"] = wl.prefill(timed, peaks, sampler=ClockSampler(local))
     else:

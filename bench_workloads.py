@@ -334,7 +334,7 @@ class Workloads:
             return {"workload": f"decode_attn_ctx{args.context}", "us": ms * 1e3, "replicas": d.replicas,
                     "gbs": (args.context * 2048 + 24576) / (ms * 1e-3) / 1e9}
         if which == "gdn_step":
-            return self.gdn_step(timed, steps, warmup)
+            return self.gdn_step(timed, steps, warmup, n=args.lanes)
         if which == "lanes32":
             return self.lanes32(timed, steps, warmup)
         if which == "gdn_prefill":

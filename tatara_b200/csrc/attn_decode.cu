@@ -365,14 +365,19 @@ __device__ __forceinline__ unsigned long long combine_now_ns() {
     return t;
 }
 
-// One CTA per (head, 64-dim quarter, lane): 32 warps, warp w merges records w, w+32, ... (four
-// in flight per thread), lane owns a float2 of the quarter; then the 32 warp partials are summed
-// in warp order.  Every order is fixed by nparts alone.
-constexpr uint32_t kCombineThreads = 1024, kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
+// One CTA per (head, 64-dim quarter, lane).  The merge is defined over 32 phases: phase f sums
+// records f, f+32, ... in index order (four in flight per thread), a thread owns a float2 of the
+// quarter; then the 32 phase partials are summed in phase order.  Every order is fixed by nparts
+// alone, whatever the CTA size: a single lane runs one phase per warp (32 warps, lowest
+// latency), a batch runs four phases per warp (8 warps, many small CTAs per SM).
+constexpr uint32_t kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
+template <uint32_t N>
+constexpr uint32_t combine_warps() { return N == 1 ? 32u : 8u; }
 
 template <uint32_t N>
-__global__ void __launch_bounds__(kCombineThreads)
+__global__ void __launch_bounds__(combine_warps<N>() * 32u)
 attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
+    constexpr uint32_t kWarps = combine_warps<N>(), kCombineThreads = kWarps * 32u;
     __shared__ float red_max[kCombinePhases];
     __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
     // When launched as a programmatic dependent of the partition kernel: wait for its records.
@@ -407,7 +412,7 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     }
     const CombineLane& cl = p.lane[blockIdx.y];
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
-    const uint32_t lane = threadIdx.x & 31u, phase = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride;
     const uint32_t nparts = cl.nparts;
     float big = -INFINITY;
@@ -415,37 +420,52 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
         big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
 #pragma unroll
     for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-    if (lane == 0) red_max[phase] = big;
+    if (lane == 0) red_max[warp] = big;
     __syncthreads();
     big = red_max[0];
 #pragma unroll
-    for (uint32_t i = 1; i < kCombinePhases; ++i) big = fmaxf(big, red_max[i]);
+    for (uint32_t i = 1; i < kWarps; ++i) big = fmaxf(big, red_max[i]);
 
     const uint32_t d = quarter * kCombineDims + lane * 2u;
-    float a0 = 0.0f, a1 = 0.0f, denom = 0.0f;
-    for (uint32_t first = phase; first < nparts; first += kCombinePhases * kCombineUnroll) {
-        float lm[kCombineUnroll], ls[kCombineUnroll];
-        float2 v[kCombineUnroll];
+    // Thread state: one accumulator set per phase this warp owns; all of a round's record loads
+    // (phases x unroll) are issued before the first use.
+    constexpr uint32_t kOwn = kCombinePhases / kWarps;
+    float a0[kOwn], a1[kOwn], denom[kOwn];
 #pragma unroll
-        for (uint32_t u = 0; u < kCombineUnroll; ++u) {
-            const uint32_t part = first + u * kCombinePhases;
-            const bool live = part < nparts;
-            const float* rec = base + (live ? part : first) * cl.part_stride;
-            lm[u] = live ? rec[kHeadDim] : -INFINITY;
-            ls[u] = rec[kHeadDim + 1u];
-            v[u] = *reinterpret_cast<const float2*>(rec + d);
+    for (uint32_t j = 0; j < kOwn; ++j) a0[j] = a1[j] = denom[j] = 0.0f;
+    for (uint32_t round = 0; round < nparts; round += kCombinePhases * kCombineUnroll) {
+        float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
+        float2 v[kOwn][kCombineUnroll];
+#pragma unroll
+        for (uint32_t j = 0; j < kOwn; ++j) {
+#pragma unroll
+            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+                const uint32_t part = round + (warp + j * kWarps) + u * kCombinePhases;
+                const bool live = part < nparts;
+                const float* rec = base + (live ? part : 0u) * cl.part_stride;
+                lm[j][u] = live ? rec[kHeadDim] : -INFINITY;
+                ls[j][u] = rec[kHeadDim + 1u];
+                v[j][u] = *reinterpret_cast<const float2*>(rec + d);
+            }
         }
 #pragma unroll
-        for (uint32_t u = 0; u < kCombineUnroll; ++u) {
-            const float w = lm[u] == -INFINITY ? 0.0f : expf(lm[u] - big);
-            a0 = fmaf(w, v[u].x, a0);
-            a1 = fmaf(w, v[u].y, a1);
-            denom = fmaf(w, ls[u], denom);
+        for (uint32_t j = 0; j < kOwn; ++j) {
+#pragma unroll
+            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+                const float w = lm[j][u] == -INFINITY ? 0.0f : expf(lm[j][u] - big);
+                a0[j] = fmaf(w, v[j][u].x, a0[j]);
+                a1[j] = fmaf(w, v[j][u].y, a1[j]);
+                denom[j] = fmaf(w, ls[j][u], denom[j]);
+            }
         }
     }
-    red_acc[phase][lane * 2u] = a0;
-    red_acc[phase][lane * 2u + 1u] = a1;
-    if (lane == 0) red_acc[phase][kCombineDims] = denom;
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j) {
+        const uint32_t phase = warp + j * kWarps;
+        red_acc[phase][lane * 2u] = a0[j];
+        red_acc[phase][lane * 2u + 1u] = a1[j];
+        if (lane == 0) red_acc[phase][kCombineDims] = denom[j];
+    }
     __syncthreads();
     if (threadIdx.x < kCombineDims + 1u) {
         float total = 0.0f;
@@ -582,7 +602,7 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     tatara_status st = check_launch(ctx, what);
     if (st != TATARA_OK) return st;
     cfg.gridDim = dim3(kQHeads * 4, n_lanes);
-    cfg.blockDim = dim3(kCombineThreads);
+    cfg.blockDim = dim3(combine_warps<N>() * 32u);
     cfg.dynamicSmemBytes = 0;
     (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp);
     return check_launch(ctx, what);
@@ -677,7 +697,7 @@ extern "C" tatara_status tatara_attn_combine(tatara_ctx* ctx, void* stream, cons
     cp.record_out = nullptr;
     cp.query_stride = kQHeads * kHeadDim;
     cp.lane[0] = CombineLane{static_cast<const float*>(records), head_stride, part_stride, nparts, 0};
-    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(cp);
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), combine_warps<1>() * 32u, 0, static_cast<cudaStream_t>(stream)>>>(cp);
     return check_launch(ctx, "attn_combine");
 }
 
@@ -793,7 +813,7 @@ extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream
     const uint32_t grid = dp.total_items < uint32_t(setup.sm_count) ? dp.total_items : uint32_t(setup.sm_count);
     auto s = static_cast<cudaStream_t>(stream);
     attn_decode_partition_kernel<1><<<grid, kDecThreads, kDecSmemBytes, s>>>(dp);
-    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, s>>>(cp);
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), combine_warps<1>() * 32u, 0, s>>>(cp);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return fail(ctx, TATARA_CUDA_ERROR, cudaGetErrorString(err));
     if (ctx != nullptr) ctx->launches += 2;
@@ -892,6 +912,6 @@ extern "C" tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream,
     cp.px.world = world;
     cp.px.epoch = epoch;
     cp.px.wait_limit_us = wait_limit_us;
-    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), kCombineThreads, 0, static_cast<cudaStream_t>(stream)>>>(cp);
+    attn_combine_kernel<1><<<dim3(kQHeads * 4, 1), combine_warps<1>() * 32u, 0, static_cast<cudaStream_t>(stream)>>>(cp);
     return check_launch(ctx, "attn_combine_wait");
 }
