@@ -264,6 +264,53 @@ class Workloads:
                 "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
                 "l2": "Q/gate/out 402 MB > L2"}
 
+    # ---- the projections on either side of the layers (affine Q4, group 64)
+    def project(self, timed, peaks, steps, warmup, rows=16384):
+        """Exact-row policy at decode sizes (1, 4, 16 rows; bound by the Q4 weight stream, then by FMA rate)
+        and tensor-unit policy at the prefill size, for the three call sites of the model."""
+        torch = self.torch
+        g = torch.Generator(device="cuda").manual_seed(13)
+        bf = torch.bfloat16
+        sites = {"attn_project": ((8192, 512, 512), 2048), "gdn_project": ((8192, 4096, 32, 32), 2048),
+                 "out_projection": ((2048,), 4096)}
+        out = {}
+        for name, (sizes, k) in sites.items():
+            n = sum(sizes)
+            wbytes = n * k // 2 + 2 * n * (k // 64) * 2
+            reps = replicas_for(wbytes)
+            sets = []
+            for _ in range(reps):
+                held = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (m, k // 8), generator=g, device="cuda", dtype=torch.int32),
+                         (0.35 * 0.32 / k ** 0.5 * (1 + 0.2 * (2 * torch.rand((m, k // 64), generator=g, device="cuda") - 1))).to(bf),
+                         (-0.35 * 2.4 / k ** 0.5 * (1 + 0.1 * torch.randn((m, k // 64), generator=g, device="cuda"))).to(bf))
+                        for m in sizes]
+                sets.append((held, tb.Context.q4_matrices(held)))
+            res = {"n": n, "k": k, "q4_weight_bytes": wbytes}
+            for r in (1, 4, 16):
+                x = torch.randn((r, k), generator=g, device="cuda").to(bf)
+                y = torch.zeros((r, n), dtype=bf, device="cuda")
+                ms = timed(lambda i=0: self.ctx.q4_project(x, sets[i % reps][1], k, y), max(steps, 2 * reps), max(warmup, reps))
+                res[f"exact_rows{r}"] = {"us": ms * 1e3, "weight_gbs": wbytes / (ms * 1e-3) / 1e9,
+                                         "gflops": 2.0 * r * n * k / (ms * 1e-3) / 1e9}
+            # tensor-unit policy: dequantise once (load-time step, timed separately), then the GEMM
+            w = torch.zeros((n, k), dtype=bf, device="cuda")
+            ms = timed(lambda i=0: self.ctx.q4_dequantize(sets[0][1], k, w), 5, 3)
+            res["dequantize_us"] = ms * 1e3
+            x = torch.randn((rows, k), generator=g, device="cuda").to(bf)
+            y = torch.zeros((rows, n), dtype=bf, device="cuda")
+            try:
+                ms = timed(lambda i=0: self.ctx.project_dense(x, w, y), 5, 3)
+                tf = 2.0 * rows * n * k / (ms * 1e-3) / 1e12
+                res[f"dense_rows{rows}"] = {"ms": ms, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                                            "bytes": 2 * (rows * k + n * k + rows * n)}
+            except tb.TataraError as e:
+                res[f"dense_rows{rows}"] = {"unavailable": str(e)}
+            del sets, x, y, w
+            torch.cuda.empty_cache()
+            out[name] = res
+        out["l2"] = "exact-row: rotating weight sets (> 2x L2 between reuse); dense: input + output > L2"
+        return out
+
     # ---- config 4a: one lane at 262144 split along KV over the ranks, LSE merge over NCCL
     def split_kv(self, dist, n_keys, timed, steps, warmup):
         torch = self.torch
@@ -339,6 +386,8 @@ class Workloads:
             return self.lanes32(timed, steps, warmup)
         if which == "gdn_prefill":
             return self.gdn_prefill(timed, rows=args.rows)
+        if which == "project":
+            return self.project(timed, measured_peaks(), steps, warmup, rows=args.rows)
         if which == "prefill":
             return self.prefill(timed, measured_peaks(), rows=args.rows, steps=steps)
         raise ValueError(which)

@@ -255,6 +255,52 @@ tatara_status tatara_gdn_prefill(tatara_ctx* ctx, void* stream, const void* qk, 
                                  void* scratch, uint64_t scratch_bytes);
 uint64_t tatara_gdn_prefill_scratch_bytes(uint32_t rows);
 
+/* ---- affine-Q4 projections on either side of the layers --------------------------------
+ * The step before attn_qk_rope / gdn_prepare (hidden row -> projection row) and the step
+ * after the gated output (attended / gated row -> hidden row).  Weights keep the reference's
+ * layout: words [rows][k/8] u32 with nibble j of word w = column 8w + j, scales and biases
+ * [rows][k/64] bf16 (group of 64 columns), w = q * scale + bias. */
+typedef struct tatara_q4_matrix {
+    const void* words;
+    const void* scales;
+    const void* biases;
+    uint32_t rows; /* output columns this matrix contributes; a multiple of 16 */
+    uint32_t reserved;
+} tatara_q4_matrix;
+
+/* Exact-row policy.  out[r][c] = bf16(q4_dot(input[r], row c)) with the reference's per-row
+ * arithmetic sequence (q4_dot.metal:9-42; fused multiply-add chains, adjacent-pairs 32-lane
+ * tree), so a row's bits do not depend on how many rows share the call: the row-batched and
+ * block forms of the reference keep the same property (q4_dot.metal:44-104,
+ * prefill_dense.metal:1-49).  The matrices' output columns are concatenated in order:
+ *   attn_project  (attention.metal:1-41;  decode_step.cpp:705-711, prefill_step.cpp:1428):
+ *                 {query+gate 8192, key 512, value 512}, k = 2048 -> projection[9216]
+ *   gdn_project   (gdn.metal:1-46;        decode_step.cpp:657-664, prefill_step.cpp:1909-1915):
+ *                 {qkv 8192, z 4096, b 32, a 32}, k = 2048 -> projection[12352]
+ *   out_projection (gdn.metal:209-226;    decode_step.cpp:698-702, 732-736): one matrix of
+ *                 2048 rows, k = 4096.
+ * input [n_rows][input_stride] bf16, out [n_rows][out_stride] bf16 (strides in elements);
+ * k a multiple of 512 and at most 6144 (four staged rows fit the default shared memory), at most
+ * 4 matrices. */
+tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const void* input,
+                                uint64_t input_stride, uint32_t n_rows,
+                                const tatara_q4_matrix* matrices, uint32_t n_matrices, uint32_t k,
+                                void* out, uint64_t out_stride);
+
+/* Tensor-unit policy (the reference's QuantizedGemmPolicy::NativeDenseMma,
+ * native_dense_qgemm.metal; prefill_step.cpp:1867-1907): weights are dequantised once to
+ * bf16(q * scale + bias), [sum of rows][k], and block projections run as a bf16 GEMM with f32
+ * accumulation on the tensor cores.  tatara_q4_dequantize is a load-time step; the result is
+ * reused by every tatara_project_dense call. */
+tatara_status tatara_q4_dequantize(tatara_ctx* ctx, void* stream, const tatara_q4_matrix* matrices,
+                                   uint32_t n_matrices, uint32_t k, void* weights);
+/* out[r][c] = bf16(sum_k input[r][k] * weights[c][k]); input [n_rows][input_stride], weights
+ * [n][k] bf16, out [n_rows][out_stride].  k a multiple of 64, n a multiple of 32, strides
+ * multiples of 8 elements, buffers 16-byte aligned. */
+tatara_status tatara_project_dense(tatara_ctx* ctx, void* stream, const void* input,
+                                   uint64_t input_stride, uint32_t n_rows, const void* weights,
+                                   uint32_t n, uint32_t k, void* out, uint64_t out_stride);
+
 #ifdef __cplusplus
 }
 #endif

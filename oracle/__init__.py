@@ -65,6 +65,7 @@ def lib() -> ctypes.CDLL:
         _lib.orc_rope_divisor.restype = ctypes.c_float
         _lib.orc_bf16_from_f32.argtypes = [ctypes.c_float]
         _lib.orc_bf16_from_f32.restype = ctypes.c_uint16
+        _lib.orc_q4_dot.restype = ctypes.c_float
     return _lib
 
 
@@ -171,6 +172,45 @@ def gdn_gate_norm(y, z, weight):
     return out
 
 
+def _u32a(a):
+    assert a.dtype == np.uint32
+    return _p(a, ctypes.POINTER(ctypes.c_uint32))
+
+
+def q4_dot(x, words, scales, biases, fused=True) -> float:
+    """One affine-Q4 output row over x[k]: words [k/8] u32, scales/biases [k/64] bf16 bits."""
+    return float(lib().orc_q4_dot(_u16(x), _u32a(words), _u16(scales), _u16(biases), _u32(x.shape[0]),
+                                  _int(1 if fused else 0)))
+
+
+def q4_project(x, words, scales, biases, fused=True, threads=1):
+    """Exact-row projection of x [rows][k] through one Q4 matrix (words [n][k/8]) -> bf16 [rows][n]."""
+    rows, k = x.shape
+    n = words.shape[0]
+    out = np.zeros((rows, n), np.uint16)
+    lib().orc_q4_project(_u16(x), _u32(k), _u32(rows), _u32a(words), _u16(scales), _u16(biases), _u32(n),
+                         _u32(k), _u16(out), _u32(n), _int(1 if fused else 0), _int(threads))
+    return out
+
+
+def q4_dequantize(words, scales, biases):
+    """bf16(q*scale + bias) weights [n][k] of the tensor-unit policy."""
+    n, k = words.shape[0], words.shape[1] * 8
+    out = np.zeros((n, k), np.uint16)
+    lib().orc_q4_dequantize(_u32a(words), _u16(scales), _u16(biases), _u32(n), _u32(k), _u16(out))
+    return out
+
+
+def project_dense(x, weights, threads=1):
+    """bf16 x [rows][k] times bf16 weights [n][k], f32 accumulation in k order -> bf16 [rows][n]."""
+    rows, k = x.shape
+    n = weights.shape[0]
+    out = np.zeros((rows, n), np.uint16)
+    lib().orc_project_dense(_u16(x), _u32(k), _u32(rows), _u16(weights), _u32(n), _u32(k), _u16(out), _u32(n),
+                            _int(threads))
+    return out
+
+
 # ---------------------------------------------------------------- reference CPU model
 _ref = None
 
@@ -185,6 +225,12 @@ def ref() -> ctypes.CDLL:
     if _ref is None:
         _ref = ctypes.CDLL(_REF_PATH)
     return _ref
+
+
+def ref_q4_dot(x, words, scales, biases, fused=True) -> float:
+    f = ref().ref_q4_dot
+    f.restype = ctypes.c_float
+    return float(f(_u16(x), _u32a(words), _u16(scales), _u16(biases), _u32(x.shape[0]), _int(1 if fused else 0)))
 
 
 def ref_attn_qk_rope(projection, q_weight, k_weight, keys, values, position, capacity):

@@ -158,4 +158,11 @@ void ref_gdn_gate_norm(const u16* y, const u16* z, const u16* weight, u16* out) 
                             {out, 4096});
 }
 
+// q4_dot_reference with the adjacent-pairs tree; `fused` picks the chain order.
+float ref_q4_dot(const u16* x, const u32* words, const u16* scales, const u16* biases, u32 k,
+                 int fused) {
+    return q4_dot_reference({x, k}, {words, k / 8}, {scales, k / 64}, {biases, k / 64}, k, kTree,
+                            fused ? ChainOrder::Fused : ChainOrder::Separate);
+}
+
 } // extern "C"

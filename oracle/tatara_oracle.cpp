@@ -186,6 +186,65 @@ inline u16 gated_output(float acc, float denom, u16 gate) {
     return ftzb(bf16r(ftz(value * sig)));
 }
 
+// Affine Q4, group 64, one output row (q4_dot.metal:9-42; CPU model
+// kernel_reference.cpp:388-442).  Lane l of 32 owns 16 consecutive inputs of every
+// 512-column block; nibbles are taken in place with masks and the inputs are
+// pre-divided by the nibble's place value; per block the lane adds
+// scale*quant + sum*bias; the 32 lane results go through the adjacent-pairs tree.
+// `fused` selects the reference model's ChainOrder::Fused (fma chains) or
+// ChainOrder::Separate (each product and sum rounded).
+float q4_dot(const u16* x, const u16* packed, const u16* scales, const u16* biases, u32 k_size,
+             bool fused) {
+    float lanes[32];
+    for (u32 lane = 0; lane < 32; ++lane) {
+        float result = 0.0f;
+        for (u32 k = 0; k < k_size; k += 512) {
+            const u32 x0 = k + lane * 16;
+            float xv[16];
+            float sum = 0.0f;
+            for (u32 i = 0; i < 16; i += 4) {
+                const float a0 = bf(x[x0 + i]), a1 = bf(x[x0 + i + 1]);
+                const float a2 = bf(x[x0 + i + 2]), a3 = bf(x[x0 + i + 3]);
+                sum = ftz(sum + ftz(ftz(a0 + a1) + a2 + a3));
+                xv[i] = a0;
+                xv[i + 1] = a1 / 16.0f;
+                xv[i + 2] = a2 / 256.0f;
+                xv[i + 3] = a3 / 4096.0f;
+            }
+            float quant = 0.0f;
+            const u32 word0 = (k >> 2) + lane * 4;
+            for (u32 i = 0; i < 4; ++i) {
+                const u16 word = packed[word0 + i];
+                const float w0 = static_cast<float>(word & 0x000Fu), w1 = static_cast<float>(word & 0x00F0u);
+                const float w2 = static_cast<float>(word & 0x0F00u), w3 = static_cast<float>(word & 0xF000u);
+                if (fused) {
+                    quant = std::fma(xv[i * 4 + 3], w3,
+                                     std::fma(xv[i * 4 + 2], w2,
+                                              std::fma(xv[i * 4 + 1], w1, std::fma(xv[i * 4], w0, quant))));
+                } else {
+                    const float t0 = xv[i * 4] * w0, t1 = xv[i * 4 + 1] * w1;
+                    const float t2 = xv[i * 4 + 2] * w2, t3 = xv[i * 4 + 3] * w3;
+                    quant = quant + (((t0 + t1) + t2) + t3);
+                }
+            }
+            const u32 group = (k >> 6) + (lane >> 2);
+            const float scale = bf(scales[group]), bias = bf(biases[group]);
+            if (fused) result = std::fma(sum, bias, std::fma(scale, quant, result));
+            else result = result + (scale * quant + sum * bias);
+        }
+        lanes[lane] = result;
+    }
+    return pairs_sum(lanes, 32);
+}
+
+// bf16(q*scale + bias) of one weight, the staging step of the reference's tensor-unit
+// projection policy (native_dense_qgemm.metal, "weight_tile[...] = bfloat(float(quantized) *
+// affine_scale + affine_bias)"); nibble j of a 32-bit word is column 8*word + j.
+inline u16 q4_weight_bf16(const u32* words, const u16* scales, const u16* biases, u32 k) {
+    const u32 q = (words[k >> 3] >> (4u * (k & 7u))) & 15u;
+    return bf16r(std::fma(static_cast<float>(q), bf(scales[k >> 6]), bf(biases[k >> 6])));
+}
+
 } // namespace
 
 extern "C" {
@@ -466,6 +525,57 @@ void orc_gdn_gate_norm(const u16* y, const u16* z, const u16* weight, u16* out, 
                 out[base + i] = ftzb(bf16r(ftz(ftz(g * sigmoid_f32(g)) * bf(weighted))));
             }
         }
+}
+
+// ---- affine-Q4 projections on either side of the layers -------------------------------
+// One matrix of `n` output rows: words [n][k/8] u32, scales/biases [n][k/64] bf16.
+
+float orc_q4_dot(const u16* x, const u32* words, const u16* scales, const u16* biases, u32 k,
+                 int fused) {
+    return q4_dot(x, reinterpret_cast<const u16*>(words), scales, biases, k, fused != 0);
+}
+
+// Exact-row policy: out[r*out_stride + col] = bf16(q4_dot(x[r], row col)) for every input row r
+// (attn_project attention.metal:1-41, gdn_project gdn.metal:1-46, gdn_outproj gdn.metal:209-226 and
+// their row-batched / block forms, which keep each row's sequence: q4_dot.metal:44-104,
+// prefill_dense.metal:1-49).
+void orc_q4_project(const u16* x, u32 x_stride, u32 rows, const u32* words, const u16* scales,
+                    const u16* biases, u32 n, u32 k, u16* out, u32 out_stride, int fused,
+                    int threads) {
+    parallel_for(n, threads, [&](u32 col) {
+        const u16* packed = reinterpret_cast<const u16*>(words + static_cast<u64>(col) * (k / 8));
+        const u16* sc = scales + static_cast<u64>(col) * (k / 64);
+        const u16* bi = biases + static_cast<u64>(col) * (k / 64);
+        for (u32 r = 0; r < rows; ++r)
+            out[static_cast<u64>(r) * out_stride + col] =
+                bf16r(q4_dot(x + static_cast<u64>(r) * x_stride, packed, sc, bi, k, fused != 0));
+    });
+}
+
+// Dequantised bf16 weights [n][k] of the tensor-unit policy.
+void orc_q4_dequantize(const u32* words, const u16* scales, const u16* biases, u32 n, u32 k,
+                       u16* weights) {
+    for (u32 col = 0; col < n; ++col)
+        for (u32 i = 0; i < k; ++i)
+            weights[static_cast<u64>(col) * k + i] =
+                q4_weight_bf16(words + static_cast<u64>(col) * (k / 8), scales + static_cast<u64>(col) * (k / 64),
+                               biases + static_cast<u64>(col) * (k / 64), i);
+}
+
+// Tensor-unit policy: out = bf16(sum_k x[r][k] * w_bf16[col][k]), f32 accumulation in k order
+// (native_dense_qgemm.metal: bf16 operands, float accumulators, bf16 store).  The accumulation
+// order of a matrix unit is not specified, so this is a tolerance oracle, not a bit oracle.
+void orc_project_dense(const u16* x, u32 x_stride, u32 rows, const u16* weights, u32 n, u32 k,
+                       u16* out, u32 out_stride, int threads) {
+    parallel_for(n, threads, [&](u32 col) {
+        const u16* w = weights + static_cast<u64>(col) * k;
+        for (u32 r = 0; r < rows; ++r) {
+            const u16* xr = x + static_cast<u64>(r) * x_stride;
+            float acc = 0.0f;
+            for (u32 i = 0; i < k; ++i) acc = std::fma(bf(xr[i]), bf(w[i]), acc);
+            out[static_cast<u64>(r) * out_stride + col] = bf16r(acc);
+        }
+    });
 }
 
 } // extern "C"

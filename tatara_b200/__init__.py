@@ -35,6 +35,11 @@ class AttnLane(ctypes.Structure):
     _fields_ = [("kv_offset", ctypes.c_uint64), ("context", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
+class Q4Matrix(ctypes.Structure):
+    _fields_ = [("words", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("biases", ctypes.c_void_p),
+                ("rows", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
+
+
 class GdnLane(ctypes.Structure):
     _fields_ = [("conv_in", ctypes.c_uint64), ("conv_out", ctypes.c_uint64),
                 ("rec_in", ctypes.c_uint64), ("rec_out", ctypes.c_uint64)]
@@ -265,6 +270,32 @@ class Context:
                                              _ptr(decay), _ptr(beta), _ptr(state_in), _ptr(y),
                                              _ptr(state_out), _u32(rows), _u32(chunk), _ptr(scratch),
                                              _u64(nbytes)))
+
+    # ---- affine-Q4 projections
+    @staticmethod
+    def q4_matrices(triples):
+        """(words [n][k/8] int32, scales [n][k/64] bf16, biases) device tensors -> tatara_q4_matrix[]."""
+        arr = (Q4Matrix * len(triples))()
+        for i, (w, s, b) in enumerate(triples):
+            arr[i] = Q4Matrix(w.data_ptr(), s.data_ptr(), b.data_ptr(), w.shape[0], 0)
+        return arr
+
+    def q4_project(self, x, matrices, k, out, n_rows=None, x_stride=None, out_stride=None, stream=None):
+        n_rows = x.shape[0] if n_rows is None else n_rows
+        self._check(lib().tatara_q4_project(
+            self._h, self._stream(stream), _ptr(x), _u64(x.stride(0) if x_stride is None else x_stride),
+            _u32(n_rows), matrices, _u32(len(matrices)), _u32(k), _ptr(out),
+            _u64(out.stride(0) if out_stride is None else out_stride)))
+
+    def q4_dequantize(self, matrices, k, weights, stream=None):
+        self._check(lib().tatara_q4_dequantize(self._h, self._stream(stream), matrices, _u32(len(matrices)),
+                                               _u32(k), _ptr(weights)))
+
+    def project_dense(self, x, weights, out, n_rows=None, stream=None):
+        n_rows = x.shape[0] if n_rows is None else n_rows
+        self._check(lib().tatara_project_dense(
+            self._h, self._stream(stream), _ptr(x), _u64(x.stride(0)), _u32(n_rows), _ptr(weights),
+            _u32(weights.shape[0]), _u32(weights.shape[1]), _ptr(out), _u64(out.stride(0))))
 
 
 def gdn_prefill_scratch_bytes(rows: int) -> int:

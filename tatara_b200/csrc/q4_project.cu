@@ -1,0 +1,509 @@
+// Affine-Q4 (group 64) projections on either side of the attention / Gated DeltaNet layers:
+// hidden row -> projection row (attn_project, gdn_project) and gated row -> hidden row
+// (out_projection).  Two policies, as in the reference:
+//
+//   exact row   q4_project_kernel: the reference's per-row sequence (q4_dot.metal:9-42) on CUDA
+//               cores, one warp per output column; lane l owns 16 consecutive inputs of each
+//               512-column block, nibbles are used in place (mask, no shift) against inputs
+//               pre-divided by the nibble's place value, fused multiply-add chains, one
+//               adjacent-pairs tree at the end.  A row's bits are the same for any batch size.
+//               Bound by the Q4 weight stream (0.5 B per weight) for a few rows, by FMA rate
+//               beyond about four rows.
+//   tensor unit q4_dequant_kernel once at load time (bf16(q*scale + bias), the staging step of
+//               native_dense_qgemm.metal), then dense_project_kernel: a bf16 GEMM with f32
+//               accumulation on tcgen05 -- TMA-fed 4-stage ring of 128x64 (input) and 256x64
+//               (weight) swizzled tiles, 128x256 accumulators double-buffered in tensor memory so
+//               that the epilogue of one tile overlaps the MMAs of the next, persistent CTAs.
+#include "tc05.cuh"
+
+namespace tb {
+
+// =========================================================================================
+// exact-row policy
+// =========================================================================================
+constexpr uint32_t kQ4MaxMats = 4;
+constexpr uint32_t kQ4Warps = 8;
+
+struct Q4Mat {
+    const uint2* words;            // [rows][k/16] (8 bytes = one lane's 16 nibbles of a block)
+    const __nv_bfloat16* scales;   // [rows][k/64]
+    const __nv_bfloat16* biases;
+    uint32_t col_begin, col_end;
+};
+struct Q4Params {
+    const __nv_bfloat16* x;
+    __nv_bfloat16* out;
+    uint64_t x_stride, out_stride;
+    uint32_t n_rows, k, n_cols, n_mats;
+    Q4Mat mat[kQ4MaxMats];
+};
+
+// float(v) for an integer 0 <= v < 2^23 without a conversion instruction
+__device__ __forceinline__ float small_int_to_float(uint32_t v) {
+    return __uint_as_float(v | 0x4B000000u) - 8388608.0f;
+}
+
+// R input rows and C output columns per warp pass.  A CTA stages its R input rows in shared
+// memory once; each warp then walks a flat sequence of (column group, 512-column block) items
+// in one rolled loop (a decode call runs a warp through a handful of items only, so a long
+// unrolled body would spend the kernel fetching instructions) and requests the next item's
+// words and affine constants two items ahead of the arithmetic, across group boundaries too.
+template <int R, int C>
+__global__ void __launch_bounds__(kQ4Warps * 32) q4_project_kernel(const __grid_constant__ Q4Params p) {
+    extern __shared__ uint4 xs[];   // [R][k/8]: row r, 8 inputs per uint4
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row0 = blockIdx.y * R;
+    const uint32_t blocks = p.k >> 9, wpr = p.k >> 4, gpr = p.k >> 6, xpr = p.k >> 3;
+    // Launched as a programmatic dependent of its predecessor in the stream: the weights do not
+    // depend on it, so the first two items are requested at once; the input rows (and the output)
+    // are touched only after griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t n_groups = p.n_cols / C;
+    const uint32_t nwarps = gridDim.x * kQ4Warps;
+    uint32_t g = blockIdx.x * kQ4Warps + (threadIdx.x >> 5);   // group being computed
+
+    // fetch cursor: one item ahead of the arithmetic
+    const uint2* fw;
+    const unsigned short *fs, *fb;
+    uint32_t fg = g, fblock = 0;
+    auto locate = [&](uint32_t group) {
+        const uint32_t col0 = group * C;
+        uint32_t m = 0;
+        while (m + 1u < p.n_mats && col0 >= p.mat[m].col_end) ++m;
+        const uint32_t local = col0 - p.mat[m].col_begin;
+        fw = p.mat[m].words + uint64_t(local) * wpr + lane;
+        fs = reinterpret_cast<const unsigned short*>(p.mat[m].scales) + uint64_t(local) * gpr + (lane >> 2);
+        fb = reinterpret_cast<const unsigned short*>(p.mat[m].biases) + uint64_t(local) * gpr + (lane >> 2);
+    };
+    uint2 wd[C], wn[C], wf[C];                 // current item, next, the one after
+    uint32_t sd[C], bd[C], sn[C], bn[C], sf[C], bf_[C];
+    auto fetch = [&](uint2* w, uint32_t* s, uint32_t* b) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            w[c] = __ldg(fw + uint64_t(c) * wpr + fblock * 32u);
+            s[c] = __ldg(fs + uint64_t(c) * gpr + fblock * 8u);
+            b[c] = __ldg(fb + uint64_t(c) * gpr + fblock * 8u);
+        }
+        if (++fblock == blocks) {
+            fblock = 0;
+            fg += nwarps;
+            if (fg < n_groups) locate(fg);
+        }
+    };
+    if (g < n_groups) {
+        locate(fg);
+        fetch(wd, sd, bd);
+        if (fg < n_groups) fetch(wn, sn, bn);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t i = threadIdx.x; i < R * xpr; i += kQ4Warps * 32u) {
+        const uint32_t r = i / xpr, j = i - r * xpr;
+        const uint32_t row = min(row0 + r, p.n_rows - 1u);
+        xs[i] = *(reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride) + j);
+    }
+    __syncthreads();
+
+    float result[R][C];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < C; ++c) result[r][c] = 0.0f;
+    uint32_t b = 0;
+#pragma unroll 1
+    while (g < n_groups) {
+        if (fg < n_groups) fetch(wf, sf, bf_);
+        float xv[R][16], sum[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint4 v0 = xs[r * xpr + b * 64u + lane * 2u], v1 = xs[r * xpr + b * 64u + lane * 2u + 1u];
+            const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float a0 = __uint_as_float(raw[2 * i] << 16), a1 = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
+                const float a2 = __uint_as_float(raw[2 * i + 1] << 16), a3 = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
+                s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
+                xv[r][4 * i] = a0;
+                xv[r][4 * i + 1] = __fmul_rn(a1, 0.0625f);           // exact: a1 / 16
+                xv[r][4 * i + 2] = __fmul_rn(a2, 0.00390625f);       // a2 / 256
+                xv[r][4 * i + 3] = __fmul_rn(a3, 0.000244140625f);   // a3 / 4096
+            }
+            sum[r] = s;
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const uint32_t half[4] = {wd[c].x & 0xFFFFu, wd[c].x >> 16, wd[c].y & 0xFFFFu, wd[c].y >> 16};
+            const float scale = __uint_as_float(sd[c] << 16), bias = __uint_as_float(bd[c] << 16);
+            float wq[16];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                wq[4 * i] = small_int_to_float(half[i] & 0x000Fu);
+                wq[4 * i + 1] = small_int_to_float(half[i] & 0x00F0u);
+                wq[4 * i + 2] = small_int_to_float(half[i] & 0x0F00u);
+                wq[4 * i + 3] = small_int_to_float(half[i] & 0xF000u);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float quant = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    quant = __fmaf_rn(xv[r][4 * i + 3], wq[4 * i + 3],
+                                      __fmaf_rn(xv[r][4 * i + 2], wq[4 * i + 2],
+                                                __fmaf_rn(xv[r][4 * i + 1], wq[4 * i + 1],
+                                                          __fmaf_rn(xv[r][4 * i], wq[4 * i], quant))));
+                result[r][c] = __fmaf_rn(sum[r], bias, __fmaf_rn(scale, quant, result[r][c]));
+            }
+        }
+        if (++b == blocks) {
+            // adjacent-pairs tree per (row, column); lane c keeps column c and stores it
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float keep = 0.0f;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    const float total = warp_sum(result[r][c]);
+                    if (lane == uint32_t(c)) keep = total;
+                    result[r][c] = 0.0f;
+                }
+                if (lane < uint32_t(C) && row0 + uint32_t(r) < p.n_rows)
+                    p.out[uint64_t(row0 + r) * p.out_stride + g * C + lane] = f2bf(keep);
+            }
+            b = 0;
+            g += nwarps;
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            wd[c] = wn[c];
+            sd[c] = sn[c];
+            bd[c] = bn[c];
+            wn[c] = wf[c];
+            sn[c] = sf[c];
+            bn[c] = bf_[c];
+        }
+    }
+}
+
+// Up to 4 rows per warp pass (more rows run as further row tiles that re-read the weights from L2).
+template <int R, int C>
+static void launch_q4(const Q4Params& p, uint32_t sm_count, uint32_t ctas_per_sm, cudaStream_t stream) {
+    const uint32_t groups = p.n_cols / C;
+    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count * ctas_per_sm);
+    const uint32_t smem = R * (p.k >> 3) * 16u;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, (p.n_rows + R - 1) / R);
+    cfg.blockDim = dim3(kQ4Warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, q4_project_kernel<R, C>, p);
+}
+
+// =========================================================================================
+// tensor-unit policy: dequantise once ...
+// =========================================================================================
+__global__ void __launch_bounds__(256) q4_dequant_kernel(const uint32_t* __restrict__ words,
+                                                         const __nv_bfloat16* __restrict__ scales,
+                                                         const __nv_bfloat16* __restrict__ biases,
+                                                         __nv_bfloat16* __restrict__ weights, uint64_t n_words) {
+    for (uint64_t i = blockIdx.x * 256ull + threadIdx.x; i < n_words; i += uint64_t(gridDim.x) * 256ull) {
+        const uint32_t word = __ldg(words + i);
+        const float scale = bf2f(scales[i >> 3]), bias = bf2f(biases[i >> 3]);
+        __nv_bfloat16 res[8];
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) res[j] = f2bf(__fmaf_rn(float((word >> (4u * j)) & 15u), scale, bias));
+        *reinterpret_cast<uint4*>(weights + i * 8ull) = *reinterpret_cast<const uint4*>(res);
+    }
+}
+
+// ... then out[M][N] = x[M][K] . w[N][K]^T on the tensor cores.
+constexpr uint32_t kGM = 128, kGN = 256, kGK = 64, kGStages = 4, kGAccs = 2;
+constexpr uint32_t kGABytes = kGM * 128, kGBBytes = kGN * 128, kGStageBytes = kGABytes + kGBBytes;
+constexpr uint32_t kGOffBar = kGStages * kGStageBytes;
+constexpr uint32_t kGemmSmem = kGOffBar + 256;
+constexpr uint32_t kGemmThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue (one TMEM lane quarter each)
+enum : uint32_t { kGBarFull = 0, kGBarEmpty = kGBarFull + kGStages, kGBarAccFull = kGBarEmpty + kGStages,
+                  kGBarAccEmpty = kGBarAccFull + kGAccs, kGBarCount = kGBarAccEmpty + kGAccs };
+static_assert(8 * kGBarCount + 16 <= 256, "barrier block");
+
+struct GemmParams {
+    __nv_bfloat16* out;
+    uint32_t* status;
+    uint64_t out_stride;
+    uint32_t m, n, k, m_tiles, n_tiles;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+dense_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                     const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t base = s2u(smem), bars = base + kGOffBar;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kGOffBar + 8 * kGBarCount);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kGOffBar + 8 * kGBarCount + 8);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+    const uint32_t n_tiles_total = p.m_tiles * p.n_tiles, kblocks = p.k / kGK;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kGStages; ++s) {
+            mbar_init(bar(kGBarFull + s), 1);
+            mbar_init(bar(kGBarEmpty + s), 1);
+        }
+        for (uint32_t a = 0; a < kGAccs; ++a) {
+            mbar_init(bar(kGBarAccFull + a), 1);
+            mbar_init(bar(kGBarAccEmpty + a), 128);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)),
+                     "r"(kGAccs * kGN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // Tile order: the weight tiles of one band of input rows are adjacent, so the CTAs running
+    // at the same time share a few input tiles and walk the (L2-resident) weight matrix.
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t n = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < n_tiles_total; t += gridDim.x) {
+                const int m0 = int((t / p.n_tiles) * kGM), n0 = int((t % p.n_tiles) * kGN);
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++n) {
+                    const uint32_t s = n % kGStages, use = n / kGStages;
+                    if (use > 0 && !mbar_wait(bar(kGBarEmpty + s), (use - 1u) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(bar(kGBarFull + s), kGStageBytes);
+                    tma_load_2d(base + s * kGStageBytes, &map_x, bar(kGBarFull + s), int(kb * kGK), m0);
+                    tma_load_2d(base + s * kGStageBytes + kGABytes, &map_w, bar(kGBarFull + s), int(kb * kGK), n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(kGM, kGN, false);
+            uint32_t n = 0, it = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < n_tiles_total; t += gridDim.x, ++it) {
+                const uint32_t ab = it % kGAccs, ause = it / kGAccs;
+                if (ause > 0 && !mbar_wait(bar(kGBarAccEmpty + ab), (ause - 1u) & 1u, abort_flag)) break;
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++n) {
+                    const uint32_t s = n % kGStages;
+                    if (!mbar_wait(bar(kGBarFull + s), (n / kGStages) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 4; ++ks) {
+                        const uint64_t ad = smem_desc(base + s * kGStageBytes + ks * 32u, 16, 1024);
+                        const uint64_t bd = smem_desc(base + s * kGStageBytes + kGABytes + ks * 32u, 16, 1024);
+                        tc_mma(tmem + ab * kGN, ad, bd, idesc, (kb | ks) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kGBarEmpty + s));
+                }
+                if (ok) tc_commit(bar(kGBarAccFull + ab));
+            }
+        }
+    } else {
+        // epilogue: thread = one output row of the tile (its TMEM lane), 32 columns at a time
+        const uint32_t quarter = warp & 3u, row_in_tile = quarter * 32u + lane;
+        const uint32_t tlane = (quarter * 32u) << 16;
+        uint32_t it = 0;
+        for (uint32_t t = blockIdx.x; t < n_tiles_total; t += gridDim.x, ++it) {
+            const uint32_t ab = it % kGAccs;
+            if (!mbar_wait(bar(kGBarAccFull + ab), (it / kGAccs) & 1u, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t row = (t / p.n_tiles) * kGM + row_in_tile, n0 = (t % p.n_tiles) * kGN;
+            __nv_bfloat16* orow = p.out + uint64_t(row) * p.out_stride + n0;
+#pragma unroll 2
+            for (uint32_t ch = 0; ch < kGN / 32u; ++ch) {
+                float v[32];
+                tmem_ld32(tmem + tlane + ab * kGN + ch * 32u, v);
+                tmem_wait_ld();
+                if (row < p.m && n0 + ch * 32u < p.n) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 4; ++q) {
+                        __nv_bfloat162 h[4];
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+                        *reinterpret_cast<uint4*>(orow + ch * 32u + q * 8u) = *reinterpret_cast<const uint4*>(h);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(kGBarAccEmpty + ab));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000); // let copies still in flight land before the shared memory is released
+        __syncthreads();
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kGAccs * kGN) : "memory");
+    }
+}
+
+// 2-D bf16 tensor map {k, rows} with a {64, box_rows} box and the 128-byte swizzle.
+static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint64_t stride_bytes,
+                        uint32_t box_rows) {
+    EncodeTiled fn = encode_tiled_entry();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {stride_bytes};
+    const cuuint32_t box[2] = {kGK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static tatara_status check_matrices(tatara_ctx* ctx, const tatara_q4_matrix* matrices, uint32_t n_matrices,
+                                    uint32_t k, uint32_t k_multiple, const char* what, uint32_t* total) {
+    if (matrices == nullptr || n_matrices == 0 || n_matrices > kQ4MaxMats)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, what);
+    if (k == 0 || k % k_multiple != 0) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, what);
+    uint32_t cols = 0;
+    for (uint32_t i = 0; i < n_matrices; ++i) {
+        const tatara_q4_matrix& m = matrices[i];
+        if (!m.words || !m.scales || !m.biases) return fail(ctx, TATARA_INVALID_BUFFER, what);
+        if (!aligned(m.words, 16) || !aligned(m.scales, 2) || !aligned(m.biases, 2))
+            return fail(ctx, TATARA_INVALID_BUFFER, what);
+        if (m.rows == 0 || m.rows % 16u != 0) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, what);
+        cols += m.rows;
+    }
+    *total = cols;
+    return TATARA_OK;
+}
+
+} // namespace tb
+
+using namespace tb;
+
+extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const void* input,
+                                           uint64_t input_stride, uint32_t n_rows,
+                                           const tatara_q4_matrix* matrices, uint32_t n_matrices,
+                                           uint32_t k, void* out, uint64_t out_stride) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!input || !out) return fail(ctx, TATARA_INVALID_BUFFER, "q4_project: null buffer");
+    if (!aligned(input, 16) || !aligned(out, 2))
+        return fail(ctx, TATARA_INVALID_BUFFER, "q4_project: misaligned buffer");
+    uint32_t cols = 0;
+    const tatara_status st = check_matrices(ctx, matrices, n_matrices, k, 512, "q4_project: matrices", &cols);
+    if (st != TATARA_OK) return st;
+    if (n_rows == 0 || input_stride < k || input_stride % 8u != 0 || out_stride < cols)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "q4_project: rows or strides");
+    Q4Params p{};
+    p.x = static_cast<const __nv_bfloat16*>(input);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.x_stride = input_stride;
+    p.out_stride = out_stride;
+    p.n_rows = n_rows;
+    p.k = k;
+    p.n_cols = cols;
+    p.n_mats = n_matrices;
+    uint32_t at = 0;
+    for (uint32_t i = 0; i < n_matrices; ++i) {
+        p.mat[i].words = static_cast<const uint2*>(matrices[i].words);
+        p.mat[i].scales = static_cast<const __nv_bfloat16*>(matrices[i].scales);
+        p.mat[i].biases = static_cast<const __nv_bfloat16*>(matrices[i].biases);
+        p.mat[i].col_begin = at;
+        at += matrices[i].rows;
+        p.mat[i].col_end = at;
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    const uint32_t sms = uint32_t(ctx->sm_count);
+    if (k > 6144u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "q4_project: k above 6144");
+    if (n_rows == 1) {
+        // few warps with many bytes in flight each; narrow matrices get narrower groups (more warps)
+        if (cols >= 8192u) launch_q4<1, 8>(p, sms, 1, s);
+        else launch_q4<1, 4>(p, sms, 1, s);
+    } else if (n_rows == 2) {
+        launch_q4<2, 4>(p, sms, 1, s);
+    } else {
+        launch_q4<4, 4>(p, sms, 1, s);
+    }
+    return check_launch(ctx, "q4_project");
+}
+
+extern "C" tatara_status tatara_q4_dequantize(tatara_ctx* ctx, void* stream,
+                                              const tatara_q4_matrix* matrices, uint32_t n_matrices,
+                                              uint32_t k, void* weights) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!weights || !aligned(weights, 16)) return fail(ctx, TATARA_INVALID_BUFFER, "q4_dequantize: weights");
+    uint32_t cols = 0;
+    const tatara_status st = check_matrices(ctx, matrices, n_matrices, k, 64, "q4_dequantize: matrices", &cols);
+    if (st != TATARA_OK) return st;
+    auto* w = static_cast<__nv_bfloat16*>(weights);
+    for (uint32_t i = 0; i < n_matrices; ++i) {
+        const uint64_t n_words = uint64_t(matrices[i].rows) * (k / 8u);
+        const uint64_t want = (n_words + 255u) / 256u, cap = uint64_t(ctx->sm_count) * 16u;
+        const uint32_t grid = uint32_t(want < cap ? want : cap);
+        q4_dequant_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint32_t*>(matrices[i].words), static_cast<const __nv_bfloat16*>(matrices[i].scales),
+            static_cast<const __nv_bfloat16*>(matrices[i].biases), w, n_words);
+        const tatara_status ls = check_launch(ctx, "q4_dequantize");
+        if (ls != TATARA_OK) return ls;
+        w += uint64_t(matrices[i].rows) * k;
+    }
+    return TATARA_OK;
+}
+
+extern "C" tatara_status tatara_project_dense(tatara_ctx* ctx, void* stream, const void* input,
+                                              uint64_t input_stride, uint32_t n_rows,
+                                              const void* weights, uint32_t n, uint32_t k, void* out,
+                                              uint64_t out_stride) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!input || !weights || !out) return fail(ctx, TATARA_INVALID_BUFFER, "project_dense: null buffer");
+    if (!aligned(input, 16) || !aligned(weights, 16) || !aligned(out, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "project_dense: buffers must be 16-byte aligned");
+    if (n_rows == 0 || n == 0 || n % 32u != 0 || k == 0 || k % kGK != 0 || input_stride < k ||
+        input_stride % 8u != 0 || out_stride < n || out_stride % 8u != 0)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "project_dense: extents");
+    CUtensorMap map_x, map_w;
+    if (!make_map_2d(&map_x, input, k, n_rows, input_stride * 2ull, kGM) ||
+        !make_map_2d(&map_w, weights, k, n, uint64_t(k) * 2ull, kGN))
+        return fail(ctx, TATARA_CUDA_ERROR, "project_dense: tensor map encoding failed");
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(dense_project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) !=
+            cudaSuccess)
+            return check_launch(ctx, "project_dense: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    GemmParams gp{};
+    gp.out = static_cast<__nv_bfloat16*>(out);
+    gp.status = ctx->device_status;
+    gp.out_stride = out_stride;
+    gp.m = n_rows;
+    gp.n = n;
+    gp.k = k;
+    gp.m_tiles = (n_rows + kGM - 1u) / kGM;
+    gp.n_tiles = (n + kGN - 1u) / kGN;
+    const uint32_t tiles = gp.m_tiles * gp.n_tiles;
+    const uint32_t grid = tiles < uint32_t(ctx->sm_count) ? tiles : uint32_t(ctx->sm_count);
+    dense_project_kernel<<<grid, kGemmThreads, kGemmSmem, static_cast<cudaStream_t>(stream)>>>(map_x, map_w, gp);
+    return check_launch(ctx, "project_dense");
+}

@@ -50,6 +50,7 @@ inline constexpr std::uint32_t kGdnProjectionRows = 12352, kGdnValueValues = 409
 inline constexpr std::uint64_t kGdnConvStateValues = 3ull * 8192ull;             // bf16
 inline constexpr std::uint64_t kGdnRecurrentStateValues = 32ull * 128ull * 128ull; // f32
 inline constexpr std::uint32_t kMaximumBatchRows = TATARA_MAX_LANES;
+inline constexpr std::uint32_t kHidden = 2048;
 
 // A context is a cache position, so equality with capacity is already one past the allocation
 // (include/tatara/runtime/decode_geometry.h:133-135).
@@ -164,6 +165,21 @@ struct GatedDeltaWeights {
     const void* norm;      // [128] bf16
 };
 
+// One affine-Q4 weight as the reference binds it (words, scales, biases of `rows` output rows;
+// encode.quantized(...), src/runtime/decode_step.cpp:658-664, 705-708).
+struct QuantizedWeight {
+    const void* words{nullptr};
+    const void* scales{nullptr};
+    const void* biases{nullptr};
+    std::uint32_t rows{0};
+};
+struct AttentionProjection {   // bound.attention.{query, key, value, out}
+    QuantizedWeight query, key, value, out;
+};
+struct GatedDeltaProjection {  // bound.gated_delta.{qkv, z, b, a, out}
+    QuantizedWeight qkv, z, b, a, out;
+};
+
 // Per-batch scratch slabs, one row per stream (include/tatara/runtime/decode_step.h:278-305).
 struct DecodeBatchScratch {
     std::uint32_t rows{0};
@@ -240,6 +256,27 @@ class LayerPass {
         return st == TATARA_OK ? CommandError::None : latch(to_command_error(st));
     }
 
+    // attn_project: normed [rows][2048] bf16 -> projection_slab [rows][9216] bf16, each row with the
+    // reference's exact per-row sequence (decode_step.cpp:705-711).
+    CommandError encode_attention_project(const AttentionProjection& w, const void* normed, std::uint32_t rows,
+                                          void* projection_slab) {
+        const tatara_q4_matrix m[3] = {as_matrix(w.query), as_matrix(w.key), as_matrix(w.value)};
+        return project(m, 3, kHidden, normed, kHidden, rows, projection_slab, kAttnProjectionRows);
+    }
+    // gdn_project: normed -> projection_slab [rows][12352] bf16 (decode_step.cpp:657-664).
+    CommandError encode_gated_delta_project(const GatedDeltaProjection& w, const void* normed, std::uint32_t rows,
+                                            void* projection_slab) {
+        const tatara_q4_matrix m[4] = {as_matrix(w.qkv), as_matrix(w.z), as_matrix(w.b), as_matrix(w.a)};
+        return project(m, 4, kHidden, normed, kHidden, rows, projection_slab, kGdnProjectionRows);
+    }
+    // out_projection: attended / gated [rows][4096] bf16 -> branch [rows][branch_stride] bf16
+    // (decode_step.cpp:698-702, 732-736).
+    CommandError encode_out_projection(const QuantizedWeight& out, const void* input, std::uint32_t rows, void* branch,
+                                       std::uint64_t branch_stride) {
+        const tatara_q4_matrix m[1] = {as_matrix(out)};
+        return project(m, 1, kAttnQueryValues, input, kAttnQueryValues, rows, branch, branch_stride);
+    }
+
     // commit() + wait_until_completed(): returns the latched host error or a device-side one.
     CommandError commit_and_wait() {
         if (error_ != CommandError::None) return error_;
@@ -248,6 +285,16 @@ class LayerPass {
     }
 
   private:
+    static tatara_q4_matrix as_matrix(const QuantizedWeight& w) noexcept {
+        return tatara_q4_matrix{w.words, w.scales, w.biases, w.rows, 0};
+    }
+    CommandError project(const tatara_q4_matrix* m, std::uint32_t n, std::uint32_t k, const void* input,
+                         std::uint64_t input_stride, std::uint32_t rows, void* out, std::uint64_t out_stride) {
+        if (error_ != CommandError::None) return error_;
+        if (rows == 0 || rows > kMaximumBatchRows) return latch(CommandError::InvalidStreamGroup);
+        const tatara_status st = tatara_q4_project(ctx_, stream_, input, input_stride, rows, m, n, k, out, out_stride);
+        return st == TATARA_OK ? CommandError::None : latch(to_command_error(st));
+    }
     CommandError latch(CommandError e) noexcept {
         if (error_ == CommandError::None) error_ = e;
         return e;

@@ -108,3 +108,24 @@ def gdn_state(rng: np.random.Generator, zero: bool = False):
         return conv, np.zeros((GDN_HEADS, GDN_DIM, GDN_DIM), np.float32)
     rec = (rng.standard_normal((GDN_HEADS, GDN_DIM, GDN_DIM), dtype=np.float32) * np.float32(0.02))
     return conv, rec
+
+
+def q4_matrix(rng: np.random.Generator, n: int, k: int, gain: float = 0.35):
+    """An affine-Q4 group-64 weight matrix of n output rows over k inputs.
+
+    words [n][k/8] u32 (nibble j of word w is column 8w + j), scales and biases [n][k/64] bf16 bits.
+    Nibbles are uniform in 0..15; scale ~ 0.32 gain/sqrt(k) (1 +- 0.2) and bias ~ -7.5 scale (1 +- 0.1),
+    the shape a min/max group quantiser gives weights of standard deviation ~ gain/sqrt(k); a
+    unit-variance input row then projects to outputs of standard deviation ~ 1.5 gain (0.5 at the
+    default gain, so that one bf16 step of the largest outputs stays below the 2e-2 gate).
+    """
+    words = rng.integers(0, 1 << 32, size=(n, k // 8), dtype=np.uint64).astype(np.uint32)
+    sigma = gain / np.sqrt(k)
+    scale = 0.32 * sigma * (1.0 + 0.2 * rng.uniform(-1, 1, size=(n, k // 64)))
+    bias = -7.5 * scale * (1.0 + 0.1 * rng.standard_normal((n, k // 64)))
+    return words, to_bf16(scale.astype(np.float32)), to_bf16(bias.astype(np.float32))
+
+
+def hidden_rows(rng: np.random.Generator, rows: int, k: int) -> np.ndarray:
+    """RMS-normalised hidden rows [rows][k] bf16 bits (unit variance)."""
+    return normal_bf16(rng, (rows, k))

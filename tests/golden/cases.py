@@ -41,3 +41,13 @@ def gdn_chain(steps: int = 4):
     conv, state = syn.gdn_state(rng)
     projections = [syn.gdn_projection(rng, 1)[0] for _ in range(steps)]
     return weights, conv, state, projections
+
+
+def q4_cases():
+    """(name, x[k], words[k/8], scales[k/64], biases[k/64]) single-row dots at the three widths in use."""
+    for k in (512, 2048, 4096):
+        rng = np.random.default_rng(7300 + k)
+        words, scales, biases = syn.q4_matrix(rng, 8, k)
+        x = syn.hidden_rows(rng, 1, k)[0]
+        for row in range(8):
+            yield f"q4/{k}/{row}", (x, words[row].copy(), scales[row].copy(), biases[row].copy())

@@ -53,6 +53,10 @@ def main():
     out["gdn/final_state_head3"] = state[3].copy()
     out["gdn/final_state_rowsum"] = state.astype(np.float64).sum(axis=2)
     out["gdn/checksum"] = cases.checksum(conv_w, a_log, dt_bias, norm_w, *projections)
+    for name, (x, words, scales, biases) in cases.q4_cases():
+        out[f"{name}/fused"] = np.array([oracle.ref_q4_dot(x, words, scales, biases, True)], np.float32)
+        out[f"{name}/separate"] = np.array([oracle.ref_q4_dot(x, words, scales, biases, False)], np.float32)
+        out[f"{name}/checksum"] = cases.checksum(x, words, scales, biases)
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays")
 

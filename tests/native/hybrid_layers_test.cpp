@@ -21,6 +21,8 @@ void orc_gdn_prepare(const u16*, const u16*, const u16*, u16*, u16*, u16*, u16*,
 void orc_gdn_gates(const u16*, std::uint32_t, const u16*, const u16*, float*, float*, std::uint32_t);
 void orc_gdn_scan(const u16*, const u16*, const float*, const float*, const float*, u16*, float*, std::uint32_t, int);
 void orc_gdn_gate_norm(const u16*, const u16*, const u16*, u16*, std::uint32_t);
+void orc_q4_project(const u16*, std::uint32_t, std::uint32_t, const std::uint32_t*, const u16*, const u16*, std::uint32_t,
+                    std::uint32_t, u16*, std::uint32_t, int, int);
 }
 
 namespace {
@@ -207,13 +209,60 @@ int device_checks(tatara_ctx* ctx) {
 
 } // namespace
 
+// Projection encoders: gdn_project geometry (four matrices, 12352 columns) for two rows, bit for bit
+// against the oracle's fused chain, and the latched error for an empty row group.
+int projection_checks(tatara_ctx* ctx) {
+    Rng rng{0xC0FFEEull};
+    constexpr std::uint32_t k = kHidden, rows = 2;
+    const std::uint32_t sizes[4] = {8192, 4096, 32, 32};
+    std::vector<std::vector<std::uint32_t>> words(4);
+    std::vector<std::vector<u16>> scales(4), biases(4);
+    std::vector<DeviceBuffer> dw, ds, db;
+    QuantizedWeight q[4];
+    for (int m = 0; m < 4; ++m) {
+        words[m].resize(std::size_t{sizes[m]} * k / 8);
+        for (auto& w : words[m]) w = static_cast<std::uint32_t>(rng.next());
+        scales[m].resize(std::size_t{sizes[m]} * k / 64);
+        biases[m].resize(scales[m].size());
+        for (std::size_t i = 0; i < scales[m].size(); ++i) {
+            const float sc = 0.0025f * (1.0f + 0.2f * (2.0f * rng.uniform() - 1.0f));
+            scales[m][i] = to_bf16(sc);
+            biases[m][i] = to_bf16(-7.5f * sc * (1.0f + 0.1f * rng.normal()));
+        }
+        dw.emplace_back(words[m].size() * 4); ds.emplace_back(scales[m].size() * 2); db.emplace_back(biases[m].size() * 2);
+        if (!upload(dw.back().data(), words[m]) || !upload(ds.back().data(), scales[m]) || !upload(db.back().data(), biases[m])) return 60;
+        q[m] = QuantizedWeight{dw.back().data(), ds.back().data(), db.back().data(), sizes[m]};
+    }
+    std::vector<u16> x(rows * k); rng.fill(x);
+    DeviceBuffer dx(x.size() * 2), dout(std::size_t{rows} * kGdnProjectionRows * 2);
+    if (!upload(dx.data(), x)) return 61;
+    LayerPass pass(ctx, nullptr);
+    const GatedDeltaProjection gp{q[0], q[1], q[2], q[3], QuantizedWeight{}};
+    if (pass.encode_gated_delta_project(gp, dx.data(), rows, dout.data()) != CommandError::None) return 62;
+    if (pass.commit_and_wait() != CommandError::None) return 63;
+    std::vector<u16> got(std::size_t{rows} * kGdnProjectionRows), want(got.size());
+    if (cudaMemcpy(got.data(), dout.data(), got.size() * 2, cudaMemcpyDeviceToHost) != cudaSuccess) return 64;
+    std::uint32_t col = 0;
+    for (int m = 0; m < 4; ++m) {
+        orc_q4_project(x.data(), k, rows, words[m].data(), scales[m].data(), biases[m].data(), sizes[m], k,
+                       want.data() + col, kGdnProjectionRows, 1, 4);
+        col += sizes[m];
+    }
+    if (std::memcmp(got.data(), want.data(), got.size() * 2) != 0) return 65;
+    LayerPass bad(ctx, nullptr);
+    if (bad.encode_gated_delta_project(gp, dx.data(), 0, dout.data()) != CommandError::InvalidStreamGroup) return 66;
+    if (bad.encode_out_projection(q[1], dx.data(), 1, dout.data(), kHidden) != CommandError::InvalidStreamGroup) return 67;  // latched
+    return 0;
+}
+
 int main() {
     if (const int rc = host_only_checks(); rc != 0) { std::printf("host check failed: %d\n", rc); return rc; }
     tatara_ctx* ctx = nullptr;
     const tatara_status st = tatara_ctx_create(0, &ctx);
     if (st == TATARA_INVALID_DEVICE) { std::printf("host checks passed; no B200 present, device checks skipped\n"); return 0; }
     if (st != TATARA_OK) return 2;
-    const int rc = device_checks(ctx);
+    int rc = device_checks(ctx);
+    if (rc == 0) rc = projection_checks(ctx);
     tatara_ctx_destroy(ctx);
     if (rc != 0) { std::printf("device check failed: %d\n", rc); return rc; }
     std::printf("host and device checks passed\n");

@@ -126,3 +126,41 @@ def test_prefill_rows_equal_decode_steps():
     out = oracle.attn_prefill(q, gate, keys, values, 290, 320, row_list=[0, 3, 9], threads=2)
     for r in (0, 3, 9):
         assert np.array_equal(out[r], oracle.attn_decode(q[r], gate[r], keys, values, 290 + r, 320))
+
+
+@pytest.mark.parametrize("name_inputs", list(cases.q4_cases()), ids=lambda c: c[0])
+def test_q4_dot_golden(name_inputs):
+    """Affine-Q4 row dot, both chain orders of the reference's CPU model (kernel_reference.cpp:388-442)."""
+    name, (x, words, scales, biases) = name_inputs
+    assert cases.checksum(x, words, scales, biases) == GOLD[f"{name}/checksum"]
+    for order, fused in (("fused", True), ("separate", False)):
+        got = np.float32(oracle.q4_dot(x, words, scales, biases, fused))
+        assert got.view(np.uint32) == GOLD[f"{name}/{order}"].view(np.uint32)[0]
+
+
+def test_q4_closed_forms():
+    """Known answers: all-zero nibbles leave sum*bias; nibble value v at every column gives
+    (v*scale + bias) * sum(x) when the arithmetic is exact (small integers, power-of-two scales)."""
+    k = 512
+    x = syn.to_bf16(np.ones(k, np.float32))
+    scales = syn.to_bf16(np.full(k // 64, 0.5, np.float32))
+    biases = syn.to_bf16(np.full(k // 64, -2.0, np.float32))
+    for v in (0, 1, 7, 15):
+        words = np.full(k // 8, v * 0x11111111, np.uint32)
+        for fused in (True, False):
+            assert oracle.q4_dot(x, words, scales, biases, fused) == (v * 0.5 - 2.0) * k
+    # dequantised weights of the tensor-unit policy
+    w = syn.from_bf16(oracle.q4_dequantize(np.full((1, k // 8), 0x76543210, np.uint32), scales[None], biases[None]))
+    assert np.array_equal(w[0, :8], np.arange(8) * 0.5 - 2.0)
+
+
+def test_q4_project_policies_agree_within_rounding():
+    """Exact-row and tensor-unit policies differ only by the bf16 rounding of the dequantised weights."""
+    rng = np.random.default_rng(5)
+    words, scales, biases = syn.q4_matrix(rng, 48, 2048)
+    x = syn.hidden_rows(rng, 3, 2048)
+    exact = syn.from_bf16(oracle.q4_project(x, words, scales, biases))
+    dense = syn.from_bf16(oracle.project_dense(x, oracle.q4_dequantize(words, scales, biases)))
+    assert np.abs(exact - dense).max() <= 2e-2
+    assert np.dot(exact.ravel(), dense.ravel()) / np.linalg.norm(exact) / np.linalg.norm(dense) >= 0.9999
+    assert 0.2 < exact.std() < 2.0

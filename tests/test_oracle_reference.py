@@ -6,6 +6,8 @@ Shapes follow the reference's fixture probes: capacity 512, contexts 0 / 4 / 200
 (tools/native/attention_fixture_probe.cpp:27-36) and a 4-step GDN chain
 (tools/native/gdn_fixture_probe.cpp:44, 805-851).
 """
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -111,3 +113,27 @@ def test_gdn_block_prepare_equals_stepwise():
         rqk, rv, rz, c = oracle.ref_gdn_prepare(proj[r], c, conv_w)
         assert np.array_equal(qk[r], rqk) and np.array_equal(v[r], rv) and np.array_equal(z[r], rz)
     assert np.array_equal(new_conv, c)
+
+
+@pytest.mark.parametrize("k", [512, 2048, 4096])
+def test_q4_dot_bit_exact(k):
+    """q4_dot_reference (kernel_reference.cpp:388-442), adjacent-pairs tree, both chain orders; inputs from
+    the reference's banded bf16 generator as in kernel_reference_test.cpp:165-184 and from the bench's."""
+    rng = np.random.default_rng(k)
+    for trial in range(40):
+        if trial % 2:
+            n = k + k // 8 * 2 + 2 * (k // 64)
+            band = np.zeros(n, np.uint16)
+            oracle.ref().ref_xorshift_banded(ctypes.c_uint64(trial + 1), band.ctypes.data_as(oracle._u16p),
+                                             ctypes.c_uint32(n))
+            x, rest = band[:k].copy(), band[k:]
+            words = rest[: k // 4].copy().view(np.uint32)
+            scales, biases = rest[k // 4: k // 4 + k // 64].copy(), rest[k // 4 + k // 64:].copy()
+        else:
+            w, s, b = syn.q4_matrix(rng, 1, k)
+            words, scales, biases = w[0], s[0], b[0]
+            x = syn.hidden_rows(rng, 1, k)[0]
+        for fused in (True, False):
+            a = np.float32(oracle.q4_dot(x, words, scales, biases, fused))
+            r = np.float32(oracle.ref_q4_dot(x, words, scales, biases, fused))
+            assert a.view(np.uint32) == r.view(np.uint32), (trial, fused, a, r)
