@@ -112,7 +112,12 @@ tatara_status tatara_attn_qk_rope_batch(tatara_ctx* ctx, void* stream, const voi
 
 /* Decode attention of one lane: slots 0 q, 1 gate, 2 K, 3 V, 4 context, 5 out, 6 capacity,
  * plus the record scratch of the partitioned family
- * (src/runtime/decode_step.cpp:239-247, 296-337).  Attends keys 0..context inclusive. */
+ * (src/runtime/decode_step.cpp:239-247, 296-337).  Attends keys 0..context inclusive.
+ * The decode kernels are programmatic dependent launches: K/V rows below the lane's last
+ * partition (rows that cannot be the one a preceding tatara_attn_qk_rope call appends) may be
+ * requested while the previous kernel of the stream is still finishing; q, gate, the last
+ * partition and every output wait for it.  Library kernels that write more than the appended
+ * row keep plain stream order. */
 tatara_status tatara_attn_decode(tatara_ctx* ctx, void* stream, const void* q, const void* gate,
                                  const void* keys, const void* values, uint32_t context,
                                  uint32_t capacity, void* out, void* scratch,

@@ -168,36 +168,44 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     uint32_t* item_start = reinterpret_cast<uint32_t*>(merge_ml + kDecWarps * kHeadsPerKv * 2);
     for (uint32_t i = threadIdx.x; i <= p.n_lanes; i += kDecThreads)
         item_start[i] = i < p.n_lanes ? p.lane[i].item_start : p.total_items;
-    // Launched with programmatic stream serialization: everything above overlapped the tail of
-    // the previous kernel in the stream; nothing below (which reads q, K, V and writes records)
-    // runs until that kernel has completed and its writes are visible.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
-
-    // Let a programmatic dependent (the combine) be staged; it still waits for this grid to finish.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t ring = smem_u32(smem + warp * kRingBytes);
 
     // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
     SliceCursor pc{};
     pc.item = blockIdx.x;
     pc.valid = pc.item < p.total_items;
+    bool early = false;
     if (pc.valid) {
         cursor_load_item(pc, p, item_start);
         pc.slice = warp;
+        // Every partition but a lane's last is full (at least 128 keys = 2 slices for each warp) and
+        // holds only keys written before this token, so its first slices can be requested at once.
+        early = pc.part + 1u < p.lane[pc.lane].nparts;
         cursor_settle(pc, p, item_start, warp);
     }
     uint32_t issued = 0, consumed = 0;
+    auto fill_ring = [&]() {
 #pragma unroll
-    for (uint32_t i = 0; i + 1 < kDecStages; ++i) {
-        if (pc.valid) {
-            issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
-            pc.slice += kDecWarps;
-            cursor_settle(pc, p, item_start, warp);
+        for (uint32_t i = 0; i + 1 < kDecStages; ++i) {
+            if (pc.valid) {
+                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
+                pc.slice += kDecWarps;
+                cursor_settle(pc, p, item_start, warp);
+            }
+            cp_async_commit();
+            ++issued;
         }
-        cp_async_commit();
-        ++issued;
-    }
+    };
+    // Launched with programmatic stream serialization: everything above, and the first K/V slices
+    // of partitions that cannot contain the row the predecessor appends, overlap the tail of the
+    // previous kernel in the stream.  q, the appended row and the record scratch are touched only
+    // after griddepcontrol.wait (the predecessor has completed and its writes are visible).
+    if (early) fill_ring();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Let a programmatic dependent (the combine) be staged; it still waits for this grid to finish.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!early) fill_ring();
 
     // Per-lane ldmatrix address pieces (see the fragment layouts of mma.m16n8k16).
     const uint32_t lm_j = lane >> 3, lm_r = lane & 7u;
@@ -380,9 +388,12 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     constexpr uint32_t kWarps = combine_warps<N>(), kCombineThreads = kWarps * 32u;
     __shared__ float red_max[kCombinePhases];
     __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
-    // When launched as a programmatic dependent of the partition kernel: wait for its records.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The next kernel of the stream may be staged as soon as every CTA of this grid is resident:
+    // whatever it does before its own dependency wait must not depend on this grid (the decode
+    // partition kernel only requests old K/V rows there).  Then wait for the partition kernel's
+    // records (this grid is its programmatic dependent).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (p.px.wait_flags != nullptr) {
         // Split-KV merge: the records of the other ranks are pushed into this GPU's memory by
         // kernels running on THEIR GPUs; wait, with a time limit, until every rank's flag carries
@@ -580,7 +591,13 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
         if (cudaFuncSetAttribute(attn_decode_partition_kernel<1>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess ||
             cudaFuncSetAttribute(attn_decode_partition_kernel<TATARA_MAX_LANES>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess)
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes) != cudaSuccess ||
+            // the merge runs between two partition kernels: same shared-memory carve-out as theirs,
+            // so that the SMs are not reconfigured at every kernel boundary of a decode step
+            cudaFuncSetAttribute(attn_combine_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_combine_kernel<TATARA_MAX_LANES>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess)
             return check_launch(ctx, "attn_decode: shared memory attribute");
         configured[ctx->device & 63] = true;
     }

@@ -29,8 +29,11 @@ attn_qk_rope_kernel(const __nv_bfloat16* __restrict__ projection,
     constexpr bool kBatched = N > 1;
     __shared__ float normed[kHeadDim];
     __shared__ float stage[2];
-    // a kernel queued behind this one with programmatic serialization may be staged already
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A kernel queued behind this one with programmatic serialization may be staged already --
+    // but only when each lane appends ONE row: the decode kernel then reads, before its own
+    // dependency wait, nothing but partitions that cannot hold that row.  A block of rows
+    // (prefill) keeps plain stream order.
+    if (kBatched || gridDim.y == 1u) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x;
     uint32_t pos = position + row;
     uint64_t kv_offset = 0;
