@@ -149,7 +149,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project"],
+    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project", "state_copy"],
                     help="run one workload only (small profiling runs)")
     ap.add_argument("--context", type=int, default=HEADLINE_CONTEXT)
     ap.add_argument("--rows", type=int, default=PREFILL_ROWS)
@@ -280,6 +280,7 @@ def main():
         extra["gdn_step_lanes32"] = wl.gdn_step(timed, steps, warmup, n=32)
         extra["gdn_prefill"] = wl.gdn_prefill(timed)
         extra["projections"] = wl.project(timed, peaks, steps, warmup)
+        extra["state_snapshot"] = wl.state_copy(timed, peaks)
         extra["prefill_attn"] = wl.prefill(timed, peaks, sampler=ClockSampler(local))
     else:
         extra["split_kv"] = wl.split_kv(dist, n, timed, steps, warmup)

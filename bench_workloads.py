@@ -311,6 +311,33 @@ class Workloads:
         out["l2"] = "exact-row: rotating weight sets (> 2x L2 between reuse); dense: input + output > L2"
         return out
 
+    # ---- state snapshot: the canonical prefix payload of the 40-layer schedule in one launch
+    def state_copy(self, timed, peaks, positions=65536, capacity=65536):
+        """60 gated-delta segments (48 KiB / 2 MiB) + 40 packed K/V head prefixes of `positions` rows, slot ->
+        arena, as tatara_state_copy executes them: bytes moved = 2 x payload (read + write)."""
+        torch = self.torch
+        seg = positions * 512
+        payload = 30 * (49152 + 2097152) + 40 * seg
+        slot_attn = [torch.empty(2 * capacity * 512, dtype=torch.uint8, device="cuda") for _ in range(20)]   # K, V per layer
+        slot_gdn = torch.empty(30 * (49152 + 2097152), dtype=torch.uint8, device="cuda")
+        arena = torch.empty(payload, dtype=torch.uint8, device="cuda")
+        entries, at = [], 0
+        for l in range(30):
+            for n in (49152, 2097152):
+                entries.append((slot_gdn.data_ptr() + at, arena.data_ptr() + at, n))
+                at += n
+        for plane in slot_attn:
+            for head in range(2):
+                entries.append((plane.data_ptr() + head * capacity * 512, arena.data_ptr() + at, seg))
+                at += seg
+        segs = tb.Context.copy_segments(entries)
+        ms = timed(lambda i=0: self.ctx.state_copy(segs), 5, 3)
+        gbs = 2 * payload / (ms * 1e-3) / 1e9
+        del slot_attn, slot_gdn, arena
+        torch.cuda.empty_cache()
+        return {"positions": positions, "segments": len(entries), "payload_bytes": payload, "ms": ms, "gbs_read_plus_write": gbs,
+                "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "l2": "payload 1.4 GB > L2"}
+
     # ---- config 4a: one lane at 262144 split along KV over the ranks, LSE merge over NCCL
     def split_kv(self, dist, n_keys, timed, steps, warmup):
         torch = self.torch
@@ -386,6 +413,8 @@ class Workloads:
             return self.lanes32(timed, steps, warmup)
         if which == "gdn_prefill":
             return self.gdn_prefill(timed, rows=args.rows)
+        if which == "state_copy":
+            return self.state_copy(timed, measured_peaks())
         if which == "project":
             return self.project(timed, measured_peaks(), steps, warmup, rows=args.rows)
         if which == "prefill":

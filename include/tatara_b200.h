@@ -306,6 +306,22 @@ tatara_status tatara_project_dense(tatara_ctx* ctx, void* stream, const void* in
                                    uint64_t input_stride, uint32_t n_rows, const void* weights,
                                    uint32_t n, uint32_t k, void* out, uint64_t out_stride);
 
+/* ---- state snapshots --------------------------------------------------------------------
+ * Device-to-device copy of a list of segments in one launch (all SMs, 32 KiB chunks dealt
+ * round-robin).  Replaces the per-segment blit copies of the reference's prefix-state transfer
+ * (src/runtime/prefix_state_transfer.cpp:236-262: one copy_buffer per segment between a decode
+ * slot and the prefix-cache arena) and the per-head copies of its state record loader
+ * (tools/native/decode_harness.cpp:339-461).  Addresses 16-byte aligned, lengths multiples of
+ * 16 bytes; the whole list is validated before anything is enqueued; segments must not overlap
+ * one another's destinations. */
+typedef struct tatara_copy_segment {
+    const void* src;
+    void* dst;
+    uint64_t bytes;
+} tatara_copy_segment;
+tatara_status tatara_state_copy(tatara_ctx* ctx, void* stream, const tatara_copy_segment* segments,
+                                uint32_t n_segments);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,10 @@ class Q4Matrix(ctypes.Structure):
                 ("rows", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
+class CopySegment(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("bytes", ctypes.c_uint64)]
+
+
 class GdnLane(ctypes.Structure):
     _fields_ = [("conv_in", ctypes.c_uint64), ("conv_out", ctypes.c_uint64),
                 ("rec_in", ctypes.c_uint64), ("rec_out", ctypes.c_uint64)]
@@ -296,6 +300,18 @@ class Context:
         self._check(lib().tatara_project_dense(
             self._h, self._stream(stream), _ptr(x), _u64(x.stride(0)), _u32(n_rows), _ptr(weights),
             _u32(weights.shape[0]), _u32(weights.shape[1]), _ptr(out), _u64(out.stride(0))))
+
+    # ---- state snapshots
+    @staticmethod
+    def copy_segments(entries):
+        """[(src address, dst address, bytes)] -> tatara_copy_segment[]."""
+        arr = (CopySegment * len(entries))()
+        for i, (src, dst, n) in enumerate(entries):
+            arr[i] = CopySegment(src, dst, n)
+        return arr
+
+    def state_copy(self, segments, stream=None):
+        self._check(lib().tatara_state_copy(self._h, self._stream(stream), segments, _u32(len(segments))))
 
 
 def gdn_prefill_scratch_bytes(rows: int) -> int:

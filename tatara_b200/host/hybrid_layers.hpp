@@ -109,13 +109,20 @@ struct DecodeStatePool {
     std::vector<DecodeStatePoolLayer> layers;
 };
 
-enum class DecodeStateSlotStatus : std::uint8_t { Ready, Poisoned };
+enum class DecodeStateSlotStatus : std::uint8_t { Ready, SnapshotPending, RestorePending, Poisoned };
 
 struct DecodeStateSlot {
     std::uint32_t capacity{0};
     std::uint32_t stripe{0};
     std::vector<bool> swapped;  // per layer; meaningful for gated-delta layers only
     DecodeStateSlotStatus status{DecodeStateSlotStatus::Ready};
+    // prefix-state transfer in flight (include/tatara/runtime/decode_step.h: active_transfer_*)
+    std::uint64_t next_transfer_generation{1};
+    std::uint64_t active_transfer_generation{0};
+    const void* active_transfer_arena{nullptr};
+    std::uint32_t active_transfer_positions{0};
+    std::uint64_t active_transfer_offset_bytes{0};
+    std::uint64_t active_transfer_state_bytes{0};
 };
 
 struct DecodeStream {

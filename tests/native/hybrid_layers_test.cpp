@@ -7,9 +7,10 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <utility>
 #include <vector>
 
-#include "../../tatara_b200/host/hybrid_layers.hpp"
+#include "../../tatara_b200/host/state_transfer.hpp"
 
 using namespace tatara::runtime;
 using u16 = std::uint16_t;
@@ -255,14 +256,186 @@ int projection_checks(tatara_ctx* ctx) {
     return 0;
 }
 
+// Canonical prefix-state layout: the reference's frozen figures (tests/native/prefix_state_transfer_test.cpp:
+// 223-231, 236-262, 376-432) restated as checks on this planner.
+int layout_checks() {
+    std::vector<LayerKind> model(40);
+    for (std::size_t l = 0; l < model.size(); ++l) model[l] = (l % 4 == 3) ? LayerKind::FullAttention : LayerKind::GatedDelta;
+    const std::pair<std::uint32_t, std::uint64_t> frozen[4] = {
+        {4096, 148275200ull}, {49408, 1076264960ull}, {50000, 1088389120ull}, {65536, 1406566400ull}};
+    for (const auto& [positions, bytes] : frozen) {
+        PrefixStateLayoutSpec spec{model.data(), model.size(), 65536, positions, 2, 256, 30, 10, 49152, 2097152, bytes};
+        const PrefixStateLayoutResult r = make_prefix_state_layout(spec);
+        if (!r || r.layout.segment_count != 100 || r.layout.total_bytes != bytes) return 70;
+    }
+    PrefixStateLayoutSpec spec{model.data(), model.size(), 16384, 4096, 2, 256, 30, 10, 49152, 2097152, 148275200ull};
+    const PrefixStateLayoutResult planned = make_prefix_state_layout(spec);
+    if (!planned || planned.layout.gated_delta_layers != 30 || planned.layout.attention_layers != 10) return 71;
+    if (planned.layout.attention_segment_bytes != 2097152 || planned.layout.attention_slot_head_stride_bytes != 8388608) return 72;
+    if (prefix_state_phase_evidence_bytes(model.size()) != 5) return 73;
+    // segments tile the payload exactly, family-major, each family in schedule order
+    std::uint64_t next = 0;
+    std::uint32_t gated = 0, attention = 0;
+    for (std::uint32_t i = 0; i < planned.layout.segment_count; ++i) {
+        const PrefixStateSegmentResult s = prefix_state_segment(planned.layout, i);
+        if (!s || s.segment.snapshot_offset_bytes != next) return 74;
+        next += s.segment.length_bytes;
+        const bool g = s.segment.kind == PrefixStateSegmentKind::GatedDeltaConvolution || s.segment.kind == PrefixStateSegmentKind::GatedDeltaRecurrent;
+        if ((model[s.segment.layer_index] == LayerKind::GatedDelta) != g) return 75;
+        ++(g ? gated : attention);
+    }
+    if (next != planned.layout.total_bytes || gated != 60 || attention != 40) return 76;
+    const PrefixStateSegment a0 = prefix_state_segment(planned.layout, 60).segment, a1 = prefix_state_segment(planned.layout, 61).segment,
+                             v0 = prefix_state_segment(planned.layout, 62).segment;
+    if (a0.layer_index != 3 || a0.kind != PrefixStateSegmentKind::AttentionKey || a0.head_index != 0 || a0.slot_offset_bytes != 0) return 77;
+    if (a1.kind != PrefixStateSegmentKind::AttentionKey || a1.head_index != 1 || a1.slot_offset_bytes != 8388608) return 78;
+    if (v0.kind != PrefixStateSegmentKind::AttentionValue || v0.head_index != 0) return 79;
+    if (validate_prefix_state_arena_extent(planned.layout, 64, planned.layout.total_bytes + 64) != PrefixStateTransferError::None) return 80;
+    if (validate_prefix_state_arena_extent(planned.layout, 64, planned.layout.total_bytes + 63) != PrefixStateTransferError::ArenaOutOfRange) return 81;
+    // copy routes: snapshot reads the live half, restore writes the canonical input half
+    const PrefixStateSegment conv = prefix_state_segment(planned.layout, 0).segment, rec = prefix_state_segment(planned.layout, 1).segment;
+    if (prefix_state_copy_route(conv, PrefixStateTransferDirection::Snapshot, false).source != PrefixStateBufferPlane::First ||
+        prefix_state_copy_route(conv, PrefixStateTransferDirection::Snapshot, true).source != PrefixStateBufferPlane::FirstOutput ||
+        prefix_state_copy_route(rec, PrefixStateTransferDirection::Snapshot, true).source != PrefixStateBufferPlane::SecondOutput) return 82;
+    const PrefixStateCopyRoute rc = prefix_state_copy_route(conv, PrefixStateTransferDirection::Restore, true);
+    if (rc.source != PrefixStateBufferPlane::Arena || rc.destination != PrefixStateBufferPlane::First ||
+        prefix_state_copy_route(rec, PrefixStateTransferDirection::Restore, true).destination != PrefixStateBufferPlane::Second) return 83;
+    // a small mixed schedule and the typed failures
+    const LayerKind mixed[4] = {LayerKind::FullAttention, LayerKind::GatedDelta, LayerKind::FullAttention, LayerKind::GatedDelta};
+    const PrefixStateLayoutSpec small{mixed, 4, 19, 7, 4, 8, 2, 2, 24, 40, 1920};
+    const PrefixStateLayoutResult synthetic = make_prefix_state_layout(small);
+    if (!synthetic || synthetic.layout.segment_count != 20 || synthetic.layout.total_bytes != 1920) return 84;
+    if (prefix_state_segment(synthetic.layout, 0).segment.layer_index != 1 || prefix_state_segment(synthetic.layout, 4).segment.layer_index != 0) return 85;
+    PrefixStateLayoutSpec bad = small;
+    bad.positions = 0;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::PositionOutOfRange) return 86;
+    bad.positions = 20;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::PositionOutOfRange) return 87;
+    bad = small; bad.expected_attention_layers = 3;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::FamilyCountMismatch) return 88;
+    bad = small; ++bad.expected_total_bytes;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::TotalMismatch) return 89;
+    bad = small; bad.gated_delta_convolution_bytes = ~0ull;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::Overflow) return 90;
+    const LayerKind unknown[2] = {LayerKind::GatedDelta, static_cast<LayerKind>(255)};
+    bad = small; bad.schedule = unknown; bad.layers = 2; bad.expected_gated_delta_layers = 1; bad.expected_attention_layers = 1;
+    if (make_prefix_state_layout(bad).error != PrefixStateLayoutError::InvalidSchedule) return 91;
+    if (prefix_state_segment(synthetic.layout, 20).error != PrefixStateLayoutError::SegmentOutOfRange) return 92;
+    // state record framing
+    const std::vector<LayerKind> two{LayerKind::GatedDelta, LayerKind::FullAttention};
+    if (state_record_bytes(two, 5) != 12 + 49152 + 2097152 + 2 * 2 * 5 * 512) return 93;
+    DecodeStatePool none;
+    DecodeStateSlot slot;
+    const std::byte junk[16] = {};
+    if (load_state_record(junk, sizeof(junk), none, two, slot, nullptr) != StateRecordError::MagicMismatch) return 94;
+    return 0;
+}
+
+// Snapshot -> scribble -> restore through one launch each, from a swapped phase; and the state
+// record written from one slot and loaded into another.
+int transfer_checks(tatara_ctx* ctx) {
+    constexpr std::uint32_t kCapacity = 96, kPositions = 40;
+    const std::vector<LayerKind> schedule{LayerKind::GatedDelta, LayerKind::FullAttention, LayerKind::GatedDelta};
+    DecodeStatePool pool;
+    std::vector<DecodeStateSlot> slots;
+    if (!create_state_pool(2, kCapacity, schedule, pool, slots)) return 100;
+    Rng rng{0xABCDull};
+    // fill every pool buffer with noise
+    for (auto& pl : pool.layers)
+        for (DeviceBuffer* b : {&pl.first, &pl.second}) {
+            std::vector<std::uint32_t> noise(b->bytes() / 4);
+            for (auto& w : noise) w = static_cast<std::uint32_t>(rng.next());
+            if (!upload(b->data(), noise)) return 101;
+        }
+    DecodeStateSlot& slot = slots[1];
+    slot.swapped[0] = true;   // layer 0 live in the output half, layer 2 in the input half
+    const PrefixStateLayoutResult planned = make_prefix_state_layout(pool, schedule, kPositions);
+    if (!planned || planned.layout.segment_count != 8) return 102;
+    DeviceBuffer arena(planned.layout.total_bytes + 256);
+    std::byte evidence[1] = {};
+    PrefixStateTransferResult snap = encode_prefix_state_snapshot(ctx, nullptr, pool, schedule, slot, arena, 256, kPositions, evidence, 1);
+    if (!snap || snap.segment_count != 8 || snap.state_bytes != planned.layout.total_bytes) return 103;
+    if (slot.status != DecodeStateSlotStatus::SnapshotPending || evidence[0] != std::byte{1}) return 104;
+    // a pending slot refuses layer work and a second transfer
+    {
+        LayerPass pass(ctx, nullptr);
+        DecodeBatchScratch scratch;
+        if (!create_batch_scratch(1, kCapacity, scratch)) return 105;
+        if (pass.encode_gated_delta(pool, 0, GatedDeltaWeights{}, {DecodeStream{&slot, 0}}, arena.data(), scratch) != CommandError::StateSlotMismatch) return 106;
+        if (encode_prefix_state_restore(ctx, nullptr, pool, schedule, slot, arena, 256, kPositions).error != PrefixStateTransferError::StateSlotNotReady) return 107;
+    }
+    if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 108;
+    PrefixStateTransferTicket stale = snap.ticket;
+    if (complete_prefix_state_transfer(snap.ticket, pool, slot, arena) != PrefixStateTransferError::None) return 109;
+    if (complete_prefix_state_transfer(snap.ticket, pool, slot, arena) != PrefixStateTransferError::AlreadyCompleted) return 110;
+    if (complete_prefix_state_transfer(stale, pool, slot, arena) != PrefixStateTransferError::StaleTicket) return 111;
+    if (slot.status != DecodeStateSlotStatus::Ready || slot.active_transfer_generation != 0) return 112;
+
+    // expected payload, assembled on the host from the pool contents
+    std::vector<std::byte> want(planned.layout.total_bytes), got(planned.layout.total_bytes);
+    for (std::uint32_t i = 0; i < planned.layout.segment_count; ++i) {
+        const PrefixStateSegment seg = prefix_state_segment(planned.layout, i).segment;
+        const PrefixStateCopyRoute route = prefix_state_copy_route(seg, PrefixStateTransferDirection::Snapshot, slot.swapped[seg.layer_index]);
+        const std::byte* src = state_transfer_detail::plane_address(pool, slot, seg.layer_index, route.source) + seg.slot_offset_bytes;
+        if (cudaMemcpy(want.data() + seg.snapshot_offset_bytes, src, seg.length_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return 113;
+    }
+    if (cudaMemcpy(got.data(), static_cast<std::byte*>(arena.data()) + 256, got.size(), cudaMemcpyDeviceToHost) != cudaSuccess) return 114;
+    if (got != want) return 115;
+
+    // restore into the other slot: canonical halves, phases reset, positions beyond the prefix untouched
+    DecodeStateSlot& other = slots[0];
+    other.swapped[2] = true;
+    std::vector<std::byte> tail_before(16);
+    const std::byte* tail = state_transfer_detail::plane_address(pool, other, 1, PrefixStateBufferPlane::First) + kPositions * 512;
+    if (cudaMemcpy(tail_before.data(), tail, 16, cudaMemcpyDeviceToHost) != cudaSuccess) return 116;
+    PrefixStateTransferResult rest = encode_prefix_state_restore(ctx, nullptr, pool, schedule, other, arena, 256, kPositions);
+    if (!rest || other.status != DecodeStateSlotStatus::RestorePending) return 117;
+    if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 118;
+    if (complete_prefix_state_transfer(rest.ticket, pool, other, arena) != PrefixStateTransferError::None) return 119;
+    if (other.swapped[0] || other.swapped[2] || other.status != DecodeStateSlotStatus::Ready) return 120;
+    for (std::uint32_t i = 0; i < planned.layout.segment_count; ++i) {
+        const PrefixStateSegment seg = prefix_state_segment(planned.layout, i).segment;
+        const PrefixStateCopyRoute route = prefix_state_copy_route(seg, PrefixStateTransferDirection::Restore, false);
+        const std::byte* dst = state_transfer_detail::plane_address(pool, other, seg.layer_index, route.destination) + seg.slot_offset_bytes;
+        if (cudaMemcpy(got.data() + seg.snapshot_offset_bytes, dst, seg.length_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return 121;
+    }
+    if (got != want) return 122;
+    std::vector<std::byte> tail_after(16);
+    if (cudaMemcpy(tail_after.data(), tail, 16, cudaMemcpyDeviceToHost) != cudaSuccess || tail_after != tail_before) return 123;
+
+    // the state record: slot 1 (layer 0 swapped) -> bytes -> slot 0; both then serialise identically
+    std::vector<std::byte> record, again;
+    if (write_state_record(pool, schedule, slot, kPositions, record) != StateRecordError::None) return 124;
+    if (record.size() != state_record_bytes(schedule, kPositions) || std::memcmp(record.data(), "Q36BRS01", 8) != 0) return 125;
+    std::uint32_t count = 0;
+    other.swapped[0] = true;
+    if (load_state_record(record.data(), record.size(), pool, schedule, other, &count) != StateRecordError::None || count != kPositions) return 126;
+    if (other.swapped[0]) return 127;
+    if (write_state_record(pool, schedule, other, kPositions, again) != StateRecordError::None || again != record) return 128;
+    if (load_state_record(record.data(), record.size() - 1, pool, schedule, other, nullptr) != StateRecordError::Truncated) return 129;
+    record.push_back(std::byte{0});
+    if (load_state_record(record.data(), record.size(), pool, schedule, other, nullptr) != StateRecordError::UnconsumedBytes) return 130;
+    const std::uint32_t too_many = kCapacity + 1;
+    std::memcpy(record.data() + 8, &too_many, 4);
+    if (load_state_record(record.data(), record.size(), pool, schedule, other, nullptr) != StateRecordError::PositionOutOfRange) return 131;
+    // arena bounds and poisoned slots are typed
+    if (encode_prefix_state_snapshot(ctx, nullptr, pool, schedule, slot, arena, 512, kPositions, evidence, 1).error != PrefixStateTransferError::ArenaOutOfRange) return 132;
+    if (encode_prefix_state_snapshot(ctx, nullptr, pool, schedule, slot, arena, 256, kPositions, evidence, 0).error != PrefixStateTransferError::PhaseEvidenceTooSmall) return 133;
+    slot.status = DecodeStateSlotStatus::Poisoned;
+    if (encode_prefix_state_snapshot(ctx, nullptr, pool, schedule, slot, arena, 256, kPositions, evidence, 1).error != PrefixStateTransferError::PoisonedStateSlot) return 134;
+    return 0;
+}
+
 int main() {
     if (const int rc = host_only_checks(); rc != 0) { std::printf("host check failed: %d\n", rc); return rc; }
+    if (const int rc = layout_checks(); rc != 0) { std::printf("layout check failed: %d\n", rc); return rc; }
     tatara_ctx* ctx = nullptr;
     const tatara_status st = tatara_ctx_create(0, &ctx);
     if (st == TATARA_INVALID_DEVICE) { std::printf("host checks passed; no B200 present, device checks skipped\n"); return 0; }
     if (st != TATARA_OK) return 2;
     int rc = device_checks(ctx);
     if (rc == 0) rc = projection_checks(ctx);
+    if (rc == 0) rc = transfer_checks(ctx);
     tatara_ctx_destroy(ctx);
     if (rc != 0) { std::printf("device check failed: %d\n", rc); return rc; }
     std::printf("host and device checks passed\n");
