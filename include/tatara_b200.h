@@ -322,6 +322,35 @@ typedef struct tatara_copy_segment {
 tatara_status tatara_state_copy(tatara_ctx* ctx, void* stream, const tatara_copy_segment* segments,
                                 uint32_t n_segments);
 
+/* ---- speculative-decode support: the GDN tape of a verify band and its replay -----------
+ * A verify band of at most 16 rows runs the block kernels in their tape forms; after partial
+ * acceptance the host restores the pre-band state and replays the committed rows
+ * (src/engine/speculative_decode.cpp:517-596).  Tape geometry is the reference's
+ * (tools/generate_kernel_library.py:2045-2049): 40 layers x 16 rows;
+ *   tape      f32: delta [layer][row][32][128] | key [layer][row][16][128] | gates [layer][row][32][2]
+ *   conv_tape bf16: [layer][row][3][8192], the conv tail after each row.
+ * Unlike the reference kernels, which silently skip the tape when rows > 16, these reject it. */
+uint64_t tatara_gdn_tape_bytes(void);
+uint64_t tatara_gdn_conv_tape_bytes(void);
+/* gdn_conv_tape_blk: tatara_gdn_prepare plus slots 8 conv_tape, 9 tape_layer
+ * (src/backend/metal/kernels/prefill_gdn.metal:322-420; src/runtime/prefill_step.cpp:1931-1946). */
+tatara_status tatara_gdn_prepare_tape(tatara_ctx* ctx, void* stream, const void* projection,
+                                      const void* conv_in, const void* conv_weights, void* qk,
+                                      void* value, void* z, void* conv_out, uint32_t rows,
+                                      void* conv_tape, uint32_t tape_layer);
+/* gdn_recurrence_gates_tape_blk: the sequential scan of tatara_gdn_prefill (chunk 1) plus slots
+ * 9 tape, 10 tape_layer (prefill_gdn.metal:434-527; prefill_step.cpp:2003-2028). */
+tatara_status tatara_gdn_prefill_tape(tatara_ctx* ctx, void* stream, const void* qk,
+                                      const void* value, const void* decay, const void* beta,
+                                      const void* state_in, void* y, void* state_out, uint32_t rows,
+                                      void* tape, uint32_t tape_layer);
+/* gdn_tape_replay_blk: slots 0 tape, 1 state_in, 2 state_out, 3 steps, 4 tape_layer
+ * (prefill_gdn.metal:529-569; speculative_decode.cpp:546-555).  state_out has the bits the
+ * taped scan itself reaches after `steps` rows; steps == 0 copies the state. */
+tatara_status tatara_gdn_tape_replay(tatara_ctx* ctx, void* stream, const void* tape,
+                                     const void* state_in, void* state_out, uint32_t steps,
+                                     uint32_t tape_layer);
+
 #ifdef __cplusplus
 }
 #endif

@@ -172,6 +172,36 @@ def gdn_gate_norm(y, z, weight):
     return out
 
 
+TAPE_ROWS, TAPE_LAYERS = 16, 40
+
+
+def gdn_tape_floats() -> int:
+    f = lib().orc_gdn_tape_floats
+    f.restype = ctypes.c_uint64
+    return int(f())
+
+
+def gdn_scan_tape(qk, value, decay, beta, state_in, tape, tape_layer, threads=1):
+    """Sequential scan of rows <= 16 that also fills `tape` (f32, gdn_tape_floats()) for `tape_layer`."""
+    rows = qk.shape[0]
+    y = np.zeros((rows, 4096), np.uint16)
+    state_out = np.zeros((32, 128, 128), np.float32)
+    lib().orc_gdn_scan_tape(_u16(qk), _u16(value), _f32(decay), _f32(beta), _f32(state_in), _u16(y), _f32(state_out),
+                            _u32(rows), _f32(tape), _u32(tape_layer), _int(threads))
+    return y, state_out
+
+
+def gdn_tape_replay(tape, state_in, steps, tape_layer, threads=1):
+    state_out = np.zeros((32, 128, 128), np.float32)
+    lib().orc_gdn_tape_replay(_f32(tape), _f32(state_in), _f32(state_out), _u32(steps), _u32(tape_layer), _int(threads))
+    return state_out
+
+
+def gdn_conv_tape(projection, conv_state, conv_tape, tape_layer):
+    """Fills conv_tape [40][16][3][8192] u16 for `tape_layer` with the conv tail after every row."""
+    lib().orc_gdn_conv_tape(_u16(projection), _u16(conv_state), _u32(projection.shape[0]), _u16(conv_tape), _u32(tape_layer))
+
+
 def _u32a(a):
     assert a.dtype == np.uint32
     return _p(a, ctypes.POINTER(ctypes.c_uint32))

@@ -578,4 +578,104 @@ void orc_project_dense(const u16* x, u32 x_stride, u32 rows, const u16* weights,
     });
 }
 
+// ---- speculative-decode support: the GDN tape of a verify band and its replay ----------
+// Tape geometry of the reference (tools/generate_kernel_library.py:2045-2049): 40 layers x 16
+// rows; f32 regions  delta [layer][row][32 v-heads][128]  at 0,  key [layer][row][16 k-heads][128]
+// at 40*16*32*128,  gates [layer][row][32][2] = (decay, beta)  after the key region.
+constexpr u32 kTapeRows = 16, kTapeLayers = 40;
+constexpr u64 kTapeKeyOff = static_cast<u64>(kTapeLayers) * kTapeRows * 32 * 128;
+constexpr u64 kTapeGateOff = kTapeKeyOff + static_cast<u64>(kTapeLayers) * kTapeRows * 16 * 128;
+
+u64 orc_gdn_tape_floats() { return kTapeGateOff + static_cast<u64>(kTapeLayers) * kTapeRows * 32 * 2; }
+
+// The sequential scan that also records, per row: delta per (v-head, v-dim), the key row of each
+// k-head as f32, and (decay, beta) per v-head (gdn_recurrence_gates_tape_blk,
+// prefill_gdn.metal:434-527).  rows <= 16.
+void orc_gdn_scan_tape(const u16* qk, const u16* value, const float* decay, const float* beta,
+                       const float* state_in, u16* y, float* state_out, u32 rows, float* tape,
+                       u32 tape_layer, int threads) {
+    parallel_for(kGdnValueHeads * kGd, threads, [&](u32 item) {
+        const u32 vh = item / kGd, vd = item % kGd;
+        const u32 qbase = (vh >> 1) * kGd, kbase = kGdnQk / 2 + qbase;
+        const u64 sbase = static_cast<u64>(item) * kGd;
+        float state[kGd];
+        for (u32 e = 0; e < kGd; ++e) state[e] = state_in[sbase + e];
+        for (u32 step = 0; step < rows; ++step) {
+            const u16* qkr = qk + static_cast<u64>(step) * kGdnQk;
+            const float dec = decay[step * kGdnValueHeads + vh];
+            const float bet = beta[step * kGdnValueHeads + vh];
+            float lanes[32];
+            for (u32 l = 0; l < 32; ++l) {
+                float kvp = 0.0f;
+                for (u32 i = 0; i < 4; ++i) {
+                    const u32 e = l * 4 + i;
+                    state[e] = ftz(state[e] * dec);
+                    kvp = std::fma(state[e], bf(qkr[kbase + e]), kvp);
+                }
+                lanes[l] = kvp;
+            }
+            const float kv = pairs_sum(lanes, 32);
+            const float v = bf(value[static_cast<u64>(step) * kGdnV + vh * kGd + vd]);
+            const float delta = ftz(ftz(v - kv) * bet);
+            const u64 tape_row = static_cast<u64>(tape_layer) * kTapeRows + step;
+            tape[(tape_row * kGdnValueHeads + vh) * kGd + vd] = delta;
+            if (vd == 0) {
+                if ((vh & 1u) == 0)
+                    for (u32 e = 0; e < kGd; ++e)
+                        tape[kTapeKeyOff + (tape_row * kGdnKeyHeads + (vh >> 1)) * kGd + e] = bf(qkr[kbase + e]);
+                tape[kTapeGateOff + (tape_row * kGdnValueHeads + vh) * 2] = dec;
+                tape[kTapeGateOff + (tape_row * kGdnValueHeads + vh) * 2 + 1] = bet;
+            }
+            for (u32 l = 0; l < 32; ++l) {
+                float o = 0.0f;
+                for (u32 i = 0; i < 4; ++i) {
+                    const u32 e = l * 4 + i;
+                    state[e] = std::fma(bf(qkr[kbase + e]), delta, state[e]);
+                    o = std::fma(state[e], bf(qkr[qbase + e]), o);
+                }
+                lanes[l] = o;
+            }
+            y[static_cast<u64>(step) * kGdnV + vh * kGd + vd] = ftzb(bf16r(pairs_sum(lanes, 32)));
+        }
+        for (u32 e = 0; e < kGd; ++e) state_out[sbase + e] = state[e];
+    });
+}
+
+// Rebuilds the state after `steps` committed rows from the pre-band state and the tape, with the
+// scan's own two update statements (gdn_tape_replay_blk, prefill_gdn.metal:529-569).
+void orc_gdn_tape_replay(const float* tape, const float* state_in, float* state_out, u32 steps,
+                         u32 tape_layer, int threads) {
+    parallel_for(kGdnValueHeads * kGd, threads, [&](u32 item) {
+        const u32 vh = item / kGd, vd = item % kGd;
+        const u64 sbase = static_cast<u64>(item) * kGd;
+        float state[kGd];
+        for (u32 e = 0; e < kGd; ++e) state[e] = state_in[sbase + e];
+        for (u32 step = 0; step < steps; ++step) {
+            const u64 tape_row = static_cast<u64>(tape_layer) * kTapeRows + step;
+            const float dec = tape[kTapeGateOff + (tape_row * kGdnValueHeads + vh) * 2];
+            const float delta = tape[(tape_row * kGdnValueHeads + vh) * kGd + vd];
+            const float* key = tape + kTapeKeyOff + (tape_row * kGdnKeyHeads + (vh >> 1)) * kGd;
+            for (u32 e = 0; e < kGd; ++e) {
+                state[e] = ftz(state[e] * dec);
+                state[e] = std::fma(key[e], delta, state[e]);
+            }
+        }
+        for (u32 e = 0; e < kGd; ++e) state_out[sbase + e] = state[e];
+    });
+}
+
+// gdn_conv_tape_blk (prefill_gdn.metal:322-420): gdn_prepare that also records the conv tail
+// (the three newest taps) after EVERY row: conv_tape [layer][16 rows][3][8192] bf16.
+void orc_gdn_conv_tape(const u16* projection, const u16* conv_state, u32 rows, u16* conv_tape,
+                       u32 tape_layer) {
+    for (u32 row = 0; row < rows; ++row)
+        for (u32 ch = 0; ch < kGdnConv; ++ch)
+            for (u32 t = 0; t < 3; ++t) {
+                const u32 logical = row + t + 1;
+                const u16 tap = logical < 3 ? conv_state[logical * kGdnConv + ch]
+                                            : projection[static_cast<u64>(logical - 3) * kGdnProj + ch];
+                conv_tape[((static_cast<u64>(tape_layer) * kTapeRows + row) * 3 + t) * kGdnConv + ch] = tap;
+            }
+}
+
 } // extern "C"

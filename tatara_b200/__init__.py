@@ -275,6 +275,22 @@ class Context:
                                              _ptr(state_out), _u32(rows), _u32(chunk), _ptr(scratch),
                                              _u64(nbytes)))
 
+    # ---- speculative-decode support: GDN tape and replay
+    def gdn_prepare_tape(self, projection, conv_in, conv_weights, qk, value, z, conv_out, rows, conv_tape, tape_layer,
+                         stream=None):
+        self._check(lib().tatara_gdn_prepare_tape(self._h, self._stream(stream), _ptr(projection), _ptr(conv_in),
+                                                  _ptr(conv_weights), _ptr(qk), _ptr(value), _ptr(z), _ptr(conv_out),
+                                                  _u32(rows), _ptr(conv_tape), _u32(tape_layer)))
+
+    def gdn_prefill_tape(self, qk, value, decay, beta, state_in, y, state_out, rows, tape, tape_layer, stream=None):
+        self._check(lib().tatara_gdn_prefill_tape(self._h, self._stream(stream), _ptr(qk), _ptr(value), _ptr(decay),
+                                                  _ptr(beta), _ptr(state_in), _ptr(y), _ptr(state_out), _u32(rows),
+                                                  _ptr(tape), _u32(tape_layer)))
+
+    def gdn_tape_replay(self, tape, state_in, state_out, steps, tape_layer, stream=None):
+        self._check(lib().tatara_gdn_tape_replay(self._h, self._stream(stream), _ptr(tape), _ptr(state_in),
+                                                 _ptr(state_out), _u32(steps), _u32(tape_layer)))
+
     # ---- affine-Q4 projections
     @staticmethod
     def q4_matrices(triples):
@@ -312,6 +328,18 @@ class Context:
 
     def state_copy(self, segments, stream=None):
         self._check(lib().tatara_state_copy(self._h, self._stream(stream), segments, _u32(len(segments))))
+
+
+def gdn_tape_bytes() -> int:
+    f = lib().tatara_gdn_tape_bytes
+    f.restype = ctypes.c_uint64
+    return int(f())
+
+
+def gdn_conv_tape_bytes() -> int:
+    f = lib().tatara_gdn_conv_tape_bytes
+    f.restype = ctypes.c_uint64
+    return int(f())
 
 
 def gdn_prefill_scratch_bytes(rows: int) -> int:

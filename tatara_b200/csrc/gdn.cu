@@ -55,13 +55,17 @@ __device__ __forceinline__ __nv_bfloat16 head_normalise(float* head_smem, uint32
     return bmul(f2bf(activated * inverse), scale);
 }
 
-// grid (96, rows) x 128 threads, exactly the reference's decomposition.
+// grid (96, rows) x 128 threads, exactly the reference's decomposition.  kTape: the conv tail
+// (the three newest taps) is also recorded after EVERY row, conv_tape [layer][16][3][8192], so a
+// rollback can restore it at any row (gdn_conv_tape_blk, prefill_gdn.metal:322-420).
+template <bool kTape>
 __global__ void __launch_bounds__(128)
 gdn_prepare_kernel(const __nv_bfloat16* __restrict__ projection,
                    const __nv_bfloat16* __restrict__ conv_state,
                    const __nv_bfloat16* __restrict__ conv_weights, __nv_bfloat16* __restrict__ qk,
                    __nv_bfloat16* __restrict__ value, __nv_bfloat16* __restrict__ z,
-                   __nv_bfloat16* __restrict__ new_conv_state, uint32_t rows) {
+                   __nv_bfloat16* __restrict__ new_conv_state, uint32_t rows,
+                   __nv_bfloat16* __restrict__ conv_tape, uint32_t tape_layer) {
     __shared__ float head_smem[kGdnDim];
     const uint32_t group = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
     if (group < kGdnConv / kGdnDim) {
@@ -71,6 +75,11 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ projection,
         if (row + 1u == rows) {
 #pragma unroll
             for (uint32_t t = 0; t < 3; ++t) new_conv_state[t * kGdnConv + channel] = f2bf(taps[t + 1u]);
+        }
+        if (kTape) {
+#pragma unroll
+            for (uint32_t t = 0; t < 3; ++t)
+                conv_tape[((uint64_t(tape_layer) * 16u + row) * 3u + t) * kGdnConv + channel] = f2bf(taps[t + 1u]);
         }
         if (group < kGdnQk / kGdnDim) {
             qk[uint64_t(row) * kGdnQk + channel] =
@@ -317,11 +326,29 @@ extern "C" tatara_status tatara_gdn_prepare(tatara_ctx* ctx, void* stream, const
     if (!aligned(conv_weights, 8)) return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare: conv weights alignment");
     if (conv_in == conv_out) return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_prepare: conv_in aliases conv_out");
     if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_prepare: rows");
-    gdn_prepare_kernel<<<dim3(96, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    gdn_prepare_kernel<false><<<dim3(96, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(projection), static_cast<const bf16*>(conv_in),
         static_cast<const bf16*>(conv_weights), static_cast<bf16*>(qk), static_cast<bf16*>(value),
-        static_cast<bf16*>(z), static_cast<bf16*>(conv_out), rows);
+        static_cast<bf16*>(z), static_cast<bf16*>(conv_out), rows, nullptr, 0);
     return check_launch(ctx, "gdn_prepare");
+}
+
+extern "C" tatara_status tatara_gdn_prepare_tape(tatara_ctx* ctx, void* stream, const void* projection,
+                                                 const void* conv_in, const void* conv_weights, void* qk,
+                                                 void* value, void* z, void* conv_out, uint32_t rows,
+                                                 void* conv_tape, uint32_t tape_layer) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !conv_in || !conv_weights || !qk || !value || !z || !conv_out || !conv_tape)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare_tape: null buffer");
+    if (!aligned(conv_weights, 8)) return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare_tape: conv weights alignment");
+    if (conv_in == conv_out) return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_prepare_tape: conv_in aliases conv_out");
+    if (rows == 0 || rows > 16u || tape_layer >= 40u)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_prepare_tape: rows above 16 or layer above 39");
+    gdn_prepare_kernel<true><<<dim3(96, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(projection), static_cast<const bf16*>(conv_in),
+        static_cast<const bf16*>(conv_weights), static_cast<bf16*>(qk), static_cast<bf16*>(value),
+        static_cast<bf16*>(z), static_cast<bf16*>(conv_out), rows, static_cast<bf16*>(conv_tape), tape_layer);
+    return check_launch(ctx, "gdn_prepare_tape");
 }
 
 extern "C" tatara_status tatara_gdn_gates(tatara_ctx* ctx, void* stream, const void* projection,

@@ -492,4 +492,38 @@ inline StateRecordError load_state_record(const std::byte* record, std::size_t r
     return StateRecordError::None;
 }
 
+// ---- speculative-decode rollback (src/engine/speculative_decode.cpp:517-596) -----------------
+// After a verify band of at most 16 rows was run with the tape kernels and only `committed` rows
+// were accepted: the caller has put the pre-band gated-delta state back into the slot's live
+// halves; this replays `committed` taped rows from each live recurrent plane into its partner
+// and installs the conv tail recorded after row committed-1 into the partner conv plane (all conv
+// tails in one tatara_state_copy launch).  When the stream has completed, advance_decode_state
+// flips the halves, exactly as after a decode token.
+inline CommandError encode_gdn_tape_rollback(tatara_ctx* ctx, cudaStream_t stream, const DecodeStatePool& pool,
+                                             const std::vector<LayerKind>& schedule, const DecodeStateSlot& slot,
+                                             const void* tape, const void* conv_tape, std::uint32_t committed) {
+    using namespace state_transfer_detail;
+    if (ctx == nullptr) return CommandError::InvalidDevice;
+    if (tape == nullptr || conv_tape == nullptr) return CommandError::InvalidBuffer;
+    if (committed == 0 || committed > 16u || schedule.size() > 40u) return CommandError::InvalidDispatchExtent;
+    if (!slot_fits_pool(pool, slot) || schedule.size() != pool.layers.size() || slot.status != DecodeStateSlotStatus::Ready)
+        return CommandError::StateSlotMismatch;
+    const std::uint64_t conv_row_bytes = kGdnConvStateValues * 2;
+    std::vector<tatara_copy_segment> tails;
+    for (std::uint32_t l = 0; l < schedule.size(); ++l) {
+        if (schedule[l] != LayerKind::GatedDelta) continue;
+        const bool swapped = slot.swapped[l];
+        const std::byte* rec_in = plane_address(pool, slot, l, swapped ? PrefixStateBufferPlane::SecondOutput : PrefixStateBufferPlane::Second);
+        std::byte* rec_out = plane_address(pool, slot, l, swapped ? PrefixStateBufferPlane::Second : PrefixStateBufferPlane::SecondOutput);
+        const tatara_status st = tatara_gdn_tape_replay(ctx, stream, tape, rec_in, rec_out, committed, l);
+        if (st != TATARA_OK) return to_command_error(st);
+        std::byte* conv_out = plane_address(pool, slot, l, swapped ? PrefixStateBufferPlane::First : PrefixStateBufferPlane::FirstOutput);
+        tails.push_back(tatara_copy_segment{static_cast<const std::byte*>(conv_tape) + (std::uint64_t{l} * 16u + (committed - 1u)) * conv_row_bytes,
+                                            conv_out, conv_row_bytes});
+    }
+    if (tails.empty()) return CommandError::None;
+    const tatara_status st = tatara_state_copy(ctx, stream, tails.data(), static_cast<std::uint32_t>(tails.size()));
+    return st == TATARA_OK ? CommandError::None : to_command_error(st);
+}
+
 } // namespace tatara::runtime

@@ -426,6 +426,56 @@ int transfer_checks(tatara_ctx* ctx) {
     return 0;
 }
 
+// Rollback of a verify band: a 6-row band is taped on one gated-delta layer, 4 rows are committed;
+// the rolled-back slot must hold the bits of a straight 4-row run.
+int rollback_checks(tatara_ctx* ctx) {
+    constexpr std::uint32_t kBand = 6, kCommitted = 4;
+    const std::vector<LayerKind> schedule{LayerKind::FullAttention, LayerKind::GatedDelta};
+    DecodeStatePool pool;
+    std::vector<DecodeStateSlot> slots;
+    if (!create_state_pool(1, 64, schedule, pool, slots)) return 140;
+    DecodeStateSlot& slot = slots[0];
+    Rng rng{0x7A9Eull};
+    std::vector<u16> proj(kBand * 12352), conv_w(8192 * 4), conv(3 * 8192), a_log(32), dt_bias(32);
+    rng.fill(proj); rng.fill(conv_w, 0.5f); rng.fill(conv); rng.fill(dt_bias, 0.5f);
+    for (auto& x : a_log) x = to_bf16(std::log(1.0f + 15.0f * rng.uniform()));
+    std::vector<float> state(32 * 128 * 128);
+    for (auto& x : state) x = 0.02f * rng.normal();
+    using state_transfer_detail::plane_address;
+    std::byte* conv_live = plane_address(pool, slot, 1, PrefixStateBufferPlane::First);
+    std::byte* rec_live = plane_address(pool, slot, 1, PrefixStateBufferPlane::Second);
+    std::byte* conv_other = plane_address(pool, slot, 1, PrefixStateBufferPlane::FirstOutput);
+    std::byte* rec_other = plane_address(pool, slot, 1, PrefixStateBufferPlane::SecondOutput);
+    if (!upload(conv_live, conv) || !upload(rec_live, state)) return 141;
+    DeviceBuffer d_proj(proj.size() * 2), d_w(conv_w.size() * 2), d_alog(64), d_dt(64), qk(kBand * 4096 * 2), v(kBand * 4096 * 2),
+        z(kBand * 4096 * 2), y(kBand * 4096 * 2), decay(kBand * 32 * 4), beta(kBand * 32 * 4), tape(tatara_gdn_tape_bytes()),
+        conv_tape(tatara_gdn_conv_tape_bytes()), scratch_conv(3 * 8192 * 2), scratch_state(state.size() * 4);
+    if (!upload(d_proj.data(), proj) || !upload(d_w.data(), conv_w) || !upload(d_alog.data(), a_log) || !upload(d_dt.data(), dt_bias)) return 142;
+    // the verify band, taped, writing into scratch planes (the slot keeps the pre-band state)
+    if (tatara_gdn_prepare_tape(ctx, nullptr, d_proj.data(), conv_live, d_w.data(), qk.data(), v.data(), z.data(), scratch_conv.data(), kBand,
+                                conv_tape.data(), 1) != TATARA_OK) return 143;
+    if (tatara_gdn_gates(ctx, nullptr, d_proj.data(), 12352, d_alog.data(), d_dt.data(), decay.data(), beta.data(), kBand) != TATARA_OK) return 144;
+    if (tatara_gdn_prefill_tape(ctx, nullptr, qk.data(), v.data(), decay.data(), beta.data(), rec_live, y.data(), scratch_state.data(), kBand,
+                                tape.data(), 1) != TATARA_OK) return 145;
+    if (encode_gdn_tape_rollback(ctx, nullptr, pool, schedule, slot, tape.data(), conv_tape.data(), 0) != CommandError::InvalidDispatchExtent) return 146;
+    if (encode_gdn_tape_rollback(ctx, nullptr, pool, schedule, slot, tape.data(), conv_tape.data(), kCommitted) != CommandError::None) return 147;
+    // the straight run of the committed rows
+    DeviceBuffer want_conv(3 * 8192 * 2), want_state(state.size() * 4);
+    if (tatara_gdn_prepare(ctx, nullptr, d_proj.data(), conv_live, d_w.data(), qk.data(), v.data(), z.data(), want_conv.data(), kCommitted) != TATARA_OK) return 148;
+    if (tatara_gdn_prefill(ctx, nullptr, qk.data(), v.data(), decay.data(), beta.data(), rec_live, y.data(), want_state.data(), kCommitted, 1,
+                           nullptr, 0) != TATARA_OK) return 149;
+    if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 150;
+    std::vector<std::byte> a(state.size() * 4), b(a.size()), c(3 * 8192 * 2), d(c.size());
+    if (cudaMemcpy(a.data(), rec_other, a.size(), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(b.data(), want_state.data(), b.size(), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(c.data(), conv_other, c.size(), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(d.data(), want_conv.data(), d.size(), cudaMemcpyDeviceToHost) != cudaSuccess) return 151;
+    if (a != b) return 152;
+    if (c != d) return 153;
+    advance_decode_state(pool, {DecodeStream{&slot, 0}});
+    return slot.swapped[1] ? 0 : 154;
+}
+
 int main() {
     if (const int rc = host_only_checks(); rc != 0) { std::printf("host check failed: %d\n", rc); return rc; }
     if (const int rc = layout_checks(); rc != 0) { std::printf("layout check failed: %d\n", rc); return rc; }
@@ -436,6 +486,7 @@ int main() {
     int rc = device_checks(ctx);
     if (rc == 0) rc = projection_checks(ctx);
     if (rc == 0) rc = transfer_checks(ctx);
+    if (rc == 0) rc = rollback_checks(ctx);
     tatara_ctx_destroy(ctx);
     if (rc != 0) { std::printf("device check failed: %d\n", rc); return rc; }
     std::printf("host and device checks passed\n");

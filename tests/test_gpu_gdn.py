@@ -294,3 +294,79 @@ def test_chunked_prefill_config3_full_size(ctx):
     ctx.sync()
     assert_close_bf16(host_u16(y), oy, "config 3 outputs")
     state_close(host_f32(s), ostate, "config 3 final state")
+
+
+# ---- speculative-decode support: tape of a verify band and its replay ------------------------
+def _band(rng, rows):
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    qk, v, z, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    decay, beta = oracle.gdn_gates(proj, a_log, dt_bias)
+    return proj, conv, conv_w, qk, v, decay, beta, state
+
+
+@pytest.mark.parametrize("rows", [1, 7, 16])
+def test_tape_scan_and_replay(ctx, rows):
+    """The taped scan computes what the plain scan computes (same bits), its tape matches the oracle's, and
+    replaying r rows onto the pre-band state gives the bits of the device scan after r rows."""
+    rng = np.random.default_rng(40 + rows)
+    proj, conv, conv_w, qk, v, decay, beta, state = _band(rng, rows)
+    d_qk, d_v, d_dec, d_beta, d_state = dev_bf16(qk), dev_bf16(v), dev_f32(decay), dev_f32(beta), dev_f32(state)
+    tape = torch.full((tb.gdn_tape_bytes() // 4,), 7.5, dtype=torch.float32, device="cuda")
+    y, out = bf((rows, 4096)), torch.zeros_like(d_state)
+    y0, out0 = bf((rows, 4096)), torch.zeros_like(d_state)
+    layer = 17
+    ctx.gdn_prefill_tape(d_qk, d_v, d_dec, d_beta, d_state, y, out, rows, tape, layer)
+    ctx.gdn_prefill(d_qk, d_v, d_dec, d_beta, d_state, y0, out0, rows, chunk=1)
+    ctx.sync()
+    assert torch.equal(y.view(torch.int16), y0.view(torch.int16)) and torch.equal(out.view(torch.int32), out0.view(torch.int32))
+    want = np.full(oracle.gdn_tape_floats(), np.float32(7.5))
+    oracle.gdn_scan_tape(qk, v, decay, beta, state, want, layer, threads=oracle.hardware_threads())
+    got = host_f32(tape)
+    assert np.array_equal(got == np.float32(7.5), want == np.float32(7.5))          # same cells written
+    key_off, gate_off = 40 * 16 * 32 * 128, 40 * 16 * 32 * 128 + 40 * 16 * 16 * 128
+    assert np.array_equal(got[key_off:], want[key_off:])                              # keys and gates exactly
+    np.testing.assert_allclose(got[:key_off], want[:key_off], rtol=2e-4, atol=2e-5)   # deltas: f32 reduction order
+    for r in sorted({0, 1, rows // 2, rows}):
+        replayed = torch.zeros_like(d_state)
+        ctx.gdn_tape_replay(tape, d_state, replayed, r, layer)
+        if r == 0:
+            ref = d_state
+        else:
+            ref, yy = torch.zeros_like(d_state), bf((r, 4096))
+            ctx.gdn_prefill(d_qk, d_v, d_dec, d_beta, d_state, yy, ref, r, chunk=1)
+        ctx.sync()
+        assert torch.equal(replayed.view(torch.int32), ref.view(torch.int32)), f"replay of {r} rows"
+    np.testing.assert_allclose(host_f32(out), oracle.gdn_tape_replay(want, state, rows, layer, threads=4), rtol=1e-3, atol=1e-4)
+
+
+def test_conv_tape_matches_oracle_and_block_prepare(ctx):
+    rng = np.random.default_rng(50)
+    rows = 11
+    proj, conv, conv_w, *_ = _band(rng, rows)
+    d_proj, d_conv, d_w = dev_bf16(proj), dev_bf16(conv), dev_bf16(conv_w)
+    conv_tape = torch.zeros((40, 16, 3, 8192), dtype=torch.bfloat16, device="cuda")
+    assert conv_tape.numel() * 2 == tb.gdn_conv_tape_bytes()
+    qk, v, z, new_conv = bf((rows, 4096)), bf((rows, 4096)), bf((rows, 4096)), bf((3, 8192))
+    ctx.gdn_prepare_tape(d_proj, d_conv, d_w, qk, v, z, new_conv, rows, conv_tape, 5)
+    ctx.sync()
+    want = np.zeros((40, 16, 3, 8192), np.uint16)
+    oracle.gdn_conv_tape(proj, conv, want, 5)
+    assert np.array_equal(host_u16(conv_tape), want)
+    pqk, pv, pz, pconv = gpu_prepare(ctx, proj, conv, conv_w)
+    assert np.array_equal(host_u16(qk), pqk) and np.array_equal(host_u16(v), pv) and np.array_equal(host_u16(new_conv), pconv)
+    assert np.array_equal(host_u16(conv_tape)[5, rows - 1], pconv)
+
+
+def test_tape_entry_points_reject_long_bands(ctx):
+    t = torch.zeros(64, device="cuda")
+    before = ctx.launches
+    for call in (lambda: ctx.gdn_prefill_tape(t, t, t, t, t, t, torch.zeros(64, device="cuda"), 17, t, 0),
+                 lambda: ctx.gdn_prefill_tape(t, t, t, t, t, t, torch.zeros(64, device="cuda"), 4, t, 40),
+                 lambda: ctx.gdn_tape_replay(t, t, torch.zeros(64, device="cuda"), 17, 0),
+                 lambda: ctx.gdn_prepare_tape(t, t, t, t, t, t, torch.zeros(64, device="cuda"), 17, t, 0)):
+        with pytest.raises(tb.TataraError) as e:
+            call()
+        assert e.value.status == tb.STATUS_NAMES.index("InvalidDispatchExtent")
+    assert ctx.launches == before

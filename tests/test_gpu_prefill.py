@@ -34,7 +34,8 @@ def run_prefill(ctx, q, gate, keys, values, base, rows, cap, pad_rows=3):
 
 
 @pytest.mark.parametrize("base,rows", [(0, 1), (0, 64), (0, 128), (0, 129), (0, 200), (300, 77), (64, 256),
-                                       (1000, 130), (5, 513)])
+                                       (1000, 130), (5, 513),
+                                       (2047, 16), (777, 5)])   # the 16-row verify band of speculative decoding
 def test_prefill_matches_oracle(ctx, base, rows):
     rng = np.random.default_rng(base * 7 + rows)
     cap = base + rows + 5

@@ -164,3 +164,45 @@ def test_q4_project_policies_agree_within_rounding():
     assert np.abs(exact - dense).max() <= 2e-2
     assert np.dot(exact.ravel(), dense.ravel()) / np.linalg.norm(exact) / np.linalg.norm(dense) >= 0.9999
     assert 0.2 < exact.std() < 2.0
+
+
+def _band(rng, rows):
+    """A verify band: prepared q/k/v rows, gates, conv state, initial state (the GDN step's distributions)."""
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    qk, v, z, new_conv = oracle.gdn_prepare(proj, conv, conv_w)
+    decay, beta = oracle.gdn_gates(proj, a_log, dt_bias)
+    return proj, conv, conv_w, qk, v, decay, beta, state
+
+
+def test_gdn_tape_replay_reaches_the_scan_state():
+    """Replay of r taped rows onto the pre-band state has the bits of the scan after r rows
+    (the generation pin of gdn_tape_replay_blk, prefill_gdn.metal:529-534); the taped scan's own
+    outputs are those of the plain scan; layers do not share tape cells."""
+    rng = np.random.default_rng(31)
+    rows = 16
+    proj, conv, conv_w, qk, v, decay, beta, state = _band(rng, rows)
+    tape = np.full(oracle.gdn_tape_floats(), np.float32(7.5))
+    y, out = oracle.gdn_scan_tape(qk, v, decay, beta, state, tape, tape_layer=39, threads=4)
+    y_plain, out_plain = oracle.gdn_scan(qk, v, decay, beta, state, threads=4)
+    assert np.array_equal(y, y_plain) and np.array_equal(out, out_plain)
+    for r in (0, 1, 5, 16):
+        want = state if r == 0 else oracle.gdn_scan(qk[:r], v[:r], decay[:r], beta[:r], state, threads=4)[1]
+        assert np.array_equal(oracle.gdn_tape_replay(tape, state, r, 39, threads=4).view(np.uint32), want.view(np.uint32))
+    # geometry: layer 39 wrote the last 1/40 of each region and nothing else
+    key_off, gate_off = 40 * 16 * 32 * 128, 40 * 16 * 32 * 128 + 40 * 16 * 16 * 128
+    touched = tape != np.float32(7.5)
+    assert touched[39 * 16 * 32 * 128:key_off].all() and not touched[:39 * 16 * 32 * 128].any()
+    assert not touched[key_off:key_off + 39 * 16 * 16 * 128].any() and not touched[gate_off:gate_off + 39 * 16 * 64].any()
+    assert np.array_equal(tape[gate_off + 39 * 16 * 64:].reshape(16, 32, 2)[:, :, 0], decay)
+
+
+def test_gdn_conv_tape_rows_are_the_conv_state_after_each_row():
+    rng = np.random.default_rng(32)
+    proj, conv, conv_w, *_ = _band(rng, 9)
+    conv_tape = np.zeros((40, 16, 3, 8192), np.uint16)
+    oracle.gdn_conv_tape(proj, conv, conv_tape, 2)
+    for r in range(9):
+        assert np.array_equal(conv_tape[2, r], oracle.gdn_prepare(proj[:r + 1], conv, conv_w)[3])
+    assert not conv_tape[2, 9:].any() and not conv_tape[:2].any() and not conv_tape[3:].any()
