@@ -426,27 +426,13 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride;
     const uint32_t nparts = cl.nparts;
-    float big = -INFINITY;
-    for (uint32_t part = threadIdx.x; part < nparts; part += kCombineThreads)
-        big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
-#pragma unroll
-    for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-    if (lane == 0) red_max[warp] = big;
-    __syncthreads();
-    big = red_max[0];
-#pragma unroll
-    for (uint32_t i = 1; i < kWarps; ++i) big = fmaxf(big, red_max[i]);
-
     const uint32_t d = quarter * kCombineDims + lane * 2u;
-    // Thread state: one accumulator set per phase this warp owns; all of a round's record loads
-    // (phases x unroll) are issued before the first use.
-    constexpr uint32_t kOwn = kCombinePhases / kWarps;
-    float a0[kOwn], a1[kOwn], denom[kOwn];
-#pragma unroll
-    for (uint32_t j = 0; j < kOwn; ++j) a0[j] = a1[j] = denom[j] = 0.0f;
-    for (uint32_t round = 0; round < nparts; round += kCombinePhases * kCombineUnroll) {
-        float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
-        float2 v[kOwn][kCombineUnroll];
+    constexpr uint32_t kOwn = kCombinePhases / kWarps, kRound = kCombinePhases * kCombineUnroll;
+    // The first round of records (parts 0..127: every record of a lane cut by tb::partition_keys)
+    // is requested before the maximum is known, so the merge costs one trip to L2, not two.
+    float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
+    float2 v[kOwn][kCombineUnroll];
+    auto load_round = [&](uint32_t round) {
 #pragma unroll
         for (uint32_t j = 0; j < kOwn; ++j) {
 #pragma unroll
@@ -459,6 +445,29 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
                 v[j][u] = *reinterpret_cast<const float2*>(rec + d);
             }
         }
+    };
+    load_round(0);
+    float big = -INFINITY;
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j)
+#pragma unroll
+        for (uint32_t u = 0; u < kCombineUnroll; ++u) big = fmaxf(big, lm[j][u]);
+    for (uint32_t part = kRound + threadIdx.x; part < nparts; part += kCombineThreads)
+        big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    if (lane == 0) red_max[warp] = big;
+    __syncthreads();
+    big = red_max[0];
+#pragma unroll
+    for (uint32_t i = 1; i < kWarps; ++i) big = fmaxf(big, red_max[i]);
+
+    // One accumulator set per phase this warp owns.
+    float a0[kOwn], a1[kOwn], denom[kOwn];
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j) a0[j] = a1[j] = denom[j] = 0.0f;
+    for (uint32_t round = 0; round < nparts; round += kRound) {
+        if (round != 0) load_round(round);
 #pragma unroll
         for (uint32_t j = 0; j < kOwn; ++j) {
 #pragma unroll

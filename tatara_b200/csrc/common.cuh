@@ -47,15 +47,14 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // ---- split-KV partition function -------------------------------------------------------
 // Keys per partition for a lane that attends `n` keys.  A pure function of n (and of the
 // fixed SM count), so a lane is cut the same way alone or inside any batch.  Work items are
-// (kv head, partition): 2 per partition, so 74*k partitions fill k waves of 148 SMs.
+// (kv head, partition): 2 per partition, so 74 partitions give every SM exactly one item of a
+// single lane -- one pass over its keys and ONE merge of its four warps at the end (with several
+// items per CTA the key stream of an SM stalls at every merge: measured 9 us over the streaming
+// time at 65 536 keys with two items per CTA).
 __host__ __device__ inline uint32_t partition_keys(uint32_t n) {
     constexpr uint32_t per_wave = kSmCount / kKvHeads; // 74
     if (n <= per_wave * 128u) return 128u;   // short lanes: at least 128 keys per item
-    const uint32_t target_keys = n < 49152u ? 256u : (n < 196608u ? 512u : 1024u);
-    uint32_t waves = (n + per_wave * target_keys / 2u) / (per_wave * target_keys);
-    if (waves == 0) waves = 1;
-    const uint32_t parts = per_wave * waves;
-    const uint32_t keys = (n + parts - 1u) / parts;
+    const uint32_t keys = (n + per_wave - 1u) / per_wave;
     return (keys + 15u) & ~15u;
 }
 __host__ __device__ inline uint32_t partition_count(uint32_t n) {
