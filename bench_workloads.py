@@ -139,9 +139,9 @@ class Workloads:
     def traffic_hint(self):
         """DRAM bytes (read + write) per launch of attn_decode_partition_kernel at the headline
         context, from the ncu capture summarised in
-        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.261248 + 6.488832) MB at
+        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.283776 + 3.959552) MB at
         65 536 keys, scaled by keys (traffic is proportional to keys) to 262 144."""
-        return int((134.261248e6 + 6.488832e6) * 4)
+        return int((134.283776e6 + 3.959552e6) * 4)
 
     def decode_setup(self, n_keys):
         return DecodeCase(self.ctx, self.torch, n_keys, seed=self.rank * 100)
