@@ -114,10 +114,10 @@ uint32_t tatara_attn_partitions(uint32_t n_keys) {
 }
 
 uint64_t tatara_attn_decode_scratch_bytes(uint32_t max_keys, uint32_t lanes) {
-    // The partition count is not monotonic in n (the partition size grows in steps); n/112 + 75
-    // bounds it for every n <= max_keys (partitions hold at least 128 keys up to 9472 keys, and
-    // at least n/148 rounded up to 16 beyond).
-    const uint32_t worst = max_keys / 112u + 75u;
+    // A lane has ceil(n/128) partitions up to 9472 keys and at most 74 beyond (tb::partition_keys),
+    // so 74 bounds every n <= max_keys.
+    (void)max_keys;
+    const uint32_t worst = 74u;
     return static_cast<uint64_t>(lanes) * worst * tb::kQHeads * tb::kRecordFloats * sizeof(float);
 }
 

@@ -366,6 +366,201 @@ dense_project_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     }
 }
 
+// ---- CTA-pair form: two SMs on one 256 x 256 output tile (tcgen05 cta_group::2) -------------
+// A cluster of two CTAs; CTA r owns rows [128r, 128r+128) of the tile (its own 128 TMEM lanes)
+// and loads, per 128-wide k step, its 128 input rows and HALF of the 256 weight rows (32 KiB
+// each): the pair's tensor cores exchange the weight halves, so every SM pulls 64 KiB per 128 of k
+// from L2 instead of 96 KiB and reads 8 KiB instead of 12 KiB of shared memory per MMA.  The even
+// CTA (leader) issues the M256 N256 K16 MMAs for both; both CTAs run a TMA producer and an
+// epilogue.  Barriers: `full` lives in the leader (the leader's producer arrives expecting the
+// bytes of both CTAs; both CTAs' copies complete on it), `empty` and `acc_full` live in each CTA
+// and are signalled by one tcgen05.commit of the leader that arrives in both CTAs, `acc_empty`
+// lives in the leader and counts one arrival per epilogue warp of both CTAs.
+constexpr uint32_t kPK = 128, kPStages = 3, kPStageBytes = 65536, kPABytes = 32768, kPAtomBytes = 16384;
+constexpr uint32_t kPOffBar = kPStages * kPStageBytes;
+constexpr uint32_t kPairSmem = kPOffBar + 256;
+enum : uint32_t { kPBarFull = 0, kPBarEmpty = kPBarFull + kPStages, kPBarAccFull = kPBarEmpty + kPStages,
+                  kPBarAccEmpty = kPBarAccFull + kGAccs, kPBarCount = kPBarAccEmpty + kGAccs };
+static_assert(8 * kPBarCount + 16 <= 256, "barrier block");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// One commit that arrives on the barrier at the same offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(uint16_t(3))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+dense_project_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                          const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t base = s2u(smem), bars = base + kPOffBar;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kPOffBar + 8 * kPBarCount);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kPOffBar + 8 * kPBarCount + 8);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0u;
+    const uint32_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const uint32_t n_tiles_total = p.m_tiles * p.n_tiles, kblocks = p.k / kPK;   // tiles of 256 x 256
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kPStages; ++s) {
+            mbar_init(bar(kPBarFull + s), 1);    // the leader arrives, expecting the bytes of both CTAs
+            mbar_init(bar(kPBarEmpty + s), 1);
+        }
+        for (uint32_t a = 0; a < kGAccs; ++a) {
+            mbar_init(bar(kPBarAccFull + a), 1);
+            mbar_init(bar(kPBarAccEmpty + a), 8);   // 4 epilogue warps x 2 CTAs
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // the same warp of both CTAs allocates the pair's tensor memory
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)),
+                     "r"(kGAccs * kGN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();   // barriers of both CTAs are initialised before any remote arrival
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t n = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < n_tiles_total; t += n_pairs) {
+                const int m0 = int((t / p.n_tiles) * 256u + rank * 128u), n0 = int((t % p.n_tiles) * 256u + rank * 128u);
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++n) {
+                    const uint32_t s = n % kPStages, use = n / kPStages;
+                    if (use > 0 && !mbar_wait(bar(kPBarEmpty + s), (use - 1u) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    // Both CTAs' copies complete on the leader's barrier; the leader alone arrives on it,
+                    // expecting the bytes of both (a remote arrive.expect_tx with cluster-scope release
+                    // cost the producers 1200 cycles per stage: measured with cycle counters).
+                    const uint32_t full = map_to_cta(bar(kPBarFull + s), 0u);
+                    if (leader) mbar_expect_tx(bar(kPBarFull + s), 2u * kPStageBytes);
+#pragma unroll
+                    for (uint32_t a = 0; a < 2; ++a) {   // two 64-wide swizzle atoms per operand
+                        tma_load_2d_pair(base + s * kPStageBytes + a * kPAtomBytes, &map_x, full, int(kb * kPK + a * 64u), m0);
+                        tma_load_2d_pair(base + s * kPStageBytes + kPABytes + a * kPAtomBytes, &map_w, full, int(kb * kPK + a * 64u), n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc(256, kGN, false);
+            uint32_t n = 0, it = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < n_tiles_total; t += n_pairs, ++it) {
+                const uint32_t ab = it % kGAccs, ause = it / kGAccs;
+                if (ause > 0 && !mbar_wait(bar(kPBarAccEmpty + ab), (ause - 1u) & 1u, abort_flag)) break;
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < kblocks; ++kb, ++n) {
+                    const uint32_t s = n % kPStages;
+                    if (!mbar_wait(bar(kPBarFull + s), (n / kPStages) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = (ks >> 2) * kPAtomBytes + (ks & 3u) * 32u;
+                        const uint64_t ad = smem_desc(base + s * kPStageBytes + off, 16, 1024);
+                        const uint64_t bd = smem_desc(base + s * kPStageBytes + kPABytes + off, 16, 1024);
+                        tc_mma_pair(tmem + ab * kGN, ad, bd, idesc, (kb | ks) ? 1u : 0u);
+                    }
+                    tc_commit_both(bar(kPBarEmpty + s));
+                }
+                if (ok) {
+                    tc_commit_both(bar(kPBarAccFull + ab));
+                }
+            }
+        }
+    } else {
+        const uint32_t quarter = warp & 3u, row_in_tile = quarter * 32u + lane;
+        const uint32_t tlane = (quarter * 32u) << 16;
+        uint32_t it = 0;
+        for (uint32_t t = pair; t < n_tiles_total; t += n_pairs, ++it) {
+            const uint32_t ab = it % kGAccs;
+            if (!mbar_wait(bar(kPBarAccFull + ab), (it / kGAccs) & 1u, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t row = (t / p.n_tiles) * 256u + rank * 128u + row_in_tile, n0 = (t % p.n_tiles) * 256u;
+            __nv_bfloat16* orow = p.out + uint64_t(row) * p.out_stride + n0;
+#pragma unroll 2
+            for (uint32_t ch = 0; ch < kGN / 32u; ++ch) {
+                float v[32];
+                tmem_ld32(tmem + tlane + ab * kGN + ch * 32u, v);
+                tmem_wait_ld();
+                if (row < p.m && n0 + ch * 32u < p.n) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 4; ++q) {
+                        __nv_bfloat162 h[4];
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+                        *reinterpret_cast<uint4*>(orow + ch * 32u + q * 8u) = *reinterpret_cast<const uint4*>(h);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(bar(kPBarAccEmpty + ab), 0u));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000); // let copies still in flight land before the shared memory is released
+    }
+    // neither CTA leaves (or frees tensor memory) while its peer may still arrive on its barriers
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kGAccs * kGN) : "memory");
+    }
+}
+
 // 2-D bf16 tensor map {k, rows} with a {64, box_rows} box and the 128-byte swizzle.
 static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint64_t stride_bytes,
                         uint32_t box_rows) {
@@ -482,14 +677,12 @@ extern "C" tatara_status tatara_project_dense(tatara_ctx* ctx, void* stream, con
     if (n_rows == 0 || n == 0 || n % 32u != 0 || k == 0 || k % kGK != 0 || input_stride < k ||
         input_stride % 8u != 0 || out_stride < n || out_stride % 8u != 0)
         return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "project_dense: extents");
-    CUtensorMap map_x, map_w;
-    if (!make_map_2d(&map_x, input, k, n_rows, input_stride * 2ull, kGM) ||
-        !make_map_2d(&map_w, weights, k, n, uint64_t(k) * 2ull, kGN))
-        return fail(ctx, TATARA_CUDA_ERROR, "project_dense: tensor map encoding failed");
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
         if (cudaFuncSetAttribute(dense_project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem) !=
-            cudaSuccess)
+                cudaSuccess ||
+            cudaFuncSetAttribute(dense_project_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem) !=
+                cudaSuccess)
             return check_launch(ctx, "project_dense: shared memory attribute");
         configured[ctx->device & 63] = true;
     }
@@ -500,6 +693,22 @@ extern "C" tatara_status tatara_project_dense(tatara_ctx* ctx, void* stream, con
     gp.m = n_rows;
     gp.n = n;
     gp.k = k;
+    CUtensorMap map_x, map_w;
+    // Blocks of at least 256 rows run on CTA pairs (256 x 256 tiles, half a weight tile per CTA).
+    if (n_rows >= 256u && n >= 256u && k % kPK == 0 && ctx->sm_count >= 2) {
+        if (!make_map_2d(&map_x, input, k, n_rows, input_stride * 2ull, 128) ||
+            !make_map_2d(&map_w, weights, k, n, uint64_t(k) * 2ull, 128))
+            return fail(ctx, TATARA_CUDA_ERROR, "project_dense: tensor map encoding failed");
+        gp.m_tiles = (n_rows + 255u) / 256u;
+        gp.n_tiles = (n + 255u) / 256u;
+        const uint32_t tiles = gp.m_tiles * gp.n_tiles, pairs = uint32_t(ctx->sm_count) / 2u;
+        const uint32_t grid = 2u * (tiles < pairs ? tiles : pairs);
+        dense_project_pair_kernel<<<grid, kGemmThreads, kPairSmem, static_cast<cudaStream_t>(stream)>>>(map_x, map_w, gp);
+        return check_launch(ctx, "project_dense(pair)");
+    }
+    if (!make_map_2d(&map_x, input, k, n_rows, input_stride * 2ull, kGM) ||
+        !make_map_2d(&map_w, weights, k, n, uint64_t(k) * 2ull, kGN))
+        return fail(ctx, TATARA_CUDA_ERROR, "project_dense: tensor map encoding failed");
     gp.m_tiles = (n_rows + kGM - 1u) / kGM;
     gp.n_tiles = (n + kGN - 1u) / kGN;
     const uint32_t tiles = gp.m_tiles * gp.n_tiles;

@@ -110,7 +110,9 @@ def test_dequantize_bits(ctx):
 
 
 @pytest.mark.parametrize("rows,n,k", [(1, 32, 64), (7, 544, 2048), (128, 256, 512), (300, 544, 2048),
-                                      (129, 800, 4096), (1000, 96, 128)])
+                                      (129, 800, 4096), (1000, 96, 128),
+                                      # 256 rows and 256 columns or more: the CTA-pair kernel (256 x 256 tiles)
+                                      (256, 256, 64), (257, 288, 512), (700, 1280, 2048), (513, 544, 4096)])
 def test_dense_matches_oracle(ctx, rows, n, k):
     rng = np.random.default_rng(rows + n + k)
     mat = syn.q4_matrix(rng, n, k)
