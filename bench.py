@@ -149,7 +149,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project", "state_copy"],
+    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project", "state_copy", "layers"],
                     help="run one workload only (small profiling runs)")
     ap.add_argument("--context", type=int, default=HEADLINE_CONTEXT)
     ap.add_argument("--rows", type=int, default=PREFILL_ROWS)
@@ -281,6 +281,7 @@ def main():
         extra["gdn_prefill"] = wl.gdn_prefill(timed)
         extra["projections"] = wl.project(timed, peaks, steps, warmup)
         extra["state_snapshot"] = wl.state_copy(timed, peaks)
+        extra["decode_layer_slices"] = wl.layer_slices(timed, steps, warmup)
         extra["prefill_attn"] = wl.prefill(timed, peaks, sampler=ClockSampler(local))
     else:
         extra["split_kv"] = wl.split_kv(dist, n, timed, steps, warmup)

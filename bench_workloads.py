@@ -311,6 +311,85 @@ class Workloads:
         out["l2"] = "exact-row: rotating weight sets (> 2x L2 between reuse); dense: input + output > L2"
         return out
 
+    # ---- decode layer slices: projection -> layer kernels -> output projection, one token
+    def layer_slices(self, timed, steps, warmup, lanes=1, context=32768):
+        """The kernels of this library that one decode token runs in one layer, chained in stream order:
+        attention layer = attn_project (exact row) -> qk_rope -> decode attention -> out_projection;
+        gated-delta layer = gdn_project -> fused conv/recurrence/gate-norm -> out_projection.
+        Residual, norms and the MoE between them are not part of this library."""
+        torch = self.torch
+        g = torch.Generator(device="cuda").manual_seed(21)
+        bf = torch.bfloat16
+
+        def q4(sizes, k):
+            held = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (m, k // 8), generator=g, device="cuda", dtype=torch.int32),
+                     (0.35 * 0.32 / k ** 0.5 * (1 + 0.2 * (2 * torch.rand((m, k // 64), generator=g, device="cuda") - 1))).to(bf),
+                     (-0.35 * 2.4 / k ** 0.5 * (1 + 0.1 * torch.randn((m, k // 64), generator=g, device="cuda"))).to(bf))
+                    for m in sizes]
+            return held, tb.Context.q4_matrices(held)
+
+        x = torch.randn((lanes, 2048), generator=g, device="cuda").to(bf)
+        hidden = torch.zeros((lanes, 2048), dtype=bf, device="cuda")
+        out = {"lanes": lanes, "context": context}
+        # attention layer: per-lane caches in one pool, rotated replicas so that K/V never sit in L2
+        cap = context + 1
+        per_lane = 2 * cap * 256
+        reps = replicas_for(lanes * context * 2048)
+        kpool = torch.randn((reps, lanes, per_lane), generator=g, device="cuda").to(bf)
+        vpool = torch.randn((reps, lanes, per_lane), generator=g, device="cuda").to(bf)
+        attn_w = [q4((8192, 512, 512), 2048) for _ in range(4)]
+        out_w = [q4((2048,), 4096) for _ in range(4)]
+        proj = torch.zeros((lanes, 9216), dtype=bf, device="cuda")
+        qb, gb = torch.zeros((lanes, 4096), dtype=bf, device="cuda"), torch.zeros((lanes, 4096), dtype=bf, device="cuda")
+        attended = torch.zeros((lanes, 4096), dtype=bf, device="cuda")
+        ones = torch.ones(256, dtype=bf, device="cuda")
+        table = tb.Context.attn_lanes([(i * per_lane, context - 1) for i in range(lanes)])
+        scratch = torch.empty(tb.decode_scratch_bytes(cap, lanes) // 4, dtype=torch.float32, device="cuda")
+
+        def attn_layer(i=0):
+            r, w = i % reps, i % 4
+            self.ctx.q4_project(x, attn_w[w][1], 2048, proj)
+            self.ctx.attn_qk_rope_batch(proj, ones, ones, qb, gb, kpool[r], vpool[r], cap, table)
+            self.ctx.attn_decode_batch(qb, gb, kpool[r], vpool[r], table, cap, attended, scratch)
+            self.ctx.q4_project(attended, out_w[w][1], 4096, hidden)
+
+        ms = timed(attn_layer, max(steps, 2 * reps), max(warmup, reps))
+        kv = lanes * context * 2048
+        wbytes = 10616832 + 4718592
+        out["attention_layer"] = {"us": ms * 1e3, "bytes": kv + wbytes, "gbs": (kv + wbytes) / (ms * 1e-3) / 1e9,
+                                  "kernels": "q4_project, attn_qk_rope, attn_decode_partition, attn_combine, q4_project"}
+        del kpool, vpool
+        torch.cuda.empty_cache()
+        # gated-delta layer
+        nb = lanes * (2 * 2097152 + 2 * 49152)
+        reps = replicas_for(nb + 14229504 + 4718592)
+        conv_pool = torch.randn((reps, lanes, 2, 3, 8192), generator=g, device="cuda").to(bf)
+        rec_pool = 0.02 * torch.randn((reps, lanes, 2, 32, 128, 128), generator=g, device="cuda")
+        gdn_w = [q4((8192, 4096, 32, 32), 2048) for _ in range(4)]
+        gproj = torch.zeros((lanes, 12352), dtype=bf, device="cuda")
+        conv_w = (0.5 * torch.randn((8192, 4), generator=g, device="cuda")).to(bf)
+        a_log = torch.log(1 + 15 * torch.rand(32, generator=g, device="cuda")).to(bf)
+        dt_bias = (0.5 * torch.randn(32, generator=g, device="cuda")).to(bf)
+        norm_w = torch.ones(128, device="cuda").to(bf)
+        y, gated = torch.zeros((lanes, 4096), dtype=bf, device="cuda"), torch.zeros((lanes, 4096), dtype=bf, device="cuda")
+        cs, rs = 3 * 8192, 32 * 128 * 128
+        tables = [tb.Context.gdn_lanes([((2 * i + a) * cs, (2 * i + b) * cs, (2 * i + a) * rs, (2 * i + b) * rs)
+                                        for i in range(lanes)]) for a, b in ((0, 1), (1, 0))]
+
+        def gdn_layer(i=0):
+            r, w = i % reps, i % 4
+            self.ctx.q4_project(x, gdn_w[w][1], 2048, gproj)
+            self.ctx.gdn_decode_batch(gproj, conv_w, a_log, dt_bias, norm_w, conv_pool[r], rec_pool[r],
+                                      tables[(i // reps) & 1], y, gated)
+            self.ctx.q4_project(gated, out_w[w][1], 4096, hidden)
+
+        ms = timed(gdn_layer, max(steps, 2 * reps), max(warmup, reps))
+        gb_ = nb + 14229504 + 4718592
+        out["gated_delta_layer"] = {"us": ms * 1e3, "bytes": gb_, "gbs": gb_ / (ms * 1e-3) / 1e9,
+                                    "kernels": "q4_project, gdn_decode_fused, q4_project"}
+        out["l2"] = "caches / states rotate through replicas (> 2x L2 between reuse); 4 weight sets (62 MB) rotate"
+        return out
+
     # ---- state snapshot: the canonical prefix payload of the 40-layer schedule in one launch
     def state_copy(self, timed, peaks, positions=65536, capacity=65536):
         """60 gated-delta segments (48 KiB / 2 MiB) + 40 packed K/V head prefixes of `positions` rows, slot ->
@@ -413,6 +492,8 @@ class Workloads:
             return self.lanes32(timed, steps, warmup)
         if which == "gdn_prefill":
             return self.gdn_prefill(timed, rows=args.rows)
+        if which == "layers":
+            return self.layer_slices(timed, steps, warmup, lanes=args.lanes if args.lanes != 4 else 1, context=min(args.context, 65536))
         if which == "state_copy":
             return self.state_copy(timed, measured_peaks())
         if which == "project":

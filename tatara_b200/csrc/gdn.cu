@@ -251,6 +251,13 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j)
             rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
+    // Launched as a programmatic dependent of its predecessor in the stream (the projection that
+    // produces `projection`): the recurrent state it reads above is this layer's own and is not
+    // written by that predecessor, so those loads are in flight while the predecessor finishes;
+    // the projection row, the conv state and every store wait here.  This kernel never signals its
+    // own dependents early: the next call on the same layer reads the state written below, so it
+    // must not start before this grid has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // prologue: threads 0..127 -> q channel, 128..255 -> k channel; then v channel on 0..127
     const uint32_t l128 = threadIdx.x & 127u;
@@ -422,10 +429,19 @@ extern "C" tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, 
             return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch: recurrent offset alignment");
         table.lane[i] = l;
     }
-    gdn_decode_fused_kernel<<<dim3(kGdnValueHeads, n_lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const bf16*>(projection), projection_stride, static_cast<const bf16*>(conv_weights),
-        static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
-        static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool), static_cast<float*>(rec_pool),
-        static_cast<bf16*>(y), static_cast<bf16*>(gated), table);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kGdnValueHeads, n_lanes);
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, gdn_decode_fused_kernel, static_cast<const bf16*>(projection),
+                             uint64_t(projection_stride), static_cast<const bf16*>(conv_weights),
+                             static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
+                             static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool),
+                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), table);
     return check_launch(ctx, "gdn_decode_batch");
 }

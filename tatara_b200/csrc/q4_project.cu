@@ -184,6 +184,188 @@ __global__ void __launch_bounds__(kQ4Warps * 32) q4_project_kernel(const __grid_
     }
 }
 
+// Batched form for more than two rows: 2*RP rows per pass, rows taken in PAIRS so that every
+// multiply-add of the chain is one packed fma.rn.f32x2 (sm_100): the pair {row 2p, row 2p+1}
+// shares the decoded nibble and each component keeps the scalar kernel's exact sequence
+// (per-component rounding of fma.rn.f32x2 is that of fma.rn.f32), so a row's bits are still
+// those of the single-row chain.  The pre-divided inputs and their block sums are computed ONCE
+// per CTA into shared memory as row pairs ([pair][block][i/2][lane] -> {x0[i], x1[i], x0[i+1],
+// x1[i+1]}, one conflict-free LDS.128 per two inputs) instead of once per warp and block.
+template <int RP, int C>
+__global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_kernel(const __grid_constant__ Q4Params p) {
+    extern __shared__ float4 xs4[];   // [RP][blocks][8][32] float4, then the sums [RP][blocks][32] float2
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row0 = blockIdx.y * (2 * RP);
+    const uint32_t blocks = p.k >> 9, wpr = p.k >> 4, gpr = p.k >> 6;
+    float2* sum2 = reinterpret_cast<float2*>(xs4 + RP * blocks * 256u);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t n_groups = p.n_cols / C;
+    const uint32_t nwarps = gridDim.x * kQ4Warps;
+    uint32_t g = blockIdx.x * kQ4Warps + (threadIdx.x >> 5);
+
+    const uint2* fw;
+    const unsigned short *fs, *fb;
+    uint32_t fg = g, fblock = 0;
+    auto locate = [&](uint32_t group) {
+        const uint32_t col0 = group * C;
+        uint32_t m = 0;
+        while (m + 1u < p.n_mats && col0 >= p.mat[m].col_end) ++m;
+        const uint32_t local = col0 - p.mat[m].col_begin;
+        fw = p.mat[m].words + uint64_t(local) * wpr + lane;
+        fs = reinterpret_cast<const unsigned short*>(p.mat[m].scales) + uint64_t(local) * gpr + (lane >> 2);
+        fb = reinterpret_cast<const unsigned short*>(p.mat[m].biases) + uint64_t(local) * gpr + (lane >> 2);
+    };
+    // three items of words and affine constants (scale bits << 16 | bias bits) in registers:
+    // the one being used and the two behind it already requested
+    uint2 wd[C], wn[C], wf[C];
+    uint32_t ad[C], an[C], af[C];
+    auto fetch = [&](uint2* w, uint32_t* a) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            w[c] = __ldg(fw + uint64_t(c) * wpr + fblock * 32u);
+            a[c] = (uint32_t(__ldg(fs + uint64_t(c) * gpr + fblock * 8u)) << 16) |
+                   uint32_t(__ldg(fb + uint64_t(c) * gpr + fblock * 8u));
+        }
+        if (++fblock == blocks) {
+            fblock = 0;
+            fg += nwarps;
+            if (fg < n_groups) locate(fg);
+        }
+    };
+    if (g < n_groups) {
+        locate(fg);
+        fetch(wd, ad);
+        if (fg < n_groups) fetch(wn, an);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // stage the row pairs: one (row, block, lane) item = 16 inputs
+    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += kQ4Warps * 32u) {
+        const uint32_t l = item & 31u, b = (item >> 5) % blocks, r = item / (32u * blocks);
+        const uint32_t row = min(row0 + r, p.n_rows - 1u);
+        const uint4* xp = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride + b * 512u + l * 16u);
+        const uint4 v0 = xp[0], v1 = xp[1];
+        const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float* dst = reinterpret_cast<float*>(xs4 + ((r >> 1) * blocks + b) * 256u) + (r & 1u);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a0 = __uint_as_float(raw[2 * i] << 16), a1 = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
+            const float a2 = __uint_as_float(raw[2 * i + 1] << 16), a3 = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
+            s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
+            // float4 index (i4 = 2i, 2i+1), lane l: components {x0[2j], x1[2j], x0[2j+1], x1[2j+1]}
+            dst[((2 * i) * 32u + l) * 4u] = a0;
+            dst[((2 * i) * 32u + l) * 4u + 2u] = __fmul_rn(a1, 0.0625f);
+            dst[((2 * i + 1) * 32u + l) * 4u] = __fmul_rn(a2, 0.00390625f);
+            dst[((2 * i + 1) * 32u + l) * 4u + 2u] = __fmul_rn(a3, 0.000244140625f);
+        }
+        reinterpret_cast<float*>(sum2 + ((r >> 1) * blocks + b) * 32u + l)[r & 1u] = s;
+    }
+    __syncthreads();
+    if (g >= n_groups) return;
+
+    float2 result[RP][C];
+#pragma unroll
+    for (int rp = 0; rp < RP; ++rp)
+#pragma unroll
+        for (int c = 0; c < C; ++c) result[rp][c] = make_float2(0.0f, 0.0f);
+    uint32_t b = 0;
+    const float2 magic = make_float2(-8388608.0f, -8388608.0f);
+#pragma unroll 1
+    while (g < n_groups) {
+        if (fg < n_groups) fetch(wf, af);
+        float4 xv[RP][8];
+        float2 sum[RP];
+#pragma unroll
+        for (int rp = 0; rp < RP; ++rp) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[rp][i] = xs4[((rp * blocks + b) * 8u + i) * 32u + lane];
+            sum[rp] = sum2[(rp * blocks + b) * 32u + lane];
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const uint32_t half[4] = {wd[c].x & 0xFFFFu, wd[c].x >> 16, wd[c].y & 0xFFFFu, wd[c].y >> 16};
+            const float scale = __uint_as_float(ad[c] & 0xFFFF0000u), bias = __uint_as_float(ad[c] << 16);
+            float2 quant[RP];
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) quant[rp] = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // the four nibbles of half-word i, each as {w, w}; inputs 4i .. 4i+3 are xv[.][2i].xy, .zw, xv[.][2i+1].xy, .zw
+                const float w0 = __uint_as_float((half[i] & 0x000Fu) | 0x4B000000u), w1 = __uint_as_float((half[i] & 0x00F0u) | 0x4B000000u);
+                const float w2 = __uint_as_float((half[i] & 0x0F00u) | 0x4B000000u), w3 = __uint_as_float((half[i] & 0xF000u) | 0x4B000000u);
+                const float2 q0 = __fadd2_rn(make_float2(w0, w0), magic), q1 = __fadd2_rn(make_float2(w1, w1), magic);
+                const float2 q2 = __fadd2_rn(make_float2(w2, w2), magic), q3 = __fadd2_rn(make_float2(w3, w3), magic);
+#pragma unroll
+                for (int rp = 0; rp < RP; ++rp) {
+                    const float4 lo = xv[rp][2 * i], hi = xv[rp][2 * i + 1];
+                    quant[rp] = __ffma2_rn(make_float2(lo.x, lo.y), q0, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(lo.z, lo.w), q1, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(hi.x, hi.y), q2, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(hi.z, hi.w), q3, quant[rp]);
+                }
+            }
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp)
+                result[rp][c] = __ffma2_rn(sum[rp], make_float2(bias, bias),
+                                           __ffma2_rn(make_float2(scale, scale), quant[rp], result[rp][c]));
+        }
+        if (++b == blocks) {
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) {
+                float keep0 = 0.0f, keep1 = 0.0f;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    const float t0 = warp_sum(result[rp][c].x), t1 = warp_sum(result[rp][c].y);
+                    if (lane == uint32_t(c)) {
+                        keep0 = t0;
+                        keep1 = t1;
+                    }
+                    result[rp][c] = make_float2(0.0f, 0.0f);
+                }
+                const uint32_t r0 = row0 + 2u * rp;
+                if (lane < uint32_t(C)) {
+                    if (r0 < p.n_rows) p.out[uint64_t(r0) * p.out_stride + g * C + lane] = f2bf(keep0);
+                    if (r0 + 1u < p.n_rows) p.out[uint64_t(r0 + 1u) * p.out_stride + g * C + lane] = f2bf(keep1);
+                }
+            }
+            b = 0;
+            g += nwarps;
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            wd[c] = wn[c];
+            ad[c] = an[c];
+            wn[c] = wf[c];
+            an[c] = af[c];
+        }
+    }
+}
+
+template <int RP, int C>
+static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+    const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
+    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
+    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_kernel<RP, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 212992);
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, (p.n_rows + 2 * RP - 1) / (2 * RP));
+    cfg.blockDim = dim3(kQ4Warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
+}
+
 // Up to 4 rows per warp pass (more rows run as further row tiles that re-read the weights from L2).
 template <int R, int C>
 static void launch_q4(const Q4Params& p, uint32_t sm_count, uint32_t ctas_per_sm, cudaStream_t stream) {
@@ -600,8 +782,10 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
         else launch_q4<1, 4>(p, sms, 1, s);
     } else if (n_rows == 2) {
         launch_q4<2, 4>(p, sms, 1, s);
-    } else {
+    } else if (n_rows <= 4) {
         launch_q4<4, 4>(p, sms, 1, s);
+    } else {
+        (void)launch_q4_pairs<4, 4>(p, sms, s);   // 8 rows per pass; more rows run as further row tiles
     }
     return check_launch(ctx, "q4_project");
 }
