@@ -6,26 +6,29 @@
 // One CTA owns 128 query rows of one head and streams the visible keys in tiles of 128:
 //     S = Q K^T      tcgen05.mma  M128 N128 K256   (A = Q, B = K tile, both K-major swizzled smem)
 //     P = exp2(S*c - m)  in registers, one thread per query row (tcgen05.ld of its TMEM lane)
-//     O += P V       tcgen05.mma  M128 N256 K128   (A = P from TMEM, B = V tile, MN-major smem)
+//     O += P V       tcgen05.mma  M128 N256 K128   (A = P, K-major swizzled smem; B = V tile, MN-major smem)
 // An M128 MMA costs about 64 cycles whatever its N up to 128 (measured: N = 64 tiles ran the
-// tensor pipe at half rate), so the score tile is 128 keys wide.  A 128-key K or V tile is
-// 64 KiB, too large to double-buffer next to the 64 KiB Q tile, so K and V stream through rings
-// of 32 KiB slots that are released and refilled INSIDE a tile: a K slot holds 128 of the 256 dims
+// tensor pipe at half rate), so the score tile is 128 keys wide.  K and V stream through rings of
+// 32 KiB slots that are released and refilled INSIDE a tile: a K slot holds 128 of the 256 dims
 // (the operand of eight consecutive k-steps), a V slot holds 64 of the 128 keys (four k-steps);
 // a tcgen05.commit after each slot's MMAs hands the slot back to the TMA producer.
-// TMEM map (512 columns): S/P buffer 0 at 0..127, buffer 1 at 128..255, O at 256..511; P (bf16
-// pairs per 32-bit column) overwrites the first 64 columns of the S buffer it was computed from
-// and is consumed from TMEM.  Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9
-// softmax + epilogue (two warps per 32-row TMEM lane quarter, each owning one 64-key half of the
-// score tile; the halves exchange their row maxima through shared memory).  The running maximum is updated lazily (O and l are rescaled only when the
-// maximum grows by more than 2^8), which keeps the TMEM round trip of O off the steady-state path.
+// TMEM map (512 columns): S buffer 0 at 0..127, buffer 1 at 128..255, O at 256..511.  P goes
+// through SHARED memory (bf16, written by the softmax threads under the 128-byte swizzle as the
+// K-major A operand), not through the S buffer: an S buffer is released the moment its scores are
+// in registers, so the score MMAs run two tiles ahead and the softmax of a tile (about 1750
+// cycles) is no longer the latency between two MMAs on one TMEM buffer.  Shared memory: Q 64 KiB,
+// K ring 2 x 32 KiB, V ring 2 x 32 KiB, P 32 KiB.  Warp roles: warp 0 TMA producer, warp 1 MMA
+// issuer, warps 2..9 softmax + epilogue (two warps per 32-row TMEM lane quarter, each owning one
+// 64-key half of the score tile; the halves exchange their row maxima through shared memory).
+// The running maximum is updated lazily (O and l are rescaled only when the maximum grows by more
+// than 2^8), which keeps the TMEM round trip of O off the steady-state path.
 // Every mbarrier wait is bounded; on a timeout the CTA latches TATARA_DEVICE_WAIT_TIMEOUT in the
 // context's status word, frees its TMEM and returns.
 #include "tc05.cuh"
 
 namespace tb {
 
-constexpr uint32_t kBM = 128, kBN = 128, kKSlots = 3, kVSlots = 2, kSBufs = 2;
+constexpr uint32_t kBM = 128, kBN = 128, kKSlots = 2, kVSlots = 2, kSBufs = 2;
 constexpr uint32_t kAtomBytesQ = kBM * 128;          // one 64-dim swizzle atom of the Q tile
 constexpr uint32_t kQBytes = 4 * kAtomBytesQ;        // 64 KiB
 constexpr uint32_t kSlotBytes = 32768;               // K slot: 128 keys x 128 dims; V slot: 64 keys x 256 d
@@ -34,7 +37,9 @@ constexpr uint32_t kVAtomBytes = 64 * 128;           // one 64-d atom of a V slo
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + kKSlots * kSlotBytes;
-constexpr uint32_t kOffBar = kOffV + kVSlots * kSlotBytes;
+constexpr uint32_t kOffP = kOffV + kVSlots * kSlotBytes;   // P tile [128 rows x 128 keys] bf16, K-major, two 64-key atoms
+constexpr uint32_t kPAtomBytes = kBM * 128, kPBytes = 2 * kPAtomBytes;
+constexpr uint32_t kOffBar = kOffP + kPBytes;
 constexpr uint32_t kPrefillSmem = kOffBar + 256 + 2 * 256 * 4;  // + row-max exchange (2 phases)
 static_assert(kPrefillSmem <= 232448, "shared memory budget");
 constexpr uint32_t kPrefillThreads = 320;   // TMA warp, MMA warp, 8 softmax warps
@@ -43,8 +48,8 @@ constexpr uint32_t kTmemCols = 512, kColS = 0, kColO = 256;
 
 // barrier slots
 enum : uint32_t { kBarQ = 0, kBarKFull = 1, kBarKEmpty = kBarKFull + kKSlots, kBarVFull = kBarKEmpty + kKSlots,
-                  kBarVEmpty = kBarVFull + kVSlots, kBarSFull = kBarVEmpty + kVSlots, kBarPFull = kBarSFull + kSBufs,
-                  kBarPvDone = kBarPFull + kSBufs, kBarCount = kBarPvDone + kSBufs };
+                  kBarVEmpty = kBarVFull + kVSlots, kBarSFull = kBarVEmpty + kVSlots, kBarSFree = kBarSFull + kSBufs,
+                  kBarPFull = kBarSFree + kSBufs, kBarPvDone = kBarPFull + 1, kBarCount = kBarPvDone + 1 };
 static_assert(8 * kBarCount + 16 <= 256, "barrier block");
 constexpr uint32_t kOffPair = kOffBar + 256;       // [2 halves][128 rows] f32 exchange between the two warps of a row
 
@@ -87,9 +92,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         for (uint32_t s = 0; s < kSBufs; ++s) {
             mbar_init(bar(kBarSFull + s), 1);
-            mbar_init(bar(kBarPFull + s), kSoftmaxThreads);
-            mbar_init(bar(kBarPvDone + s), 1);
+            mbar_init(bar(kBarSFree + s), kSoftmaxThreads);
         }
+        mbar_init(bar(kBarPFull), kSoftmaxThreads);
+        mbar_init(bar(kBarPvDone), 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -147,8 +153,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
             auto issue_s = [&](uint32_t j) {
                 const uint32_t b = j % kSBufs;
-                // Buffer b held P of tile j-2: its P.V was issued before this point and the
-                // tcgen05.mma instructions of one thread execute in issue order.
+                // S buffer b is free once the softmax threads have read tile j-2 out of it
+                if (j >= kSBufs && !mbar_wait(bar(kBarSFree + b), (j / kSBufs - 1u) & 1u, abort_flag)) return false;
+                tc_fence_after();
                 for (uint32_t h = 0; h < 2; ++h) {
                     const uint32_t n = j * 2u + h, slot = n % kKSlots;
                     if (!mbar_wait(bar(kBarKFull + slot), (n / kKSlots) & 1u, abort_flag)) return false;
@@ -166,31 +173,34 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 return true;
             };
             auto issue_pv = [&](uint32_t i) {
-                const uint32_t b = i % kSBufs;
-                if (!mbar_wait(bar(kBarPFull + b), (i / kSBufs) & 1u, abort_flag)) return false;
+                if (!mbar_wait(bar(kBarPFull), i & 1u, abort_flag)) return false;
                 for (uint32_t g = 0; g < 2; ++g) {
                     const uint32_t n = i * 2u + g, slot = n % kVSlots;
                     if (!mbar_wait(bar(kBarVFull + slot), (n / kVSlots) & 1u, abort_flag)) return false;
                     tc_fence_after();
 #pragma unroll
                     for (uint32_t h = 0; h < 4; ++h) {
-                        // A = P [128 x 128] in TMEM: 8 columns per 16-key step.
+                        // A = P [128 x 128] bf16 in shared memory, K-major: atom g holds keys 64g..64g+63,
+                        // 32 bytes per 16-key step.
                         // B = V slot [64 keys x 256 d] MN-major: atoms of 64 d are kVAtomBytes apart
                         // (leading offset), groups of 8 keys 1024 B apart (stride offset); 16 keys = 2048 B
+                        const uint64_t ad = smem_desc(base + kOffP + g * kPAtomBytes + h * 32u, 16, 1024);
                         const uint64_t bd = smem_desc(base + kOffV + slot * kSlotBytes + h * 2048u, kVAtomBytes, 1024);
-                        tc_mma_ts(tmem + kColO, tmem + kColS + b * kBN + (g * 4u + h) * 8u, bd, idesc_pv,
-                                  (i | g | h) ? 1u : 0u);
+                        tc_mma(tmem + kColO, ad, bd, idesc_pv, (i | g | h) ? 1u : 0u);
                     }
                     tc_commit(bar(kBarVEmpty + slot));
                 }
-                tc_commit(bar(kBarPvDone + b));
+                tc_commit(bar(kBarPvDone));
                 return true;
             };
+            // The score MMAs run up to two tiles ahead of the softmax (their buffer is released as soon
+            // as it has been read); P.V of a tile follows as soon as its P is in shared memory.
+            if (ok) ok = issue_s(0);
+            if (ok && ntiles > 1u) ok = issue_s(1);
             for (uint32_t j = 0; ok && j < ntiles; ++j) {
-                ok = issue_s(j);
-                if (ok && j > 0) ok = issue_pv(j - 1u);
+                ok = issue_pv(j);
+                if (ok && j + 2u < ntiles) ok = issue_s(j + 2u);
             }
-            if (ok) issue_pv(ntiles - 1u);
         }
     } else {
         // ---------------- softmax + epilogue: two threads per query row ----------------
@@ -218,6 +228,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u, sv);
             tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u + 32u, sv + 32);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(kBarSFree + s));   // the scores are in registers: the buffer may take tile j+2
             const uint32_t key0 = j * kBN + half * 64u;
             if (j * kBN + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
 #pragma unroll
@@ -244,7 +256,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (__any_sync(0xffffffffu, grow)) {
                     // O holds P.V of tiles < j: wait for tile j-1, then rescale this row's half of O
                     const uint32_t jp = j - 1u;
-                    if (!mbar_wait(bar(kBarPvDone + jp % kSBufs), (jp / kSBufs) & 1u, abort_flag)) { ok = false; continue; }
+                    if (!mbar_wait(bar(kBarPvDone), jp & 1u, abort_flag)) { ok = false; continue; }
                     tc_fence_after();
                     const float f = grow ? ex2(m_used - mx) : 1.0f;
                     for (uint32_t ch = 0; ch < 4; ++ch) {
@@ -272,27 +284,33 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 s0 += sv[i]; s1 += sv[i + 1]; s2 += sv[i + 2]; s3 += sv[i + 3];
             }
             l += (s0 + s1) + (s2 + s3);
-            // P (bf16 pairs) overwrites the first 64 columns of the S buffer: this half's 64 keys
-            // are columns 32*half .. 32*half+31.  The partner may still be reading its S half
-            // (columns 64.. for half 1) -- the pair barrier above ordered both loads before this store.
-            uint32_t packed[32];
+            // P goes to shared memory as the K-major A operand of P.V: this thread's 64 keys are one
+            // 128-byte row of atom `half`, eight 16-byte chunks under the 128-byte swizzle.  The single
+            // P tile is free once P.V of the previous tile has completed.
+            if (j > 0 && !mbar_wait(bar(kBarPvDone), (j - 1u) & 1u, abort_flag)) { ok = false; continue; }
+            {
+                uint8_t* prow = smem + kOffP + half * kPAtomBytes + row * 128u;
 #pragma unroll
-            for (uint32_t i = 0; i < 32; ++i) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(sv[2 * i], sv[2 * i + 1]);
-                packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                for (uint32_t ch = 0; ch < 8; ++ch) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(sv[ch * 8 + 2 * i], sv[ch * 8 + 2 * i + 1]);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7u)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
             }
-            tmem_st32(tmem + tlane + kColS + s * kBN + half * 32u, reinterpret_cast<const float*>(packed));
-            tmem_wait_st();
             if (j + 1u == ntiles) {   // the partner reads this half's row sum after the last P.V completes
                 reinterpret_cast<float*>(smem + kOffQ)[half * 128u + row] = l; // Q is dead: every S MMA has completed
                 __threadfence_block();
             }
-            tc_fence_before();
-            mbar_arrive(bar(kBarPFull + s));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> the MMA's async proxy
+            mbar_arrive(bar(kBarPFull));
         }
         if (ok) {
             const uint32_t jl = ntiles - 1u;
-            ok = mbar_wait(bar(kBarPvDone + jl % kSBufs), (jl / kSBufs) & 1u, abort_flag);
+            ok = mbar_wait(bar(kBarPvDone), jl & 1u, abort_flag);
         }
         if (ok) {
             tc_fence_after();
