@@ -68,6 +68,20 @@ def test_exact_row_bits_model_geometry(ctx, name, sizes, k):
     assert 0.2 < syn.from_bf16(want).std() < 2.0
 
 
+def test_exact_row_batch_of_16_model_geometry(ctx):
+    """gdn_project at the largest decode batch of the reference (16 rows: two passes of the row-pair kernel);
+    every row has the bits of the oracle's chain, i.e. of the same row projected alone."""
+    rng = np.random.default_rng(1616)
+    sizes, k = (8192, 4096, 32, 32), 2048
+    mats = [syn.q4_matrix(rng, n, k) for n in sizes]
+    x = syn.hidden_rows(rng, 16, k)
+    held, arr = dev_mats(mats)
+    out = torch.zeros((16, sum(sizes)), dtype=torch.bfloat16, device="cuda")
+    ctx.q4_project(dev_bf16(x), arr, k, out)
+    ctx.sync()
+    assert np.array_equal(host_u16(out), oracle_project(x, mats, oracle.hardware_threads()))
+
+
 def test_exact_row_strides(ctx):
     """Input rows inside a wider buffer, output into a column window of a wider projection buffer."""
     rng = np.random.default_rng(77)
