@@ -126,6 +126,33 @@ class DecodeCase:
         self.ctx.attn_decode(self.q2, self.g2, keys, values, self.n - 1, self.capacity, self.out, self.scratch)
         self.h_out.copy_(self.out, non_blocking=True)
 
+    def token_graph(self):
+        """One decode token end to end as ONE CUDA graph: pinned H2D of the projection row, qk_rope and decode
+        attention through the device-table entry points (nothing about the token is a kernel argument), D2H of the
+        attended row.  Returns a callable that replays it (one graph launch per token, as an engine would)."""
+        torch = self.torch
+        keys, values = self.caches[0]
+        table = tb.Context.device_lanes(tb.Context.attn_lanes([(0, self.n - 1)]))
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+
+        def body():
+            self.d_proj.copy_(self.h_proj, non_blocking=True)
+            self.ctx.attn_qk_rope_batch_indirect(self.d_proj, self.ones, self.ones, self.q2, self.g2, keys, values,
+                                                 self.capacity, table, 1)
+            self.ctx.attn_decode_batch_indirect(self.q2, self.g2, keys, values, table, 1, self.capacity, self.out,
+                                                self.scratch)
+            self.h_out.copy_(self.out, non_blocking=True)
+
+        with torch.cuda.stream(stream):
+            body()
+            stream.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                body()
+        torch.cuda.synchronize()
+        self._graph_keepalive = (graph, table, stream)
+        return lambda i=0: graph.replay()
+
     def free(self):
         del self.caches, self.scratch
         self.torch.cuda.empty_cache()

@@ -351,6 +351,39 @@ tatara_status tatara_gdn_tape_replay(tatara_ctx* ctx, void* stream, const void* 
                                      const void* state_in, void* state_out, uint32_t steps,
                                      uint32_t tape_layer);
 
+/* ---- lane tables in device memory (CUDA-graph replay of a decode token) ------------------
+ * The reference re-encodes a command buffer per token with the stream group's contexts and state
+ * slots as constants (src/runtime/decode_step.cpp:1002-1426, tools/native/tatara_serve.cpp:
+ * 1463-1777).  Here the same tables may live in DEVICE memory: nothing about a token is then a
+ * kernel argument, so a token's launches can be captured once into a CUDA graph and replayed for
+ * every token, with tatara_lanes_advance (context + 1; gated-delta in / out offsets swapped) as
+ * the node between tokens.  Same kernels, same per-lane cut, same output bits as the host-table
+ * entry points.  What the host cannot check any more is checked on the device: a context beyond
+ * the capacity reads and writes nothing for that lane and latches TATARA_CONTEXT_OUT_OF_RANGE
+ * for the next tatara_ctx_sync.  `scratch` must hold tatara_attn_decode_scratch_bytes(capacity,
+ * n_lanes).  The calls of one context share one schedule buffer: use one stream per context. */
+tatara_status tatara_attn_qk_rope_batch_indirect(tatara_ctx* ctx, void* stream, const void* projection,
+                                                 const void* q_weight, const void* k_weight,
+                                                 void* q_out, void* gate_out, void* keys_pool,
+                                                 void* values_pool, uint32_t capacity,
+                                                 const tatara_attn_lane* lanes_device,
+                                                 uint32_t n_lanes, uint32_t projection_stride,
+                                                 uint32_t query_stride);
+tatara_status tatara_attn_decode_batch_indirect(tatara_ctx* ctx, void* stream, const void* q,
+                                                const void* gate, const void* keys_pool,
+                                                const void* values_pool,
+                                                const tatara_attn_lane* lanes_device, uint32_t n_lanes,
+                                                uint32_t capacity, uint32_t query_stride, void* out,
+                                                void* scratch, uint64_t scratch_bytes);
+tatara_status tatara_gdn_decode_batch_indirect(tatara_ctx* ctx, void* stream, const void* projection,
+                                               uint32_t projection_stride, const void* conv_weights,
+                                               const void* a_log, const void* dt_bias,
+                                               const void* norm_weight, void* conv_pool,
+                                               void* rec_pool, const tatara_gdn_lane* lanes_device,
+                                               uint32_t n_lanes, void* y, void* gated);
+tatara_status tatara_lanes_advance(tatara_ctx* ctx, void* stream, tatara_attn_lane* attn_lanes_device,
+                                   uint32_t n_attn, tatara_gdn_lane* gdn_lanes_device, uint32_t n_gdn);
+
 #ifdef __cplusplus
 }
 #endif

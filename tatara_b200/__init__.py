@@ -275,6 +275,40 @@ class Context:
                                              _ptr(state_out), _u32(rows), _u32(chunk), _ptr(scratch),
                                              _u64(nbytes)))
 
+    # ---- lane tables in device memory (CUDA-graph replay)
+    @staticmethod
+    def device_lanes(table):
+        """A ctypes lane table (attn_lanes / gdn_lanes) as a device tensor of its bytes."""
+        import torch
+        raw = bytes(table)
+        return torch.frombuffer(bytearray(raw), dtype=torch.uint8).cuda()
+
+    def attn_qk_rope_batch_indirect(self, projection, q_weight, k_weight, q_out, gate_out, keys_pool, values_pool,
+                                    capacity, lanes_device, n_lanes, projection_stride=ATTN_PROJ,
+                                    query_stride=Q_HEADS * HEAD_DIM, stream=None):
+        self._check(lib().tatara_attn_qk_rope_batch_indirect(
+            self._h, self._stream(stream), _ptr(projection), _ptr(q_weight), _ptr(k_weight), _ptr(q_out),
+            _ptr(gate_out), _ptr(keys_pool), _ptr(values_pool), _u32(capacity), _ptr(lanes_device), _u32(n_lanes),
+            _u32(projection_stride), _u32(query_stride)))
+
+    def attn_decode_batch_indirect(self, q, gate, keys_pool, values_pool, lanes_device, n_lanes, capacity, out, scratch,
+                                   query_stride=Q_HEADS * HEAD_DIM, stream=None):
+        self._check(lib().tatara_attn_decode_batch_indirect(
+            self._h, self._stream(stream), _ptr(q), _ptr(gate), _ptr(keys_pool), _ptr(values_pool), _ptr(lanes_device),
+            _u32(n_lanes), _u32(capacity), _u32(query_stride), _ptr(out), _ptr(scratch),
+            _u64(scratch.numel() * scratch.element_size())))
+
+    def gdn_decode_batch_indirect(self, projection, conv_weights, a_log, dt_bias, norm_weight, conv_pool, rec_pool,
+                                  lanes_device, n_lanes, y, gated, projection_stride=GDN_PROJ, stream=None):
+        self._check(lib().tatara_gdn_decode_batch_indirect(
+            self._h, self._stream(stream), _ptr(projection), _u32(projection_stride), _ptr(conv_weights),
+            _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), _ptr(conv_pool), _ptr(rec_pool), _ptr(lanes_device),
+            _u32(n_lanes), _ptr(y), _ptr(gated)))
+
+    def lanes_advance(self, attn_lanes_device, n_attn, gdn_lanes_device, n_gdn, stream=None):
+        self._check(lib().tatara_lanes_advance(self._h, self._stream(stream), _ptr(attn_lanes_device), _u32(n_attn),
+                                               _ptr(gdn_lanes_device), _u32(n_gdn)))
+
     # ---- speculative-decode support: GDN tape and replay
     def gdn_prepare_tape(self, projection, conv_in, conv_weights, qk, value, z, conv_out, rows, conv_tape, tape_layer,
                          stream=None):

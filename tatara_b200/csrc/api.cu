@@ -62,7 +62,8 @@ tatara_status tatara_ctx_create(int device, tatara_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     if (cudaMalloc(&ctx->device_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
         cudaMemset(ctx->device_status, 0, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMallocHost(&ctx->host_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess) {
+        cudaMallocHost(&ctx->host_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMalloc(&ctx->lane_schedule, tb::kLaneScheduleBytes) != cudaSuccess) {
         (void)cudaGetLastError();
         tatara_ctx_destroy(ctx);
         return TATARA_CUDA_ERROR;
@@ -76,6 +77,7 @@ void tatara_ctx_destroy(tatara_ctx* ctx) {
     if (ctx == nullptr) return;
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
     if (ctx->host_status != nullptr) cudaFreeHost(ctx->host_status);
+    if (ctx->lane_schedule != nullptr) cudaFree(ctx->lane_schedule);
     delete ctx;
 }
 

@@ -44,8 +44,10 @@ struct DecLane {
     uint32_t row;        // q / gate / out row
 };
 
+struct DecTables;   // the same tables in device memory (lane tables that a CUDA graph can replay)
 template <uint32_t N>
 struct DecParams {
+    const DecTables* tables;   // null: the tables below, built on the host for this call
     const __nv_bfloat16* q;
     const __nv_bfloat16* keys;
     const __nv_bfloat16* values;
@@ -105,15 +107,23 @@ struct SliceCursor {
     bool valid;
 };
 
+__device__ const DecLane* dec_lanes_of(const DecTables* t);
+__device__ uint32_t tables_n_lanes(const DecTables* t);
+__device__ uint32_t tables_total_items(const DecTables* t);
+// The schedule a kernel works from: the by-value tables of its parameters or the device copy.
+struct Sched {
+    const DecLane* lanes;
+    uint32_t n_lanes, total_items;
+};
 template <uint32_t N>
-__device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams<N>& p,
+__device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams<N>& p, const Sched& sch,
                                                  const uint32_t* item_start) {
-    uint32_t lo = 0, hi = p.n_lanes; // last lane with item_start <= item
+    uint32_t lo = 0, hi = sch.n_lanes; // last lane with item_start <= item
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;
         if (item_start[mid] <= c.item) lo = mid; else hi = mid;
     }
-    const DecLane& l = p.lane[lo];
+    const DecLane& l = sch.lanes[lo];
     const uint32_t local = c.item - l.item_start;
     c.lane = lo;
     c.part = local >> 1;
@@ -127,15 +137,15 @@ __device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams
 }
 
 template <uint32_t N>
-__device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>& p,
+__device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>& p, const Sched& sch,
                                               const uint32_t* item_start, uint32_t warp) {
     while (c.valid && c.slice * kSliceKeys >= c.nkeys) {
         c.item += gridDim.x;
-        if (c.item >= p.total_items) {
+        if (c.item >= sch.total_items) {
             c.valid = false;
             break;
         }
-        cursor_load_item(c, p, item_start);
+        cursor_load_item(c, p, sch, item_start);
         c.slice = warp;
     }
 }
@@ -166,23 +176,28 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     float* merge_o = reinterpret_cast<float*>(smem + kDecWarps * kRingBytes);
     float* merge_ml = merge_o + kMergeFloats;
     uint32_t* item_start = reinterpret_cast<uint32_t*>(merge_ml + kDecWarps * kHeadsPerKv * 2);
-    for (uint32_t i = threadIdx.x; i <= p.n_lanes; i += kDecThreads)
-        item_start[i] = i < p.n_lanes ? p.lane[i].item_start : p.total_items;
+    Sched sch;
+    // (the device copy is written by a setup kernel that precedes this one in plain stream order)
+    sch.lanes = p.tables != nullptr ? dec_lanes_of(p.tables) : p.lane;
+    sch.n_lanes = p.tables != nullptr ? tables_n_lanes(p.tables) : p.n_lanes;
+    sch.total_items = p.tables != nullptr ? tables_total_items(p.tables) : p.total_items;
+    for (uint32_t i = threadIdx.x; i <= sch.n_lanes; i += kDecThreads)
+        item_start[i] = i < sch.n_lanes ? sch.lanes[i].item_start : sch.total_items;
     __syncthreads();
     const uint32_t ring = smem_u32(smem + warp * kRingBytes);
 
     // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
     SliceCursor pc{};
     pc.item = blockIdx.x;
-    pc.valid = pc.item < p.total_items;
+    pc.valid = pc.item < sch.total_items;
     bool early = false;
     if (pc.valid) {
-        cursor_load_item(pc, p, item_start);
+        cursor_load_item(pc, p, sch, item_start);
         pc.slice = warp;
         // Every partition but a lane's last is full (at least 128 keys = 2 slices for each warp) and
         // holds only keys written before this token, so its first slices can be requested at once.
-        early = pc.part + 1u < p.lane[pc.lane].nparts;
-        cursor_settle(pc, p, item_start, warp);
+        early = pc.part + 1u < sch.lanes[pc.lane].nparts;
+        cursor_settle(pc, p, sch, item_start, warp);
     }
     uint32_t issued = 0, consumed = 0;
     auto fill_ring = [&]() {
@@ -191,7 +206,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
             if (pc.valid) {
                 issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
                 pc.slice += kDecWarps;
-                cursor_settle(pc, p, item_start, warp);
+                cursor_settle(pc, p, sch, item_start, warp);
             }
             cp_async_commit();
             ++issued;
@@ -216,9 +231,9 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     const float score_scale = kAttnScale * kLog2e;
 
     SliceCursor cc{};
-    for (cc.item = blockIdx.x; cc.item < p.total_items; cc.item += gridDim.x) {
-        cursor_load_item(cc, p, item_start);
-        const DecLane& dl = p.lane[cc.lane];
+    for (cc.item = blockIdx.x; cc.item < sch.total_items; cc.item += gridDim.x) {
+        cursor_load_item(cc, p, sch, item_start);
+        const DecLane& dl = sch.lanes[cc.lane];
         // Q fragments of head (kv*8 + g): A rows 0..7 of every k-step.
         uint32_t qa[16][2];
         {
@@ -240,7 +255,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
             if (pc.valid) {
                 issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
                 pc.slice += kDecWarps;
-                cursor_settle(pc, p, item_start, warp);
+                cursor_settle(pc, p, sch, item_start, warp);
             }
             cp_async_commit();
             ++issued;
@@ -348,6 +363,18 @@ struct CombineLane {
     uint32_t nparts;
     uint32_t row;
 };
+// Both kernels' lane tables in device memory, written by attn_decode_setup_kernel from a lane
+// table that itself lives in device memory: nothing about a token's contexts is a kernel
+// argument, so one captured CUDA graph serves every token.
+struct DecTables {
+    uint32_t n_lanes, total_items, pad0, pad1;
+    DecLane dec[TATARA_MAX_LANES];
+    CombineLane comb[TATARA_MAX_LANES];
+};
+static_assert(sizeof(DecTables) <= kLaneScheduleBytes, "lane schedule buffer");
+__device__ __forceinline__ const DecLane* dec_lanes_of(const DecTables* t) { return t->dec; }
+__device__ __forceinline__ uint32_t tables_n_lanes(const DecTables* t) { return t->n_lanes; }
+__device__ __forceinline__ uint32_t tables_total_items(const DecTables* t) { return t->total_items; }
 constexpr uint32_t kMaxPeers = 8;
 // Peer exchange of the split-KV merge (one process per GPU, buffers mapped through CUDA IPC).
 struct PeerExchange {
@@ -360,6 +387,7 @@ struct PeerExchange {
 };
 template <uint32_t N>
 struct CombineParams {
+    const DecTables* tables;   // null: the lane table below
     const __nv_bfloat16* gate;
     __nv_bfloat16* out;  // [row][16][256] gated output, or null
     float* record_out;   // [lane][16][258] merged un-normalised record, or null
@@ -421,7 +449,8 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
         __syncthreads();
         if (arrived == 0u) return;
     }
-    const CombineLane& cl = p.lane[blockIdx.y];
+    const CombineLane& cl = p.tables != nullptr ? p.tables->comb[blockIdx.y] : p.lane[blockIdx.y];
+    if (cl.nparts == 0u) return;   // a lane the setup kernel rejected (context beyond capacity): status is latched
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride;
@@ -634,9 +663,161 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     return check_launch(ctx, what);
 }
 
+// ---- lane tables in device memory -------------------------------------------------------
+// One CTA of 256 threads: thread i derives lane i's cut (tb::partition_keys of its own key count)
+// and an exclusive scan over the lanes gives the item and record offsets -- the same tables
+// launch_decode builds on the host, so a lane's output bits do not depend on which path ran.
+__global__ void __launch_bounds__(TATARA_MAX_LANES)
+attn_decode_setup_kernel(const tatara_attn_lane* __restrict__ lanes, uint32_t n_lanes, uint32_t capacity,
+                         float* records, DecTables* t, uint32_t* status) {
+    __shared__ uint32_t warp_total[TATARA_MAX_LANES / 32];
+    const uint32_t i = threadIdx.x, lane = i & 31u, warp = i >> 5;
+    uint32_t nparts = 0, part_keys = 16, n = 0;
+    uint64_t kv_offset = 0;
+    if (i < n_lanes) {
+        const tatara_attn_lane l = lanes[i];
+        kv_offset = l.kv_offset;
+        if (l.context < capacity) {
+            n = l.context + 1u;
+            part_keys = partition_keys(n);
+            nparts = partition_count(n);
+        } else {   // nothing is read or written for this lane; the host sees the status at the next sync
+            atomicCAS(status + kStatusCode, 0u, uint32_t(TATARA_CONTEXT_OUT_OF_RANGE));
+            status[kStatusDetail] = i;
+        }
+    }
+    uint32_t incl = nparts;   // inclusive scan of the partition counts
+#pragma unroll
+    for (uint32_t off = 1; off < 32; off <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+    }
+    if (lane == 31u) warp_total[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0, total = 0;
+    for (uint32_t w = 0; w < TATARA_MAX_LANES / 32; ++w) {
+        if (w < warp) before += warp_total[w];
+        total += warp_total[w];
+    }
+    const uint32_t prefix = before + incl - nparts;
+    if (i < n_lanes) {
+        const uint64_t rec_floats = uint64_t(prefix) * kQHeads * kRecordFloats;
+        t->dec[i] = DecLane{kv_offset, rec_floats, 0u, n, part_keys, nparts, prefix * kKvHeads, i};
+        t->comb[i] = CombineLane{records + rec_floats, uint64_t(nparts) * kRecordFloats, kRecordFloats, nparts, i};
+    }
+    if (i == 0) {
+        t->n_lanes = n_lanes;
+        t->total_items = total * kKvHeads;
+    }
+}
+
+// After a token: every attention lane's context moves on by one position and every gated-delta
+// lane's in / out state offsets trade places (src/runtime/decode_step.cpp:1432-1441 on the host).
+__global__ void lanes_advance_kernel(tatara_attn_lane* attn, uint32_t n_attn, tatara_gdn_lane* gdn, uint32_t n_gdn) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_attn) attn[i].context += 1u;
+    if (i < n_gdn) {
+        const tatara_gdn_lane g = gdn[i];
+        gdn[i] = tatara_gdn_lane{g.conv_out, g.conv_in, g.rec_out, g.rec_in};
+    }
+}
+
+template <uint32_t N>
+static tatara_status launch_decode_indirect(tatara_ctx* ctx, cudaStream_t stream, const DecodeRequest& r,
+                                            const tatara_attn_lane* lanes_device, uint32_t n_lanes, const char* what) {
+    auto* tables = static_cast<DecTables*>(ctx->lane_schedule);
+    attn_decode_setup_kernel<<<1, TATARA_MAX_LANES, 0, stream>>>(lanes_device, n_lanes, r.capacity,
+                                                                 static_cast<float*>(r.scratch), tables, ctx->device_status);
+    tatara_status st = check_launch(ctx, what);
+    if (st != TATARA_OK) return st;
+    DecParams<N> dp{};
+    CombineParams<N> cp{};
+    dp.tables = tables;
+    dp.q = static_cast<const __nv_bfloat16*>(r.q);
+    dp.keys = static_cast<const __nv_bfloat16*>(r.keys);
+    dp.values = static_cast<const __nv_bfloat16*>(r.values);
+    dp.records = static_cast<float*>(r.scratch);
+    dp.query_stride = r.query_stride;
+    dp.capacity = r.capacity;
+    cp.tables = tables;
+    cp.gate = static_cast<const __nv_bfloat16*>(r.gate);
+    cp.out = static_cast<__nv_bfloat16*>(r.out);
+    cp.query_stride = r.query_stride;
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(attn_decode_partition_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kDecSmemBytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_combine_kernel<N>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+            return check_launch(ctx, "attn_decode: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    // The item count is only known on the device: every SM gets a (persistent) CTA.  The partition
+    // kernel follows the setup kernel in plain stream order (it reads the tables at once); the merge
+    // is its programmatic dependent as in the host-table path.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(uint32_t(ctx->sm_count));
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = kDecSmemBytes;
+    cfg.stream = stream;
+    (void)cudaLaunchKernelEx(&cfg, attn_decode_partition_kernel<N>, dp);
+    st = check_launch(ctx, what);
+    if (st != TATARA_OK) return st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(kQHeads * 4, n_lanes);
+    cfg.blockDim = dim3(combine_warps<N>() * 32u);
+    cfg.dynamicSmemBytes = 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp);
+    return check_launch(ctx, what);
+}
+
 } // namespace tb
 
 using namespace tb;
+
+extern "C" tatara_status tatara_attn_decode_batch_indirect(tatara_ctx* ctx, void* stream, const void* q,
+                                                           const void* gate, const void* keys_pool,
+                                                           const void* values_pool,
+                                                           const tatara_attn_lane* lanes_device, uint32_t n_lanes,
+                                                           uint32_t capacity, uint32_t query_stride, void* out,
+                                                           void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !gate || !keys_pool || !values_pool || !out || !scratch || !lanes_device)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_batch_indirect: null buffer");
+    if (!aligned(q, 4) || !aligned(keys_pool, 16) || !aligned(values_pool, 16) || !aligned(scratch, 16) ||
+        !aligned(lanes_device, 8))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_batch_indirect: misaligned buffer");
+    if (n_lanes == 0 || n_lanes > TATARA_MAX_LANES)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_decode_batch_indirect: lanes");
+    if (capacity == 0) return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_batch_indirect: capacity");
+    if (query_stride < kQHeads * kHeadDim)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_decode_batch_indirect: query stride");
+    // contexts are not known here: the scratch must cover the worst cut of every lane
+    if (scratch_bytes < tatara_attn_decode_scratch_bytes(capacity, n_lanes))
+        return fail(ctx, TATARA_SCRATCH_TOO_SMALL, "attn_decode_batch_indirect: scratch");
+    const DecodeRequest r{q, gate, keys_pool, values_pool, out, nullptr, scratch, scratch_bytes, query_stride, capacity};
+    if (n_lanes == 1)
+        return launch_decode_indirect<1>(ctx, static_cast<cudaStream_t>(stream), r, lanes_device, 1,
+                                         "attn_decode_batch_indirect");
+    return launch_decode_indirect<TATARA_MAX_LANES>(ctx, static_cast<cudaStream_t>(stream), r, lanes_device, n_lanes,
+                                                    "attn_decode_batch_indirect");
+}
+
+extern "C" tatara_status tatara_lanes_advance(tatara_ctx* ctx, void* stream, tatara_attn_lane* attn_lanes_device,
+                                              uint32_t n_attn, tatara_gdn_lane* gdn_lanes_device, uint32_t n_gdn) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if ((n_attn != 0 && attn_lanes_device == nullptr) || (n_gdn != 0 && gdn_lanes_device == nullptr))
+        return fail(ctx, TATARA_INVALID_BUFFER, "lanes_advance: null table");
+    if (n_attn > TATARA_MAX_LANES || n_gdn > TATARA_MAX_LANES || (n_attn | n_gdn) == 0)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "lanes_advance: lanes");
+    lanes_advance_kernel<<<1, TATARA_MAX_LANES, 0, static_cast<cudaStream_t>(stream)>>>(attn_lanes_device, n_attn,
+                                                                                      gdn_lanes_device, n_gdn);
+    return check_launch(ctx, "lanes_advance");
+}
 
 extern "C" tatara_status tatara_attn_decode(tatara_ctx* ctx, void* stream, const void* q,
                                             const void* gate, const void* keys, const void* values,

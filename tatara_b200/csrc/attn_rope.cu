@@ -25,7 +25,7 @@ attn_qk_rope_kernel(const __nv_bfloat16* __restrict__ projection,
                     __nv_bfloat16* __restrict__ gate_out, __nv_bfloat16* __restrict__ keys,
                     __nv_bfloat16* __restrict__ values, uint32_t position, uint32_t capacity,
                     uint64_t projection_stride, uint64_t query_stride,
-                    const __grid_constant__ RopeLanes<N> lanes) {
+                    const __grid_constant__ RopeLanes<N> lanes, const tatara_attn_lane* lanes_device) {
     constexpr bool kBatched = N > 1;
     __shared__ float normed[kHeadDim];
     __shared__ float stage[2];
@@ -38,8 +38,11 @@ attn_qk_rope_kernel(const __nv_bfloat16* __restrict__ projection,
     uint32_t pos = position + row;
     uint64_t kv_offset = 0;
     if (kBatched) {
-        pos = lanes.lane[row].context;
-        kv_offset = lanes.lane[row].kv_offset;
+        // the lane table of this call, or the one kept in device memory (CUDA-graph replay)
+        const tatara_attn_lane l = lanes_device != nullptr ? lanes_device[row] : lanes.lane[row];
+        pos = l.context;
+        kv_offset = l.kv_offset;
+        if (pos >= capacity) return;   // device table only: the decode setup kernel latches the status
     }
     const __nv_bfloat16* proj = projection + row * projection_stride;
     const bool is_q = head < kQHeads;
@@ -101,7 +104,7 @@ extern "C" tatara_status tatara_attn_qk_rope(tatara_ctx* ctx, void* stream, cons
         static_cast<const __nv_bfloat16*>(projection), static_cast<const __nv_bfloat16*>(q_weight),
         static_cast<const __nv_bfloat16*>(k_weight), static_cast<__nv_bfloat16*>(q_out),
         static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(keys),
-        static_cast<__nv_bfloat16*>(values), position, capacity, kAttnProj, kQHeads * kHeadDim, none);
+        static_cast<__nv_bfloat16*>(values), position, capacity, kAttnProj, kQHeads * kHeadDim, none, nullptr);
     return check_launch(ctx, "attn_qk_rope");
 }
 
@@ -129,6 +132,29 @@ extern "C" tatara_status tatara_attn_qk_rope_batch(tatara_ctx* ctx, void* stream
         static_cast<const __nv_bfloat16*>(projection), static_cast<const __nv_bfloat16*>(q_weight),
         static_cast<const __nv_bfloat16*>(k_weight), static_cast<__nv_bfloat16*>(q_out),
         static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(keys_pool),
-        static_cast<__nv_bfloat16*>(values_pool), 0u, capacity, projection_stride, query_stride, table);
+        static_cast<__nv_bfloat16*>(values_pool), 0u, capacity, projection_stride, query_stride, table, nullptr);
     return check_launch(ctx, "attn_qk_rope_batch");
+}
+
+extern "C" tatara_status tatara_attn_qk_rope_batch_indirect(tatara_ctx* ctx, void* stream, const void* projection,
+                                                            const void* q_weight, const void* k_weight, void* q_out,
+                                                            void* gate_out, void* keys_pool, void* values_pool,
+                                                            uint32_t capacity, const tatara_attn_lane* lanes_device,
+                                                            uint32_t n_lanes, uint32_t projection_stride,
+                                                            uint32_t query_stride) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !q_weight || !k_weight || !q_out || !gate_out || !keys_pool || !values_pool || !lanes_device)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_qk_rope_batch_indirect: null buffer");
+    if (n_lanes == 0 || n_lanes > TATARA_MAX_LANES)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_qk_rope_batch_indirect: lane count");
+    if (capacity == 0) return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_qk_rope_batch_indirect: capacity");
+    if (projection_stride < kAttnProj || query_stride < kQHeads * kHeadDim)
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "attn_qk_rope_batch_indirect: stride");
+    const RopeLanes<TATARA_MAX_LANES> unused{};
+    attn_qk_rope_kernel<TATARA_MAX_LANES><<<dim3(kQHeads + kKvHeads, n_lanes), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(projection), static_cast<const __nv_bfloat16*>(q_weight),
+        static_cast<const __nv_bfloat16*>(k_weight), static_cast<__nv_bfloat16*>(q_out),
+        static_cast<__nv_bfloat16*>(gate_out), static_cast<__nv_bfloat16*>(keys_pool),
+        static_cast<__nv_bfloat16*>(values_pool), 0u, capacity, projection_stride, query_stride, unused, lanes_device);
+    return check_launch(ctx, "attn_qk_rope_batch_indirect");
 }

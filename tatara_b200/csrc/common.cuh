@@ -25,6 +25,7 @@ constexpr uint32_t kSmCount = 148; // B200; the partition function is pinned to 
 
 // Device-side status word slots (ctx->device_status).
 enum : uint32_t { kStatusCode = 0, kStatusDetail = 1, kStatusWords = 4 };
+constexpr size_t kLaneScheduleBytes = 32768;   // holds attn_decode.cu's DecTables
 
 } // namespace tb
 
@@ -33,6 +34,7 @@ struct tatara_ctx {
     int sm_count = 0;
     uint32_t* device_status = nullptr; // kStatusWords u32, zero while healthy
     uint32_t* host_status = nullptr;   // pinned mirror
+    void* lane_schedule = nullptr;     // device scratch of the calls whose lane tables live in device memory
     uint64_t launches = 0;
     char error[256] = {0};
 };

@@ -229,12 +229,14 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
                         const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
                         const __nv_bfloat16* __restrict__ norm_weight, __nv_bfloat16* conv_pool,
                         float* rec_pool, __nv_bfloat16* __restrict__ y_out,
-                        __nv_bfloat16* __restrict__ gated, const __grid_constant__ GdnLanes lanes) {
+                        __nv_bfloat16* __restrict__ gated, const __grid_constant__ GdnLanes lanes,
+                        const tatara_gdn_lane* lanes_device) {
     __shared__ float head_q[kGdnDim], head_k[kGdnDim];
     __shared__ float qn[kGdnDim], kn[kGdnDim], vn[kGdnDim], ys[kGdnDim];
     const uint32_t head = blockIdx.x, row_lane = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const tatara_gdn_lane gl = lanes.lane[row_lane];
+    // the lane table of this call, or the one kept in device memory (CUDA-graph replay)
+    const tatara_gdn_lane gl = lanes_device != nullptr ? lanes_device[row_lane] : lanes.lane[row_lane];
     const __nv_bfloat16* proj = projection + row_lane * projection_stride;
     const __nv_bfloat16* conv_in = conv_pool + gl.conv_in;
     __nv_bfloat16* conv_out = conv_pool + gl.conv_out;
@@ -442,6 +444,45 @@ extern "C" tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, 
                              uint64_t(projection_stride), static_cast<const bf16*>(conv_weights),
                              static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
                              static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool),
-                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), table);
+                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), table,
+                             static_cast<const tatara_gdn_lane*>(nullptr));
     return check_launch(ctx, "gdn_decode_batch");
+}
+
+extern "C" tatara_status tatara_gdn_decode_batch_indirect(tatara_ctx* ctx, void* stream, const void* projection,
+                                                          uint32_t projection_stride, const void* conv_weights,
+                                                          const void* a_log, const void* dt_bias,
+                                                          const void* norm_weight, void* conv_pool, void* rec_pool,
+                                                          const tatara_gdn_lane* lanes_device, uint32_t n_lanes,
+                                                          void* y, void* gated) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!projection || !conv_weights || !a_log || !dt_bias || !norm_weight || !conv_pool || !rec_pool ||
+        !lanes_device || !gated)
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch_indirect: null buffer");
+    if (!aligned(rec_pool, 16) || !aligned(conv_weights, 8) || !aligned(norm_weight, 8) ||
+        !aligned(gated, 8) || !aligned(projection, 8) || (y && !aligned(y, 8)) || !aligned(lanes_device, 8))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch_indirect: misaligned buffer");
+    if (n_lanes == 0 || n_lanes > TATARA_MAX_LANES)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "gdn_decode_batch_indirect: lane count");
+    if (projection_stride < kGdnProj || (projection_stride & 3u))
+        return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_decode_batch_indirect: projection stride");
+    // The offsets are the caller's (written once when the table is created; tatara_lanes_advance only
+    // swaps them): in != out and 16-byte alignment of the recurrent offsets are the caller's contract.
+    const GdnLanes unused{};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kGdnValueHeads, n_lanes);
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, gdn_decode_fused_kernel, static_cast<const bf16*>(projection),
+                             uint64_t(projection_stride), static_cast<const bf16*>(conv_weights),
+                             static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
+                             static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool),
+                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), unused,
+                             lanes_device);
+    return check_launch(ctx, "gdn_decode_batch_indirect");
 }
