@@ -265,8 +265,9 @@ def main():
     # the same token as one captured CUDA graph (lane tables in device memory), one graph launch per token
     try:
         e2e_graph_ms = timed(decode.token_graph(), steps, warmup, eager=True)
+        e2e_mapped_ms = timed(decode.token_graph(mapped_host=True), steps, warmup, eager=True)
     except tb.TataraError as e:   # pragma: no cover
-        e2e_graph_ms = None
+        e2e_graph_ms = e2e_mapped_ms = None
 
     extra = {}
     if world == 1:
@@ -316,6 +317,7 @@ def main():
                          "kernel": "attn_decode_partition_kernel (+ attn_combine_kernel in the timed step)"},
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "graph_replay_ms_per_step": e2e_graph_ms,
+                    "graph_replay_mapped_host_ms_per_step": e2e_mapped_ms,
                     "path": "host-issued C-ABI calls from Python: pinned H2D of the token projection, qk_rope, decode, D2H",
                     "h2d_bytes_per_step": 9216 * 2, "d2h_bytes_per_step": 4096 * 2},
             "gpu_launches": int(launches),

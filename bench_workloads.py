@@ -126,10 +126,14 @@ class DecodeCase:
         self.ctx.attn_decode(self.q2, self.g2, keys, values, self.n - 1, self.capacity, self.out, self.scratch)
         self.h_out.copy_(self.out, non_blocking=True)
 
-    def token_graph(self):
+    def token_graph(self, mapped_host=False):
         """One decode token end to end as ONE CUDA graph: pinned H2D of the projection row, qk_rope and decode
         attention through the device-table entry points (nothing about the token is a kernel argument), D2H of the
-        attended row.  Returns a callable that replays it (one graph launch per token, as an engine would)."""
+        attended row.  Returns a callable that replays it (one graph launch per token, as an engine would).
+        mapped_host=True drops the two copy nodes: qk_rope loads the projection row straight from the pinned
+        host buffer and the combine kernel stores the attended row straight into the pinned host buffer (pinned
+        memory is mapped into the device's address space), so the host<->device transfers ride inside the two
+        kernels instead of waiting on the copy engine."""
         torch = self.torch
         keys, values = self.caches[0]
         table = tb.Context.device_lanes(tb.Context.attn_lanes([(0, self.n - 1)]))
@@ -137,12 +141,17 @@ class DecodeCase:
         graph = torch.cuda.CUDAGraph()
 
         def body():
-            self.d_proj.copy_(self.h_proj, non_blocking=True)
-            self.ctx.attn_qk_rope_batch_indirect(self.d_proj, self.ones, self.ones, self.q2, self.g2, keys, values,
+            if mapped_host:
+                proj, out = self.h_proj, self.h_out
+            else:
+                proj, out = self.d_proj, self.out
+                self.d_proj.copy_(self.h_proj, non_blocking=True)
+            self.ctx.attn_qk_rope_batch_indirect(proj, self.ones, self.ones, self.q2, self.g2, keys, values,
                                                  self.capacity, table, 1)
-            self.ctx.attn_decode_batch_indirect(self.q2, self.g2, keys, values, table, 1, self.capacity, self.out,
+            self.ctx.attn_decode_batch_indirect(self.q2, self.g2, keys, values, table, 1, self.capacity, out,
                                                 self.scratch)
-            self.h_out.copy_(self.out, non_blocking=True)
+            if not mapped_host:
+                self.h_out.copy_(self.out, non_blocking=True)
 
         with torch.cuda.stream(stream):
             body()
@@ -150,7 +159,7 @@ class DecodeCase:
             with torch.cuda.graph(graph, stream=stream):
                 body()
         torch.cuda.synchronize()
-        self._graph_keepalive = (graph, table, stream)
+        self._graph_keepalive = getattr(self, '_graph_keepalive', []) + [(graph, table, stream)]
         return lambda i=0: graph.replay()
 
     def free(self):

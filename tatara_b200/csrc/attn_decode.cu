@@ -107,23 +107,35 @@ struct SliceCursor {
     bool valid;
 };
 
-__device__ const DecLane* dec_lanes_of(const DecTables* t);
+__device__ const DecLane& table_lane(const DecTables* t, uint32_t i);
 __device__ uint32_t tables_n_lanes(const DecTables* t);
 __device__ uint32_t tables_total_items(const DecTables* t);
-// The schedule a kernel works from: the by-value tables of its parameters or the device copy.
-struct Sched {
-    const DecLane* lanes;
-    uint32_t n_lanes, total_items;
-};
-template <uint32_t N>
-__device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams<N>& p, const Sched& sch,
+// The schedule a kernel works from: the by-value tables of its parameters (kInd = false, the
+// host built them for this call) or their copy in device memory (kInd = true).
+template <uint32_t N, bool kInd>
+__device__ __forceinline__ const DecLane& lane_at(const DecParams<N>& p, uint32_t i) {
+    if constexpr (kInd) return table_lane(p.tables, i);
+    else return p.lane[i];
+}
+template <uint32_t N, bool kInd>
+__device__ __forceinline__ uint32_t lanes_in(const DecParams<N>& p) {
+    if constexpr (kInd) return tables_n_lanes(p.tables);
+    else return p.n_lanes;
+}
+template <uint32_t N, bool kInd>
+__device__ __forceinline__ uint32_t items_in(const DecParams<N>& p) {
+    if constexpr (kInd) return tables_total_items(p.tables);
+    else return p.total_items;
+}
+template <uint32_t N, bool kInd>
+__device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams<N>& p,
                                                  const uint32_t* item_start) {
-    uint32_t lo = 0, hi = sch.n_lanes; // last lane with item_start <= item
+    uint32_t lo = 0, hi = lanes_in<N, kInd>(p); // last lane with item_start <= item
     while (hi - lo > 1) {
         const uint32_t mid = (lo + hi) >> 1;
         if (item_start[mid] <= c.item) lo = mid; else hi = mid;
     }
-    const DecLane& l = sch.lanes[lo];
+    const DecLane& l = lane_at<N, kInd>(p, lo);
     const uint32_t local = c.item - l.item_start;
     c.lane = lo;
     c.part = local >> 1;
@@ -136,16 +148,16 @@ __device__ __forceinline__ void cursor_load_item(SliceCursor& c, const DecParams
     c.vbase = reinterpret_cast<const uint8_t*>(p.values) + first;
 }
 
-template <uint32_t N>
-__device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>& p, const Sched& sch,
+template <uint32_t N, bool kInd>
+__device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>& p,
                                               const uint32_t* item_start, uint32_t warp) {
     while (c.valid && c.slice * kSliceKeys >= c.nkeys) {
         c.item += gridDim.x;
-        if (c.item >= sch.total_items) {
+        if (c.item >= items_in<N, kInd>(p)) {
             c.valid = false;
             break;
         }
-        cursor_load_item(c, p, sch, item_start);
+        cursor_load_item<N, kInd>(c, p, item_start);
         c.slice = warp;
     }
 }
@@ -167,7 +179,7 @@ __device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage
     }
 }
 
-template <uint32_t N>
+template <uint32_t N, bool kInd = false>
 __global__ void __launch_bounds__(kDecThreads, 1)
 attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -176,28 +188,25 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     float* merge_o = reinterpret_cast<float*>(smem + kDecWarps * kRingBytes);
     float* merge_ml = merge_o + kMergeFloats;
     uint32_t* item_start = reinterpret_cast<uint32_t*>(merge_ml + kDecWarps * kHeadsPerKv * 2);
-    Sched sch;
-    // (the device copy is written by a setup kernel that precedes this one in plain stream order)
-    sch.lanes = p.tables != nullptr ? dec_lanes_of(p.tables) : p.lane;
-    sch.n_lanes = p.tables != nullptr ? tables_n_lanes(p.tables) : p.n_lanes;
-    sch.total_items = p.tables != nullptr ? tables_total_items(p.tables) : p.total_items;
-    for (uint32_t i = threadIdx.x; i <= sch.n_lanes; i += kDecThreads)
-        item_start[i] = i < sch.n_lanes ? sch.lanes[i].item_start : sch.total_items;
+    // (a device copy of the tables is written by a setup kernel that precedes this one in plain stream order)
+    const uint32_t n_lanes = lanes_in<N, kInd>(p), total_items = items_in<N, kInd>(p);
+    for (uint32_t i = threadIdx.x; i <= n_lanes; i += kDecThreads)
+        item_start[i] = i < n_lanes ? lane_at<N, kInd>(p, i).item_start : total_items;
     __syncthreads();
     const uint32_t ring = smem_u32(smem + warp * kRingBytes);
 
     // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
     SliceCursor pc{};
     pc.item = blockIdx.x;
-    pc.valid = pc.item < sch.total_items;
+    pc.valid = pc.item < total_items;
     bool early = false;
     if (pc.valid) {
-        cursor_load_item(pc, p, sch, item_start);
+        cursor_load_item<N, kInd>(pc, p, item_start);
         pc.slice = warp;
         // Every partition but a lane's last is full (at least 128 keys = 2 slices for each warp) and
         // holds only keys written before this token, so its first slices can be requested at once.
-        early = pc.part + 1u < sch.lanes[pc.lane].nparts;
-        cursor_settle(pc, p, sch, item_start, warp);
+        early = pc.part + 1u < lane_at<N, kInd>(p, pc.lane).nparts;
+        cursor_settle<N, kInd>(pc, p, item_start, warp);
     }
     uint32_t issued = 0, consumed = 0;
     auto fill_ring = [&]() {
@@ -206,7 +215,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
             if (pc.valid) {
                 issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
                 pc.slice += kDecWarps;
-                cursor_settle(pc, p, sch, item_start, warp);
+                cursor_settle<N, kInd>(pc, p, item_start, warp);
             }
             cp_async_commit();
             ++issued;
@@ -231,9 +240,9 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     const float score_scale = kAttnScale * kLog2e;
 
     SliceCursor cc{};
-    for (cc.item = blockIdx.x; cc.item < sch.total_items; cc.item += gridDim.x) {
-        cursor_load_item(cc, p, sch, item_start);
-        const DecLane& dl = sch.lanes[cc.lane];
+    for (cc.item = blockIdx.x; cc.item < total_items; cc.item += gridDim.x) {
+        cursor_load_item<N, kInd>(cc, p, item_start);
+        const DecLane& dl = lane_at<N, kInd>(p, cc.lane);
         // Q fragments of head (kv*8 + g): A rows 0..7 of every k-step.
         uint32_t qa[16][2];
         {
@@ -255,7 +264,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
             if (pc.valid) {
                 issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
                 pc.slice += kDecWarps;
-                cursor_settle(pc, p, sch, item_start, warp);
+                cursor_settle<N, kInd>(pc, p, item_start, warp);
             }
             cp_async_commit();
             ++issued;
@@ -372,7 +381,7 @@ struct DecTables {
     CombineLane comb[TATARA_MAX_LANES];
 };
 static_assert(sizeof(DecTables) <= kLaneScheduleBytes, "lane schedule buffer");
-__device__ __forceinline__ const DecLane* dec_lanes_of(const DecTables* t) { return t->dec; }
+__device__ __forceinline__ const DecLane& table_lane(const DecTables* t, uint32_t i) { return t->dec[i]; }
 __device__ __forceinline__ uint32_t tables_n_lanes(const DecTables* t) { return t->n_lanes; }
 __device__ __forceinline__ uint32_t tables_total_items(const DecTables* t) { return t->total_items; }
 constexpr uint32_t kMaxPeers = 8;
@@ -410,7 +419,7 @@ constexpr uint32_t kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
 template <uint32_t N>
 constexpr uint32_t combine_warps() { return N == 1 ? 32u : 8u; }
 
-template <uint32_t N>
+template <uint32_t N, bool kInd = false>
 __global__ void __launch_bounds__(combine_warps<N>() * 32u)
 attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     constexpr uint32_t kWarps = combine_warps<N>(), kCombineThreads = kWarps * 32u;
@@ -449,8 +458,8 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
         __syncthreads();
         if (arrived == 0u) return;
     }
-    const CombineLane& cl = p.tables != nullptr ? p.tables->comb[blockIdx.y] : p.lane[blockIdx.y];
-    if (cl.nparts == 0u) return;   // a lane the setup kernel rejected (context beyond capacity): status is latched
+    const CombineLane& cl = kInd ? p.tables->comb[blockIdx.y] : p.lane[blockIdx.y];
+    if (kInd && cl.nparts == 0u) return;   // a lane the setup kernel rejected (context beyond capacity): status is latched
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride;
@@ -745,9 +754,9 @@ static tatara_status launch_decode_indirect(tatara_ctx* ctx, cudaStream_t stream
     cp.query_stride = r.query_stride;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
-        if (cudaFuncSetAttribute(attn_decode_partition_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(attn_decode_partition_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kDecSmemBytes) != cudaSuccess ||
-            cudaFuncSetAttribute(attn_combine_kernel<N>, cudaFuncAttributePreferredSharedMemoryCarveout,
+            cudaFuncSetAttribute(attn_combine_kernel<N, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared) != cudaSuccess)
             return check_launch(ctx, "attn_decode: shared memory attribute");
         configured[ctx->device & 63] = true;
@@ -760,7 +769,7 @@ static tatara_status launch_decode_indirect(tatara_ctx* ctx, cudaStream_t stream
     cfg.blockDim = dim3(kDecThreads);
     cfg.dynamicSmemBytes = kDecSmemBytes;
     cfg.stream = stream;
-    (void)cudaLaunchKernelEx(&cfg, attn_decode_partition_kernel<N>, dp);
+    (void)cudaLaunchKernelEx(&cfg, attn_decode_partition_kernel<N, true>, dp);
     st = check_launch(ctx, what);
     if (st != TATARA_OK) return st;
     cudaLaunchAttribute attr[1];
@@ -771,7 +780,7 @@ static tatara_status launch_decode_indirect(tatara_ctx* ctx, cudaStream_t stream
     cfg.dynamicSmemBytes = 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<N>, cp);
+    (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<N, true>, cp);
     return check_launch(ctx, what);
 }
 
