@@ -1,0 +1,344 @@
+// Native test of the wave loop (tatara_b200/host/wave_loop.hpp), in the style of the reference's
+// tests (plain main(), a distinct non-zero exit code per failed check).
+//
+// The properties checked are the ones the reference states for its owner loop
+// (tools/native/tatara_serve.cpp:1463-1777): a stream's tokens do not depend on which other streams
+// share its waves or on the lane it lands on; joins advance one unit per wave beside the decode
+// work; stop ids, maximum_tokens and cancellation end a lane with the matching reason; a finished
+// lane is reset before reuse; two joiners prefer distinct lane groups.  The wave's captured graph
+// (lane tables in device memory) is compared bit for bit with a token walked eagerly through
+// LayerPass (host tables), whose layers tests/native/hybrid_layers_test.cpp holds against the CPU
+// oracle.
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <thread>
+#include <utility>
+#include <vector>
+
+#include "../../tatara_b200/host/wave_loop.hpp"
+
+using namespace tatara::runtime;
+using namespace tatara::engine;
+using u16 = std::uint16_t;
+
+namespace {
+
+u16 to_bf16(float v) {
+    std::uint32_t b;
+    std::memcpy(&b, &v, 4);
+    return static_cast<u16>((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+}
+struct Rng {
+    std::uint64_t s;
+    std::uint64_t next() { s ^= s >> 12; s ^= s << 25; s ^= s >> 27; return s * 0x2545F4914F6CDD1Dull; }
+    float uniform() { return static_cast<float>(next() >> 40) / 16777216.0f; }
+    float normal() { float a = 0; for (int i = 0; i < 12; ++i) a += uniform(); return a - 6.0f; }
+};
+
+// Device copies of one layer's weights.
+struct LayerStore {
+    std::vector<DeviceBuffer> buffers;
+    const void* put(const void* host, std::size_t bytes) {
+        buffers.emplace_back(bytes);
+        if (!buffers.back() || cudaMemcpy(buffers.back().data(), host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
+        return buffers.back().data();
+    }
+    QuantizedWeight q4(Rng& rng, std::uint32_t rows, std::uint32_t k, float gain) {
+        std::vector<std::uint32_t> words(std::size_t{rows} * k / 8);
+        for (auto& w : words) w = static_cast<std::uint32_t>(rng.next());
+        std::vector<u16> scales(std::size_t{rows} * k / 64), biases(scales.size());
+        for (std::size_t i = 0; i < scales.size(); ++i) {
+            const float sc = gain * (1.0f + 0.2f * (2.0f * rng.uniform() - 1.0f));
+            scales[i] = to_bf16(sc);
+            biases[i] = to_bf16(-7.5f * sc * (1.0f + 0.1f * rng.normal()));
+        }
+        return QuantizedWeight{put(words.data(), words.size() * 4), put(scales.data(), scales.size() * 2),
+                               put(biases.data(), biases.size() * 2), rows};
+    }
+    const void* vec(Rng& rng, std::size_t n, float scale, float shift) {
+        std::vector<u16> v(n);
+        for (auto& x : v) x = to_bf16(shift + scale * rng.normal());
+        return put(v.data(), n * 2);
+    }
+};
+
+bool make_layers(const std::vector<LayerKind>& schedule, std::vector<LayerStore>& stores, std::vector<PathLayer>& layers) {
+    Rng rng{0xBEEF5EEDull};
+    stores.resize(schedule.size());
+    for (std::size_t l = 0; l < schedule.size(); ++l) {
+        LayerStore& st = stores[l];
+        PathLayer p;
+        p.kind = schedule[l];
+        // gains keep a row's scale near one through projection -> layer -> out projection
+        if (p.kind == LayerKind::FullAttention) {
+            p.attention = AttentionWeights{st.vec(rng, 256, 0.1f, 1.0f), st.vec(rng, 256, 0.1f, 1.0f)};
+            p.attention_q4 = AttentionProjection{st.q4(rng, 8192, kHidden, 0.005f), st.q4(rng, 512, kHidden, 0.005f),
+                                                 st.q4(rng, 512, kHidden, 0.005f), st.q4(rng, kHidden, 4096, 0.02f)};
+            if (p.attention.q_norm == nullptr || p.attention_q4.out.biases == nullptr) return false;
+        } else {
+            std::vector<u16> a_log(32);
+            for (auto& x : a_log) x = to_bf16(std::log(1.0f + 15.0f * rng.uniform()));
+            p.gated_delta = GatedDeltaWeights{st.vec(rng, 8192 * 4, 0.5f, 0.0f), st.put(a_log.data(), 64),
+                                              st.vec(rng, 32, 0.5f, 0.0f), st.vec(rng, 128, 0.1f, 1.0f)};
+            p.gated_delta_q4 = GatedDeltaProjection{st.q4(rng, 8192, kHidden, 0.005f), st.q4(rng, 4096, kHidden, 0.005f),
+                                                    st.q4(rng, 32, kHidden, 0.005f), st.q4(rng, 32, kHidden, 0.005f),
+                                                    st.q4(rng, kHidden, 4096, 0.01f)};
+            if (p.gated_delta.norm == nullptr || p.gated_delta_q4.out.biases == nullptr) return false;
+        }
+        layers.push_back(p);
+    }
+    return true;
+}
+
+// Host stand-ins for embedding and sampler: a token's row is a fixed pseudo-random vector; the
+// sampled token is a hash of the output row's bits, so any differing bit changes the stream.
+TokenBoundary make_boundary() {
+    TokenBoundary b;
+    b.embed = [](std::uint32_t token, std::uint32_t, u16* row) {
+        Rng rng{0x9E3779B97F4A7C15ull ^ (std::uint64_t{token} * 0xD1B54A32D192ED03ull + 1)};
+        for (std::uint32_t i = 0; i < kHidden; ++i) row[i] = to_bf16(rng.normal());
+    };
+    b.sample = [](const u16* row) {
+        std::uint64_t h = 0xCBF29CE484222325ull;
+        for (std::uint32_t i = 0; i < kHidden; ++i) h = (h ^ row[i]) * 0x100000001B3ull;
+        return static_cast<std::uint32_t>(h % 50021u);
+    };
+    return b;
+}
+
+struct Request {
+    std::vector<std::uint32_t> prompt;
+    std::uint32_t maximum_tokens;
+    std::vector<std::uint32_t> stop_ids;
+    std::shared_ptr<LaneChannel> channel = std::make_shared<LaneChannel>();
+    std::shared_ptr<std::atomic<bool>> cancelled = std::make_shared<std::atomic<bool>>(false);
+    OwnerSubmission submission() const { return OwnerSubmission{prompt, stop_ids, maximum_tokens, channel, cancelled}; }
+    std::vector<std::uint32_t> tokens() const {
+        std::lock_guard<std::mutex> guard(channel->mutex);
+        return std::vector<std::uint32_t>(channel->tokens.begin(), channel->tokens.end());
+    }
+};
+std::vector<std::uint32_t> make_prompt(std::uint32_t n, std::uint32_t seed) {
+    std::vector<std::uint32_t> p(n);
+    for (std::uint32_t i = 0; i < n; ++i) p[i] = (seed * 7919u + i * 104729u) % 50021u;
+    return p;
+}
+// Runs waves until every submitted request is done (bounded).
+bool drain(MultiStreamOwner& owner, int limit = 2000) {
+    for (int i = 0; i < limit && owner.outstanding() != 0; ++i) (void)owner.run_wave();
+    return owner.outstanding() == 0;
+}
+
+// A single-row request walked token by token through LayerPass with host tables (no graph, no device tables).
+bool eager_tokens(tatara_ctx* ctx, const std::vector<PathLayer>& layers, const TokenBoundary& boundary, std::uint32_t capacity,
+                  std::uint32_t first_input, std::uint32_t count, std::vector<std::uint32_t>& out) {
+    std::vector<LayerKind> schedule;
+    for (const PathLayer& l : layers) schedule.push_back(l.kind);
+    DecodeStatePool pool;
+    std::vector<DecodeStateSlot> slots;
+    DecodeBatchScratch scratch;
+    if (!create_state_pool(1, capacity, schedule, pool, slots) || !create_batch_scratch(1, capacity, scratch)) return false;
+    DeviceBuffer hidden[2] = {DeviceBuffer(kHidden * 2), DeviceBuffer(kHidden * 2)}, slab(kGdnProjectionRows * 2);
+    std::vector<u16> row(kHidden);
+    std::uint32_t input = first_input;
+    for (std::uint32_t t = 0; t < count; ++t) {
+        boundary.embed(input, t, row.data());
+        if (cudaMemcpy(hidden[0].data(), row.data(), kHidden * 2, cudaMemcpyHostToDevice) != cudaSuccess) return false;
+        const std::vector<DecodeStream> streams{{&slots[0], t}};
+        LayerPass pass(ctx, nullptr);
+        std::uint32_t cur = 0;
+        for (std::size_t l = 0; l < layers.size(); ++l) {
+            if (layers[l].kind == LayerKind::FullAttention) {
+                pass.encode_attention_project(layers[l].attention_q4, hidden[cur].data(), 1, slab.data());
+                pass.encode_attention(pool, l, layers[l].attention, streams, slab.data(), scratch);
+                pass.encode_out_projection(layers[l].attention_q4.out, scratch.attended.data(), 1, hidden[cur ^ 1].data(), kHidden);
+            } else {
+                pass.encode_gated_delta_project(layers[l].gated_delta_q4, hidden[cur].data(), 1, slab.data());
+                pass.encode_gated_delta(pool, l, layers[l].gated_delta, streams, slab.data(), scratch);
+                pass.encode_out_projection(layers[l].gated_delta_q4.out, scratch.gdn_gated.data(), 1, hidden[cur ^ 1].data(), kHidden);
+            }
+            cur ^= 1u;
+        }
+        if (pass.commit_and_wait() != CommandError::None) return false;
+        if (cudaMemcpy(row.data(), hidden[cur].data(), kHidden * 2, cudaMemcpyDeviceToHost) != cudaSuccess) return false;
+        advance_decode_state(pool, streams);
+        input = boundary.sample(row.data());
+        out.push_back(input);
+    }
+    return true;
+}
+
+int host_only_checks() {
+    // nothing to walk, or no boundary: the owner refuses to build and to queue
+    MultiStreamOwner empty(OwnerConfig{}, {}, make_boundary());
+    if (empty) return 10;
+    Request r{make_prompt(3, 1), 4, {}};
+    OwnerSubmission no_channel = r.submission();
+    no_channel.channel.reset();
+    if (empty.submit(std::move(no_channel))) return 11;
+    OwnerSubmission no_prompt = r.submission();
+    no_prompt.prompt.clear();
+    if (empty.submit(std::move(no_prompt))) return 12;
+    empty.stop();
+    if (empty.submit(r.submission())) return 13;   // stopping: refused
+    return 0;
+}
+
+int device_checks(tatara_ctx* ctx) {
+    const std::vector<LayerKind> schedule{LayerKind::GatedDelta, LayerKind::GatedDelta, LayerKind::FullAttention,
+                                          LayerKind::GatedDelta};
+    std::vector<LayerStore> stores;
+    std::vector<PathLayer> layers;
+    if (!make_layers(schedule, stores, layers)) return 20;
+    const TokenBoundary boundary = make_boundary();
+    constexpr std::uint32_t kCapacity = 512;
+
+    // --- three streams sharing waves; joins of 69 and 149 prompt rows advance 64 rows per wave
+    OwnerConfig shared{0, 1, 4, kCapacity, 2, 64};
+    MultiStreamOwner owner(shared, layers, boundary);
+    if (!owner) return 21;
+    Request a{make_prompt(1, 11), 6, {}}, b{make_prompt(70, 22), 9, {}}, c{make_prompt(150, 33), 4, {}};
+    if (!owner.submit(a.submission()) || !owner.submit(b.submission()) || !owner.submit(c.submission())) return 22;
+    // first wave: a decodes alone (b and c are still joining)
+    if (owner.run_wave() != 1) return 23;
+    // second wave: b's second unit (5 rows) completed in the first wave's settle? no: units 64 + 5 -> b joins wave 3
+    if (owner.run_wave() != 1) return 24;
+    if (owner.run_wave() != 2) return 25;   // a and b
+    if (owner.run_wave() != 3) return 26;   // c placed 64 + 64 + 21 rows in three waves
+    if (!drain(owner)) return 27;
+    if (owner.last_error() != CommandError::None) return 28;
+    if (a.tokens().size() != 6 || b.tokens().size() != 9 || c.tokens().size() != 4) return 29;
+    if (a.channel->reason != LaneDoneReason::Length || !a.channel->done) return 30;
+    const WaveStatistics& st = owner.statistics();
+    if (st.wave_rows_max != 3 || st.graphs_captured != 3 || st.graph_launches != st.wave_count || st.join_units != 5) return 31;
+    if (st.wave_rows_total != 6 + 9 + 4) return 32;
+
+    // --- each stream alone on a one-lane owner: the same tokens
+    {
+        OwnerConfig solo{0, 1, 1, kCapacity, 1, 64};
+        MultiStreamOwner alone(solo, layers, boundary);
+        if (!alone) return 40;
+        const Request* shared_runs[3] = {&a, &b, &c};
+        for (int i = 0; i < 3; ++i) {
+            Request again{shared_runs[i]->prompt, shared_runs[i]->maximum_tokens, {}};
+            if (!alone.submit(again.submission()) || !drain(alone)) return 41;
+            if (again.tokens() != shared_runs[i]->tokens()) return 42 + i;   // 42, 43, 44
+        }
+        if (alone.statistics().graphs_captured != 1) return 45;   // one graph served all three streams and every context
+    }
+
+    // --- the captured wave (device tables) against the eager walk through LayerPass (host tables)
+    {
+        std::vector<std::uint32_t> eager;
+        if (!eager_tokens(ctx, layers, boundary, kCapacity, a.prompt.back(), 6, eager)) return 50;
+        if (eager != a.tokens()) return 51;
+    }
+
+    // --- stop id, cancellation, lane reuse after finish
+    {
+        const std::vector<std::uint32_t> full = b.tokens();
+        Request stopped{b.prompt, 9, {full[3]}};
+        Request cancelled{c.prompt, 400, {}};
+        Request reused{a.prompt, 6, {}};
+        if (!owner.submit(stopped.submission()) || !owner.submit(cancelled.submission())) return 60;
+        for (int i = 0; i < 6; ++i) (void)owner.run_wave();
+        cancelled.cancelled->store(true);
+        if (!drain(owner)) return 61;
+        if (stopped.channel->reason != LaneDoneReason::Stopped || stopped.tokens().size() != 4) return 62;
+        if (stopped.tokens() != std::vector<std::uint32_t>(full.begin(), full.begin() + 4)) return 63;
+        if (cancelled.channel->reason != LaneDoneReason::Cancelled) return 64;
+        const std::vector<std::uint32_t> part = cancelled.tokens(), whole = c.tokens();
+        if (part.empty() || part.size() > 400) return 65;
+        for (std::size_t i = 0; i < std::min(part.size(), whole.size()); ++i)
+            if (part[i] != whole[i]) return 66;
+        // every lane of the group has been used by now: the next request lands on a dirty lane
+        if (!owner.submit(reused.submission()) || !drain(owner)) return 67;
+        if (reused.tokens() != a.tokens()) return 68;
+        // a request cancelled while its prompt is still joining never decodes
+        Request early{make_prompt(300, 44), 5, {}};
+        if (!owner.submit(early.submission())) return 69;
+        (void)owner.run_wave();
+        early.cancelled->store(true);
+        if (!drain(owner)) return 70;
+        if (early.channel->reason != LaneDoneReason::Cancelled || !early.tokens().empty()) return 71;
+        // ... and its lane serves the next request correctly
+        Request after{b.prompt, 9, {}};
+        if (!owner.submit(after.submission()) || !drain(owner)) return 72;
+        if (after.tokens() != full) return 73;
+    }
+
+    // --- two groups: simultaneous joiners land in distinct groups; the owner thread's own loop
+    {
+        OwnerConfig two{0, 2, 2, kCapacity, 2, 64};
+        MultiStreamOwner wide(two, layers, boundary);
+        if (!wide) return 80;
+        Request p{b.prompt, 9, {}}, q{c.prompt, 4, {}};
+        if (!wide.submit(p.submission()) || !wide.submit(q.submission())) return 81;
+        (void)wide.run_wave();
+        std::uint32_t groups_joining = 0;
+        for (const MultiStreamOwner::Lane& lane : wide.lanes())
+            if (lane.request.channel) groups_joining |= 1u << lane.group;
+        if (groups_joining != 3u) return 82;
+        std::thread loop([&] { wide.run(); });
+        Request r{a.prompt, 6, {}};
+        const bool queued = wide.submit(r.submission());
+        for (Request* req : {&p, &q, &r}) {
+            std::unique_lock<std::mutex> guard(req->channel->mutex);
+            req->channel->ready.wait_for(guard, std::chrono::seconds(60), [&] { return req->channel->done; });
+        }
+        wide.stop();
+        loop.join();
+        if (!queued || !p.channel->done || !q.channel->done || !r.channel->done) return 83;
+        if (p.tokens() != b.tokens() || q.tokens() != c.tokens() || r.tokens() != a.tokens()) return 84;
+    }
+
+    // --- tensor-unit policy for prompt blocks (dequantised weights): joins complete, tokens are produced
+    {
+        std::vector<PathLayer> dense_layers = layers;
+        std::vector<DeviceBuffer> dense;
+        for (PathLayer& l : dense_layers) {
+            const bool attention = l.kind == LayerKind::FullAttention;
+            const std::uint32_t width = attention ? kAttnProjectionRows : kGdnProjectionRows;
+            dense.emplace_back(std::uint64_t{width} * kHidden * 2);
+            tatara_q4_matrix m[4];
+            std::uint32_t n = 0;
+            auto add = [&](const QuantizedWeight& w) { m[n++] = tatara_q4_matrix{w.words, w.scales, w.biases, w.rows, 0}; };
+            if (attention) { add(l.attention_q4.query); add(l.attention_q4.key); add(l.attention_q4.value); }
+            else { add(l.gated_delta_q4.qkv); add(l.gated_delta_q4.z); add(l.gated_delta_q4.b); add(l.gated_delta_q4.a); }
+            if (!dense.back() || tatara_q4_dequantize(ctx, nullptr, m, n, kHidden, dense.back().data()) != TATARA_OK) return 90;
+            l.project_dense = dense.back().data();
+            dense.emplace_back(std::uint64_t{kHidden} * 4096 * 2);
+            n = 0;
+            add(attention ? l.attention_q4.out : l.gated_delta_q4.out);
+            if (!dense.back() || tatara_q4_dequantize(ctx, nullptr, m, 1, 4096, dense.back().data()) != TATARA_OK) return 91;
+            l.out_dense = dense.back().data();
+        }
+        if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 92;
+        OwnerConfig cfg{0, 1, 2, kCapacity, 1, 128};
+        MultiStreamOwner mixed(cfg, dense_layers, boundary);
+        if (!mixed) return 93;
+        Request p{c.prompt, 4, {}}, again{c.prompt, 4, {}};
+        if (!mixed.submit(p.submission()) || !drain(mixed)) return 94;
+        if (mixed.last_error() != CommandError::None || p.tokens().size() != 4 || p.channel->reason != LaneDoneReason::Length) return 95;
+        if (!mixed.submit(again.submission()) || !drain(mixed)) return 96;
+        if (again.tokens() != p.tokens()) return 97;   // deterministic: the same prompt gives the same stream on a reused lane
+    }
+    return 0;
+}
+
+} // namespace
+
+int main() {
+    if (const int rc = host_only_checks(); rc != 0) { std::printf("host check failed: %d\n", rc); return rc; }
+    tatara_ctx* ctx = nullptr;
+    const tatara_status st = tatara_ctx_create(0, &ctx);
+    if (st == TATARA_INVALID_DEVICE) { std::printf("host checks passed; no B200 present, device checks skipped\n"); return 0; }
+    if (st != TATARA_OK) return 2;
+    const int rc = device_checks(ctx);
+    tatara_ctx_destroy(ctx);
+    if (rc != 0) { std::printf("device check failed: %d\n", rc); return rc; }
+    std::printf("host and device checks passed\n");
+    return 0;
+}
