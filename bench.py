@@ -149,7 +149,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project", "state_copy", "layers"],
+    ap.add_argument("--only", default=None, choices=[None, "decode", "prefill", "gdn_step", "gdn_prefill", "lanes32", "project", "state_copy", "layers", "wave"],
                     help="run one workload only (small profiling runs)")
     ap.add_argument("--context", type=int, default=HEADLINE_CONTEXT)
     ap.add_argument("--rows", type=int, default=PREFILL_ROWS)

@@ -516,6 +516,23 @@ class Workloads:
                 "timing": "kernel: CUDA graph; collective and end-to-end: host-issued, CUDA events, max over ranks"}
 
     # ---- single-workload runs (profiling)
+    # ---- the engine's wave loop over a 40-layer stack (native program above the C ABI)
+    def wave_loop(self, lanes=8, context=16384, tokens=40):
+        """Runs tatara_b200/wave_bench (host/wave_bench.cpp): 8 streams join through the owner loop to
+        `context` positions, then full decode waves are timed with the host clock; the same waves walked
+        eagerly with host tables beside them."""
+        import json
+        import subprocess
+        exe = os.path.join(os.path.dirname(os.path.abspath(tb.__file__)), "wave_bench")
+        if not os.path.exists(exe):
+            raise RuntimeError("tatara_b200/wave_bench is not built: run __graft_entry__.build()")
+        self.torch.cuda.empty_cache()
+        res = subprocess.run([exe, "--lanes", str(lanes), "--context", str(context), "--tokens", str(tokens)],
+                             capture_output=True, text=True, timeout=600)
+        if res.returncode != 0:
+            raise RuntimeError(f"wave_bench failed ({res.returncode}): {res.stderr[-400:]}")
+        return json.loads(res.stdout.strip().splitlines()[-1])
+
     def run_only(self, which, args, timed, steps, warmup):
         if which == "decode":
             d = self.decode_setup(args.context)
@@ -530,6 +547,8 @@ class Workloads:
             return self.gdn_prefill(timed, rows=args.rows)
         if which == "layers":
             return self.layer_slices(timed, steps, warmup, lanes=args.lanes if args.lanes != 4 else 1, context=min(args.context, 65536))
+        if which == "wave":
+            return self.wave_loop(lanes=args.lanes if args.lanes != 4 else 8, context=min(args.context, 32768))
         if which == "state_copy":
             return self.state_copy(timed, measured_peaks())
         if which == "project":
