@@ -131,6 +131,9 @@ int main(int argc, char** argv) {
         layers.push_back(p);
     }
     if (tatara_ctx_sync(ctx, nullptr) != TATARA_OK) return 6;
+    const bool verbose = std::getenv("WAVE_BENCH_VERBOSE") != nullptr;
+    const auto start = Clock::now();
+    if (verbose) std::fprintf(stderr, "weights ready (%.1f MB of Q4)\n", store.bytes / 1e6);
 
     TokenBoundary boundary;
     boundary.embed = [](std::uint32_t token, std::uint32_t, u16* row) {
@@ -151,9 +154,10 @@ int main(int argc, char** argv) {
     double join_ms = 0, wave_ms = 0;
     std::uint64_t graphs = 0, launches_per_wave = 0;
     {
-        OwnerConfig config{0, 1, lanes, capacity, std::min<std::uint32_t>(lanes, 2), unit};
+        OwnerConfig config{0, 1, lanes, capacity, std::min<std::uint32_t>(lanes, 2), unit, 5000};
         MultiStreamOwner owner(config, layers, boundary);
         if (!owner) { std::fprintf(stderr, "owner failed to build\n"); return 7; }
+        if (verbose) std::fprintf(stderr, "owner built, %.1f ms since start\n", ms_since(start));
         std::vector<std::shared_ptr<LaneChannel>> channels;
         for (std::uint32_t s = 0; s < lanes; ++s) {
             OwnerSubmission sub;
@@ -168,9 +172,19 @@ int main(int argc, char** argv) {
         // joins: until every lane decodes (the early lanes already produce tokens meanwhile)
         const auto j0 = Clock::now();
         std::size_t rows = 0;
-        for (int guard = 0; guard < 100000 && rows < lanes; ++guard) rows = owner.run_wave();
+        const int wave_limit = static_cast<int>(join_waves) + 8;
+        for (int guard = 0; guard < wave_limit && rows < lanes && owner.last_error() == CommandError::None; ++guard) {
+            rows = owner.run_wave();
+            if (verbose) std::fprintf(stderr, "wave %d: %zu rows, %.1f ms since start\n", guard, rows, ms_since(start));
+            if (ms_since(j0) > 120000.0) break;   // this program is a timing aid: never sit on a GPU
+        }
         join_ms = ms_since(j0);
-        if (rows != lanes || owner.last_error() != CommandError::None) { std::fprintf(stderr, "joins failed\n"); return 9; }
+        if (rows != lanes || owner.last_error() != CommandError::None) {
+            std::fprintf(stderr, "joins failed after %.0f ms: %zu of %u rows decode, join units %llu, last error %s, timed-out stream %d at step %d\n",
+                         join_ms, rows, lanes, static_cast<unsigned long long>(owner.statistics().join_units),
+                         to_string(owner.last_error()), owner.statistics().last_timeout_stream, owner.statistics().last_timeout_mark);
+            std::_Exit(9);   // a submission may still be in flight: leave without waiting for it
+        }
         // the last joiner has at least `tokens` tokens to go: time full waves
         for (int i = 0; i < 3; ++i) (void)owner.run_wave();
         const std::uint32_t timed = tokens > 8 ? tokens - 8 : 1;

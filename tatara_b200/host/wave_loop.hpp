@@ -13,8 +13,11 @@
 // is not re-encoded.  Per lane group and per row count it is captured ONCE as a CUDA graph whose
 // first nodes copy the wave's lane tables (state stripes, contexts, gated-delta parities) and the
 // rows' input vectors from pinned host memory; the kernels read the tables from device memory, so
-// the same graph serves every later wave of that size whatever its streams and contexts.  A
-// joining prompt advances on its own CUDA stream, so its blocks overlap the decode graph.
+// the same graph serves every later wave of that size whatever its streams and contexts.
+// Everything of a wave goes into ONE CUDA stream, decode graphs first and the joining prompts'
+// units behind them: the kernels of this library each fill the device, and its cluster /
+// tensor-memory kernels (tatara_project_dense, tatara_attn_prefill) are only ever issued with
+// nothing else in flight.  join_unit_rows bounds what a joining prompt adds to a wave.
 //
 // The walk covers the layers this library implements: per layer the fused projection, the
 // attention or gated-delta step and the out projection.  Embedding, the MoE / norm stages between
@@ -78,14 +81,18 @@ struct OwnerConfig {
     std::uint32_t groups{1};
     std::uint32_t lanes_per_group{8};   // the reference stripes up to eight lanes over one pool group
     std::uint32_t capacity{4096};
-    std::uint32_t join_streams{2};
+    std::uint32_t join_streams{2};      // join slots: prompts that advance side by side, one unit each per wave
     std::uint32_t join_unit_rows{256};  // prompt rows one join submission places
+    std::uint32_t wait_limit_ms{30000}; // a submission that has not completed by then fails its lanes
 };
 
 struct WaveStatistics {
     std::uint64_t wave_count{0}, wave_rows_total{0}, wave_rows_max{0}, full_wave_count{0};
     double wave_ms_total{0}, full_wave_ms_total{0};
     std::uint64_t graphs_captured{0}, graph_launches{0}, join_units{0};
+    std::uint64_t wait_timeouts{0};
+    int last_timeout_stream{-1};   // lane group index, or 1000 + join slot index
+    int last_timeout_mark{-1};     // join slots: first step of the unit that had not completed (3 * layer + step)
 };
 
 class PinnedBuffer {
@@ -124,8 +131,8 @@ class PinnedBuffer {
 
 // One pool group: lanes striped over shared state pools with their own batch scratch
 // (OwnerLaneGroup, tools/native/tatara_serve.cpp:1191-1197), plus what the captured wave needs:
-// a context and stream of its own, the lane tables and row vectors in pinned and device memory,
-// and one executable graph per row count.
+// a context of its own (the owner's stream), the lane tables and row vectors in pinned and device
+// memory, and one executable graph per row count.
 struct OwnerLaneGroup {
     rt::DecodeStatePool pool;
     std::vector<rt::DecodeStateSlot> slots;
@@ -137,12 +144,14 @@ struct OwnerLaneGroup {
     std::vector<cudaGraphExec_t> graphs;   // index = rows in the wave
 };
 
-// A join stream: one prompt head being placed, one unit per wave (JoiningLane, tatara_serve.cpp:1343-1347).
+// A join slot: one prompt head being placed, one unit per wave (JoiningLane, tatara_serve.cpp:1343-1347).
+// stream and ctx are the owner's (shared by every slot).
 struct JoinStream {
     cudaStream_t stream{nullptr};
     tatara_ctx* ctx{nullptr};
     PinnedBuffer rows_host;
     rt::DeviceBuffer hidden[2], projection_slab, query, gate, attended, qk, value, z, decay, beta, y, gated, scan_scratch;
+    std::vector<cudaEvent_t> marks;   // one per step of a unit (projection, layer body, out projection per layer)
 };
 
 class MultiStreamOwner {
@@ -173,20 +182,16 @@ class MultiStreamOwner {
     MultiStreamOwner(const MultiStreamOwner&) = delete;
     MultiStreamOwner& operator=(const MultiStreamOwner&) = delete;
     ~MultiStreamOwner() {
+        if (stream_ != nullptr) cudaStreamSynchronize(stream_);
         for (OwnerLaneGroup& g : groups_) {
-            if (g.stream != nullptr) cudaStreamSynchronize(g.stream);
             for (cudaGraphExec_t e : g.graphs)
                 if (e != nullptr) cudaGraphExecDestroy(e);
-            if (g.stream != nullptr) cudaStreamDestroy(g.stream);
             if (g.ctx != nullptr) tatara_ctx_destroy(g.ctx);
         }
-        for (JoiningLane& j : joining_) {
-            if (j.io.stream != nullptr) {
-                cudaStreamSynchronize(j.io.stream);
-                cudaStreamDestroy(j.io.stream);
-            }
-            if (j.io.ctx != nullptr) tatara_ctx_destroy(j.io.ctx);
-        }
+        if (stream_ != nullptr) cudaStreamDestroy(stream_);
+        for (JoiningLane& j : joining_)
+            for (cudaEvent_t e : j.io.marks) cudaEventDestroy(e);
+        if (join_ctx_ != nullptr) tatara_ctx_destroy(join_ctx_);
     }
     explicit operator bool() const noexcept { return ok_; }
     const WaveStatistics& statistics() const noexcept { return stats_; }
@@ -238,7 +243,6 @@ class MultiStreamOwner {
     // active lane, settle.  Returns the number of rows that decoded in this wave.
     std::size_t run_wave() {
         admit_joiners();
-        for (JoiningLane& stream : joining_) submit_join_units(stream);
 
         const auto wave_start = std::chrono::steady_clock::now();
         wave_.clear();
@@ -263,11 +267,12 @@ class MultiStreamOwner {
             }
             submitted_[g] = true;
         }
+        for (JoiningLane& stream : joining_) submit_join_units(stream);   // behind the decode graphs
         for (JoiningLane& stream : joining_) settle_join_units(stream);
         for (std::size_t g = 0; g < plans_.size(); ++g) {
             if (!submitted_[g]) continue;
             OwnerLaneGroup& group = groups_[g];
-            const tatara_status st = tatara_ctx_sync(group.ctx, group.stream);
+            const tatara_status st = wait_until_completed(group.ctx, group.stream, static_cast<int>(g));
             if (st != TATARA_OK) {
                 last_error_ = rt::to_command_error(st);
                 for (Lane* lane : plans_[g]) finish(*lane, LaneDoneReason::Failed);
@@ -295,6 +300,22 @@ class MultiStreamOwner {
   private:
     static constexpr std::uint64_t kRowBytes = std::uint64_t{rt::kHidden} * 2;
 
+    // wait_until_completed with a limit: the owner thread never blocks for good on a submission
+    // (every device-side wait of the library is bounded too, so this is the last line).
+    tatara_status wait_until_completed(tatara_ctx* ctx, cudaStream_t stream, int which) {
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(config_.wait_limit_ms);
+        while (true) {
+            const cudaError_t q = cudaStreamQuery(stream);
+            if (q == cudaSuccess) return tatara_ctx_sync(ctx, stream);
+            if (q != cudaErrorNotReady) return TATARA_CUDA_ERROR;
+            if (std::chrono::steady_clock::now() > deadline) {
+                stats_.wait_timeouts += 1;
+                stats_.last_timeout_stream = which;
+                return TATARA_DEVICE_WAIT_TIMEOUT;
+            }
+        }
+    }
+
     bool build() {
         if (layers_.empty() || config_.groups == 0 || config_.lanes_per_group == 0 ||
             config_.lanes_per_group > rt::kMaximumBatchRows || config_.join_unit_rows == 0 || !boundary_.embed ||
@@ -306,6 +327,7 @@ class MultiStreamOwner {
             if (l.kind == rt::LayerKind::GatedDelta) gdn_index_.push_back(gdn_layers_++);
             else gdn_index_.push_back(0);
         }
+        if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return false;
         const std::uint32_t rows = config_.lanes_per_group;
         groups_.resize(config_.groups);
         plans_.resize(config_.groups);
@@ -313,9 +335,9 @@ class MultiStreamOwner {
             OwnerLaneGroup& group = groups_[g];
             if (!rt::create_state_pool(rows, config_.capacity, schedule, group.pool, group.slots) ||
                 !rt::create_batch_scratch(rows, config_.capacity, group.batch_scratch) ||
-                tatara_ctx_create(config_.device, &group.ctx) != TATARA_OK ||
-                cudaStreamCreateWithFlags(&group.stream, cudaStreamNonBlocking) != cudaSuccess)
+                tatara_ctx_create(config_.device, &group.ctx) != TATARA_OK)
                 return false;
+            group.stream = stream_;
             group.tables_host = PinnedBuffer(table_bytes());
             group.rows_in_host = PinnedBuffer(rows * kRowBytes);
             group.rows_out_host = PinnedBuffer(rows * kRowBytes);
@@ -337,11 +359,14 @@ class MultiStreamOwner {
         }
         joining_.resize(config_.join_streams);
         const std::uint64_t u = config_.join_unit_rows;
+        if (tatara_ctx_create(config_.device, &join_ctx_) != TATARA_OK) return false;
         for (JoiningLane& j : joining_) {
             JoinStream& io = j.io;
-            if (tatara_ctx_create(config_.device, &io.ctx) != TATARA_OK ||
-                cudaStreamCreateWithFlags(&io.stream, cudaStreamNonBlocking) != cudaSuccess)
-                return false;
+            io.ctx = join_ctx_;
+            io.stream = stream_;
+            io.marks.assign(3 * layers_.size(), nullptr);
+            for (cudaEvent_t& e : io.marks)
+                if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return false;
             io.rows_host = PinnedBuffer(u * kRowBytes);
             io.hidden[0] = rt::DeviceBuffer(u * kRowBytes);
             io.hidden[1] = rt::DeviceBuffer(u * kRowBytes);
@@ -413,7 +438,7 @@ class MultiStreamOwner {
         return true;
     }
 
-    // Admit joiners while join streams are available, preferring a free lane in a group with no
+    // Admit joiners while join slots are available, preferring a free lane in a group with no
     // join in flight (tatara_serve.cpp:1471-1524).
     void admit_joiners() {
         while (true) {
@@ -475,7 +500,7 @@ class MultiStreamOwner {
         return false;
     }
 
-    // Encodes one unit of the in-flight join on the join stream: rows [placed, placed + n) of the prompt head.
+    // Encodes one unit of the in-flight join: rows [placed, placed + n) of the prompt head.
     void submit_join_units(JoiningLane& stream) {
         if (stream.lane == nullptr) return;
         Lane& lane = *stream.lane;
@@ -503,9 +528,16 @@ class MultiStreamOwner {
     void settle_join_units(JoiningLane& stream) {
         if (stream.lane == nullptr || stream.in_flight == 0) return;
         Lane& lane = *stream.lane;
-        const tatara_status st = tatara_ctx_sync(stream.io.ctx, stream.io.stream);
+        const tatara_status st =
+            wait_until_completed(stream.io.ctx, stream.io.stream, 1000 + static_cast<int>(&stream - joining_.data()));
         if (st != TATARA_OK) {
             last_error_ = rt::to_command_error(st);
+            if (st == TATARA_DEVICE_WAIT_TIMEOUT)
+                for (std::size_t m = 0; m < stream.io.marks.size(); ++m)
+                    if (cudaEventQuery(stream.io.marks[m]) != cudaSuccess) {
+                        if (stats_.last_timeout_mark < 0) stats_.last_timeout_mark = static_cast<int>(m);
+                        break;
+                    }
             finish(lane, LaneDoneReason::Failed);
             stream.lane = nullptr;
             return;
@@ -560,6 +592,7 @@ class MultiStreamOwner {
                 st = tatara_q4_project(io.ctx, s, in, rt::kHidden, rows, m, 4, rt::kHidden, io.projection_slab.data(), width);
             }
             if (st != TATARA_OK) break;
+            cudaEventRecord(io.marks[3 * l], s);
             const void* branch_in = nullptr;
             if (attention) {
                 auto* keys = static_cast<std::uint16_t*>(pl.first.data()) + std::uint64_t{lane.stripe} * pl.first_stride;
@@ -590,6 +623,7 @@ class MultiStreamOwner {
                 branch_in = io.gated.data();
             }
             if (st != TATARA_OK) break;
+            cudaEventRecord(io.marks[3 * l + 1], s);
             const rt::QuantizedWeight& ow = attention ? layer.attention_q4.out : layer.gated_delta_q4.out;
             if (layer.out_dense != nullptr) {
                 st = tatara_project_dense(io.ctx, s, branch_in, rt::kAttnQueryValues, rows, layer.out_dense, rt::kHidden,
@@ -599,6 +633,7 @@ class MultiStreamOwner {
                 st = tatara_q4_project(io.ctx, s, branch_in, rt::kAttnQueryValues, rows, m, 1, rt::kAttnQueryValues, out,
                                        rt::kHidden);
             }
+            cudaEventRecord(io.marks[3 * l + 2], s);
             cur ^= 1u;
         }
         return rt::to_command_error(st);
@@ -756,6 +791,8 @@ class MultiStreamOwner {
     std::vector<OwnerLaneGroup> groups_;
     std::vector<Lane> lanes_;
     std::vector<JoiningLane> joining_;
+    tatara_ctx* join_ctx_{nullptr};
+    cudaStream_t stream_{nullptr};   // every submission of the owner
     std::vector<Lane*> wave_;
     std::vector<std::vector<Lane*>> plans_;
     std::vector<bool> submitted_;
