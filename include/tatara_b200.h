@@ -22,6 +22,11 @@
  *     (src/runtime/decode_step.cpp:812-824); a failing call enqueues nothing.
  *   - Calls are asynchronous on `stream`; errors of earlier asynchronous work surface
  *     as TATARA_CUDA_ERROR from a later call or from tatara_ctx_sync.
+ *   - The block kernels that use thread-block clusters and tensor memory (tatara_attn_prefill,
+ *     tatara_project_dense) are issued with nothing else of this library in flight on the
+ *     device: keep them in the stream that carries the rest of the work.  Issued beside other
+ *     streams' kernels they have stalled (cause not established); the host layer's owner loop
+ *     (tatara_b200/host/wave_loop.hpp) therefore uses one stream.
  */
 #ifndef TATARA_B200_H_
 #define TATARA_B200_H_
