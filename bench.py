@@ -289,6 +289,10 @@ def main():
         extra["state_snapshot"] = wl.state_copy(timed, peaks)
         extra["decode_layer_slices"] = wl.layer_slices(timed, steps, warmup)
         extra["prefill_attn"] = wl.prefill(timed, peaks, sampler=ClockSampler(local))
+        try:   # the owner's wave loop over a 40-layer stack (a native program; its failure never costs the headline)
+            extra["wave_loop"] = wl.wave_loop(lanes=8, context=4096, tokens=24)
+        except Exception as e:   # pragma: no cover
+            extra["wave_loop"] = {"error": str(e)[-300:]}
     else:
         extra["split_kv"] = wl.split_kv(dist, n, timed, steps, warmup)
         extra["lanes32"] = wl.lanes32(timed, steps, warmup)

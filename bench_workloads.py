@@ -302,7 +302,7 @@ class Workloads:
 
     # ---- the projections on either side of the layers (affine Q4, group 64)
     def project(self, timed, peaks, steps, warmup, rows=16384):
-        """Exact-row policy at decode sizes (1, 4, 16 rows; bound by the Q4 weight stream, then by FMA rate)
+        """Exact-row policy at decode sizes (1, 4, 8, 16 rows; bound by the Q4 weight stream, then by FMA rate)
         and tensor-unit policy at the prefill size, for the three call sites of the model."""
         torch = self.torch
         g = torch.Generator(device="cuda").manual_seed(13)
@@ -322,7 +322,7 @@ class Workloads:
                         for m in sizes]
                 sets.append((held, tb.Context.q4_matrices(held)))
             res = {"n": n, "k": k, "q4_weight_bytes": wbytes}
-            for r in (1, 4, 16):
+            for r in (1, 4, 8, 16):
                 x = torch.randn((r, k), generator=g, device="cuda").to(bf)
                 y = torch.zeros((r, n), dtype=bf, device="cuda")
                 ms = timed(lambda i=0: self.ctx.q4_project(x, sets[i % reps][1], k, y), max(steps, 2 * reps), max(warmup, reps))
@@ -528,7 +528,7 @@ class Workloads:
             raise RuntimeError("tatara_b200/wave_bench is not built: run __graft_entry__.build()")
         self.torch.cuda.empty_cache()
         res = subprocess.run([exe, "--lanes", str(lanes), "--context", str(context), "--tokens", str(tokens)],
-                             capture_output=True, text=True, timeout=600)
+                             capture_output=True, text=True, timeout=150)
         if res.returncode != 0:
             raise RuntimeError(f"wave_bench failed ({res.returncode}): {res.stderr[-400:]}")
         return json.loads(res.stdout.strip().splitlines()[-1])
@@ -548,7 +548,7 @@ class Workloads:
         if which == "layers":
             return self.layer_slices(timed, steps, warmup, lanes=args.lanes if args.lanes != 4 else 1, context=min(args.context, 65536))
         if which == "wave":
-            return self.wave_loop(lanes=args.lanes if args.lanes != 4 else 8, context=min(args.context, 32768))
+            return self.wave_loop(lanes=args.lanes if args.lanes != 4 else 8, context=min(args.context, 16384))
         if which == "state_copy":
             return self.state_copy(timed, measured_peaks())
         if which == "project":
