@@ -182,6 +182,9 @@ class MultiStreamOwner {
     MultiStreamOwner(const MultiStreamOwner&) = delete;
     MultiStreamOwner& operator=(const MultiStreamOwner&) = delete;
     ~MultiStreamOwner() {
+        // After a wait that ran out the stream may never drain: leave its resources to the context
+        // instead of blocking the owner's thread for good.
+        if (stats_.wait_timeouts != 0) return;
         if (stream_ != nullptr) cudaStreamSynchronize(stream_);
         for (OwnerLaneGroup& g : groups_) {
             for (cudaGraphExec_t e : g.graphs)
