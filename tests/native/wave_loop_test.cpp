@@ -7,8 +7,9 @@
 // work; stop ids, maximum_tokens and cancellation end a lane with the matching reason; a finished
 // lane is reset before reuse; two joiners prefer distinct lane groups.  The wave's captured graph
 // (lane tables in device memory) is compared bit for bit with a token walked eagerly through
-// LayerPass (host tables), whose layers tests/native/hybrid_layers_test.cpp holds against the CPU
-// oracle.
+// LayerPass (host tables), and three tokens of a stream with the CPU oracle's own walk of the same
+// layers (projection, qk_rope + decode attention or conv + gates + scan + gate-norm, out projection)
+// within the path's gate (max-abs 2e-2, cosine 0.9999).
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -22,6 +23,17 @@
 using namespace tatara::runtime;
 using namespace tatara::engine;
 using u16 = std::uint16_t;
+
+extern "C" {  // oracle/tatara_oracle.cpp (test infrastructure)
+void orc_attn_qk_rope(const u16*, const u16*, const u16*, u16*, u16*, u16*, u16*, std::uint32_t, std::uint32_t, std::uint32_t);
+void orc_attn_decode(const u16*, const u16*, const u16*, const u16*, std::uint32_t, std::uint32_t, u16*, int);
+void orc_gdn_prepare(const u16*, const u16*, const u16*, u16*, u16*, u16*, u16*, std::uint32_t);
+void orc_gdn_gates(const u16*, std::uint32_t, const u16*, const u16*, float*, float*, std::uint32_t);
+void orc_gdn_scan(const u16*, const u16*, const float*, const float*, const float*, u16*, float*, std::uint32_t, int);
+void orc_gdn_gate_norm(const u16*, const u16*, const u16*, u16*, std::uint32_t);
+void orc_q4_project(const u16*, std::uint32_t, std::uint32_t, const std::uint32_t*, const u16*, const u16*, std::uint32_t,
+                    std::uint32_t, u16*, std::uint32_t, int, int);
+}
 
 namespace {
 
@@ -37,9 +49,25 @@ struct Rng {
     float normal() { float a = 0; for (int i = 0; i < 12; ++i) a += uniform(); return a - 6.0f; }
 };
 
-// Device copies of one layer's weights.
+float from_bf16(u16 h) {
+    const std::uint32_t b = static_cast<std::uint32_t>(h) << 16;
+    float v;
+    std::memcpy(&v, &b, 4);
+    return v;
+}
+
+// Host copy of one affine-Q4 matrix (for the oracle's walk).
+struct HostQ4 {
+    std::vector<std::uint32_t> words;
+    std::vector<u16> scales, biases;
+    std::uint32_t rows{0}, k{0};
+};
+
+// Device copies of one layer's weights, and the host copies the oracle reads.
 struct LayerStore {
     std::vector<DeviceBuffer> buffers;
+    std::vector<HostQ4> q4_host;            // in creation order
+    std::vector<std::vector<u16>> vec_host; // in creation order
     const void* put(const void* host, std::size_t bytes) {
         buffers.emplace_back(bytes);
         if (!buffers.back() || cudaMemcpy(buffers.back().data(), host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return nullptr;
@@ -54,13 +82,22 @@ struct LayerStore {
             scales[i] = to_bf16(sc);
             biases[i] = to_bf16(-7.5f * sc * (1.0f + 0.1f * rng.normal()));
         }
-        return QuantizedWeight{put(words.data(), words.size() * 4), put(scales.data(), scales.size() * 2),
-                               put(biases.data(), biases.size() * 2), rows};
+        const QuantizedWeight w{put(words.data(), words.size() * 4), put(scales.data(), scales.size() * 2),
+                                put(biases.data(), biases.size() * 2), rows};
+        q4_host.push_back(HostQ4{std::move(words), std::move(scales), std::move(biases), rows, k});
+        return w;
     }
     const void* vec(Rng& rng, std::size_t n, float scale, float shift) {
         std::vector<u16> v(n);
         for (auto& x : v) x = to_bf16(shift + scale * rng.normal());
-        return put(v.data(), n * 2);
+        const void* d = put(v.data(), n * 2);
+        vec_host.push_back(std::move(v));
+        return d;
+    }
+    const void* keep(std::vector<u16> v) {
+        const void* d = put(v.data(), v.size() * 2);
+        vec_host.push_back(std::move(v));
+        return d;
     }
 };
 
@@ -80,7 +117,7 @@ bool make_layers(const std::vector<LayerKind>& schedule, std::vector<LayerStore>
         } else {
             std::vector<u16> a_log(32);
             for (auto& x : a_log) x = to_bf16(std::log(1.0f + 15.0f * rng.uniform()));
-            p.gated_delta = GatedDeltaWeights{st.vec(rng, 8192 * 4, 0.5f, 0.0f), st.put(a_log.data(), 64),
+            p.gated_delta = GatedDeltaWeights{st.vec(rng, 8192 * 4, 0.5f, 0.0f), st.keep(a_log),
                                               st.vec(rng, 32, 0.5f, 0.0f), st.vec(rng, 128, 0.1f, 1.0f)};
             p.gated_delta_q4 = GatedDeltaProjection{st.q4(rng, 8192, kHidden, 0.005f), st.q4(rng, 4096, kHidden, 0.005f),
                                                     st.q4(rng, 32, kHidden, 0.005f), st.q4(rng, 32, kHidden, 0.005f),
@@ -94,6 +131,8 @@ bool make_layers(const std::vector<LayerKind>& schedule, std::vector<LayerStore>
 
 // Host stand-ins for embedding and sampler: a token's row is a fixed pseudo-random vector; the
 // sampled token is a hash of the output row's bits, so any differing bit changes the stream.
+std::vector<std::vector<u16>>* g_sampled_rows = nullptr;   // when set, every sampled row is kept (oracle comparison)
+
 TokenBoundary make_boundary() {
     TokenBoundary b;
     b.embed = [](std::uint32_t token, std::uint32_t, u16* row) {
@@ -101,6 +140,7 @@ TokenBoundary make_boundary() {
         for (std::uint32_t i = 0; i < kHidden; ++i) row[i] = to_bf16(rng.normal());
     };
     b.sample = [](const u16* row) {
+        if (g_sampled_rows != nullptr) g_sampled_rows->emplace_back(row, row + kHidden);
         std::uint64_t h = 0xCBF29CE484222325ull;
         for (std::uint32_t i = 0; i < kHidden; ++i) h = (h ^ row[i]) * 0x100000001B3ull;
         return static_cast<std::uint32_t>(h % 50021u);
@@ -170,6 +210,89 @@ bool eager_tokens(tatara_ctx* ctx, const std::vector<PathLayer>& layers, const T
     return true;
 }
 
+// The CPU oracle's walk of one stream through the same layers (fresh slot: zero conv / recurrent state, empty
+// cache).  LayerStore keeps the host copies in creation order: attention {q_norm, k_norm | query, key, value, out},
+// gated delta {conv, a_log, dt_bias, norm | qkv, z, b, a, out}.
+struct OracleWalk {
+    const std::vector<LayerKind>& schedule;
+    const std::vector<LayerStore>& stores;
+    std::uint32_t capacity;
+    std::vector<std::vector<u16>> keys, values, conv;   // per layer
+    std::vector<std::vector<float>> state;
+    OracleWalk(const std::vector<LayerKind>& s, const std::vector<LayerStore>& st, std::uint32_t cap)
+        : schedule(s), stores(st), capacity(cap), keys(s.size()), values(s.size()), conv(s.size()), state(s.size()) {
+        for (std::size_t l = 0; l < s.size(); ++l) {
+            if (s[l] == LayerKind::FullAttention) {
+                keys[l].assign(std::size_t{2} * cap * 256, 0);
+                values[l].assign(std::size_t{2} * cap * 256, 0);
+            } else {
+                conv[l].assign(3 * 8192, 0);
+                state[l].assign(32 * 128 * 128, 0.0f);
+            }
+        }
+    }
+    static void project(const std::vector<u16>& x, const HostQ4* mats, int n, std::vector<u16>& out) {
+        std::uint32_t total = 0;
+        for (int m = 0; m < n; ++m) total += mats[m].rows;
+        out.assign(total, 0);
+        std::uint32_t col = 0;
+        for (int m = 0; m < n; ++m) {
+            orc_q4_project(x.data(), mats[m].k, 1, mats[m].words.data(), mats[m].scales.data(), mats[m].biases.data(),
+                           mats[m].rows, mats[m].k, out.data() + col, total, 1, 4);
+            col += mats[m].rows;
+        }
+    }
+    std::vector<u16> token(std::vector<u16> hidden, std::uint32_t position) {
+        for (std::size_t l = 0; l < schedule.size(); ++l) {
+            const LayerStore& st = stores[l];
+            std::vector<u16> proj, branch;
+            if (schedule[l] == LayerKind::FullAttention) {
+                project(hidden, &st.q4_host[0], 3, proj);
+                std::vector<u16> q(4096), gate(4096);
+                branch.assign(4096, 0);
+                orc_attn_qk_rope(proj.data(), st.vec_host[0].data(), st.vec_host[1].data(), q.data(), gate.data(), keys[l].data(),
+                                 values[l].data(), position, capacity, 1);
+                orc_attn_decode(q.data(), gate.data(), keys[l].data(), values[l].data(), position, capacity, branch.data(), 4);
+                project(branch, &st.q4_host[3], 1, hidden);
+            } else {
+                project(hidden, &st.q4_host[0], 4, proj);
+                std::vector<u16> qk(4096), v(4096), z(4096), conv_out(3 * 8192), y(4096);
+                std::vector<float> decay(32), beta(32), state_out(state[l].size());
+                branch.assign(4096, 0);
+                orc_gdn_prepare(proj.data(), conv[l].data(), st.vec_host[0].data(), qk.data(), v.data(), z.data(), conv_out.data(), 1);
+                orc_gdn_gates(proj.data(), kGdnProjectionRows, st.vec_host[1].data(), st.vec_host[2].data(), decay.data(), beta.data(), 1);
+                orc_gdn_scan(qk.data(), v.data(), decay.data(), beta.data(), state[l].data(), y.data(), state_out.data(), 1, 4);
+                orc_gdn_gate_norm(y.data(), z.data(), st.vec_host[3].data(), branch.data(), 1);
+                conv[l] = conv_out;
+                state[l] = state_out;
+                project(branch, &st.q4_host[4], 1, hidden);
+            }
+        }
+        return hidden;
+    }
+};
+
+bool close_enough(const u16* got, const u16* want, std::size_t n, float widen = 1.0f) {
+    // The gate of the path (max-abs 2e-2, cosine 0.9999) is stated for outputs of order one.  A chained row
+    // is a projection of a vector whose elements differ by a bf16 step here and there, so its error scales
+    // with the row's RMS, and a large element carries one bf16 step (2^-7 relative) of its own.
+    double dot = 0, na = 0, nb = 0, rms = 0;
+    for (std::size_t i = 0; i < n; ++i) rms += double(from_bf16(want[i])) * from_bf16(want[i]);
+    rms = std::sqrt(rms / double(n));
+    float worst = 0;
+    for (std::size_t i = 0; i < n; ++i) {
+        const float a = from_bf16(got[i]), b = from_bf16(want[i]);
+        if (!std::isfinite(a)) return false;
+        const float allowed = widen * 2e-2f * std::fmax(1.0f, float(rms)) + 0.0078125f * std::fabs(b);
+        worst = std::fmax(worst, std::fabs(a - b) / allowed);
+        dot += double(a) * b; na += double(a) * a; nb += double(b) * b;
+    }
+    const double cosine = (na == 0 && nb == 0) ? 1.0 : dot / std::sqrt(na * nb);
+    const bool ok = worst <= 1.0f && cosine >= 0.9999 && rms > 1e-3;
+    if (!ok) std::printf("oracle comparison: worst error / allowance %.4g, cosine %.6f, rms %.4g\n", worst, cosine, rms);
+    return ok;
+}
+
 int host_only_checks() {
     // nothing to walk, or no boundary: the owner refuses to build and to queue
     MultiStreamOwner empty(OwnerConfig{}, {}, make_boundary());
@@ -234,6 +357,31 @@ int device_checks(tatara_ctx* ctx) {
         std::vector<std::uint32_t> eager;
         if (!eager_tokens(ctx, layers, boundary, kCapacity, a.prompt.back(), 6, eager)) return 50;
         if (eager != a.tokens()) return 51;
+    }
+
+    // --- against the CPU oracle: the first stream alone, three tokens (states carried from token to token);
+    //     every output row within the path's gate of the oracle's walk fed with the same tokens
+    {
+        OwnerConfig solo{0, 1, 1, kCapacity, 1, 64};
+        MultiStreamOwner alone(solo, layers, boundary);
+        if (!alone) return 52;
+        std::vector<std::vector<u16>> rows;
+        g_sampled_rows = &rows;
+        Request again{a.prompt, 3, {}};
+        const bool ran = alone.submit(again.submission()) && drain(alone);
+        g_sampled_rows = nullptr;
+        if (!ran || rows.size() != 3) return 53;
+        OracleWalk walk(schedule, stores, kCapacity);
+        std::uint32_t input = a.prompt.back();
+        for (std::uint32_t t = 0; t < 3; ++t) {
+            std::vector<u16> x(kHidden);
+            boundary.embed(input, t, x.data());
+            const std::vector<u16> want = walk.token(x, t);
+            // the two walks carry their own conv / recurrent state and cache from token to token, so their
+            // distance compounds: the gate for the first two tokens, twice the gate for the third
+            if (!close_enough(rows[t].data(), want.data(), kHidden, t < 2 ? 1.0f : 2.0f)) return 54 + int(t);   // 54, 55, 56
+            input = again.tokens()[t];
+        }
     }
 
     // --- stop id, cancellation, lane reuse after finish
