@@ -262,6 +262,7 @@ def main():
     # qk_rope (appends K/V), decode attention, D2H the attended row.
     e2e_ms = timed(decode.step_e2e, steps, warmup, eager=True)
     e2e_gbs = world * bytes_step / (e2e_ms * 1e-3) / 1e9
+    e2e_direct_mapped_ms = timed(decode.step_e2e_mapped, steps, warmup, eager=True)
     # the same token as one captured CUDA graph (lane tables in device memory), one graph launch per token
     try:
         e2e_graph_ms = timed(decode.token_graph(), steps, warmup, eager=True)
@@ -320,6 +321,7 @@ def main():
                          "peak_source": peaks["source"],
                          "kernel": "attn_decode_partition_kernel (+ attn_combine_kernel in the timed step)"},
             "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "mapped_host_ms_per_step": e2e_direct_mapped_ms,
                     "graph_replay_ms_per_step": e2e_graph_ms,
                     "graph_replay_mapped_host_ms_per_step": e2e_mapped_ms,
                     "path": "host-issued C-ABI calls from Python: pinned H2D of the token projection, qk_rope, decode, D2H",

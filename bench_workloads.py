@@ -126,6 +126,14 @@ class DecodeCase:
         self.ctx.attn_decode(self.q2, self.g2, keys, values, self.n - 1, self.capacity, self.out, self.scratch)
         self.h_out.copy_(self.out, non_blocking=True)
 
+    def step_e2e_mapped(self, i=0):
+        """step_e2e without the two copy nodes: qk_rope loads the projection row from the pinned host buffer and
+        the merge kernel stores the attended row into the pinned host buffer (pinned memory is device-visible)."""
+        keys, values = self.caches[i % self.replicas]
+        self.ctx.attn_qk_rope(self.h_proj, self.ones, self.ones, self.q2, self.g2, keys, values,
+                              self.n - 1, self.capacity, 1)
+        self.ctx.attn_decode(self.q2, self.g2, keys, values, self.n - 1, self.capacity, self.h_out, self.scratch)
+
     def token_graph(self, mapped_host=False):
         """One decode token end to end as ONE CUDA graph: pinned H2D of the projection row, qk_rope and decode
         attention through the device-table entry points (nothing about the token is a kernel argument), D2H of the
