@@ -466,6 +466,10 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     const uint32_t nparts = cl.nparts;
     const uint32_t d = quarter * kCombineDims + lane * 2u;
     constexpr uint32_t kOwn = kCombinePhases / kWarps, kRound = kCombinePhases * kCombineUnroll;
+    // the gate logit of the dim this thread finishes: requested now, used after the merge
+    float gate_logit = 0.0f;
+    if (threadIdx.x < kCombineDims && p.out != nullptr && p.gate != nullptr)
+        gate_logit = bf2f(p.gate[cl.row * p.query_stride + head * kHeadDim + quarter * kCombineDims + threadIdx.x]);
     // The first round of records (parts 0..127: every record of a lane cut by tb::partition_keys)
     // is requested before the maximum is known, so the merge costs one trip to L2, not two.
     float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
@@ -554,8 +558,7 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
             }
         } else {
             const uint64_t at = cl.row * p.query_stride + head * kHeadDim + dd;
-            const float gate = bf2f(p.gate[at]);
-            p.out[at] = f2bf((acc / total) * (1.0f / (1.0f + expf(-gate))));
+            p.out[at] = f2bf((acc / total) * (1.0f / (1.0f + expf(-gate_logit))));
         }
     }
     if (p.px.world != 0u && p.px.wait_flags == nullptr) {
