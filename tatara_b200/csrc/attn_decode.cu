@@ -62,9 +62,16 @@ struct DecParams {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
-                 "r"(src_bytes)
+// K / V rows are read once per token: they are marked evict-first in L2 so that the stream does
+// not push out what the step re-reads (q, gate, the partial records).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src),
+                 "r"(src_bytes), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
@@ -164,7 +171,7 @@ __device__ __forceinline__ void cursor_settle(SliceCursor& c, const DecParams<N>
 
 // Issues the 16-key K and V slice under the cursor into one ring stage (rows past the
 // partition end are zero-filled), 32 x 16-byte cp.async per lane.
-__device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage_addr, uint32_t lane) {
+__device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage_addr, uint32_t lane, uint64_t policy) {
     const uint32_t first = c.slice * kSliceKeys;
     const uint32_t rows = min(kSliceKeys, c.nkeys - first);
     const uint8_t* ksrc = c.kbase + uint64_t(first) * kRowBytes + lane * 16u;
@@ -174,8 +181,8 @@ __device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage
         const bool live = row < rows;
         const uint32_t off = live ? row * kRowBytes : 0u;
         const uint32_t dst = stage_addr + row * kRowBytes + ((lane ^ (row & 7u)) << 4);
-        cp_async_16(dst, ksrc + off, live ? 16u : 0u);
-        cp_async_16(dst + kSliceBytes, vsrc + off, live ? 16u : 0u);
+        cp_async_16(dst, ksrc + off, live ? 16u : 0u, policy);
+        cp_async_16(dst + kSliceBytes, vsrc + off, live ? 16u : 0u, policy);
     }
 }
 
@@ -194,6 +201,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         item_start[i] = i < n_lanes ? lane_at<N, kInd>(p, i).item_start : total_items;
     __syncthreads();
     const uint32_t ring = smem_u32(smem + warp * kRingBytes);
+    const uint64_t stream_policy = l2_evict_first_policy();
 
     // Producer cursor: runs kDecStages-1 slices ahead of the consumer, across items.
     SliceCursor pc{};
@@ -213,7 +221,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
 #pragma unroll
         for (uint32_t i = 0; i + 1 < kDecStages; ++i) {
             if (pc.valid) {
-                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
+                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane, stream_policy);
                 pc.slice += kDecWarps;
                 cursor_settle<N, kInd>(pc, p, item_start, warp);
             }
@@ -262,7 +270,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         for (uint32_t slice = warp; slice * kSliceKeys < cc.nkeys; slice += kDecWarps) {
             // keep the ring full, then wait for the oldest slice
             if (pc.valid) {
-                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane);
+                issue_slice(pc, ring + (issued % kDecStages) * kStageBytes, lane, stream_policy);
                 pc.slice += kDecWarps;
                 cursor_settle<N, kInd>(pc, p, item_start, warp);
             }
