@@ -183,9 +183,9 @@ class Workloads:
     def traffic_hint(self):
         """DRAM bytes (read + write) per launch of attn_decode_partition_kernel at the headline
         context, from the ncu capture summarised in
-        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.283776 + 3.959552) MB at
+        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.280448 + 4.332800) MB at
         65 536 keys, scaled by keys (traffic is proportional to keys) to 262 144."""
-        return int((134.283776e6 + 3.959552e6) * 4)
+        return int((134.280448e6 + 4.332800e6) * 4)
 
     def decode_setup(self, n_keys):
         return DecodeCase(self.ctx, self.torch, n_keys, seed=self.rank * 100)
