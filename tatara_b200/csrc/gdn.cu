@@ -14,18 +14,21 @@ namespace tb {
 // One activated conv channel: 4-tap causal conv (f32), bf16, SiLU with per-op bf16 rounding
 // (gdn.metal:66-80).  Position `row` of a block taps the logical sequence
 // [3 state rows | projection rows] at row..row+3 (prefill_gdn.metal:24-32).
-__device__ __forceinline__ __nv_bfloat16 conv_channel(const __nv_bfloat16* projection,
-                                                      uint64_t projection_stride,
-                                                      const __nv_bfloat16* conv_state,
-                                                      const __nv_bfloat16* conv_weights,
-                                                      uint32_t row, uint32_t channel, float taps[4]) {
+// The loads of one conv channel (the four taps and its weights) and, separately, its arithmetic:
+// a caller with several channels requests all of them before using any.
+__device__ __forceinline__ void conv_channel_load(const __nv_bfloat16* projection, uint64_t projection_stride,
+                                                  const __nv_bfloat16* conv_state,
+                                                  const __nv_bfloat16* conv_weights, uint32_t row,
+                                                  uint32_t channel, float taps[4], uint2& wraw) {
 #pragma unroll
     for (uint32_t t = 0; t < 4; ++t) {
         const uint32_t logical = row + t;
         taps[t] = logical < 3u ? bf2f(conv_state[logical * kGdnConv + channel])
                                : bf2f(projection[uint64_t(logical - 3u) * projection_stride + channel]);
     }
-    const uint2 wraw = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(channel) * 4u);
+    wraw = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(channel) * 4u);
+}
+__device__ __forceinline__ __nv_bfloat16 conv_channel_apply(const float taps[4], uint2 wraw) {
     const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
     const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
     float acc = __fmul_rn(bf2f(w01.x), taps[0]);
@@ -34,6 +37,15 @@ __device__ __forceinline__ __nv_bfloat16 conv_channel(const __nv_bfloat16* proje
     acc = __fadd_rn(acc, __fmul_rn(bf2f(w23.y), taps[3]));
     const __nv_bfloat16 c = f2bf(acc);
     return bmul(c, sigmoid_bf16(c));
+}
+__device__ __forceinline__ __nv_bfloat16 conv_channel(const __nv_bfloat16* projection,
+                                                      uint64_t projection_stride,
+                                                      const __nv_bfloat16* conv_state,
+                                                      const __nv_bfloat16* conv_weights,
+                                                      uint32_t row, uint32_t channel, float taps[4]) {
+    uint2 wraw;
+    conv_channel_load(projection, projection_stride, conv_state, conv_weights, row, channel, taps, wraw);
+    return conv_channel_apply(taps, wraw);
 }
 
 // l2-normalise one 128-channel head held one channel per thread of a 128-thread group:
@@ -184,17 +196,14 @@ gdn_step_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __res
 }
 
 // Weighted per-head RMSNorm of y times SiLU(z) (gdn.metal:174-207): one warp per head.
-__device__ __forceinline__ void gate_norm_head(const float yv[4], const __nv_bfloat16* z,
-                                               const __nv_bfloat16* weight, __nv_bfloat16* out,
-                                               uint32_t lane) {
+// zf: the head's z values of this lane, wraw: its four norm weights (both already loaded).
+__device__ __forceinline__ void gate_norm_head_loaded(const float yv[4], const float zf[4], uint2 wraw,
+                                                      __nv_bfloat16* out, uint32_t lane) {
     float acc = 0.0f;
 #pragma unroll
     for (uint32_t i = 0; i < 4; ++i) acc += yv[i] * yv[i];
     acc = warp_sum(acc);
     const float inverse = 1.0f / sqrtf(acc / float(kGdnDim) + kRmsEps);
-    float zf[4];
-    load_bf16x4(z + lane * 4u, zf);
-    const uint2 wraw = *reinterpret_cast<const uint2*>(weight + lane * 4u);
     const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(&wraw);
     __nv_bfloat16 res[4];
 #pragma unroll
@@ -203,6 +212,14 @@ __device__ __forceinline__ void gate_norm_head(const float yv[4], const __nv_bfl
         res[i] = f2bf((zf[i] * sigmoid_f32(zf[i])) * bf2f(normed));
     }
     *reinterpret_cast<uint2*>(out + lane * 4u) = *reinterpret_cast<const uint2*>(res);
+}
+__device__ __forceinline__ void gate_norm_head(const float yv[4], const __nv_bfloat16* z,
+                                               const __nv_bfloat16* weight, __nv_bfloat16* out,
+                                               uint32_t lane) {
+    float zf[4];
+    load_bf16x4(z + lane * 4u, zf);
+    const uint2 wraw = *reinterpret_cast<const uint2*>(weight + lane * 4u);
+    gate_norm_head_loaded(yv, zf, wraw, out, lane);
 }
 
 __global__ void __launch_bounds__(128)
@@ -253,20 +270,40 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j)
             rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
-    // Launched as a programmatic dependent of its predecessor in the stream (the projection that
-    // produces `projection`): the recurrent state it reads above is this layer's own and is not
-    // written by that predecessor, so those loads are in flight while the predecessor finishes;
-    // the projection row, the conv state and every store wait here.  This kernel never signals its
-    // own dependents early: the next call on the same layer reads the state written below, so it
-    // must not start before this grid has completed.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // prologue: threads 0..127 -> q channel, 128..255 -> k channel; then v channel on 0..127
+    // The weights are requested here too, with the state rows.  (The conv taps are not: read ahead of
+    // the wait they raced in the owner loop's captured waves -- a stream's tokens then depended on its
+    // wave -- although no writer of this layer's conv pool is in flight by the launch order; they
+    // stay behind the wait.)  threads 0..127 -> q channel, 128..255 -> k channel; v channel on 0..127.
     const uint32_t l128 = threadIdx.x & 127u;
     const bool is_q = threadIdx.x < 128u;
     const uint32_t qk_channel = (is_q ? 0u : kGdnKOff) + (head >> 1) * kGdnDim + l128;
-    float taps[4];
-    const __nv_bfloat16 act = conv_channel(proj, 0, conv_in, conv_weights, 0, qk_channel, taps);
+    const uint32_t v_channel = kGdnQk + head * kGdnDim + l128;
+    float taps[4], vtaps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint2 qk_w = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(qk_channel) * 4u);
+    const uint2 v_w = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(v_channel) * 4u);
+    const __nv_bfloat16 dt_raw = dt_bias[head], alog_raw = a_log[head];
+    const uint2 norm_w = *reinterpret_cast<const uint2*>(norm_weight + lane * 4u);
+    // Launched as a programmatic dependent of its predecessor in the stream (the projection that
+    // produces `projection`): what is read above is this layer's own recurrent state and weights, which that
+    // predecessor does not write, so those loads are in flight while the predecessor finishes; the
+    // projection row and every store wait here.  This kernel never signals its own dependents early:
+    // the next call on the same layer reads the state written below, so it must not start before this
+    // grid has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // Everything else the prologue and the epilogue read (conv taps, the projection row) is requested at once:
+    // one trip to L2 instead of one per dependent phase; the arithmetic keeps its order.
+#pragma unroll
+    for (uint32_t t = 0; t < 3; ++t) {
+        taps[t] = bf2f(conv_in[t * kGdnConv + qk_channel]);
+        if (is_q) vtaps[t] = bf2f(conv_in[t * kGdnConv + v_channel]);
+    }
+    taps[3] = bf2f(proj[qk_channel]);
+    if (is_q) vtaps[3] = bf2f(proj[v_channel]);
+    const __nv_bfloat16 a_raw = proj[kGdnAOff + head], b_raw = proj[kGdnBOff + head];
+    float zf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (warp == 0) load_bf16x4(proj + kGdnZOff + head * kGdnDim + lane * 4u, zf);
+    const __nv_bfloat16 act = conv_channel_apply(taps, qk_w);
     if ((head & 1u) == 0u) {
 #pragma unroll
         for (uint32_t t = 0; t < 3; ++t) conv_out[t * kGdnConv + qk_channel] = f2bf(taps[t + 1u]);
@@ -274,14 +311,13 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
     const __nv_bfloat16 normed = head_normalise(is_q ? head_q : head_k, l128, bf2f(act), is_q);
     (is_q ? qn : kn)[l128] = bf2f(normed);
     if (is_q) {
-        const uint32_t v_channel = kGdnQk + head * kGdnDim + l128;
-        const __nv_bfloat16 va = conv_channel(proj, 0, conv_in, conv_weights, 0, v_channel, taps);
+        const __nv_bfloat16 va = conv_channel_apply(vtaps, v_w);
 #pragma unroll
-        for (uint32_t t = 0; t < 3; ++t) conv_out[t * kGdnConv + v_channel] = f2bf(taps[t + 1u]);
+        for (uint32_t t = 0; t < 3; ++t) conv_out[t * kGdnConv + v_channel] = f2bf(vtaps[t + 1u]);
         vn[l128] = bf2f(va);
     }
-    const float decay = gdn_decay(proj[kGdnAOff + head], dt_bias[head], a_log[head]);
-    const float beta = gdn_beta(proj[kGdnBOff + head]);
+    const float decay = gdn_decay(a_raw, dt_raw, alog_raw);
+    const float beta = gdn_beta(b_raw);
     __syncthreads();
 
     float kf[4], qf[4];
@@ -317,7 +353,7 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
             for (uint32_t i = 0; i < 4; ++i) yb[i] = f2bf(yv[i]);
             *reinterpret_cast<uint2*>(y_out + obase + lane * 4u) = *reinterpret_cast<const uint2*>(yb);
         }
-        gate_norm_head(yv, proj + kGdnZOff + head * kGdnDim, norm_weight, gated + obase, lane);
+        gate_norm_head_loaded(yv, zf, norm_w, gated + obase, lane);
     }
 }
 

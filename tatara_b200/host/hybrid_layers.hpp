@@ -152,6 +152,9 @@ inline bool create_state_pool(std::uint32_t slots, std::uint32_t capacity, const
         if (!layer.first || !layer.second) return false;
         pool.layers.push_back(std::move(layer));
     }
+    // cudaMemset may return before the fill has run, and the callers' streams are non-blocking
+    // (they do not order behind the default stream): the zeroes must be there before the first launch
+    if (cudaDeviceSynchronize() != cudaSuccess) return false;
     out_slots.assign(slots, DecodeStateSlot{});
     for (std::uint32_t s = 0; s < slots; ++s) {
         out_slots[s].capacity = capacity;

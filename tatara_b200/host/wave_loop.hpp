@@ -391,7 +391,8 @@ class MultiStreamOwner {
                 !io.scan_scratch)
                 return false;
         }
-        return true;
+        // every buffer above was zero-filled on the default stream; the owner's stream does not order behind it
+        return cudaDeviceSynchronize() == cudaSuccess;
     }
 
     // Lane tables of one wave: [rows] attention rows, then [gated-delta layers][rows] rows.
