@@ -240,8 +240,11 @@ struct GdnLanes {
     tatara_gdn_lane lane[TATARA_MAX_LANES];
 };
 
+// `projection` is NOT __restrict__: it is written by the predecessor this kernel waits for, and a
+// const __restrict__ pointer lets the compiler treat its loads as invariant and move them above
+// griddepcontrol.wait (seen once: garbage rows whenever the projection kernel was still running).
 __global__ void __launch_bounds__(256)
-gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t projection_stride,
+gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_stride,
                         const __nv_bfloat16* __restrict__ conv_weights,
                         const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
                         const __nv_bfloat16* __restrict__ norm_weight, __nv_bfloat16* conv_pool,
@@ -270,34 +273,34 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ projection, uint64_t p
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j)
             rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
-    // The weights are requested here too, with the state rows.  (The conv taps are not: read ahead of
-    // the wait they raced in the owner loop's captured waves -- a stream's tokens then depended on its
-    // wave -- although no writer of this layer's conv pool is in flight by the launch order; they
-    // stay behind the wait.)  threads 0..127 -> q channel, 128..255 -> k channel; v channel on 0..127.
+    // The layer's own conv taps and the weights are not written by the predecessor either: requested
+    // here, with the state rows.  threads 0..127 -> q channel, 128..255 -> k channel; v channel on 0..127.
     const uint32_t l128 = threadIdx.x & 127u;
     const bool is_q = threadIdx.x < 128u;
     const uint32_t qk_channel = (is_q ? 0u : kGdnKOff) + (head >> 1) * kGdnDim + l128;
     const uint32_t v_channel = kGdnQk + head * kGdnDim + l128;
     float taps[4], vtaps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const unsigned short* conv_bits = reinterpret_cast<const unsigned short*>(conv_in);
+#pragma unroll
+    for (uint32_t t = 0; t < 3; ++t) {
+        taps[t] = __uint_as_float(uint32_t(__ldcg(conv_bits + t * kGdnConv + qk_channel)) << 16);
+        if (is_q) vtaps[t] = __uint_as_float(uint32_t(__ldcg(conv_bits + t * kGdnConv + v_channel)) << 16);
+    }
     const uint2 qk_w = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(qk_channel) * 4u);
     const uint2 v_w = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(v_channel) * 4u);
     const __nv_bfloat16 dt_raw = dt_bias[head], alog_raw = a_log[head];
     const uint2 norm_w = *reinterpret_cast<const uint2*>(norm_weight + lane * 4u);
     // Launched as a programmatic dependent of its predecessor in the stream (the projection that
-    // produces `projection`): what is read above is this layer's own recurrent state and weights, which that
+    // produces `projection`): what is read above is this layer's own state and weights, which that
     // predecessor does not write, so those loads are in flight while the predecessor finishes; the
     // projection row and every store wait here.  This kernel never signals its own dependents early:
     // the next call on the same layer reads the state written below, so it must not start before this
     // grid has completed.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // (`proj` is an output of the statement, so no load through it can be placed above it)
+    asm volatile("griddepcontrol.wait;" : "+l"(proj) : : "memory");
 
-    // Everything else the prologue and the epilogue read (conv taps, the projection row) is requested at once:
+    // Everything else the prologue and the epilogue read (the projection row) is requested at once:
     // one trip to L2 instead of one per dependent phase; the arithmetic keeps its order.
-#pragma unroll
-    for (uint32_t t = 0; t < 3; ++t) {
-        taps[t] = bf2f(conv_in[t * kGdnConv + qk_channel]);
-        if (is_q) vtaps[t] = bf2f(conv_in[t * kGdnConv + v_channel]);
-    }
     taps[3] = bf2f(proj[qk_channel]);
     if (is_q) vtaps[3] = bf2f(proj[v_channel]);
     const __nv_bfloat16 a_raw = proj[kGdnAOff + head], b_raw = proj[kGdnBOff + head];
