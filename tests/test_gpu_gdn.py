@@ -148,6 +148,48 @@ def test_fused_decode_batch_4_lanes(ctx):
             assert torch.equal(solo_rec[i, slot], rec_pool[i, slot])
 
 
+def test_projection_chained_into_step_matches_synchronised_calls(ctx):
+    """gdn_project -> fused step -> out projection as they run in a token: every kernel is a programmatic
+    dependent of the one before it and starts before that one has finished.  Twelve chained tokens without a
+    host synchronisation must leave the bits of the same calls with a synchronisation after each (a load of the
+    projection row that slips ahead of the dependency wait reads rows the projection kernel is still writing)."""
+    rng = np.random.default_rng(77)
+    n, tokens = 3, 12
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    convs, states, conv_pool, rec_pool = make_pools(rng, n)
+    pools = [(conv_pool, rec_pool), (conv_pool.clone(), rec_pool.clone())]
+    proj_sets = []
+    for _ in range(3):   # rotate weight sets so that the projection kernel really streams from memory
+        mats = [syn.q4_matrix(rng, m, 2048) for m in (8192, 4096, 32, 32)]
+        held = [(torch.from_numpy(a.view(np.int32)).cuda(), dev_bf16(b), dev_bf16(c)) for a, b, c in mats]
+        proj_sets.append((held, tb.Context.q4_matrices(held)))
+    out_mat = syn.q4_matrix(rng, 2048, 4096)
+    out_held = [(torch.from_numpy(out_mat[0].view(np.int32)).cuda(), dev_bf16(out_mat[1]), dev_bf16(out_mat[2]))]
+    out_arr = tb.Context.q4_matrices(out_held)
+    hidden0 = dev_bf16(syn.hidden_rows(rng, n, 2048))
+    results = []
+    for synchronise, (cp, rp) in zip((False, True), pools):
+        hidden = hidden0.clone()
+        slab, y, gated = bf((n, 12352)), bf((n, 4096)), bf((n, 4096))
+        trace = []
+        for token in range(tokens):
+            ctx.q4_project(hidden, proj_sets[token % 3][1], 2048, slab)
+            if synchronise:
+                ctx.sync()
+            ctx.gdn_decode_batch(slab, w[0], w[1], w[2], w[3], cp, rp, lane_table(n, token % 2 == 1), y, gated)
+            if synchronise:
+                ctx.sync()
+            ctx.q4_project(gated, out_arr, 4096, hidden)
+            if synchronise:
+                ctx.sync()
+                trace.append(hidden.clone())
+        ctx.sync()
+        results.append((hidden.clone(), cp.clone(), rp.clone()))
+    for chained, stepped in zip(results[0], results[1]):
+        assert torch.equal(chained, stepped)
+
+
 def test_fused_equals_unfused_ops(ctx):
     rng = np.random.default_rng(24)
     conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
