@@ -182,6 +182,52 @@ def test_qk_rope_then_decode_step(ctx):
     assert_close_bf16(host_u16(out), want, "rope+decode step")
 
 
+def test_attention_layer_chained_matches_synchronised_calls(ctx):
+    """attn_project -> qk_rope -> decode (partition + merge) -> out projection for three lanes, sixteen tokens
+    in a row without a host synchronisation: the kernels are programmatic dependents that start early (the
+    partition kernel requests K/V rows of older partitions before its dependency wait, the projections their
+    weights).  The bits must be those of the same calls with a synchronisation after each; the contexts
+    cross a 128-key partition boundary on the way."""
+    rng = np.random.default_rng(31)
+    cap, tokens = 512, 16
+    starts = [120, 250, 7]
+    n = len(starts)
+    qw, kw = (dev_bf16(w) for w in syn.attn_weights(rng, unit=False))
+    in_sets = []
+    for _ in range(3):
+        mats = [syn.q4_matrix(rng, m, 2048) for m in (8192, 512, 512)]
+        held = [(torch.from_numpy(a.view(np.int32)).cuda(), dev_bf16(b), dev_bf16(c)) for a, b, c in mats]
+        in_sets.append((held, tb.Context.q4_matrices(held)))
+    out_mat = syn.q4_matrix(rng, 2048, 4096)
+    out_held = [(torch.from_numpy(out_mat[0].view(np.int32)).cuda(), dev_bf16(out_mat[1]), dev_bf16(out_mat[2]))]
+    out_arr = tb.Context.q4_matrices(out_held)
+    hidden0 = dev_bf16(syn.hidden_rows(rng, n, 2048))
+    g = torch.Generator(device="cuda").manual_seed(5)
+    kpool0 = torch.randn((n, 2, cap, 256), generator=g, device="cuda").to(torch.bfloat16)
+    vpool0 = torch.randn((n, 2, cap, 256), generator=g, device="cuda").to(torch.bfloat16)
+    results = []
+    for synchronise in (False, True):
+        kpool, vpool, hidden = kpool0.clone(), vpool0.clone(), hidden0.clone()
+        slab = torch.zeros((n, 9216), dtype=torch.bfloat16, device="cuda")
+        q = torch.zeros((n, 16, 256), dtype=torch.bfloat16, device="cuda"); gate = torch.zeros_like(q)
+        attended = torch.zeros((n, 4096), dtype=torch.bfloat16, device="cuda")
+        scratch = scratch_for(cap, n)
+        for token in range(tokens):
+            lanes = tb.Context.attn_lanes([(i * 2 * cap * 256, c + token) for i, c in enumerate(starts)])
+            steps = (lambda: ctx.q4_project(hidden, in_sets[token % 3][1], 2048, slab),
+                     lambda: ctx.attn_qk_rope_batch(slab, qw, kw, q, gate, kpool, vpool, cap, lanes),
+                     lambda: ctx.attn_decode_batch(q, gate, kpool, vpool, lanes, cap, attended, scratch),
+                     lambda: ctx.q4_project(attended, out_arr, 4096, hidden))
+            for step in steps:
+                step()
+                if synchronise:
+                    ctx.sync()
+        ctx.sync()
+        results.append((hidden.clone(), kpool, vpool))
+    for chained, stepped in zip(results[0], results[1]):
+        assert torch.equal(chained, stepped)
+
+
 def test_batched_qk_rope_matches_solo(ctx):
     rng = np.random.default_rng(10)
     cap, contexts = 64, [0, 5, 63]
