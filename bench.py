@@ -90,24 +90,35 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------------------------
 # reference arm / cpu baseline: the scalar fp32 oracle on the host cores
-def cpu_decode_sample(n_keys: int, threads: int, repeats: int):
-    """Times the oracle's decode attention over one lane of n_keys keys (all 16 heads)."""
+def headline_config(n_gpus: int) -> dict:
+    """The `config` object of the JSON line: one dict for both arms, so the two lines can be compared
+    key by key.  The workload is ONE lane at 262144 attended keys at every N."""
+    n = HEADLINE_CONTEXT
+    return {"workload": f"decode_attn_ctx{n}", "lanes": 1, "context": n, "kv_bytes": n * 2048, "n_gpus": n_gpus,
+            "l2": "inputs larger than L2 (512 MiB of K+V streamed per step, steps back to back)",
+            "parallelism": "single GPU" if n_gpus == 1 else
+                           f"split-KV: the lane's key axis cut into {n_gpus} contiguous ranges, one per GPU; "
+                           "records merged over NVLink peer memory"}
+
+
+def cpu_decode_sample(q, gate, keys, values, n_keys: int, threads: int, repeats: int):
+    """Times the oracle's decode attention over one lane of n_keys keys (all 16 heads); host arrays
+    are bf16 bit patterns.  Returns (best seconds, total seconds, the oracle's output)."""
     import oracle
-    from tatara_b200 import synthetic as syn
-    rng = np.random.default_rng(0)
-    keys, values = syn.attn_cache(rng, n_keys, n_keys)
-    q, gate = syn.attn_query(rng, np.array([n_keys - 1]))
-    best, total = None, 0.0
+    best, total, out = None, 0.0, None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        oracle.attn_decode(q[0], gate[0], keys, values, n_keys - 1, n_keys, threads=threads)
+        out = oracle.attn_decode(q, gate, keys, values, n_keys - 1, n_keys, threads=threads)
         dt = time.perf_counter() - t0
         total += dt
         best = dt if best is None else min(best, dt)
-    return best, total
+    return best, total, out
 
 
 def run_reference(args):
+    """The reference arm: the reference's algorithm for this path on the host cores (the CPU oracle,
+    kind "port": the reference's own kernels are Metal and cannot run here), all host threads, the
+    repo arm's workload, config, steps and warm-up.  Under torchrun rank 0 alone runs and prints."""
     import oracle
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -115,25 +126,26 @@ def run_reference(args):
     oracle.lib()
     threads = oracle.hardware_threads()
     n = HEADLINE_CONTEXT
-    import oracle as _o
     from tatara_b200 import synthetic as syn
     rng = np.random.default_rng(0)
     keys, values = syn.attn_cache(rng, n, n)
     q, gate = syn.attn_query(rng, np.array([n - 1]))
-    for _ in range(max(1, min(args.warmup, 1))):
-        _o.attn_decode(q[0], gate[0], keys, values, n - 1, n, threads=threads)
-    steps = max(1, min(args.steps, 8))      # each step ~1 s of host time: bounded sample
+    steps, warmup = args.steps, max(args.warmup, 3)
+    for _ in range(warmup):
+        oracle.attn_decode(q[0], gate[0], keys, values, n - 1, n, threads=threads)
     t0 = time.perf_counter()
-    for _ in range(steps):
-        _o.attn_decode(q[0], gate[0], keys, values, n - 1, n, threads=threads)
+    for _ in range(steps):          # each step: one full decode over the lane, ~0.2 s of host time
+        oracle.attn_decode(q[0], gate[0], keys, values, n - 1, n, threads=threads)
     dt = (time.perf_counter() - t0) / steps
     gbs = decode_bytes(n) / dt / 1e9
     line = {
         "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"decode_attn_ctx{n}", "lanes": 1, "context": n,
-                   "note": "scalar fp32 CPU restatement of the reference kernels (its Metal path cannot run here)"},
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": headline_config(args.gpus),
+        "note": "scalar fp32 CPU restatement of the reference kernels (its Metal path cannot run here), timed on "
+                f"rank 0's {threads} host threads only; no GPU is used by this arm at any --gpus",
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{steps} full decode steps at context {n}, all 16 heads"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -231,6 +243,24 @@ def main():
             return ms
         graph = capture(fn, k, w)
         graph.replay()          # one untimed replay (graph upload)
+        torch.cuda.synchronize()
+        if world > 1:
+            # The ranks of a split-KV step wait for one another inside the kernels, so every rank must
+            # replay the same number of times: rank 0 turns the hold time into a replay count.
+            t0 = time.perf_counter()
+            graph.replay()
+            torch.cuda.synchronize()
+            count = torch.tensor([max(1, int(hold_s / max(time.perf_counter() - t0, 1e-5)))], device="cuda")
+            dist.broadcast(count, 0)
+            holds = int(count.item()) if hold_s > 0 else 0
+            for _ in range(holds):
+                graph.replay()
+            torch.cuda.synchronize()
+            ms = replay_ms(graph, k)
+            for _ in range(holds // 2):
+                graph.replay()
+            torch.cuda.synchronize()
+            return ms
         t_end = time.perf_counter() + hold_s
         while time.perf_counter() < t_end:
             graph.replay()
@@ -250,28 +280,28 @@ def main():
         return 0
 
     n = HEADLINE_CONTEXT
-    decode = wl.decode_setup(n)
-    launches0 = ctx.launches
-    with ClockSampler(local) as clocks:
-        ms = timed(decode.step, steps, warmup, hold_s=1.0)
-    launches = ctx.launches - launches0 - 2 * warmup   # launches captured for the k timed steps
     bytes_step = decode_bytes(n)
-    gbs = world * bytes_step / (ms * 1e-3) / 1e9
-
-    # end to end through the C ABI from host buffers: H2D the token's projection row,
-    # qk_rope (appends K/V), decode attention, D2H the attended row.
-    e2e_ms = timed(decode.step_e2e, steps, warmup, eager=True)
-    e2e_gbs = world * bytes_step / (e2e_ms * 1e-3) / 1e9
-    e2e_direct_mapped_ms = timed(decode.step_e2e_mapped, steps, warmup, eager=True)
-    # the same token as one captured CUDA graph (lane tables in device memory), one graph launch per token
-    try:
-        e2e_graph_ms = timed(decode.token_graph(), steps, warmup, eager=True)
-        e2e_mapped_ms = timed(decode.token_graph(mapped_host=True), steps, warmup, eager=True)
-    except tb.TataraError as e:   # pragma: no cover
-        e2e_graph_ms = e2e_mapped_ms = None
-
     extra = {}
+    parity = None
     if world == 1:
+        decode = wl.decode_setup(n)
+        launches0 = ctx.launches
+        with ClockSampler(local) as clocks:
+            ms = timed(decode.step, steps, warmup, hold_s=1.0)
+        launches = ctx.launches - launches0 - 2 * warmup   # launches captured for the k timed steps
+        kernel_note = "attn_decode_partition_kernel (+ attn_combine_kernel in the timed step)"
+        # end to end through the C ABI from host buffers: H2D the token's projection row,
+        # qk_rope (appends K/V), decode attention, D2H the attended row.
+        e2e_ms = timed(decode.step_e2e, steps, warmup, eager=True)
+        e2e = {"ms_per_step": e2e_ms,
+               "mapped_host_ms_per_step": timed(decode.step_e2e_mapped, steps, warmup, eager=True),
+               "path": "host-issued C-ABI calls from Python: pinned H2D of the token projection, qk_rope, decode, D2H"}
+        # the same token as one captured CUDA graph (lane tables in device memory), one graph launch per token
+        try:
+            e2e["graph_replay_ms_per_step"] = timed(decode.token_graph(), steps, warmup, eager=True)
+            e2e["graph_replay_mapped_host_ms_per_step"] = timed(decode.token_graph(mapped_host=True), steps, warmup, eager=True)
+        except tb.TataraError:   # pragma: no cover
+            pass
         sweep = []
         for c in SWEEP:
             d = decode if c == n else wl.decode_setup(c)
@@ -295,40 +325,89 @@ def main():
         except Exception as e:   # pragma: no cover
             extra["wave_loop"] = {"error": str(e)[-300:]}
     else:
-        extra["split_kv"] = wl.split_kv(dist, n, timed, steps, warmup)
+        # N > 1: the SAME lane, its key axis split over the ranks (strong scaling).  One submission per
+        # rank and step (tatara_attn_decode_split), k steps captured in one graph per rank.
+        split = wl.split_setup(dist, n)
+        parity = split.check()
+        launches0 = ctx.launches
+        with ClockSampler(local) as clocks:
+            ms = timed(split.step, steps, warmup, hold_s=1.0)
+        ctx.sync()          # a bounded device wait that ran out raises here instead of reporting a fast time
+        launches = ctx.launches - launches0 - 3 * warmup
+        kernel_note = ("attn_decode_partition_kernel over this rank's key range (+ the two attn_combine_kernel "
+                       "launches of the step: merge + peer stores, bounded wait + merge)")
+        e2e_ms = timed(split.step_e2e, steps, warmup, eager=True)
+        ctx.sync()
+        e2e = {"ms_per_step": e2e_ms,
+               "path": "host-issued C-ABI calls from Python on every rank: pinned H2D of the token projection, qk_rope, "
+                       "tatara_attn_decode_split, D2H"}
+        k_ms = timed(split.step_kernel_only, steps, warmup)
+        c_ms = timed(split.step_collective_only, steps, warmup, eager=True)
+        f_ms = timed(split.step_nccl, steps, warmup, eager=True)
+        p_ms = timed(split.step, steps, warmup, eager=True)
+        ctx.sync()
+        local_keys = split.end - split.begin
+        extra["split_kv"] = {
+            "context": n, "gpus": world, "keys_per_gpu": local_keys, "kernel_us": k_ms * 1e3,
+            "kernel_gbs_per_gpu": local_keys * 2048 / (k_ms * 1e-3) / 1e9,
+            "one_submission_graph_us": ms * 1e3, "one_submission_host_issued_us": p_ms * 1e3,
+            "nccl_form": {"collective_us": c_ms * 1e3, "end_to_end_us": f_ms * 1e3,
+                          "aggregate_gbs": bytes_step / (f_ms * 1e-3) / 1e9,
+                          "path": "partial records -> ncclAllGather (16512 B per rank) -> combine, host-issued"},
+            "message_bytes_per_rank": 16 * 258 * 4, "parity": parity,
+            "timing": "kernel and one_submission_graph: CUDA graph of k steps; the others: host-issued; CUDA events, max over ranks"}
+        split.close()
+        del split
+        torch.cuda.empty_cache()
+        # weak scaling beside it: one whole 262144-key lane per GPU, no collective
+        decode = wl.decode_setup(n)
+        w_ms = timed(decode.step, steps, warmup)
+        extra["weak_lane_per_gpu"] = {"lanes": world, "ms_per_step": w_ms, "aggregate_gbs": world * bytes_step / (w_ms * 1e-3) / 1e9,
+                                      "parallelism": "one lane per GPU, no collective"}
+        decode.free()
         extra["lanes32"] = wl.lanes32(timed, steps, warmup)
+    gbs = bytes_step / (ms * 1e-3) / 1e9           # the ONE lane's bytes over the step, whatever N
+    e2e_gbs = bytes_step / (e2e_ms * 1e-3) / 1e9
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         import oracle
+
+        def host_bits(t):   # bf16 device tensor -> uint16 bit patterns on the host
+            return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
         threads = oracle.hardware_threads()
-        best, total = cpu_decode_sample(n, threads, repeats=8)
+        keys, values = decode.caches[0]
+        hq, hg, hk, hv = (host_bits(t) for t in (decode.q, decode.gate, keys, values))
+        best, total, want = cpu_decode_sample(hq, hg, hk, hv, n, threads, repeats=8)
         cpu = {"value": decode_bytes(n) / best / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                "sample": f"best of 8 full decode steps at context {n} ({total:.1f} s of host time)"}
+        # parity of the GPU headline step against that oracle output (same inputs)
+        decode.step(0)
+        ctx.sync()
+        got = host_bits(decode.out).astype(np.uint32) << 16
+        got, ref = got.view(np.float32).astype(np.float64).ravel(), (want.astype(np.uint32) << 16).view(np.float32).astype(np.float64).ravel()
+        parity = {"max_abs": float(np.abs(got - ref).max()),
+                  "cosine": float(got @ ref / (np.linalg.norm(got) * np.linalg.norm(ref))),
+                  "against": "the CPU oracle's decode of the headline step's own inputs", "gate": "max_abs <= 2e-2, cosine >= 0.9999"}
 
     if rank == 0:
+        cfg = headline_config(world)
         line = {
             "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms, "us_per_layer": ms * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": f"decode_attn_ctx{n}", "lanes_per_gpu": 1, "context": n,
-                       "kv_bytes": n * 2048, "l2": "inputs larger than L2 (512 MiB of K+V streamed per step, steps back to back)",
-                       "timing": "k steps captured in one CUDA graph, timed with CUDA events around its replay",
-                       "parallelism": "one lane per GPU, no collective" if world > 1 else "single GPU"},
+            "config": cfg,
+            "timing": "k steps captured in one CUDA graph per rank, timed with CUDA events around its replay, max over ranks",
             "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs / world / peaks["hbm_gbs"], "traffic": wl.traffic_hint(),
-                         "peak_source": peaks["source"],
-                         "kernel": "attn_decode_partition_kernel (+ attn_combine_kernel in the timed step)"},
-            "e2e": {"value": e2e_gbs, "unit": "GB/s", "ms_per_step": e2e_ms,
-                    "mapped_host_ms_per_step": e2e_direct_mapped_ms,
-                    "graph_replay_ms_per_step": e2e_graph_ms,
-                    "graph_replay_mapped_host_ms_per_step": e2e_mapped_ms,
-                    "path": "host-issued C-ABI calls from Python: pinned H2D of the token projection, qk_rope, decode, D2H",
-                    "h2d_bytes_per_step": 9216 * 2, "d2h_bytes_per_step": 4096 * 2},
+                         "frac": gbs / world / peaks["hbm_gbs"], "traffic": wl.traffic_hint() // world,
+                         "peak_source": peaks["source"], "per": "GPU",
+                         "kernel": kernel_note},
+            "e2e": dict({"value": e2e_gbs, "unit": "GB/s", "h2d_bytes_per_step": 9216 * 2, "d2h_bytes_per_step": 4096 * 2}, **e2e),
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "cpu_baseline": cpu,
+            "parity": parity,
         }
         line.update(extra)
         print(json.dumps(line))

@@ -175,6 +175,94 @@ class DecodeCase:
         self.torch.cuda.empty_cache()
 
 
+class SplitCase:
+    """Config 4a: ONE lane of `n_keys` keys, its key axis cut into contiguous ranges, one per rank.
+
+    Every rank draws the whole lane from the same seed (so that each can also run the unsplit decode
+    as the check) and attends only its own range [begin, end) of it; the records cross NVLink.  Two
+    forms of the step: `step` = tatara_attn_decode_split (one submission: partitions, merge + peer
+    stores + flag, bounded wait + merge in rank order; replayable as a graph), and `step_nccl` =
+    partial records -> all_gather -> combine (the library-collective form)."""
+
+    def __init__(self, ctx, torch, dist, n_keys, rank, world):
+        self.ctx, self.torch, self.dist, self.n, self.rank, self.world = ctx, torch, dist, n_keys, rank, world
+        self.begin, self.end = sharding.split_kv_ranges(n_keys, world)[rank]
+        self.keys, self.values = device_cache(torch, n_keys, n_keys, 31)
+        q, gate = device_query(torch, [n_keys - 1], 32)
+        self.q, self.gate = q[0].contiguous(), gate[0].contiguous()
+        self.out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
+        self.out_nccl = torch.zeros_like(self.out)
+        self.rec = torch.zeros((16, 258), device="cuda")
+        self.allrec = torch.zeros((world, 16, 258), device="cuda")
+        self.scratch = torch.empty(tb.decode_scratch_bytes(n_keys, 1) // 4, dtype=torch.float32, device="cuda")
+        self.px = sharding.PeerExchange(ctx, dist, rank, world)
+        g = torch.Generator().manual_seed(33)
+        self.h_proj = torch.randn((1, 9216), generator=g).to(torch.bfloat16).pin_memory()
+        self.d_proj = torch.zeros((1, 9216), dtype=torch.bfloat16, device="cuda")
+        self.h_out = torch.zeros((16, 256), dtype=torch.bfloat16).pin_memory()
+        self.q2 = torch.zeros((1, 16, 256), dtype=torch.bfloat16, device="cuda")
+        self.g2 = torch.zeros_like(self.q2)
+        self.ones = torch.ones(256, dtype=torch.bfloat16, device="cuda")
+
+    def step(self, i=0):
+        self.ctx.attn_decode_split(self.q, self.gate, self.keys, self.values, self.begin, self.end, self.n,
+                                   self.px.pointer_array, self.rank, self.out, self.scratch)
+
+    def step_kernel_only(self, i=0):
+        self.ctx.attn_decode_partial(self.q, self.keys, self.values, self.begin, self.end, self.n, self.rec, self.scratch)
+
+    def step_nccl(self, i=0):
+        self.ctx.attn_decode_partial(self.q, self.keys, self.values, self.begin, self.end, self.n, self.rec, self.scratch)
+        self.dist.all_gather_into_tensor(self.allrec.view(-1), self.rec.view(-1))
+        # all-gather layout [rank][head][258]: head stride 258, part stride 16*258
+        self.ctx.attn_combine(self.allrec, self.world, 258, 16 * 258, self.gate, self.out_nccl)
+
+    def step_collective_only(self, i=0):
+        self.dist.all_gather_into_tensor(self.allrec.view(-1), self.rec.view(-1))
+
+    def step_e2e(self, i=0):
+        """The step from host buffers: pinned H2D of the token's projection row, qk_rope at the lane's
+        last position (the rank that owns that position attends the row it appends), the split step,
+        D2H of the attended row -- on every rank."""
+        self.d_proj.copy_(self.h_proj, non_blocking=True)
+        self.ctx.attn_qk_rope(self.d_proj, self.ones, self.ones, self.q2, self.g2, self.keys, self.values,
+                              self.n - 1, self.n, 1)
+        self.ctx.attn_decode_split(self.q2, self.g2, self.keys, self.values, self.begin, self.end, self.n,
+                                   self.px.pointer_array, self.rank, self.out, self.scratch)
+        self.h_out.copy_(self.out, non_blocking=True)
+
+    def check(self):
+        """Split results against the unsplit decode of the same lane on this GPU (tolerance of the
+        parity tests: max-abs 2e-2, cosine 0.9999), peer form against NCCL form (same records, same
+        rank-order merge: equal bits); worst case over the ranks."""
+        torch, dist = self.torch, self.dist
+        unsplit = torch.zeros_like(self.out)
+        self.out.zero_()
+        self.out_nccl.zero_()
+        self.step()
+        self.step_nccl()
+        self.ctx.attn_decode(self.q, self.gate, self.keys, self.values, self.n - 1, self.n, unsplit, self.scratch)
+        self.ctx.sync()     # raises if a bounded wait ran out
+
+        def distance(a, b):
+            a, b = a.float().flatten(), b.float().flatten()
+            cos = torch.dot(a, b) / (a.norm() * b.norm()).clamp_min(1e-30)
+            return float((a - b).abs().max()), float(cos)
+
+        pe, pc = distance(self.out, unsplit)
+        ne, nc = distance(self.out_nccl, unsplit)
+        t = torch.tensor([pe, ne, -pc, -nc, 0.0 if torch.equal(self.out, self.out_nccl) else 1.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pe, ne, pc, nc, differ = (float(x) for x in t)
+        return {"peer_max_abs": pe, "peer_cosine": -pc, "nccl_max_abs": ne, "nccl_cosine": -nc,
+                "matches_unsplit": bool(pe <= 2e-2 and -pc >= 0.9999 and ne <= 2e-2 and -nc >= 0.9999),
+                "peer_equals_nccl_bits": differ == 0.0,
+                "checked": "every rank: split out vs tatara_attn_decode of the whole lane; worst over ranks"}
+
+    def close(self):
+        self.px.close(self.dist, sync=self.ctx.sync)
+
+
 class Workloads:
     def __init__(self, ctx, torch, rank=0, world=1):
         self.ctx, self.torch, self.rank, self.world = ctx, torch, rank, world
@@ -182,9 +270,8 @@ class Workloads:
 
     def traffic_hint(self):
         """DRAM bytes (read + write) per launch of attn_decode_partition_kernel at the headline
-        context, from the ncu capture summarised in
-        profiles/attn_decode_partition_kernel_ctx65536_ncu_full.md: (134.280448 + 4.332800) MB at
-        65 536 keys, scaled by keys (traffic is proportional to keys) to 262 144."""
+        context, from an ncu capture at 65 536 keys (134.280448 MB read + 4.332800 MB written),
+        scaled by keys (traffic is proportional to keys) to 262 144."""
         return int((134.280448e6 + 4.332800e6) * 4)
 
     def decode_setup(self, n_keys):
@@ -215,15 +302,21 @@ class Workloads:
         res = {"lanes": 32, "contexts": "uniform[4096,32768] seed 0", "ms": ms, "lanes_per_s": 32 / (ms * 1e-3),
                "gbs": total_bytes / (ms * 1e-3) / 1e9, "total_kv_bytes": total_bytes,
                "max_rank_keys": max(loads)}
-        # bit-identity: the first local lane alone gives the bits it got inside the batch
+        # bit-identity: EVERY local lane alone gives the bits it got inside the batch
         if n:
+            step()
+            self.ctx.sync()
+            batched = out.clone()
             solo = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
-            step()
-            self.ctx.attn_decode(q[0], gate[0], kpool[0], vpool[0], contexts[mine[0]] - 1, cap, solo, scratch)
-            torch.cuda.synchronize()
-            step()
-            torch.cuda.synchronize()
-            res["lane_bits_identical_alone_vs_batched"] = bool(torch.equal(solo, out[0]))
+            solo_scratch = torch.empty(tb.decode_scratch_bytes(cap, 1) // 4, dtype=torch.float32, device="cuda")
+            same = 0
+            for i in range(n):
+                solo.zero_()
+                self.ctx.attn_decode(q[i], gate[i], kpool[i], vpool[i], contexts[mine[i]] - 1, cap, solo, solo_scratch)
+                self.ctx.sync()
+                same += int(torch.equal(solo, batched[i]))
+            res["lanes_checked_alone_vs_batched"] = n
+            res["lane_bits_identical_alone_vs_batched"] = bool(same == n)
         del kpool, vpool
         torch.cuda.empty_cache()
         return res
@@ -461,67 +554,9 @@ class Workloads:
         return {"positions": positions, "segments": len(entries), "payload_bytes": payload, "ms": ms, "gbs_read_plus_write": gbs,
                 "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "l2": "payload 1.4 GB > L2"}
 
-    # ---- config 4a: one lane at 262144 split along KV over the ranks, LSE merge over NCCL
-    def split_kv(self, dist, n_keys, timed, steps, warmup):
-        torch = self.torch
-        w, r = self.world, self.rank
-        begin, end = sharding.split_kv_ranges(n_keys, w)[r]
-        local = end - begin
-        keys, values = device_cache(torch, local, local, 31 + r)   # this rank's slice of the lane
-        q, gate = device_query(torch, [n_keys - 1], 32)
-        q, gate = q[0].contiguous(), gate[0].contiguous()
-        rec = torch.zeros((16, 258), device="cuda")
-        allrec = torch.zeros((w, 16, 258), device="cuda")
-        out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
-        scratch = torch.empty(tb.decode_scratch_bytes(local, 1) // 4, dtype=torch.float32, device="cuda")
-
-        def partial():
-            self.ctx.attn_decode_partial(q, keys, values, 0, local, local, rec, scratch)
-            return rec
-
-        def combine(gathered):
-            # all-gather layout [rank][head][258]: head stride 258, part stride 16*258
-            self.ctx.attn_combine(gathered, w, 258, 16 * 258, gate, out)
-
-        def kernel_only(i=0):
-            partial()
-
-        def full(i=0):
-            sharding.split_kv_decode(dist, w, partial, allrec, combine)
-
-        def collective_only(i=0):
-            dist.all_gather_into_tensor(allrec.view(-1), rec.view(-1))
-
-        k_ms = timed(kernel_only, steps, warmup)
-        c_ms = timed(collective_only, steps, warmup, eager=True)
-        f_ms = timed(full, steps, warmup, eager=True)
-        total = n_keys * 2048 + 3 * 8192
-        # the same step without a library collective: records pushed over peer memory
-        peer = None
-        try:
-            px = sharding.PeerExchange(self.ctx, dist, r, w)
-
-            def push(gathers, flags, epoch):
-                self.ctx.attn_decode_partial_push(q, keys, values, 0, local, local, gathers, flags, r, epoch, scratch)
-
-            def wait(gather, flags, epoch):
-                self.ctx.attn_combine_wait(gather, flags, w, epoch, gate, out)
-
-            p_ms = timed(lambda i=0: px.step(push, wait), steps, warmup, eager=True)
-            dist.barrier()
-            torch.cuda.synchronize()
-            px.close()
-            peer = {"end_to_end_us": p_ms * 1e3, "aggregate_gbs": total / (p_ms * 1e-3) / 1e9,
-                    "exchange": "records stored into every rank's buffer by the combine kernel (CUDA IPC peer "
-                                "memory over NVLink) + bounded flag wait; no NCCL call in the step"}
-        except tb.TataraError as e:
-            peer = {"unavailable": str(e)}
-        return {"context": n_keys, "gpus": w, "keys_per_gpu": local, "kernel_us": k_ms * 1e3,
-                "collective_us": c_ms * 1e3, "end_to_end_us": f_ms * 1e3,
-                "aggregate_gbs": total / (f_ms * 1e-3) / 1e9, "peer_memory": peer,
-                "kernel_gbs_per_gpu": (local * 2048) / (k_ms * 1e-3) / 1e9,
-                "message_bytes_per_rank": 16 * 258 * 4, "scaling": "strong",
-                "timing": "kernel: CUDA graph; collective and end-to-end: host-issued, CUDA events, max over ranks"}
+    # ---- config 4a: one lane at 262144 split along KV over the ranks
+    def split_setup(self, dist, n_keys):
+        return SplitCase(self.ctx, self.torch, dist, n_keys, self.rank, self.world)
 
     # ---- single-workload runs (profiling)
     # ---- the engine's wave loop over a 40-layer stack (native program above the C ABI)

@@ -85,6 +85,18 @@ int tatara_abi_version(void);
 /* Kernels launched through this context since creation (for benchmark accounting). */
 uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx);
 
+/* Execution policy of a context: choices that change how a kernel runs and never what it computes
+ * (the reference keeps such choices in policy structs fixed at boot: DecodeAttentionSplitPolicy,
+ * include/tatara/runtime/decode_step.h:15-21; PrefillExecutionPolicy, prefill_step.h:42-73).
+ * Set before the first call that the policy affects, not between calls in flight. */
+typedef enum tatara_policy {
+    /* Rows of K and of V of each decode CTA's first partition that are requested into L2 before the
+     * kernel waits for its predecessor in the stream (0 switches the requests off). */
+    TATARA_POLICY_DECODE_L2_PREFETCH_KEYS = 0
+} tatara_policy;
+tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
+uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);
+
 /* ---- geometry (pure functions; include/tatara/runtime/decode_geometry.h:133-135, 165-273) */
 /* Keys per partition and partition count of the split-KV decode for `n_keys` attended
  * keys.  Depends on n_keys only, never on the batch: this is what keeps a lane's output
@@ -142,18 +154,20 @@ tatara_status tatara_attn_decode_batch(tatara_ctx* ctx, void* stream, const void
  * whose allocator it may not touch, or any code path where cudaMalloc (a synchronising call
  * that can fail under memory pressure) is off limits.  It has no counterpart in the reference,
  * whose record scratch is always a caller-owned buffer.  Same arithmetic and output as
- * tatara_attn_decode, but the partial records go to a 4 MiB array built into the library, so
+ * tatara_attn_decode, but the partial records go to a 1.2 MB array built into the library, so
  * no scratch pointer is passed and this call never calls cudaMalloc, cudaFree or any routine
  * that allocates.  Limits and sharing:
- *   - at most 65536 attended keys (context <= 65535); longer lanes return
+ *   - at most 262144 attended keys (context <= 262143, the model's maximum context: a lane is
+ *     never cut into more than 74 partitions, which is what the array holds); longer lanes return
  *     TATARA_SCRATCH_TOO_SMALL and must use tatara_attn_decode with caller scratch;
  *   - every call on a device shares the one array: calls that may overlap on the GPU
  *     (different streams, or several host threads) race on it; serialise them.  The array
  *     keeps the previous call's records, which is harmless: each call rewrites every record it
  *     later reads, so nothing has to start at zero;
  *   - the first call on each device (with that device current) looks up the array's device
- *     address and configures the kernel; make that first call before any stream capture;
- *   - every GPU that loads the library holds the 4 MiB until the process exits;
+ *     address and configures the kernel (host threads that make it together are serialised
+ *     inside the call); make that first call before any stream capture;
+ *   - every GPU that loads the library holds the 1.2 MB until the process exits;
  *   - ctx may be NULL (it only receives the error text and the launch count). */
 tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream, const void* q,
                                         const void* gate, const void* keys, const void* values,
@@ -201,6 +215,24 @@ tatara_status tatara_attn_decode_partial_push(tatara_ctx* ctx, void* stream, con
 tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream, const void* gather,
                                        const void* flags, uint32_t world, uint32_t epoch,
                                        uint32_t wait_limit_us, const void* gate, void* out);
+
+/* One split-KV decode step of this rank as ONE submission: the local partitions of keys
+ * [key_begin, key_end) of this rank's cache slice are merged to one record per head, stored into slot
+ * `rank` of every rank's peer buffer and announced by a flag (as tatara_attn_decode_partial_push);
+ * a dependent kernel then waits (bounded by wait_limit_us, as tatara_attn_combine_wait) for the
+ * flags of all ranks and merges the `world` records in rank order with the reference's combine
+ * (src/backend/metal/kernels/attention.metal:1086-1108) into `out` on every rank.
+ * peer_buffers: `world` device pointers, entry r = rank r's buffer of tatara_split_buffer_bytes(world)
+ * bytes (tatara_peer_buffer_create / _open), laid out as [2 parities][world][16][258] f32 records |
+ * [2 parities][world] u32 flags | u32 step counter.  The step counter lives on the device and is
+ * advanced by the step itself, so no argument changes from token to token: the call may be captured
+ * in a CUDA graph and replayed.  Every rank must issue the same sequence of steps. */
+uint64_t tatara_split_buffer_bytes(uint32_t world);
+tatara_status tatara_attn_decode_split(tatara_ctx* ctx, void* stream, const void* q, const void* gate,
+                                       const void* keys, const void* values, uint32_t key_begin,
+                                       uint32_t key_end, uint32_t capacity, void* const* peer_buffers,
+                                       uint32_t rank, uint32_t world, uint32_t wait_limit_us, void* out,
+                                       void* scratch, uint64_t scratch_bytes);
 
 /* Causal block prefill: slots 0 query, 1 K, 2 V, 3 gate, 4 out, 5 visible, 6 capacity,
  * 7 tile_rows, 8 tile_context (src/runtime/prefill_step.cpp:1661-1683).  Row r sits at

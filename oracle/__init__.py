@@ -18,7 +18,17 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libtatara_oracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libtatara_ref.so")
-REFERENCE_ROOT = os.environ.get("TATARA_REFERENCE_ROOT", "/root/reference")
+
+
+def reference_root() -> str | None:
+    """The reference checkout: $TATARA_REFERENCE_ROOT, else a directory named `reference` beside
+    this repository (where the build container keeps it); None where neither exists."""
+    for root in (os.environ.get("TATARA_REFERENCE_ROOT"),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if root and os.path.exists(os.path.join(root, "tests", "native", "kernel_reference.cpp")):
+            return root
+    return None
+
 
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _u32p = ctypes.POINTER(ctypes.c_uint32)
@@ -30,11 +40,13 @@ _int = ctypes.c_int
 def build(with_reference: bool | None = None) -> None:
     """Compile the oracle (and, where the reference tree is present, its CPU model)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+    root = reference_root()
     if with_reference is None:
-        with_reference = os.path.exists(
-            os.path.join(REFERENCE_ROOT, "tests", "native", "kernel_reference.cpp"))
+        with_reference = root is not None
     if with_reference:
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REFERENCE_ROOT={REFERENCE_ROOT}"])
+        if root is None:
+            raise RuntimeError("the reference checkout was not found: set TATARA_REFERENCE_ROOT")
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REFERENCE_ROOT={root}"])
 
 
 def _p(a: np.ndarray, ty):

@@ -70,7 +70,16 @@ def lib() -> ctypes.CDLL:
         _lib.tatara_attn_partition_keys.restype = ctypes.c_uint32
         _lib.tatara_gdn_prefill_scratch_bytes.restype = ctypes.c_uint64
         _lib.tatara_attn_partitions.restype = ctypes.c_uint32
+        _lib.tatara_split_buffer_bytes.restype = ctypes.c_uint64
+        _lib.tatara_ctx_get_policy.restype = ctypes.c_uint64
     return _lib
+
+
+POLICY_DECODE_L2_PREFETCH_KEYS = 0
+
+
+def split_buffer_bytes(world: int) -> int:
+    return int(lib().tatara_split_buffer_bytes(ctypes.c_uint32(world)))
 
 
 def partition_keys(n_keys: int) -> int:
@@ -221,6 +230,24 @@ class Context:
             self._h, self._stream(stream), _ptr(q), _ptr(keys), _ptr(values), _u32(key_begin), _u32(key_end),
             _u32(capacity), pg, pf, _u32(rank), _u32(world), _u32(epoch), _ptr(scratch),
             _u64(scratch.numel() * scratch.element_size())))
+
+    def attn_decode_split(self, q, gate, keys, values, key_begin, key_end, capacity, peer_buffers, rank,
+                          out, scratch, wait_limit_us=1000000, stream=None):
+        """peer_buffers: a ctypes array of `world` device pointers (Context.pointer_array), built once."""
+        self._check(lib().tatara_attn_decode_split(
+            self._h, self._stream(stream), _ptr(q), _ptr(gate), _ptr(keys), _ptr(values), _u32(key_begin),
+            _u32(key_end), _u32(capacity), peer_buffers, _u32(rank), _u32(len(peer_buffers)), _u32(wait_limit_us),
+            _ptr(out), _ptr(scratch), _u64(scratch.numel() * scratch.element_size())))
+
+    @staticmethod
+    def pointer_array(pointers):
+        return (ctypes.c_void_p * len(pointers))(*pointers)
+
+    def set_policy(self, policy: int, value: int):
+        self._check(lib().tatara_ctx_set_policy(self._h, ctypes.c_int(policy), _u64(value)))
+
+    def get_policy(self, policy: int) -> int:
+        return int(lib().tatara_ctx_get_policy(self._h, ctypes.c_int(policy)))
 
     def attn_combine_wait(self, gather_ptr, flags_ptr, world, epoch, gate, out, wait_limit_us=1000000, stream=None):
         self._check(lib().tatara_attn_combine_wait(self._h, self._stream(stream), ctypes.c_void_p(gather_ptr),

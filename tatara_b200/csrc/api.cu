@@ -108,6 +108,24 @@ const char* tatara_last_error_string(const tatara_ctx* ctx) {
 
 uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx) { return ctx == nullptr ? 0 : ctx->launches; }
 
+tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    switch (policy) {
+    case TATARA_POLICY_DECODE_L2_PREFETCH_KEYS:
+        if (value > TATARA_MAX_CONTEXT) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: prefetch rows");
+        ctx->decode_l2_prefetch_keys = static_cast<uint32_t>(value);
+        return TATARA_OK;
+    }
+    return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: unknown policy");
+}
+uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy) {
+    if (ctx == nullptr) return 0;
+    switch (policy) {
+    case TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: return ctx->decode_l2_prefetch_keys;
+    }
+    return 0;
+}
+
 uint32_t tatara_attn_partition_keys(uint32_t n_keys) {
     return n_keys == 0 ? 0 : tb::partition_keys(n_keys);
 }

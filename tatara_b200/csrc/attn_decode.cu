@@ -18,6 +18,7 @@
 #include "common.cuh"
 
 #include <cstring>
+#include <mutex>
 
 namespace tb {
 
@@ -56,6 +57,7 @@ struct DecParams {
     uint32_t capacity;
     uint32_t n_lanes;
     uint32_t total_items;
+    uint32_t l2_prefetch_keys; // K/V rows of a CTA's first item requested into L2 before the dependency wait
     DecLane lane[N];
 };
 
@@ -73,6 +75,12 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint3
     asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src),
                  "r"(src_bytes), "l"(policy)
                  : "memory");
+}
+// Asks for `bytes` (a multiple of 16, from a 16-byte aligned address) to be brought into L2; nothing
+// is written to shared memory or registers, so the request may precede the dependency wait even for
+// rows the predecessor is still writing (L2 is the point of coherence: a later store updates the line).
+__device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int kPending>
@@ -214,6 +222,18 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         // Every partition but a lane's last is full (at least 128 keys = 2 slices for each warp) and
         // holds only keys written before this token, so its first slices can be requested at once.
         early = pc.part + 1u < lane_at<N, kInd>(p, pc.lane).nparts;
+        // The ring holds (kDecStages - 1) slices per warp before the dependency wait; the rows after
+        // those are asked into L2 now, so that the K/V stream out of HBM keeps running while this CTA
+        // waits for its predecessor and for q (one 16-row request of each plane per thread and pass).
+        if (p.l2_prefetch_keys != 0u) {
+            const uint32_t ring_keys = early ? kDecWarps * (kDecStages - 1u) * kSliceKeys : 0u;
+            const uint32_t stop = min(pc.nkeys, ring_keys + p.l2_prefetch_keys);
+            for (uint32_t row = ring_keys + threadIdx.x * kSliceKeys; row < stop; row += kDecThreads * kSliceKeys) {
+                const uint32_t bytes = min(kSliceKeys, stop - row) * kRowBytes;
+                l2_prefetch_bulk(pc.kbase + uint64_t(row) * kRowBytes, bytes);
+                l2_prefetch_bulk(pc.vbase + uint64_t(row) * kRowBytes, bytes);
+            }
+        }
         cursor_settle<N, kInd>(pc, p, item_start, warp);
     }
     uint32_t issued = 0, consumed = 0;
@@ -398,10 +418,22 @@ struct PeerExchange {
     float* peer_out[kMaxPeers];      // push: slot [rank] of every rank's gather buffer ([16][258] f32)
     uint32_t* peer_flag[kMaxPeers];  // push: word [rank] of every rank's flag array
     const uint32_t* wait_flags;      // wait: this rank's flag array, or null
-    uint32_t* done_counter;          // push: local counter of finished CTAs (self-resetting)
+    uint32_t* done_counter;          // local counter of finished CTAs (self-resetting)
     uint32_t* status;                // device status word of the context
+    // Step counter in this rank's own memory, or null.  With a counter the epoch of a call is
+    // counter + 1, the pointers above address parity 0 and the parity in use is epoch & 1 (the strides
+    // below lead to parity 1); the waiting merge advances the counter when its last CTA is done.  So a
+    // step has no host-side argument that changes from token to token, and a captured graph replays.
+    uint32_t* step;
+    uint32_t out_parity_floats, flag_parity_words;
     uint32_t world, epoch, wait_limit_us;
 };
+__device__ __forceinline__ uint32_t exchange_epoch(const PeerExchange& px) {
+    if (px.step == nullptr) return px.epoch;
+    uint32_t done;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(done) : "l"(px.step) : "memory");
+    return done + 1u;
+}
 template <uint32_t N>
 struct CombineParams {
     const DecTables* tables;   // null: the lane table below
@@ -439,6 +471,8 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     // records (this grid is its programmatic dependent).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t px_epoch = p.px.world != 0u ? exchange_epoch(p.px) : 0u;
+    const uint32_t px_parity = p.px.step != nullptr ? (px_epoch & 1u) : 0u;
     if (p.px.wait_flags != nullptr) {
         // Split-KV merge: the records of the other ranks are pushed into this GPU's memory by
         // kernels running on THEIR GPUs; wait, with a time limit, until every rank's flag carries
@@ -446,12 +480,13 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
         __shared__ uint32_t arrived;
         if (threadIdx.x == 0) {
             const unsigned long long t0 = combine_now_ns();
+            const uint32_t* flags = p.px.wait_flags + px_parity * p.px.flag_parity_words;
             uint32_t ok = 1u;
             for (uint32_t r = 0; r < p.px.world && ok; ++r) {
                 for (;;) {
                     uint32_t v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.px.wait_flags + r) : "memory");
-                    if (v == p.px.epoch) break;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+                    if (v == px_epoch) break;
                     if (combine_now_ns() - t0 > 1000ull * p.px.wait_limit_us) {
                         ok = 0u;
                         atomicCAS(p.px.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
@@ -464,13 +499,14 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
             arrived = ok;
         }
         __syncthreads();
-        if (arrived == 0u) return;
+        if (arrived == 0u) return;   // (the step counter stays: the caller sees the status and starts over)
     }
     const CombineLane& cl = kInd ? p.tables->comb[blockIdx.y] : p.lane[blockIdx.y];
     if (kInd && cl.nparts == 0u) return;   // a lane the setup kernel rejected (context beyond capacity): status is latched
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const float* base = cl.records + head * cl.head_stride;
+    const float* base = cl.records + head * cl.head_stride +
+                        (p.px.wait_flags != nullptr ? uint64_t(px_parity) * p.px.out_parity_floats : 0ull);
     const uint32_t nparts = cl.nparts;
     const uint32_t d = quarter * kCombineDims + lane * 2u;
     constexpr uint32_t kOwn = kCombinePhases / kWarps, kRound = kCombinePhases * kCombineUnroll;
@@ -550,7 +586,7 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
         if (p.px.world != 0u && p.px.wait_flags == nullptr) {
             // push this head's slice of the merged record into every rank's gather buffer
             for (uint32_t r = 0; r < p.px.world; ++r) {
-                float* ro = p.px.peer_out[r] + head * kRecordFloats;
+                float* ro = p.px.peer_out[r] + uint64_t(px_parity) * p.px.out_parity_floats + head * kRecordFloats;
                 ro[dd] = acc;
                 if (dd == 0) {
                     ro[kHeadDim] = big;
@@ -580,7 +616,19 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
                 *p.px.done_counter = 0u;
                 __threadfence_system();
                 for (uint32_t r = 0; r < p.px.world; ++r)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.px.peer_flag[r]), "r"(p.px.epoch) : "memory");
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.px.peer_flag[r] + px_parity * p.px.flag_parity_words),
+                                 "r"(px_epoch) : "memory");
+            }
+        }
+    }
+    if (p.px.wait_flags != nullptr && p.px.step != nullptr) {
+        // Every CTA has read the step counter by now; the one that finishes last moves it on.
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t total_ctas = gridDim.x * gridDim.y;
+            if (atomicAdd(p.px.done_counter, 1u) == total_ctas - 1u) {
+                *p.px.done_counter = 0u;
+                asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.px.step), "r"(px_epoch) : "memory");
             }
         }
     }
@@ -614,6 +662,7 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     dp.records = static_cast<float*>(r.scratch);
     dp.query_stride = r.query_stride;
     dp.capacity = r.capacity;
+    dp.l2_prefetch_keys = ctx->decode_l2_prefetch_keys;
     dp.n_lanes = n_lanes;
     uint64_t rec_floats = 0;
     uint32_t items = 0;
@@ -759,6 +808,7 @@ static tatara_status launch_decode_indirect(tatara_ctx* ctx, cudaStream_t stream
     dp.records = static_cast<float*>(r.scratch);
     dp.query_stride = r.query_stride;
     dp.capacity = r.capacity;
+    dp.l2_prefetch_keys = ctx->decode_l2_prefetch_keys;
     cp.tables = tables;
     cp.gate = static_cast<const __nv_bfloat16*>(r.gate);
     cp.out = static_cast<__nv_bfloat16*>(r.out);
@@ -962,18 +1012,22 @@ extern "C" tatara_status tatara_attn_prefill_control(tatara_ctx* ctx, void* stre
 
 // ---- allocation-free decode ---------------------------------------------------------------
 // Record scratch that lives inside the library image instead of in caller memory.  Every GPU
-// that loads the library holds these 4 MiB until the process exits.
+// that loads the library holds these 1.2 MB until the process exits.
 namespace tb {
-constexpr uint32_t kStaticMaxKeys = 65536;
-constexpr uint32_t kStaticMaxParts = 256; // partition_count(n) <= 222 for every n <= 65536
+// tb::partition_keys never cuts a lane into more than 74 partitions (128-key partitions up to
+// 9472 keys, 74 equal ones beyond), so 74 x 16 records serve any key count; the cap on the key
+// count is the model's maximum context (include/tatara/runtime/prefill_geometry.h:14).
+constexpr uint32_t kStaticMaxKeys = 262144;
+constexpr uint32_t kStaticMaxParts = kSmCount / kKvHeads;
 static __device__ __align__(256) float g_static_records[kStaticMaxParts * kQHeads * kRecordFloats];
 
 struct StaticSetup {
-    bool ready;
-    float* records; // device address of g_static_records on that device
-    int sm_count;
+    std::once_flag once;
+    cudaError_t error = cudaErrorNotReady;
+    float* records = nullptr; // device address of g_static_records on that device
+    int sm_count = 0;
 };
-static StaticSetup g_static_setup[64] = {};
+static StaticSetup g_static_setup[64];
 } // namespace tb
 
 extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream, const void* q,
@@ -987,18 +1041,19 @@ extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream
         return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_static: misaligned buffer");
     if (capacity == 0 || context >= capacity)
         return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_static: context >= capacity");
-    const uint32_t n = context + 1u;
-    if (n > kStaticMaxKeys || partition_count(n) > kStaticMaxParts)
+    if (context >= kStaticMaxKeys || partition_count(context + 1u) > kStaticMaxParts)
         return fail(ctx, TATARA_SCRATCH_TOO_SMALL,
-                    "attn_decode_static: the built-in scratch covers at most 65536 attended keys; "
+                    "attn_decode_static: the built-in scratch covers at most 262144 attended keys; "
                     "use tatara_attn_decode with caller scratch beyond that");
+    const uint32_t n = context + 1u;
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64)
         return fail(ctx, TATARA_INVALID_DEVICE, "attn_decode_static: no current device");
     StaticSetup& setup = g_static_setup[device];
-    if (!setup.ready) {
-        // Once per device, with that device current.  In host code the array's name is only a
-        // stand-in for the symbol; the address a kernel may use comes from the runtime.
+    // Once per device, with that device current; a second host thread that arrives meanwhile waits
+    // here until the first has finished.  In host code the array's name is only a stand-in for the
+    // symbol; the address a kernel may use comes from the runtime.
+    std::call_once(setup.once, [&setup, device]() {
         float* address = nullptr;
         cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_records);
         if (err == cudaSuccess)
@@ -1006,12 +1061,13 @@ extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream
         if (err == cudaSuccess)
             err = cudaFuncSetAttribute(attn_decode_partition_kernel<1>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes);
-        if (err != cudaSuccess || address == nullptr) {
-            (void)cudaGetLastError();
-            return fail(ctx, TATARA_CUDA_ERROR, "attn_decode_static: set-up of the built-in scratch failed");
-        }
+        if (err == cudaSuccess && address == nullptr) err = cudaErrorInvalidSymbol;
         setup.records = address;
-        setup.ready = true;
+        setup.error = err;
+    });
+    if (setup.error != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(ctx, TATARA_CUDA_ERROR, "attn_decode_static: set-up of the built-in scratch failed");
     }
     DecParams<1> dp{};
     dp.q = static_cast<const __nv_bfloat16*>(q);
@@ -1020,6 +1076,7 @@ extern "C" tatara_status tatara_attn_decode_static(tatara_ctx* ctx, void* stream
     dp.records = setup.records;
     dp.query_stride = kQHeads * kHeadDim;
     dp.capacity = capacity;
+    dp.l2_prefetch_keys = ctx != nullptr ? ctx->decode_l2_prefetch_keys : kDecodeL2PrefetchKeys;
     dp.n_lanes = 1;
     DecLane& l = dp.lane[0];
     l.kv_offset = 0;
@@ -1117,6 +1174,74 @@ extern "C" tatara_status tatara_attn_decode_partial_push(tatara_ctx* ctx, void* 
     const uint32_t row = 0;
     return launch_decode<1>(ctx, static_cast<cudaStream_t>(stream), r, &lane, &key_begin, &key_end, &row, 1,
                             "attn_decode_partial_push");
+}
+
+extern "C" uint64_t tatara_split_buffer_bytes(uint32_t world) {
+    // [2 parities][world][16][258] f32 records | [2 parities][world] u32 flags | u32 step counter, rounded up to 16 bytes
+    const uint64_t bytes = 2ull * world * kQHeads * kRecordFloats * sizeof(float) + 2ull * world * sizeof(uint32_t) + 4ull;
+    return (bytes + 15ull) & ~15ull;
+}
+
+extern "C" tatara_status tatara_attn_decode_split(tatara_ctx* ctx, void* stream, const void* q, const void* gate,
+                                                  const void* keys, const void* values, uint32_t key_begin,
+                                                  uint32_t key_end, uint32_t capacity, void* const* peer_buffers,
+                                                  uint32_t rank, uint32_t world, uint32_t wait_limit_us, void* out,
+                                                  void* scratch, uint64_t scratch_bytes) {
+    if (ctx == nullptr) return TATARA_INVALID_BUFFER;
+    if (!q || !gate || !keys || !values || !out || !scratch || !peer_buffers)
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_split: null buffer");
+    if (!aligned(q, 4) || !aligned(keys, 16) || !aligned(values, 16) || !aligned(scratch, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_split: misaligned buffer");
+    if (world == 0 || world > kMaxPeers || rank >= world || wait_limit_us == 0 || wait_limit_us > 2000000u)
+        return fail(ctx, TATARA_INVALID_STREAM_GROUP, "attn_decode_split: rank / world / time limit");
+    if (capacity == 0 || key_begin >= key_end || key_end > capacity)
+        return fail(ctx, TATARA_CONTEXT_OUT_OF_RANGE, "attn_decode_split: key range");
+    const uint64_t gather_floats = uint64_t(world) * kQHeads * kRecordFloats;   // one parity
+    PeerExchange px{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!peer_buffers[r] || !aligned(peer_buffers[r], 16))
+            return fail(ctx, TATARA_INVALID_BUFFER, "attn_decode_split: peer buffer");
+        float* base = static_cast<float*>(peer_buffers[r]);
+        px.peer_out[r] = base + uint64_t(rank) * kQHeads * kRecordFloats;
+        px.peer_flag[r] = reinterpret_cast<uint32_t*>(base + 2ull * gather_floats) + rank;
+    }
+    float* own = static_cast<float*>(peer_buffers[rank]);
+    uint32_t* own_flags = reinterpret_cast<uint32_t*>(own + 2ull * gather_floats);
+    px.step = own_flags + 2u * world;
+    px.out_parity_floats = uint32_t(gather_floats);
+    px.flag_parity_words = world;
+    px.done_counter = ctx->device_status + 2;
+    px.status = ctx->device_status;
+    px.world = world;
+    // local partitions -> one merged record per head, pushed into every rank's buffer, flags raised
+    DecodeRequest r{q, nullptr, keys, values, nullptr, nullptr, scratch, scratch_bytes, kQHeads * kHeadDim, capacity};
+    r.px = &px;
+    const tatara_attn_lane lane{0, key_end - 1u, 0};
+    const uint32_t row = 0;
+    auto s = static_cast<cudaStream_t>(stream);
+    const tatara_status st = launch_decode<1>(ctx, s, r, &lane, &key_begin, &key_end, &row, 1, "attn_decode_split");
+    if (st != TATARA_OK) return st;
+    // wait for every rank's flags, merge the world's records in rank order, gate, store
+    CombineParams<1> cp{};
+    cp.gate = static_cast<const __nv_bfloat16*>(gate);
+    cp.out = static_cast<__nv_bfloat16*>(out);
+    cp.query_stride = kQHeads * kHeadDim;
+    cp.lane[0] = CombineLane{own, kRecordFloats, uint64_t(kQHeads) * kRecordFloats, world, 0};
+    cp.px = px;
+    cp.px.wait_flags = own_flags;
+    cp.px.done_counter = ctx->device_status + 3;
+    cp.px.wait_limit_us = wait_limit_us;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kQHeads * 4, 1);
+    cfg.blockDim = dim3(combine_warps<1>() * 32u);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, attn_combine_kernel<1>, cp);
+    return check_launch(ctx, "attn_decode_split");
 }
 
 extern "C" tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream, const void* gather,

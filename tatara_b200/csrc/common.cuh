@@ -26,6 +26,9 @@ constexpr uint32_t kSmCount = 148; // B200; the partition function is pinned to 
 // Device-side status word slots (ctx->device_status).
 enum : uint32_t { kStatusCode = 0, kStatusDetail = 1, kStatusWords = 4 };
 constexpr size_t kLaneScheduleBytes = 32768;   // holds attn_decode.cu's DecTables
+// Default of TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: K/V rows per plane that a decode CTA asks into L2
+// beyond its shared-memory ring before its dependency wait (512 bytes per row and plane).
+constexpr uint32_t kDecodeL2PrefetchKeys = 256;
 
 } // namespace tb
 
@@ -36,6 +39,7 @@ struct tatara_ctx {
     uint32_t* host_status = nullptr;   // pinned mirror
     void* lane_schedule = nullptr;     // device scratch of the calls whose lane tables live in device memory
     uint64_t launches = 0;
+    uint32_t decode_l2_prefetch_keys = tb::kDecodeL2PrefetchKeys;   // TATARA_POLICY_DECODE_L2_PREFETCH_KEYS
     char error[256] = {0};
 };
 

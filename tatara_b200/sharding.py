@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import Callable, List, Sequence, Tuple
 
+from . import split_buffer_bytes as tb_split_buffer_bytes
+
 RECORD_FLOATS = 258
 Q_HEADS = 16
 
@@ -65,8 +67,11 @@ def split_kv_decode(dist, world: int, partial: Callable[[], "object"], gathered,
 
 class PeerExchange:
     """Peer buffers of the collective-free split-KV merge: per rank one buffer holding
-    [2 parities][world][16][258] f32 records followed by [2][world] u32 flags, mapped into every
-    process through CUDA IPC (handles exchanged once with all_gather_object)."""
+    [2 parities][world][16][258] f32 records followed by [2][world] u32 flags and the device step
+    counter (tatara_split_buffer_bytes), mapped into every process through CUDA IPC (handles
+    exchanged once with all_gather_object).  Use EITHER step() (host-numbered epochs, two calls per
+    step) OR tatara_attn_decode_split with pointer_array (device-numbered steps, one call) on one
+    exchange: both write the same flags."""
 
     RECORD_BYTES = Q_HEADS * RECORD_FLOATS * 4
 
@@ -74,7 +79,7 @@ class PeerExchange:
         self.ctx, self.rank, self.world = ctx, rank, world
         self.gather_bytes = world * self.RECORD_BYTES
         self.flags_offset = 2 * self.gather_bytes
-        nbytes = self.flags_offset + 2 * world * 4
+        nbytes = tb_split_buffer_bytes(world)                # ... then the device step counter
         self.own_ptr, handle = ctx.peer_buffer_create(nbytes)
         handles = [None] * world
         if world > 1:
@@ -82,6 +87,7 @@ class PeerExchange:
         else:
             handles[0] = handle
         self.ptrs = [self.own_ptr if r == rank else ctx.peer_buffer_open(handles[r]) for r in range(world)]
+        self.pointer_array = ctx.pointer_array(self.ptrs)     # argument of tatara_attn_decode_split
         self.epoch = 0
 
     def step(self, push, combine_wait):
@@ -93,7 +99,18 @@ class PeerExchange:
         push(gathers, flags, self.epoch)
         combine_wait(gathers[self.rank], flags[self.rank], self.epoch)
 
-    def close(self):
+    def close(self, dist=None, sync=None):
+        """Releases the mappings in three phases: (1) after `sync()` has drained this rank's stream (no
+        kernel of this rank still stores into a peer's buffer) every rank closes the mappings it
+        imported; (2) all ranks meet at a barrier; (3) each rank frees the buffer it exported.
+        Freeing an exported buffer while another process still has it mapped is undefined."""
+        if sync is not None:
+            sync()
         for r, p in enumerate(self.ptrs):
-            self.ctx.peer_buffer_close(p, owned=(r == self.rank))
+            if r != self.rank:
+                self.ctx.peer_buffer_close(p, owned=False)
+        if dist is not None and self.world > 1:
+            dist.barrier()
+        if self.ptrs:
+            self.ctx.peer_buffer_close(self.ptrs[self.rank], owned=True)
         self.ptrs = []

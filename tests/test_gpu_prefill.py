@@ -35,7 +35,12 @@ def run_prefill(ctx, q, gate, keys, values, base, rows, cap, pad_rows=3):
 
 @pytest.mark.parametrize("base,rows", [(0, 1), (0, 64), (0, 128), (0, 129), (0, 200), (300, 77), (64, 256),
                                        (1000, 130), (5, 513),
-                                       (2047, 16), (777, 5)])   # the 16-row verify band of speculative decoding
+                                       (2047, 16), (777, 5),    # the 16-row verify band of speculative decoding
+                                       # the reference's own chunk shapes: a first chunk of 256 rows at position 0, then
+                                       # chunks of at most 2048 rows at a large context_base (14336 = 256 + 6*2048 + 1792:
+                                       # the last full chunk of a 16384-token prompt;
+                                       # include/tatara/runtime/prefill_geometry.h:13-15, tools/native/tatara_serve.cpp:485-497)
+                                       (0, 256), (256, 2048), (14336, 2048)])
 def test_prefill_matches_oracle(ctx, base, rows):
     rng = np.random.default_rng(base * 7 + rows)
     cap = base + rows + 5
@@ -46,7 +51,8 @@ def test_prefill_matches_oracle(ctx, base, rows):
     values[:, base + rows:] = 0x7F80
     q, gate = syn.attn_query(rng, np.arange(base, base + rows))
     got = run_prefill(ctx, q, gate, keys, values, base, rows, cap)
-    pick = sorted(set(int(r) for r in [0, min(1, rows - 1), rows // 2, rows - 1] + list(rng.integers(0, rows, size=12))))
+    pick = sorted(set(int(r) for r in [0, min(1, rows - 1), rows // 2, rows - 1] + [r for r in (127, 128, 255, 256, 1023, 1024) if r < rows] +
+                                   list(rng.integers(0, rows, size=12))))
     want = oracle.attn_prefill(q, gate, keys, values, base, cap, row_list=pick, threads=8)
     for r in pick:
         assert_close_bf16(got[r], want[r], f"prefill base={base} rows={rows} row {r}")

@@ -50,6 +50,50 @@ def test_push_and_wait_merge_two_emulated_ranks():
     ctx.close()
 
 
+def test_single_submission_step_counts_on_the_device_and_replays_as_a_graph():
+    """tatara_attn_decode_split with a world of one rank (a second rank cannot run beside it on one
+    GPU: its waiting kernel would wait for a kernel queued behind it): the whole step is one call, the
+    step counter and the parity live on the device, so five eager steps and three replays of a captured
+    step all give the unsplit decode's result and leave the counter at eight."""
+    ctx = tb.Context(0)
+    rng = np.random.default_rng(82)
+    n = 5000
+    keys, values = syn.attn_cache(rng, n, n)
+    q, gate = syn.attn_query(rng, np.array([n - 1]))
+    dq, dg, dk, dv = dev_bf16(q[0]), dev_bf16(gate[0]), dev_bf16(keys), dev_bf16(values)
+    want = oracle.attn_decode(q[0], gate[0], keys, values, n - 1, n, threads=8)
+    nbytes = tb.split_buffer_bytes(1)
+    buf, _ = ctx.peer_buffer_create(nbytes)
+    peers = tb.Context.pointer_array([buf])
+    scratch = torch.empty(tb.decode_scratch_bytes(n) // 4, dtype=torch.float32, device="cuda")
+    out = torch.zeros((16, 256), dtype=torch.bfloat16, device="cuda")
+    solo = torch.zeros_like(out)
+    ctx.attn_decode(dq, dg, dk, dv, n - 1, n, solo, scratch)
+    for step in range(5):
+        out.zero_()
+        ctx.attn_decode_split(dq, dg, dk, dv, 0, n, n, peers, 0, out, scratch)
+        ctx.sync()
+        assert_close_bf16(host_u16(out), want, f"single-submission step {step}")
+        assert_close_bf16(host_u16(out), host_u16(solo), f"single-submission step {step} vs unsplit")
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            ctx.attn_decode_split(dq, dg, dk, dv, 0, n, n, peers, 0, out, scratch, stream=stream.cuda_stream)
+    for replay in range(3):
+        out.zero_()
+        graph.replay()
+        ctx.sync()
+        assert_close_bf16(host_u16(out), want, f"replayed step {replay}")
+    words = torch.zeros(nbytes // 4, dtype=torch.int32, device="cuda")
+    ctx.state_copy(tb.Context.copy_segments([(buf, words.data_ptr(), nbytes)]))
+    ctx.sync()
+    step_word = (2 * 16 * 258 * 4 + 2 * 4) // 4
+    assert int(words[step_word]) == 8, "the device step counter counts every step, eager or replayed"
+    ctx.peer_buffer_close(buf, owned=True)
+    ctx.close()
+
+
 def test_wait_runs_out_and_reports_timeout():
     ctx = tb.Context(0)
     world = 2

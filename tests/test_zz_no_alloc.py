@@ -4,13 +4,15 @@ tatara_attn_decode_static serves callers that cannot allocate device memory (a s
 with a frozen memory plan, a plug-in that may not touch its host's allocator): its record
 scratch is an array inside the library instead of a caller buffer.  The test calls it through
 the C ABI twice in a row -- the second call starts from the first call's leftover records --
-and requires the output of tatara_attn_decode on the same inputs each time.  It runs last so a
-stop-at-first-failure run has already covered every other test.
+and requires the bits of tatara_attn_decode on the same inputs each time, and the CPU oracle's
+result within the repository's tolerance.  It runs last so a stop-at-first-failure run has
+already covered every other test.
 """
 import numpy as np
 import pytest
 import torch
 
+import oracle
 import tatara_b200 as tb
 from gpu_util import assert_close_bf16, host_u16
 
@@ -38,12 +40,15 @@ def test_static_scratch_decode_matches_caller_scratch_decode_twice():
             assert torch.cuda.mem_get_info()[0] == free_before
         assert_close_bf16(host_u16(got), host_u16(want), f"static decode call {call}")
         assert torch.equal(got, want), f"call {call}: same kernels, same partitions, so the same bits"
+        cpu = oracle.attn_decode(host_u16(q), host_u16(gate), host_u16(keys), host_u16(values), context, cap,
+                                 threads=oracle.hardware_threads())
+        assert_close_bf16(host_u16(got), cpu, f"static decode call {call} vs the CPU oracle")
     # beyond the built-in maximum the call refuses, clearly, and enqueues nothing
     big = torch.zeros((2, 8, 256), dtype=torch.bfloat16, device="cuda")
     launches = ctx.launches
     with pytest.raises(tb.TataraError) as e:
-        ctx.attn_decode_static(q, gate, big, big, 70000, 70001, got)
+        ctx.attn_decode_static(q, gate, big, big, 262144, 262145, got)
     assert e.value.status == tb.STATUS_NAMES.index("ScratchTooSmall")
-    assert "65536" in str(e.value)
+    assert "262144" in str(e.value)
     assert ctx.launches == launches
     ctx.close()
