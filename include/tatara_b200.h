@@ -216,17 +216,21 @@ tatara_status tatara_attn_combine_wait(tatara_ctx* ctx, void* stream, const void
                                        const void* flags, uint32_t world, uint32_t epoch,
                                        uint32_t wait_limit_us, const void* gate, void* out);
 
-/* One split-KV decode step of this rank as ONE submission: the local partitions of keys
- * [key_begin, key_end) of this rank's cache slice are merged to one record per head, stored into slot
- * `rank` of every rank's peer buffer and announced by a flag (as tatara_attn_decode_partial_push);
- * a dependent kernel then waits (bounded by wait_limit_us, as tatara_attn_combine_wait) for the
- * flags of all ranks and merges the `world` records in rank order with the reference's combine
- * (src/backend/metal/kernels/attention.metal:1086-1108) into `out` on every rank.
+/* One split-KV decode step of this rank as ONE submission of the same two kernels as
+ * tatara_attn_decode: the partitions of keys [key_begin, key_end) of this rank's cache slice, then
+ * one merge kernel that (a) merges this rank's partitions to one record per head, (b) stores it into
+ * slot `rank` of every rank's peer buffer (plain 8-byte peer stores over NVLink, each word carrying
+ * {value, step number}, so no fence, flag or collective follows), (c) waits, bounded by
+ * wait_limit_us (<= 2 000 000; on expiry nothing is written and tatara_ctx_sync returns
+ * TATARA_DEVICE_WAIT_TIMEOUT), until the words of all `world` ranks carry this step's number and
+ * (d) merges the world's records in rank order with the reference's combine
+ * (src/backend/metal/kernels/attention.metal:1086-1108), gates and stores `out` on every rank --
+ * the bits tatara_attn_combine gives on the gathered records.
  * peer_buffers: `world` device pointers, entry r = rank r's buffer of tatara_split_buffer_bytes(world)
- * bytes (tatara_peer_buffer_create / _open), laid out as [2 parities][world][16][258] f32 records |
- * [2 parities][world] u32 flags | u32 step counter.  The step counter lives on the device and is
- * advanced by the step itself, so no argument changes from token to token: the call may be captured
- * in a CUDA graph and replayed.  Every rank must issue the same sequence of steps. */
+ * zero-initialised bytes (tatara_peer_buffer_create / _open).  The step number lives on the device
+ * and is advanced by the step itself, so no argument changes from token to token: the call may be
+ * captured in a CUDA graph and replayed.  Every rank must issue the same sequence of steps, each
+ * rank's kernels running at the same time as the others' (one process per GPU). */
 uint64_t tatara_split_buffer_bytes(uint32_t world);
 tatara_status tatara_attn_decode_split(tatara_ctx* ctx, void* stream, const void* q, const void* gate,
                                        const void* keys, const void* values, uint32_t key_begin,

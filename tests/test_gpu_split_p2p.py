@@ -88,9 +88,34 @@ def test_single_submission_step_counts_on_the_device_and_replays_as_a_graph():
     words = torch.zeros(nbytes // 4, dtype=torch.int32, device="cuda")
     ctx.state_copy(tb.Context.copy_segments([(buf, words.data_ptr(), nbytes)]))
     ctx.sync()
-    step_word = (2 * 16 * 258 * 4 + 2 * 4) // 4
+    step_word = (nbytes - 16) // 4
     assert int(words[step_word]) == 8, "the device step counter counts every step, eager or replayed"
     ctx.peer_buffer_close(buf, owned=True)
+    ctx.close()
+
+
+def test_single_submission_step_gives_up_when_a_rank_never_stores():
+    """A world of two whose second rank never runs: the merge kernel's bounded wait (0.2 s) runs out,
+    nothing is written, the status is DeviceWaitTimeout and the context stays usable."""
+    ctx = tb.Context(0)
+    n = 2000
+    g = torch.Generator(device="cuda").manual_seed(83)
+    kv = torch.randn((2, n, 256), generator=g, device="cuda").to(torch.bfloat16)
+    q = torch.randn((16, 256), generator=g, device="cuda").to(torch.bfloat16)
+    bufs = [ctx.peer_buffer_create(tb.split_buffer_bytes(2))[0] for _ in range(2)]
+    scratch = torch.empty(tb.decode_scratch_bytes(n) // 4, dtype=torch.float32, device="cuda")
+    out = torch.full((16, 256), 4.0, dtype=torch.bfloat16, device="cuda")
+    ctx.attn_decode_split(q, q, kv, kv, 0, n // 2, n, tb.Context.pointer_array(bufs), 0, out, scratch, wait_limit_us=200000)
+    with pytest.raises(tb.TataraError) as e:
+        ctx.sync()
+    assert e.value.status == tb.STATUS_NAMES.index("DeviceWaitTimeout")
+    assert torch.all(out == 4.0), "a step that gave up must not write its output"
+    ctx.sync()
+    solo = torch.zeros_like(out)
+    ctx.attn_decode(q, q, kv, kv, n - 1, n, solo, scratch)
+    ctx.sync()
+    for b in bufs:
+        ctx.peer_buffer_close(b, owned=True)
     ctx.close()
 
 
