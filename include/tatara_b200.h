@@ -92,7 +92,11 @@ uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx);
 typedef enum tatara_policy {
     /* Rows of K and of V of each decode CTA's first partition that are requested into L2 before the
      * kernel waits for its predecessor in the stream (0 switches the requests off). */
-    TATARA_POLICY_DECODE_L2_PREFETCH_KEYS = 0
+    TATARA_POLICY_DECODE_L2_PREFETCH_KEYS = 0,
+    /* Which implementation evaluates tatara_gdn_prefill with chunk 64: 0 = the tensor-memory form
+     * (tcgen05 MMAs fed by TMA, the state as an f32 accumulator in tensor memory), 1 = the
+     * register-resident mma.sync form.  Same algebra, same tolerance against the sequential scan. */
+    TATARA_POLICY_GDN_CHUNK_FORM = 1
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

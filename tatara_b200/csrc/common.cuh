@@ -40,6 +40,7 @@ struct tatara_ctx {
     void* lane_schedule = nullptr;     // device scratch of the calls whose lane tables live in device memory
     uint64_t launches = 0;
     uint32_t decode_l2_prefetch_keys = tb::kDecodeL2PrefetchKeys;   // TATARA_POLICY_DECODE_L2_PREFETCH_KEYS
+    uint32_t gdn_chunk_form = 0;                                     // TATARA_POLICY_GDN_CHUNK_FORM
     char error[256] = {0};
 };
 

@@ -449,7 +449,7 @@ uint64_t gdn_chunked_scratch_bytes(uint32_t rows) {
     return nchunks * kGdnValueHeads * kChunkScratch;
 }
 
-tatara_status launch_gdn_chunked(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
+static tatara_status launch_gdn_chunked_regs(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
                                  const __nv_bfloat16* value, const float* decay, const float* beta,
                                  const float* state_in, __nv_bfloat16* y, float* state_out, uint32_t rows,
                                  void* scratch, uint64_t scratch_bytes) {
@@ -474,6 +474,27 @@ tatara_status launch_gdn_chunked(tatara_ctx* ctx, cudaStream_t stream, const __n
     return check_launch(ctx, "gdn_prefill(scan)");
 }
 
+uint64_t gdn_tc_scratch_bytes(uint32_t rows);
+tatara_status launch_gdn_chunked_tc(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
+                                    const __nv_bfloat16* value, const float* decay, const float* beta,
+                                    const float* state_in, __nv_bfloat16* y, float* state_out, uint32_t rows,
+                                    void* scratch, uint64_t scratch_bytes);
+
+// The chunked form has two implementations of the same algebra, chosen by TATARA_POLICY_GDN_CHUNK_FORM:
+// 0 (default) the tensor-memory form of gdn_chunked_tc.cu, 1 the register-resident mma.sync form above.
+tatara_status launch_gdn_chunked(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
+                                 const __nv_bfloat16* value, const float* decay, const float* beta,
+                                 const float* state_in, __nv_bfloat16* y, float* state_out, uint32_t rows,
+                                 void* scratch, uint64_t scratch_bytes) {
+    if (ctx->gdn_chunk_form == 1u)
+        return launch_gdn_chunked_regs(ctx, stream, qk, value, decay, beta, state_in, y, state_out, rows, scratch, scratch_bytes);
+    return launch_gdn_chunked_tc(ctx, stream, qk, value, decay, beta, state_in, y, state_out, rows, scratch, scratch_bytes);
+}
+
 } // namespace tb
 
-extern "C" uint64_t tatara_gdn_prefill_scratch_bytes(uint32_t rows) { return tb::gdn_chunked_scratch_bytes(rows); }
+// Enough for either form of the chunked evaluation.
+extern "C" uint64_t tatara_gdn_prefill_scratch_bytes(uint32_t rows) {
+    const uint64_t a = tb::gdn_chunked_scratch_bytes(rows), b = tb::gdn_tc_scratch_bytes(rows);
+    return a > b ? a : b;
+}

@@ -1,0 +1,733 @@
+// Chunk-64 evaluation of the Gated DeltaNet recurrence on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory, operands brought in by TMA).  The reference
+// evaluates the same recurrence one step at a time (prefill_gdn.metal:137-281; CPU model
+// tests/native/kernel_reference.cpp:498-563).
+//
+// Per v-head, state S [128 v][128 k], a chunk of C = 64 steps, G_r = sum_{i<=r} log(decay_i):
+//     A[r,i] = beta_r e^{G_r-G_i} (k_r.k_i) (i < r),      T = (I + A)^-1
+//     W = T diag(beta e^{G}) K,   U = T diag(beta) V,      P[r,i] = e^{G_r-G_i} (q_r.k_i) (i <= r)
+//     Delta = U - W S0^T,   S_C = e^{G_C} S0 + Delta^T diag(s) K,   s_i = e^{G_C-G_i}
+//     O     = diag(e^{G}) Q S0^T + P Delta
+// Written as a TRANSITION per chunk, everything that does not involve the state moves out of the
+// serial part:
+//     S_C = e^{G_C} S0 + Us^T K - S0 M',        M' = (diag(s) W)^T K            [128 k' x 128 k]
+//     O^T = O0^T + S0 Q~^T,                     Q~ = diag(e^{G}) Q - P W,  O0 = P U
+// Two kernels:
+//   gdn_tc_prepare_kernel -- no state.  Persistent CTAs of 256 threads (two per SM) walk the (chunk,
+//     v-head) units: six small MMA groups ([K;Q] K^T, K^T T_W^T, V^T T_U^T, Ws^T K, W^T P^T, U^T P^T)
+//     with the f32 inverse of the unit lower-triangular (I + A) between the first and the second
+//     (forward substitution in panels of 16 rows, one column of T per thread pair: no bf16 enters the
+//     solve).  -M', Us^T, Q~^T, O0^T leave as bf16 images of the 128-byte-swizzled shared-memory tiles
+//     the scan wants (bulk copies out of shared memory: one coalesced stream per tile).
+//   gdn_tc_scan_kernel -- one CTA per v-head walks the chunks.  The state is the f32 accumulator of
+//     the transition MMAs in tensor memory; between two chunks four warps read it (tcgen05.ld),
+//     scale it by e^{G_C} in f32 in place (tcgen05.st) and store its bf16 copy beside it in tensor
+//     memory, from where the MMAs take it as their A operand.  The dependent chain of a chunk is that
+//     round trip plus twelve MMAs; the output MMAs, the epilogue and the operand ring run beside it.
+// Every mbarrier wait is bounded; on expiry the CTA latches DeviceWaitTimeout, frees its tensor
+// memory and returns.
+#include "tc05.cuh"
+
+namespace tb {
+
+constexpr uint32_t kTcChunk = 64;
+constexpr uint32_t kUnitM = 128u * 128u * 2u;   // -M'   [128 k'][128 k] bf16
+constexpr uint32_t kUnitU = 128u * 64u * 2u;    // Us^T  [128 v][64 i]  bf16
+constexpr uint32_t kUnitQ = 128u * 64u * 2u;    // Q~^T  [128 k'][64 r] bf16
+constexpr uint32_t kUnitO = 128u * 64u * 2u;    // O0^T  [128 v][64 r]  bf16
+
+struct TcPlanes {
+    uint8_t* m;
+    uint8_t* u;
+    uint8_t* q;
+    uint8_t* o;
+    float* gamma;     // e^{G_C} per unit
+};
+
+__host__ __device__ inline uint64_t tc_units(uint32_t rows) {
+    return uint64_t((rows + kTcChunk - 1u) / kTcChunk) * kGdnValueHeads;
+}
+uint64_t gdn_tc_scratch_bytes(uint32_t rows) {
+    const uint64_t units = tc_units(rows);
+    return units * (kUnitM + kUnitU + kUnitQ + kUnitO) + ((units * 4u + 127u) & ~uint64_t(127));
+}
+
+// kind::f16 instruction descriptor with both majors selectable (bit 15: A is MN-major, bit 16: B).
+__host__ __device__ constexpr uint32_t instr_desc2(uint32_t m, uint32_t n, bool a_mn, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// Byte offset of the 16-byte chunk `chunk` of row `row` in a 128-byte-swizzled tile of 128-byte rows.
+__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) {
+    return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---- kernel 1: per (chunk, v-head) ---------------------------------------------------------
+// 256 threads: thread (row, half) = tensor-memory lane `row` (warp & 3 selects the lane quarter) and
+// one half of the columns of whatever tile is being read (warps 0..3 the first half, 4..7 the second).
+// A CTA runs this code once, so loops over column blocks stay rolled (16 columns per pass): what
+// matters is the number of distinct instructions fetched, not the trip count.
+constexpr uint32_t kPrKQ = 0;            // [K;Q] : 2 dim-atoms x [128 rows x 128 B]; rows 0..63 K, 64..127 Q
+constexpr uint32_t kPrV = 32768;         // V : 2 v-atoms x [64 rows x 128 B]; later U^T [128 rows x 128 B]
+constexpr uint32_t kPrA = 49152;         // A f32 [64][64], 16-byte groups swizzled by row & 7; later W^T [128 rows x 128 B]
+constexpr uint32_t kPrWs = 65536;        // T columns (f32, swizzled) during the solve; later Ws^T [128 rows x 128 B]
+constexpr uint32_t kPrP = 81920;         // P [64 rows x 128 B]
+constexpr uint32_t kPrTW = 90112;        // T diag(beta e^G)  [64 rows x 128 B]
+constexpr uint32_t kPrTU = 98304;        // T diag(beta)      [64 rows x 128 B]
+constexpr uint32_t kPrVec = 106496;      // g_cum | beta | s | e^G  (4 x 64 f32)
+constexpr uint32_t kPrBar = 107520;
+constexpr uint32_t kPrSmem = kPrBar + 64;
+constexpr uint32_t kPrCols = 256;
+constexpr uint32_t kPrThreads = 256;
+// staging of the output planes (the images the scan copies back into shared memory), over dead tiles
+constexpr uint32_t kPrStU = kPrTW;       // Us^T, written while K, Q, P, W^T, Ws^T, U^T are live
+constexpr uint32_t kPrStM = kPrV;        // -M' : two tiles, 32 KiB   (final epilogue: everything but the Q rows is dead)
+constexpr uint32_t kPrStQ = kPrWs;       // Q~^T
+constexpr uint32_t kPrStO = kPrP;        // O0^T (runs over P, T_W)
+
+struct TcPrepareParams {
+    const float* decay;
+    const float* beta;
+    TcPlanes planes;
+    uint32_t* status;
+    uint32_t rows, n_units;
+};
+
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+// One contiguous block of shared memory -> global memory through the bulk-copy engine.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// 16 f32 -> two 16-byte groups of bf16 at chunks c and c + 1 of a swizzled 128-byte row
+__device__ __forceinline__ void store_bf16x16(uint8_t* tile, uint32_t row, uint32_t chunk, const float* v) {
+    *reinterpret_cast<uint4*>(tile + sw128(row, chunk)) =
+        make_uint4(pack_bf2(v[0], v[1]), pack_bf2(v[2], v[3]), pack_bf2(v[4], v[5]), pack_bf2(v[6], v[7]));
+    *reinterpret_cast<uint4*>(tile + sw128(row, chunk + 1u)) =
+        make_uint4(pack_bf2(v[8], v[9]), pack_bf2(v[10], v[11]), pack_bf2(v[12], v[13]), pack_bf2(v[14], v[15]));
+}
+// f32 tile of 64-float rows whose 16-byte groups are XORed with row & 7 (conflict-free row writes and column reads)
+__device__ __forceinline__ uint32_t swf(uint32_t row, uint32_t group) { return row * 256u + ((group ^ (row & 7u)) << 4); }
+
+__global__ void __launch_bounds__(kPrThreads, 2)
+gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_v,
+                      const TcPrepareParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t row = (warp & 3u) * 32u + lane, half = warp >> 2;
+    const uint32_t base = s2u(smem);
+    const uint32_t bar_load = base + kPrBar, bar_mma = base + kPrBar + 8;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kPrBar + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kPrBar + 24);
+    float* g_cum = reinterpret_cast<float*>(smem + kPrVec);
+    float* beta_s = g_cum + 64;
+    float* s_end = g_cum + 128;    // e^{G_C - G_r}
+    float* e_g = g_cum + 192;      // e^{G_r}
+    if (tid == 0) {
+        mbar_init(bar_load, 1);
+        mbar_init(bar_mma, 1);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kPrCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tlane = ((warp & 3u) * 32u) << 16;
+    bool ok = true;
+    uint32_t mma_phase = 0;     // completions of bar_mma so far (three per unit)
+
+    // Persistent CTAs: barriers and tensor memory are set up once, then the CTA walks its units.
+    for (uint32_t it = 0, unit32 = blockIdx.x; unit32 < p.n_units && ok; ++it, unit32 += gridDim.x) {
+    const uint32_t chunk = unit32 / kGdnValueHeads, head = unit32 % kGdnValueHeads, qkh = head >> 1;
+    const uint32_t row0 = chunk * kTcChunk;
+    const uint32_t live_rows = min(kTcChunk, p.rows - row0);
+    const uint64_t unit = unit32;
+    if (tid == 0) {
+        mbar_expect_tx(bar_load, 32768u + 16384u);
+        for (uint32_t a = 0; a < 2; ++a) {
+            tma_load_2d(base + kPrKQ + a * 16384u, &map_qk, bar_load, int(kGdnKOff + qkh * kGdnDim + a * 64u), int(row0));
+            tma_load_2d(base + kPrKQ + a * 16384u + 8192u, &map_qk, bar_load, int(qkh * kGdnDim + a * 64u), int(row0));
+            tma_load_2d(base + kPrV + a * 8192u, &map_v, bar_load, int(head * kGdnDim + a * 64u), int(row0));
+        }
+        // the tiles of this CTA's next unit are asked into L2 now: its loads start when this unit is done
+        const uint32_t next = unit32 + gridDim.x;
+        if (next < p.n_units) {
+            const uint32_t nh = next % kGdnValueHeads, nq = nh >> 1, nrow = (next / kGdnValueHeads) * kTcChunk;
+            for (uint32_t a = 0; a < 2; ++a) {
+                tma_prefetch_2d(&map_qk, int(kGdnKOff + nq * kGdnDim + a * 64u), int(nrow));
+                tma_prefetch_2d(&map_qk, int(nq * kGdnDim + a * 64u), int(nrow));
+                tma_prefetch_2d(&map_v, int(nh * kGdnDim + a * 64u), int(nrow));
+            }
+        }
+    }
+    if (warp == 1) {
+        // inclusive cumulative log-decay over the 64 steps (two per lane); rows past the block keep G flat
+        float g0 = 0.0f, g1 = 0.0f;
+        const uint32_t r0 = lane * 2u;
+        if (r0 < live_rows) g0 = fmaxf(logf(p.decay[uint64_t(row0 + r0) * kGdnValueHeads + head]), -100.0f);
+        if (r0 + 1u < live_rows) g1 = fmaxf(logf(p.decay[uint64_t(row0 + r0 + 1u) * kGdnValueHeads + head]), -100.0f);
+        float incl = g0 + g1;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= uint32_t(off)) incl += up;
+        }
+        const float g_end = __shfl_sync(0xffffffffu, incl, 31);
+        g_cum[r0] = incl - g1;
+        g_cum[r0 + 1u] = incl;
+        beta_s[r0] = r0 < live_rows ? p.beta[uint64_t(row0 + r0) * kGdnValueHeads + head] : 0.0f;
+        beta_s[r0 + 1u] = r0 + 1u < live_rows ? p.beta[uint64_t(row0 + r0 + 1u) * kGdnValueHeads + head] : 0.0f;
+        s_end[r0] = __expf(g_end - (incl - g1));
+        s_end[r0 + 1u] = __expf(g_end - incl);
+        e_g[r0] = __expf(incl - g1);
+        e_g[r0 + 1u] = __expf(incl);
+        if (lane == 0) p.planes.gamma[unit] = __expf(g_end);
+    }
+    ok = mbar_wait(bar_load, it & 1u, abort_flag);
+
+    // ---- MMA a: [K;Q] K^T -> rows 0..63 K K^T, rows 64..127 Q K^T (columns 0..63 of tensor memory)
+    if (tid == 0 && ok) {
+        tc_fence_after();
+        constexpr uint32_t idesc = instr_desc2(128, 64, false, false);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 8; ++ks) {
+            const uint32_t at = base + kPrKQ + (ks >> 2) * 16384u + (ks & 3u) * 32u;
+            tc_mma(tmem, smem_desc(at, 16, 1024), smem_desc(at, 16, 1024), idesc, ks ? 1u : 0u);
+        }
+        tc_commit(bar_mma);
+    }
+    if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
+    ++mma_phase;
+    __syncthreads();   // the decay vectors of warp 1 are visible
+    if (ok) {
+        tc_fence_after();
+        const uint32_t r = row & 63u;
+        const float gr = g_cum[r], br = row < 64u ? beta_s[r] : 1.0f;
+        const uint32_t bound = row < 64u ? r : r + 1u;      // A: columns i < r; P: i <= r
+#pragma unroll 1
+        for (uint32_t blk = 0; blk < 2; ++blk) {
+            const uint32_t c0 = half * 32u + blk * 16u;
+            float d[16];
+            tmem_ld16(tmem + tlane + c0, d);
+            tmem_wait_ld();
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) {
+                // (computed for every column and selected afterwards: rows of a warp have different bounds,
+                // and a branch per element diverges)
+                const float scaled = br * __expf(fminf(gr - g_cum[c0 + i], 0.0f)) * d[i];
+                d[i] = c0 + i < bound ? scaled : 0.0f;
+            }
+            if (row < 64u) {
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q)
+                    *reinterpret_cast<float4*>(smem + kPrA + swf(r, c0 / 4u + q)) = make_float4(d[4 * q], d[4 * q + 1], d[4 * q + 2], d[4 * q + 3]);
+            } else {
+                store_bf16x16(smem + kPrP, r, c0 / 8u, d);
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+
+    // ---- T = (I + A)^-1 in f32.  Column j of T belongs to the thread pair (2j, 2j + 1) and is built
+    // down the rows in panels of 16.  Finished panels of the column live in shared memory (row j of a
+    // swizzled f32 tile), the current panel in registers: first the contribution of the finished
+    // panels -- each thread of the pair accumulates 8 of the 16 rows, A read as broadcast float4 --
+    // then, after the pair has exchanged its sums, the 16 x 16 triangular solve inside the panel (both
+    // threads, redundantly).  No bf16 enters the solve.
+    if (ok && tid < 128u) {
+        const uint32_t j = tid >> 1, h = tid & 1u;
+        const uint8_t* amat = smem + kPrA;
+        uint8_t* tcol = smem + kPrWs;
+#pragma unroll 1
+        for (uint32_t b = 0; b < 4; ++b) {
+            float mine[8], acc[16];
+#pragma unroll
+            for (uint32_t rr = 0; rr < 8; ++rr) mine[rr] = 0.0f;
+#pragma unroll 1
+            for (uint32_t q = 0; q < 4u * b; ++q) {
+                const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
+#pragma unroll
+                for (uint32_t rr = 0; rr < 8; ++rr) {
+                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + h * 8u + rr, q));
+                    mine[rr] = fmaf(av.x, tv.x, fmaf(av.y, tv.y, fmaf(av.z, tv.z, fmaf(av.w, tv.w, mine[rr]))));
+                }
+            }
+#pragma unroll
+            for (uint32_t rr = 0; rr < 8; ++rr) {      // the partner's eight sums
+                const float theirs = __shfl_xor_sync(0xffffffffu, mine[rr], 1);
+                acc[rr] = h ? theirs : mine[rr];
+                acc[8 + rr] = h ? mine[rr] : theirs;
+            }
+            float t[16];
+#pragma unroll
+            for (uint32_t rr = 0; rr < 16; ++rr) {
+                float s0 = acc[rr], s1 = 0.0f;
+#pragma unroll
+                for (uint32_t q4 = 0; q4 < rr; q4 += 4) {
+                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + rr, 4u * b + q4 / 4u));   // zero at and above the diagonal
+                    s0 = fmaf(av.x, t[q4], s0);
+                    if (q4 + 1 < rr) s1 = fmaf(av.y, t[q4 + 1], s1);
+                    if (q4 + 2 < rr) s0 = fmaf(av.z, t[q4 + 2], s0);
+                    if (q4 + 3 < rr) s1 = fmaf(av.w, t[q4 + 3], s1);
+                }
+                t[rr] = (16u * b + rr == j ? 1.0f : 0.0f) - (s0 + s1);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 2; ++q) {
+                const uint32_t g4 = h * 2u + q;
+                *reinterpret_cast<float4*>(tcol + swf(j, 4u * b + g4)) =
+                    h ? make_float4(t[8 + 4 * q], t[9 + 4 * q], t[10 + 4 * q], t[11 + 4 * q])
+                      : make_float4(t[4 * q], t[4 * q + 1], t[4 * q + 2], t[4 * q + 3]);
+            }
+            __syncwarp();
+        }
+        // column j of T scaled by this column's factors -> the K-major B tiles T_W and T_U (row r, element j)
+        const float bj = beta_s[j], wj = bj * e_g[j];
+        const uint32_t col = (j & 7u) * 2u, chunk16 = j >> 3;
+#pragma unroll 1
+        for (uint32_t q = h * 8u; q < h * 8u + 8u; ++q) {
+            const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
+            const float te[4] = {tv.x, tv.y, tv.z, tv.w};
+#pragma unroll
+            for (uint32_t e = 0; e < 4; ++e) {
+                const uint32_t at = sw128(4u * q + e, chunk16) + col;
+                *reinterpret_cast<__nv_bfloat16*>(smem + kPrTW + at) = f2bf(te[e] * wj);
+                *reinterpret_cast<__nv_bfloat16*>(smem + kPrTU + at) = f2bf(te[e] * bj);
+            }
+        }
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    // ---- MMA b: W^T = K^T T_W^T (columns 64..127), MMA c: U^T = V^T T_U^T (columns 128..191)
+    if (tid == 0 && ok) {
+        tc_fence_after();
+        constexpr uint32_t idesc = instr_desc2(128, 64, true, false);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks)
+            tc_mma(tmem + 64u, smem_desc(base + kPrKQ + ks * 2048u, 16384, 1024), smem_desc(base + kPrTW + ks * 32u, 16, 1024),
+                   idesc, ks ? 1u : 0u);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks)
+            tc_mma(tmem + 128u, smem_desc(base + kPrV + ks * 2048u, 8192, 1024), smem_desc(base + kPrTU + ks * 32u, 16, 1024),
+                   idesc, ks ? 1u : 0u);
+        tc_commit(bar_mma);
+    }
+    if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
+    ++mma_phase;
+    if (ok) {
+        tc_fence_after();
+        // passes 0, 1: W^T (columns 64..127) -> W^T and Ws^T tiles; passes 2, 3: U^T (128..191) -> U^T tile
+        // (over V) and the Us^T plane image (over T_W, T_U).  This thread's columns: half*32 .. +31.
+#pragma unroll 1
+        for (uint32_t blk = 0; blk < 4; ++blk) {
+            const uint32_t c0 = half * 32u + (blk & 1u) * 16u;
+            const bool is_u = blk >= 2u;
+            float w[16], ws[16];
+            tmem_ld16(tmem + tlane + (is_u ? 128u : 64u) + c0, w);
+            tmem_wait_ld();
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) ws[i] = w[i] * s_end[c0 + i];
+            store_bf16x16(smem + (is_u ? kPrV : kPrA), row, c0 / 8u, w);
+            store_bf16x16(smem + (is_u ? kPrStU : kPrWs), row, c0 / 8u, ws);
+        }
+        tc_fence_before();
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    // ---- MMA d: M' = Ws^T K (columns 0..127), e: X = W^T P^T (128..191), f: O0^T = U^T P^T (192..255)
+    if (tid == 0 && ok) {
+        bulk_store(p.planes.u + unit * kUnitU, base + kPrStU, kUnitU);
+        bulk_store_commit();
+        tc_fence_after();
+        constexpr uint32_t idesc_m = instr_desc2(128, 128, false, true);
+        constexpr uint32_t idesc_p = instr_desc2(128, 64, false, false);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks)
+            tc_mma(tmem, smem_desc(base + kPrWs + ks * 32u, 16, 1024), smem_desc(base + kPrKQ + ks * 2048u, 16384, 1024),
+                   idesc_m, ks ? 1u : 0u);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks)
+            tc_mma(tmem + 128u, smem_desc(base + kPrA + ks * 32u, 16, 1024), smem_desc(base + kPrP + ks * 32u, 16, 1024),
+                   idesc_p, ks ? 1u : 0u);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks)
+            tc_mma(tmem + 192u, smem_desc(base + kPrV + ks * 32u, 16, 1024), smem_desc(base + kPrP + ks * 32u, 16, 1024),
+                   idesc_p, ks ? 1u : 0u);
+        bulk_store_wait_read();     // the Us^T image has left shared memory before anyone passes the barrier: its place takes the O0^T image
+        tc_commit(bar_mma);
+    }
+    if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
+    ++mma_phase;
+    if (ok) {
+        tc_fence_after();
+        // -M' (this thread: k-columns half*64 .. +63 = tile `half` of the image), then Q~^T and O0^T (columns half*32 .. +31)
+        const uint8_t* q_tile = smem + kPrKQ + (row >> 6) * 16384u;
+        const uint32_t qchunk = (row & 63u) >> 3, qcol = (row & 7u) * 2u;
+#pragma unroll 1
+        for (uint32_t blk = 0; blk < 8; ++blk) {
+            float v[16];
+            if (blk < 4u) {
+                tmem_ld16(tmem + tlane + half * 64u + blk * 16u, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) v[i] = -v[i];
+                store_bf16x16(smem + kPrStM + half * 16384u, row, blk * 2u, v);
+            } else {
+                const bool is_o = blk >= 6u;
+                const uint32_t c0 = half * 32u + (blk & 1u) * 16u;
+                tmem_ld16(tmem + tlane + (is_o ? 192u : 128u) + c0, v);
+                tmem_wait_ld();
+                if (!is_o) {
+                    // Q~^T row k' = row: e^{G_r} q_r[k'] - X[k'][r]; the Q rows sit at rows 64.. of the [K;Q] tile
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t r = c0 + i;
+                        const float q = bf2f(*reinterpret_cast<const __nv_bfloat16*>(q_tile + sw128(64u + r, qchunk) + qcol));
+                        v[i] = e_g[r] * q - v[i];
+                    }
+                }
+                store_bf16x16(smem + (is_o ? kPrStO : kPrStQ), row, c0 / 8u, v);
+            }
+        }
+        tc_fence_before();
+    }
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0 && ok) {
+        bulk_store(p.planes.m + unit * kUnitM, base + kPrStM, kUnitM);
+        bulk_store(p.planes.q + unit * kUnitQ, base + kPrStQ, kUnitQ);
+        bulk_store(p.planes.o + unit * kUnitO, base + kPrStO, kUnitO);
+        bulk_store_commit();
+        bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
+    }
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;   // ... before the next unit's loads land on them; leave the loop together
+    }   // units
+    if (*abort_flag) {
+        if (tid == 0) {
+            atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000);   // let copies still in flight land before the shared memory is released
+    }
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPrCols) : "memory");
+    }
+}
+
+// ---- kernel 2: serial over chunks, one CTA per v-head ------------------------------------------
+// Shared memory: a ring of three stages for the operands of the state transition (-M' 32 KiB, Us^T
+// 16 KiB, K 16 KiB: released as soon as the two state MMA groups of a chunk have completed) and a
+// ring of two for Q~^T (released after the output MMAs).  Tensor memory (512 columns): the state S
+// (f32, 128 columns), two buffers of its bf16 copy (64 columns each: two bf16 per 32-bit column, the A
+// operand of the MMAs is read from tensor memory), two output accumulators (64 columns each).
+constexpr uint32_t kScRingA = 3, kScRingB = 2;
+constexpr uint32_t kScStageM = 0, kScStageU = 32768, kScStageK = 49152, kScStageA = 65536;
+constexpr uint32_t kScOffB = kScRingA * kScStageA, kScStageB = 16384;
+constexpr uint32_t kScBar = kScOffB + kScRingB * kScStageB;
+constexpr uint32_t kScSmem = kScBar + 256;
+static_assert(kScSmem <= 232448, "shared memory budget");
+constexpr uint32_t kScThreads = 320;                 // TMA warp, MMA warp, 4 state warps, 4 output warps
+constexpr uint32_t kScCols = 512, kScColS = 0, kScColA = 128, kScColO = 256;
+enum : uint32_t { kSbFullA = 0, kSbEmptyA = 3, kSbFullB = 6, kSbEmptyB = 8, kSbConv = 10, kSbState = 11, kSbOut = 12,
+                  kSbOutFree = 14, kSbCount = 16 };
+
+struct TcScanParams {
+    const float* state_in;
+    float* state_out;
+    __nv_bfloat16* y;
+    TcPlanes planes;
+    uint32_t* status;
+    uint32_t rows, nchunks;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// D (tensor memory) (+)= A (tensor memory, bf16 pairs per column) x B (shared memory descriptor)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+        : "memory");
+}
+constexpr uint32_t kScAhead = 4;   // chunks whose plane images are asked into L2 ahead of the shared-memory ring
+
+__global__ void __launch_bounds__(kScThreads, 1)
+gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t base = s2u(smem);
+    const uint32_t bars = base + kScBar;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kScBar + 8 * kSbCount);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kScBar + 8 * kSbCount + 8);
+    auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
+    const uint32_t head = blockIdx.x, qkh = head >> 1;
+    const uint32_t nchunks = p.nchunks;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kScRingA; ++s) {
+            mbar_init(bar(kSbFullA + s), 1);
+            mbar_init(bar(kSbEmptyA + s), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(bar(kSbFullB + s), 1);
+            mbar_init(bar(kSbEmptyB + s), 1);
+            mbar_init(bar(kSbOut + s), 1);
+            mbar_init(bar(kSbOutFree + s), 128);
+        }
+        mbar_init(bar(kSbConv), 128);
+        mbar_init(bar(kSbState), 1);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kScCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            auto prefetch = [&](uint32_t c) {
+                const uint64_t unit = uint64_t(c) * kGdnValueHeads + head;
+                bulk_prefetch_l2(p.planes.m + unit * kUnitM, kUnitM);
+                bulk_prefetch_l2(p.planes.u + unit * kUnitU, kUnitU);
+                bulk_prefetch_l2(p.planes.q + unit * kUnitQ, kUnitQ);
+                bulk_prefetch_l2(p.planes.o + unit * kUnitO, kUnitO);
+            };
+            for (uint32_t c = 0; c < min(kScAhead, nchunks); ++c) prefetch(c);
+            for (uint32_t c = 0; c < nchunks; ++c) {
+                const uint32_t sa = c % kScRingA, ua = c / kScRingA, sb = c & 1u;
+                const uint32_t st = base + sa * kScStageA;
+                const uint64_t unit = uint64_t(c) * kGdnValueHeads + head;
+                if (c + kScAhead < nchunks) prefetch(c + kScAhead);
+                if (ua > 0u && !mbar_wait(bar(kSbEmptyA + sa), (ua - 1u) & 1u, abort_flag)) break;
+                mbar_expect_tx(bar(kSbFullA + sa), kScStageA);
+                bulk_load(st + kScStageM, p.planes.m + unit * kUnitM, kUnitM, bar(kSbFullA + sa));
+                bulk_load(st + kScStageU, p.planes.u + unit * kUnitU, kUnitU, bar(kSbFullA + sa));
+                tma_load_2d(st + kScStageK, &map_qk, bar(kSbFullA + sa), int(kGdnKOff + qkh * kGdnDim), int(c * kTcChunk));
+                tma_load_2d(st + kScStageK + 8192u, &map_qk, bar(kSbFullA + sa), int(kGdnKOff + qkh * kGdnDim + 64u), int(c * kTcChunk));
+                if (c >= 2u && !mbar_wait(bar(kSbEmptyB + sb), ((c >> 1) - 1u) & 1u, abort_flag)) break;
+                mbar_expect_tx(bar(kSbFullB + sb), kScStageB);
+                bulk_load(base + kScOffB + sb * kScStageB, p.planes.q + unit * kUnitQ, kUnitQ, bar(kSbFullB + sb));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc2(128, 128, false, true);
+            constexpr uint32_t idesc_o = instr_desc2(128, 64, false, true);
+            for (uint32_t c = 0; c < nchunks; ++c) {
+                const uint32_t sa = c % kScRingA, ua = c / kScRingA, s = c & 1u;
+                const uint32_t st = base + sa * kScStageA, a_s0 = tmem + kScColA + s * 64u;
+                if (!mbar_wait(bar(kSbFullA + sa), ua & 1u, abort_flag)) break;
+                if (!mbar_wait(bar(kSbConv), c & 1u, abort_flag)) break;   // e^{G_C} S0 and the bf16 copy of S0 are in tensor memory
+                tc_fence_after();
+                // S += Us^T K
+#pragma unroll
+                for (uint32_t ks = 0; ks < 4; ++ks)
+                    tc_mma(tmem + kScColS, smem_desc(st + kScStageU + ks * 32u, 16, 1024),
+                           smem_desc(st + kScStageK + ks * 2048u, 8192, 1024), idesc_s, 1u);
+                // S += S0 (-M'): sixteen bf16 of the copy = eight columns per k-step
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ++ks)
+                    tc_mma_ts(tmem + kScColS, a_s0 + ks * 8u, smem_desc(st + kScStageM + ks * 2048u, 16384, 1024), idesc_s, 1u);
+                tc_commit(bar(kSbState));
+                tc_commit(bar(kSbEmptyA + sa));
+                // O^T = S0 Q~^T into the output buffer of this chunk's parity
+                if (!mbar_wait(bar(kSbFullB + s), (c >> 1) & 1u, abort_flag)) break;
+                if (c >= 2u && !mbar_wait(bar(kSbOutFree + s), ((c >> 1) - 1u) & 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t qb = base + kScOffB + s * kScStageB;
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ++ks)
+                    tc_mma_ts(tmem + kScColO + s * 64u, a_s0 + ks * 8u, smem_desc(qb + ks * 2048u, 16384, 1024), idesc_o, ks ? 1u : 0u);
+                tc_commit(bar(kSbOut + s));
+                tc_commit(bar(kSbEmptyB + s));
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- state warps: thread = v row = tensor-memory lane ----------------
+        const uint32_t quarter = warp & 3u, row = quarter * 32u + lane;
+        const uint32_t tlane = (quarter * 32u) << 16;
+        const float* in_row = p.state_in + (uint64_t(head) * kGdnDim + row) * kGdnDim;
+        float* out_row = p.state_out + (uint64_t(head) * kGdnDim + row) * kGdnDim;
+        bool ok = true;
+        for (uint32_t c = 0; c <= nchunks && ok; ++c) {
+            const float gamma = c < nchunks ? p.planes.gamma[uint64_t(c) * kGdnValueHeads + head] : 1.0f;
+            if (c > 0u) {
+                if (!mbar_wait(bar(kSbState), (c - 1u) & 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+            }
+            // the bf16 copy of chunk c goes to buffer c & 1, which the MMAs of chunk c - 2 have left
+            if (c >= 2u && c < nchunks && !mbar_wait(bar(kSbOut + (c & 1u)), ((c >> 1) - 1u) & 1u, abort_flag)) { ok = false; break; }
+            const uint32_t copy = tmem + tlane + kScColA + (c & 1u) * 64u;
+#pragma unroll
+            for (uint32_t blk = 0; blk < 4; ++blk) {
+                float v[32];
+                if (c == 0u) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(v + 4 * i) = *reinterpret_cast<const float4*>(in_row + blk * 32u + 4u * i);
+                } else {
+                    tmem_ld32(tmem + tlane + kScColS + blk * 32u, v);
+                    tmem_wait_ld();
+                }
+                if (c == nchunks) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(out_row + blk * 32u + 4u * i) = *reinterpret_cast<const float4*>(v + 4 * i);
+                    continue;
+                }
+                uint32_t packed[16];    // k' = blk*32 + 2i, + 2i + 1 in column blk*16 + i of the copy
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) packed[i] = pack_bf2(v[2 * i], v[2 * i + 1]);
+                tmem_st16(copy + blk * 16u, packed);
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) v[i] *= gamma;
+                tmem_st32(tmem + tlane + kScColS + blk * 32u, v);
+            }
+            if (c == nchunks) break;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kSbConv));
+        }
+    } else {
+        // ---------------- output warps: thread = v row ----------------
+        const uint32_t quarter = warp & 3u, row = quarter * 32u + lane;
+        const uint32_t tlane = (quarter * 32u) << 16;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t s = c & 1u;
+            const uint32_t live_rows = min(kTcChunk, p.rows - c * kTcChunk);
+            uint4 o0[8];
+            const uint8_t* o_img = p.planes.o + (uint64_t(c) * kGdnValueHeads + head) * kUnitO;   // the swizzled tile image
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) o0[i] = *reinterpret_cast<const uint4*>(o_img + sw128(row, i));
+            if (!mbar_wait(bar(kSbOut + s), (c >> 1) & 1u, abort_flag)) break;
+            tc_fence_after();
+            float v[64];
+            tmem_ld32(tmem + tlane + kScColO + s * 64u, v);
+            tmem_ld32(tmem + tlane + kScColO + s * 64u + 32u, v + 32);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(kSbOutFree + s));
+            __nv_bfloat16* y0 = p.y + uint64_t(c) * kTcChunk * kGdnV + head * kGdnDim + row;
+            const __nv_bfloat16* o0h = reinterpret_cast<const __nv_bfloat16*>(o0);
+#pragma unroll
+            for (uint32_t r = 0; r < 64; ++r)
+                if (r < live_rows) y0[uint64_t(r) * kGdnV] = f2bf(v[r] + bf2f(o0h[r]));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000);
+        __syncthreads();
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kScCols) : "memory");
+    }
+}
+
+// 2-D bf16 tensor map {cols, rows} with a {64, box_rows} box and the 128-byte swizzle.
+static bool make_map2(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+    EncodeTiled fn = encode_tiled_entry();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2ull};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+tatara_status launch_gdn_chunked_tc(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
+                                    const __nv_bfloat16* value, const float* decay, const float* beta,
+                                    const float* state_in, __nv_bfloat16* y, float* state_out, uint32_t rows,
+                                    void* scratch, uint64_t scratch_bytes) {
+    if (scratch == nullptr || !aligned(scratch, 128))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prefill: the chunked form needs 128-byte aligned scratch");
+    if (!aligned(qk, 16) || !aligned(value, 16) || !aligned(state_in, 16) || !aligned(state_out, 16))
+        return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prefill: buffers must be 16-byte aligned");
+    if (scratch_bytes < gdn_tc_scratch_bytes(rows))
+        return fail(ctx, TATARA_SCRATCH_TOO_SMALL, "gdn_prefill: scratch smaller than tatara_gdn_prefill_scratch_bytes(rows)");
+    const uint32_t nchunks = (rows + kTcChunk - 1u) / kTcChunk;
+    const uint64_t units = tc_units(rows);
+    TcPlanes planes{};
+    uint8_t* at = static_cast<uint8_t*>(scratch);
+    planes.m = at; at += units * kUnitM;
+    planes.u = at; at += units * kUnitU;
+    planes.q = at; at += units * kUnitQ;
+    planes.o = at; at += units * kUnitO;
+    planes.gamma = reinterpret_cast<float*>(at);
+    CUtensorMap map_qk, map_v;
+    if (!make_map2(&map_qk, qk, kGdnQk, rows, 64) || !make_map2(&map_v, value, kGdnV, rows, 64))
+        return fail(ctx, TATARA_CUDA_ERROR, "gdn_prefill: tensor map encoding failed");
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(gdn_tc_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_tc_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
+            return check_launch(ctx, "gdn_prefill: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    TcPrepareParams pp{decay, beta, planes, ctx->device_status, rows, uint32_t(units)};
+    const uint32_t prep_grid = units < 2u * uint32_t(ctx->sm_count) ? uint32_t(units) : 2u * uint32_t(ctx->sm_count);
+    gdn_tc_prepare_kernel<<<prep_grid, kPrThreads, kPrSmem, stream>>>(map_qk, map_v, pp);
+    tatara_status st = check_launch(ctx, "gdn_prefill(prepare)");
+    if (st != TATARA_OK) return st;
+    TcScanParams sp{state_in, state_out, y, planes, ctx->device_status, rows, nchunks};
+    gdn_tc_scan_kernel<<<kGdnValueHeads, kScThreads, kScSmem, stream>>>(map_qk, sp);
+    return check_launch(ctx, "gdn_prefill(scan)");
+}
+
+} // namespace tb

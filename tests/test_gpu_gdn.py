@@ -319,6 +319,37 @@ def test_chunked_prefill_slow_decay_and_split_blocks(ctx):
     assert e.value.status == tb.STATUS_NAMES.index("InvalidDispatchExtent")
 
 
+def test_chunked_prefill_both_forms_agree_with_the_oracle(ctx):
+    """The chunk-64 evaluation has two implementations behind one entry point (tensor-memory
+    transition form, the default, and the register-resident mma.sync form): both against the CPU
+    oracle's sequential scan on a block with a ragged tail, slowly forgetting heads and a non-zero
+    initial state, and against each other."""
+    rng = np.random.default_rng(404)
+    rows = 333
+    conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
+    conv, state = syn.gdn_state(rng)
+    proj = syn.gdn_projection(rng, rows)
+    oqk, ov, _, _ = oracle.gdn_prepare(proj, conv, conv_w)
+    od, ob = oracle.gdn_gates(proj, a_log, dt_bias)
+    od = np.ascontiguousarray(od ** 0.02)          # decay close to 1: the state matters across many chunks
+    oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
+    outs = []
+    try:
+        for form in (0, 1):
+            ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, form)
+            y = torch.zeros((rows, 4096), dtype=torch.bfloat16, device="cuda")
+            s = torch.zeros((32, 128, 128), dtype=torch.float32, device="cuda")
+            ctx.gdn_prefill(dev_bf16(oqk), dev_bf16(ov), dev_f32(od), dev_f32(ob), dev_f32(state), y, s, rows, chunk=64,
+                            scratch=chunk_scratch(rows))
+            ctx.sync()
+            assert_close_bf16(host_u16(y), oy, f"chunk form {form}")
+            state_close(host_f32(s), ostate, f"chunk form {form}")
+            outs.append(host_u16(y))
+    finally:
+        ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 0)
+    assert_close_bf16(outs[0], outs[1], "tensor-memory form vs register form")
+
+
 def test_chunked_prefill_config3_full_size(ctx):
     """Benchmark config 3: 16384 rows, chunk 64, initial state zero; per-token outputs and the
     final f32 state against the sequential oracle."""
