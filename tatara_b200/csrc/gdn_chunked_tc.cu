@@ -16,8 +16,8 @@
 //   gdn_tc_prepare_kernel -- no state.  Persistent CTAs of 256 threads (two per SM) walk the (chunk,
 //     v-head) units: six small MMA groups ([K;Q] K^T, K^T T_W^T, V^T T_U^T, Ws^T K, W^T P^T, U^T P^T)
 //     with the f32 inverse of the unit lower-triangular (I + A) between the first and the second
-//     (forward substitution in panels of 16 rows, one column of T per thread pair: no bf16 enters the
-//     solve).  -M', Us^T, Q~^T, O0^T leave as bf16 images of the 128-byte-swizzled shared-memory tiles
+//     (panels of 16 rows: the diagonal blocks by forward substitution, the rest as matrix-vector
+//     products, one column of T per thread quad: no bf16 enters the solve).  -M', Us^T, Q~^T, O0^T leave as bf16 images of the 128-byte-swizzled shared-memory tiles
 //     the scan wants (bulk copies out of shared memory: one coalesced stream per tile).
 //   gdn_tc_scan_kernel -- one CTA per v-head walks the chunks.  The state is the f32 accumulator of
 //     the transition MMAs in tensor memory; between two chunks four warps read it (tcgen05.ld),
@@ -251,64 +251,80 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
     }
     __syncthreads();
 
-    // ---- T = (I + A)^-1 in f32.  Column j of T belongs to the thread pair (2j, 2j + 1) and is built
-    // down the rows in panels of 16.  Finished panels of the column live in shared memory (row j of a
-    // swizzled f32 tile), the current panel in registers: first the contribution of the finished
-    // panels -- each thread of the pair accumulates 8 of the 16 rows, A read as broadcast float4 --
-    // then, after the pair has exchanged its sums, the 16 x 16 triangular solve inside the panel (both
-    // threads, redundantly).  No bf16 enters the solve.
-    if (ok && tid < 128u) {
-        const uint32_t j = tid >> 1, h = tid & 1u;
+    // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), in panels of 16 rows.
+    // (1) The four 16 x 16 diagonal blocks are inverted first, one column per thread (64 threads,
+    //     forward substitution): D_b = (I + A_bb)^-1.
+    // (2) Column j of T belongs to four threads, one in each pair of warps (thread = (j, h), h = warp / 2),
+    //     and is built panel by panel.  Finished panels of the column live in shared memory (row j of a
+    //     swizzled f32 tile).  For a panel each of the four threads accumulates the contribution of the
+    //     finished panels to FOUR of its 16 rows, the four share the 16 right-hand sides through shared
+    //     memory, and each multiplies its four rows of D_b into them: the solve inside a panel is a
+    //     matrix-vector product with no serial chain.  h is uniform in a warp, so every read of A and
+    //     of D_b is one broadcast; the columns of a warp's 32 threads are conflict-free by the swizzle.
+    float* dsm = reinterpret_cast<float*>(smem + kPrTU);            // D_b [4][16][16] f32 (T_U is written after the sweep)
+    float* rhs_s = reinterpret_cast<float*>(smem + kPrTU + 4096u);  // right-hand sides [16 rows of the panel][64 columns]
+    if (ok && tid < 64u) {
+        const uint32_t b = tid >> 4, c = tid & 15u;
+        float t[16];
+#pragma unroll
+        for (uint32_t rr = 0; rr < 16; ++rr) {
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+            for (uint32_t q4 = 0; q4 < rr; q4 += 4) {
+                const float4 av = *reinterpret_cast<const float4*>(smem + kPrA + swf(16u * b + rr, 4u * b + q4 / 4u));   // zero at and above the diagonal
+                s0 = fmaf(av.x, t[q4], s0);
+                if (q4 + 1 < rr) s1 = fmaf(av.y, t[q4 + 1], s1);
+                if (q4 + 2 < rr) s0 = fmaf(av.z, t[q4 + 2], s0);
+                if (q4 + 3 < rr) s1 = fmaf(av.w, t[q4 + 3], s1);
+            }
+            t[rr] = (rr == c ? 1.0f : 0.0f) - (s0 + s1);
+            dsm[(b * 16u + rr) * 16u + c] = t[rr];
+        }
+    }
+    __syncthreads();
+    {
+        const uint32_t j = tid & 63u, h = tid >> 6;
         const uint8_t* amat = smem + kPrA;
         uint8_t* tcol = smem + kPrWs;
 #pragma unroll 1
         for (uint32_t b = 0; b < 4; ++b) {
-            float mine[8], acc[16];
-#pragma unroll
-            for (uint32_t rr = 0; rr < 8; ++rr) mine[rr] = 0.0f;
+            float mine[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
             for (uint32_t q = 0; q < 4u * b; ++q) {
                 const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
 #pragma unroll
-                for (uint32_t rr = 0; rr < 8; ++rr) {
-                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + h * 8u + rr, q));
+                for (uint32_t rr = 0; rr < 4; ++rr) {
+                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + 4u * h + rr, q));
                     mine[rr] = fmaf(av.x, tv.x, fmaf(av.y, tv.y, fmaf(av.z, tv.z, fmaf(av.w, tv.w, mine[rr]))));
                 }
             }
 #pragma unroll
-            for (uint32_t rr = 0; rr < 8; ++rr) {      // the partner's eight sums
-                const float theirs = __shfl_xor_sync(0xffffffffu, mine[rr], 1);
-                acc[rr] = h ? theirs : mine[rr];
-                acc[8 + rr] = h ? mine[rr] : theirs;
-            }
-            float t[16];
+            for (uint32_t rr = 0; rr < 4; ++rr)
+                rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - mine[rr];
+            __syncthreads();
+            float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (uint32_t rr = 0; rr < 16; ++rr) {
-                float s0 = acc[rr], s1 = 0.0f;
+            for (uint32_t g4 = 0; g4 < 4; ++g4) {
+                const float r0 = rhs_s[(4u * g4) * 64u + j], r1 = rhs_s[(4u * g4 + 1u) * 64u + j];
+                const float r2 = rhs_s[(4u * g4 + 2u) * 64u + j], r3 = rhs_s[(4u * g4 + 3u) * 64u + j];
 #pragma unroll
-                for (uint32_t q4 = 0; q4 < rr; q4 += 4) {
-                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + rr, 4u * b + q4 / 4u));   // zero at and above the diagonal
-                    s0 = fmaf(av.x, t[q4], s0);
-                    if (q4 + 1 < rr) s1 = fmaf(av.y, t[q4 + 1], s1);
-                    if (q4 + 2 < rr) s0 = fmaf(av.z, t[q4 + 2], s0);
-                    if (q4 + 3 < rr) s1 = fmaf(av.w, t[q4 + 3], s1);
+                for (uint32_t rr = 0; rr < 4; ++rr) {
+                    const float4 dv = *reinterpret_cast<const float4*>(dsm + (b * 16u + 4u * h + rr) * 16u + 4u * g4);   // zero above the diagonal
+                    t[rr] = fmaf(dv.x, r0, fmaf(dv.y, r1, fmaf(dv.z, r2, fmaf(dv.w, r3, t[rr]))));
                 }
-                t[rr] = (16u * b + rr == j ? 1.0f : 0.0f) - (s0 + s1);
             }
-#pragma unroll
-            for (uint32_t q = 0; q < 2; ++q) {
-                const uint32_t g4 = h * 2u + q;
-                *reinterpret_cast<float4*>(tcol + swf(j, 4u * b + g4)) =
-                    h ? make_float4(t[8 + 4 * q], t[9 + 4 * q], t[10 + 4 * q], t[11 + 4 * q])
-                      : make_float4(t[4 * q], t[4 * q + 1], t[4 * q + 2], t[4 * q + 3]);
-            }
-            __syncwarp();
+            *reinterpret_cast<float4*>(tcol + swf(j, 4u * b + h)) = make_float4(t[0], t[1], t[2], t[3]);
+            __syncthreads();
         }
+    }
+    if (ok) {   // (the last barrier of the sweep: everyone is done with D_b before T_U is written over it)
         // column j of T scaled by this column's factors -> the K-major B tiles T_W and T_U (row r, element j)
+        const uint32_t j = tid & 63u, h = tid >> 6;
+        const uint8_t* tcol = smem + kPrWs;
         const float bj = beta_s[j], wj = bj * e_g[j];
         const uint32_t col = (j & 7u) * 2u, chunk16 = j >> 3;
 #pragma unroll 1
-        for (uint32_t q = h * 8u; q < h * 8u + 8u; ++q) {
+        for (uint32_t q = h * 4u; q < h * 4u + 4u; ++q) {
             const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
             const float te[4] = {tv.x, tv.y, tv.z, tv.w};
 #pragma unroll
