@@ -30,7 +30,8 @@ constexpr uint32_t kRowBytes = kHeadDim * 2;                 // 512
 constexpr uint32_t kSliceBytes = kSliceKeys * kRowBytes;     // 8 KiB per plane
 constexpr uint32_t kStageBytes = 2 * kSliceBytes;            // K then V
 constexpr uint32_t kRingBytes = kDecStages * kStageBytes;    // per warp
-constexpr uint32_t kMergeFloats = kDecWarps * kHeadsPerKv * kHeadDim;
+constexpr uint32_t kMergeStride = kHeadDim + 4u;   // floats per (warp, head) row of the merge buffer: the padding spreads the heads over the banks
+constexpr uint32_t kMergeFloats = kDecWarps * kHeadsPerKv * kMergeStride;
 constexpr uint32_t kDecSmemBytes = kDecWarps * kRingBytes + kMergeFloats * 4 +
                                    kDecWarps * kHeadsPerKv * 2 * 4 + (TATARA_MAX_LANES + 1) * 4;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -108,6 +109,20 @@ __device__ __forceinline__ void mma_top_rows(float& d0, float& d1, uint32_t a0, 
         "{%8,%9}, {%0,%1,%10,%10};\n"
         : "+f"(d0), "+f"(d1), "=f"(z0), "=f"(z1)
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+}
+// D(16x8) += A(16x16) * B(16x8), bf16 in, f32 accumulate.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Transposes an 8x8 matrix of 16-bit elements held one row per four lanes (lane 4g + t: row g, columns 2t, 2t+1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -261,19 +276,26 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!early) fill_ring();
 
-    // Per-lane ldmatrix address pieces (see the fragment layouts of mma.m16n8k16).
+    // Scores and P.V run TRANSPOSED, so that every row of the 16-row MMA tile carries data (with the
+    // 8 heads in M half of each MMA multiplied zeros):
+    //     S^T [16 keys x 8 heads]  = K [16 keys x 256] . Q^T       A = K slice (ldmatrix), B = Q (registers)
+    //     O^T [256 dims x 8 heads] += V^T [dims x 16 keys] . P^T    A = V slice (ldmatrix.trans), B = P^T
+    // The accumulator of S^T holds (key g | g+8, heads 2t, 2t+1) per lane; P^T as a B operand wants
+    // (keys 2t, 2t+1 | +8, head g): one movmatrix per 8 keys transposes the packed probabilities.
+    // Per-lane ldmatrix address pieces (fragment layouts of mma.m16n8k16: A = 4 matrices ordered
+    // (rows lo, cols lo), (rows hi, cols lo), (rows lo, cols hi), (rows hi, cols hi)).
     const uint32_t lm_j = lane >> 3, lm_r = lane & 7u;
-    const uint32_t k_row_off = ((lm_j >> 1) * 8u + lm_r) * kRowBytes; // K: matrices (keys lo/hi) x (dims lo/hi)
-    const uint32_t k_chunk_lo = lm_j & 1u;
-    const uint32_t v_row_off = ((lm_j & 1u) * 8u + lm_r) * kRowBytes; // V: matrices (keys lo/hi) x (d lo/hi)
-    const uint32_t v_chunk_lo = lm_j >> 1;
+    const uint32_t k_row_off = ((lm_j & 1u) * 8u + lm_r) * kRowBytes;   // K: rows = keys, cols = dims
+    const uint32_t k_chunk_lo = lm_j >> 1;
+    const uint32_t v_row_off = ((lm_j >> 1) * 8u + lm_r) * kRowBytes;   // V^T: rows = dims (j & 1), cols = keys (j >> 1)
+    const uint32_t v_chunk_lo = lm_j & 1u;
     const float score_scale = kAttnScale * kLog2e;
 
     SliceCursor cc{};
     for (cc.item = blockIdx.x; cc.item < total_items; cc.item += gridDim.x) {
         cursor_load_item<N, kInd>(cc, p, item_start);
         const DecLane& dl = lane_at<N, kInd>(p, cc.lane);
-        // Q fragments of head (kv*8 + g): A rows 0..7 of every k-step.
+        // Q of head (kv*8 + g) as the B operand of every k-step: dims 16ks + 2t, +1 | + 8, + 9.
         uint32_t qa[16][2];
         {
             const __nv_bfloat16* qrow =
@@ -284,10 +306,11 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
                 qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16u + 8u + 2u * t);
             }
         }
-        float o[32][2];
+        // O^T: tile nt = dims 16nt .. +15; o[nt] = (dim g, head 2t), (dim g, head 2t+1), (dim g+8, 2t), (dim g+8, 2t+1)
+        float o[16][4];
 #pragma unroll
-        for (uint32_t nt = 0; nt < 32; ++nt) o[nt][0] = o[nt][1] = 0.0f;
-        float m = -INFINITY, l = 0.0f;
+        for (uint32_t nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // heads 2t and 2t+1
 
         for (uint32_t slice = warp; slice * kSliceKeys < cc.nkeys; slice += kDecWarps) {
             // keep the ring full, then wait for the oldest slice
@@ -303,55 +326,77 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
             const uint32_t kst = ring + (consumed % kDecStages) * kStageBytes;
             const uint32_t vst = kst + kSliceBytes;
 
-            float s0a = 0.0f, s0b = 0.0f, s1a = 0.0f, s1b = 0.0f;
+            float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // two chains over the 16 k-steps
 #pragma unroll
-            for (uint32_t ks = 0; ks < 16; ++ks) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(kst + k_row_off + (((ks * 2u + k_chunk_lo) ^ lm_r) << 4), b0, b1, b2, b3);
-                mma_top_rows(s0a, s0b, qa[ks][0], qa[ks][1], b0, b1);
-                mma_top_rows(s1a, s1b, qa[ks][0], qa[ks][1], b2, b3);
+            for (uint32_t ks = 0; ks < 16; ks += 2) {
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(kst + k_row_off + (((ks * 2u + k_chunk_lo) ^ lm_r) << 4), a0, a1, a2, a3);
+                mma_16816(sa, a0, a1, a2, a3, qa[ks][0], qa[ks][1]);
+                ldmatrix_x4(kst + k_row_off + ((((ks + 1u) * 2u + k_chunk_lo) ^ lm_r) << 4), a0, a1, a2, a3);
+                mma_16816(sb, a0, a1, a2, a3, qa[ks + 1][0], qa[ks + 1][1]);
             }
-            // thread (g, t): head g, keys 2t, 2t+1 (tile 0) and 8+2t, 8+2t+1 (tile 1)
-            const uint32_t key0 = slice * kSliceKeys + 2u * t;
-            s0a = key0 < cc.nkeys ? s0a * score_scale : -INFINITY;
-            s0b = key0 + 1u < cc.nkeys ? s0b * score_scale : -INFINITY;
-            s1a = key0 + 8u < cc.nkeys ? s1a * score_scale : -INFINITY;
-            s1b = key0 + 9u < cc.nkeys ? s1b * score_scale : -INFINITY;
-            float mx = fmaxf(fmaxf(s0a, s0b), fmaxf(s1a, s1b));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m, mx); // finite: key 0 of every slice is live
-            const float alpha = exp2f(m - m_new);
-            const float p0a = exp2f(s0a - m_new), p0b = exp2f(s0b - m_new);
-            const float p1a = exp2f(s1a - m_new), p1b = exp2f(s1b - m_new);
-            l = l * alpha + ((p0a + p0b) + (p1a + p1b));
-            m = m_new;
-            const uint32_t pa0 = pack_bf16x2(p0a, p0b), pa2 = pack_bf16x2(p1a, p1b);
+            // lane (g, t): keys g and g + 8 of the slice, heads 2t and 2t + 1
+            const uint32_t key0 = slice * kSliceKeys + g;
+            const bool live0 = key0 < cc.nkeys, live1 = key0 + 8u < cc.nkeys;
+            const float s00 = live0 ? (sa[0] + sb[0]) * score_scale : -INFINITY;   // key g,   head 2t
+            const float s01 = live0 ? (sa[1] + sb[1]) * score_scale : -INFINITY;   // key g,   head 2t+1
+            const float s10 = live1 ? (sa[2] + sb[2]) * score_scale : -INFINITY;   // key g+8, head 2t
+            const float s11 = live1 ? (sa[3] + sb[3]) * score_scale : -INFINITY;   // key g+8, head 2t+1
+            float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
 #pragma unroll
-            for (uint32_t pr = 0; pr < 16; ++pr) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(vst + v_row_off + (((pr * 2u + v_chunk_lo) ^ lm_r) << 4), b0, b1, b2, b3);
-                o[2 * pr][0] *= alpha;
-                o[2 * pr][1] *= alpha;
-                o[2 * pr + 1][0] *= alpha;
-                o[2 * pr + 1][1] *= alpha;
-                mma_top_rows(o[2 * pr][0], o[2 * pr][1], pa0, pa2, b0, b1);
-                mma_top_rows(o[2 * pr + 1][0], o[2 * pr + 1][1], pa0, pa2, b2, b3);
+            for (uint32_t off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);   // finite: key 0 of every slice is live
+            const float alpha0 = exp2f(m0 - n0), alpha1 = exp2f(m1 - n1);
+            const float p00 = exp2f(s00 - n0), p01 = exp2f(s01 - n1), p10 = exp2f(s10 - n0), p11 = exp2f(s11 - n1);
+            l0 = l0 * alpha0 + (p00 + p10);
+            l1 = l1 * alpha1 + (p01 + p11);
+            m0 = n0;
+            m1 = n1;
+            const uint32_t pb0 = movmatrix_trans(pack_bf16x2(p00, p01));   // keys 2t, 2t+1 of head g
+            const uint32_t pb1 = movmatrix_trans(pack_bf16x2(p10, p11));   // keys 2t+8, 2t+9 of head g
+            // a factor of exactly 1 leaves every bit as it is, so the rescale is skipped when no lane needs it
+            const bool rescale = __any_sync(0xffffffffu, alpha0 != 1.0f || alpha1 != 1.0f);
+#pragma unroll
+            for (uint32_t nt = 0; nt < 16; ++nt) {
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4_trans(vst + v_row_off + (((nt * 2u + v_chunk_lo) ^ lm_r) << 4), a0, a1, a2, a3);
+                if (rescale) {
+                    o[nt][0] *= alpha0;
+                    o[nt][1] *= alpha1;
+                    o[nt][2] *= alpha0;
+                    o[nt][3] *= alpha1;
+                }
+                mma_16816(o[nt], a0, a1, a2, a3, pb0, pb1);
             }
             __syncwarp(); // every lane is done with this stage before it is refilled
             ++consumed;
         }
 
         // ---- merge the four warps of this item and write its 8 records --------------------
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        float* mo = merge_o + (warp * kHeadsPerKv + g) * kHeadDim;
 #pragma unroll
-        for (uint32_t nt = 0; nt < 32; ++nt)
-            *reinterpret_cast<float2*>(mo + nt * 8u + 2u * t) = make_float2(o[nt][0], o[nt][1]);
-        if (t == 0) {
-            merge_ml[(warp * kHeadsPerKv + g) * 2u] = m;
-            merge_ml[(warp * kHeadsPerKv + g) * 2u + 1u] = l;
+        for (uint32_t off = 4; off < 32; off <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        }
+        {
+            float* mo0 = merge_o + (warp * kHeadsPerKv + 2u * t) * kMergeStride + g;
+            float* mo1 = mo0 + kMergeStride;
+#pragma unroll
+            for (uint32_t nt = 0; nt < 16; ++nt) {
+                mo0[nt * 16u] = o[nt][0];
+                mo1[nt * 16u] = o[nt][1];
+                mo0[nt * 16u + 8u] = o[nt][2];
+                mo1[nt * 16u + 8u] = o[nt][3];
+            }
+        }
+        if (g == 0) {
+            merge_ml[(warp * kHeadsPerKv + 2u * t) * 2u] = m0;
+            merge_ml[(warp * kHeadsPerKv + 2u * t) * 2u + 1u] = l0;
+            merge_ml[(warp * kHeadsPerKv + 2u * t + 1u) * 2u] = m1;
+            merge_ml[(warp * kHeadsPerKv + 2u * t + 1u) * 2u + 1u] = l1;
         }
         __syncthreads();
         {
@@ -370,7 +415,7 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
                 const float wt = mw[w] == -INFINITY ? 0.0f : exp2f(mw[w] - big);
                 lsum = fmaf(wt, merge_ml[(w * kHeadsPerKv + h) * 2u + 1u], lsum);
                 const float4* src =
-                    reinterpret_cast<const float4*>(merge_o + (w * kHeadsPerKv + h) * kHeadDim + d0);
+                    reinterpret_cast<const float4*>(merge_o + (w * kHeadsPerKv + h) * kMergeStride + d0);
 #pragma unroll
                 for (uint32_t i = 0; i < 4; ++i) {
                     const float4 v = src[i];
