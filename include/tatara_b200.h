@@ -90,8 +90,9 @@ uint64_t tatara_ctx_launch_count(const tatara_ctx* ctx);
  * include/tatara/runtime/decode_step.h:15-21; PrefillExecutionPolicy, prefill_step.h:42-73).
  * Set before the first call that the policy affects, not between calls in flight. */
 typedef enum tatara_policy {
-    /* Rows of K and of V of each decode CTA's first partition that are requested into L2 before the
-     * kernel waits for its predecessor in the stream (0 switches the requests off). */
+    /* Cap on the rows of K and of V of each decode CTA's partition that are requested into L2 before
+     * the kernel waits for its predecessor in the stream (the kernel asks for a quarter of the
+     * partition up to this cap; 0 switches the requests off). */
     TATARA_POLICY_DECODE_L2_PREFETCH_KEYS = 0,
     /* Which implementation evaluates tatara_gdn_prefill with chunk 64: 0 = the tensor-memory form
      * (tcgen05 MMAs fed by TMA, the state as an f32 accumulator in tensor memory), 1 = the

@@ -243,8 +243,11 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         // Only when every CTA has a single item: a batch with several items per CTA keeps HBM busy
         // across items by itself, and the extra lines only compete for L2 (measured: 32 lanes 1.5 % slower).
         if (p.l2_prefetch_keys != 0u && total_items <= gridDim.x) {
+            // (a quarter of the item, capped: measured best at 128 rows of a 443-key item, 256 of 886, 384-512 of
+            // 3543 -- more only competes in L2 with the step that is still streaming)
             const uint32_t ring_keys = early ? kDecWarps * (kDecStages - 1u) * kSliceKeys : 0u;
-            const uint32_t stop = min(pc.nkeys, ring_keys + p.l2_prefetch_keys);
+            const uint32_t window = min(p.l2_prefetch_keys, ((pc.nkeys >> 2) + 15u) & ~15u);
+            const uint32_t stop = min(pc.nkeys, ring_keys + window);
             for (uint32_t row = ring_keys + threadIdx.x * kSliceKeys; row < stop; row += kDecThreads * kSliceKeys) {
                 const uint32_t bytes = min(kSliceKeys, stop - row) * kRowBytes;
                 l2_prefetch_bulk(pc.kbase + uint64_t(row) * kRowBytes, bytes);

@@ -26,9 +26,10 @@ constexpr uint32_t kSmCount = 148; // B200; the partition function is pinned to 
 // Device-side status word slots (ctx->device_status).
 enum : uint32_t { kStatusCode = 0, kStatusDetail = 1, kStatusWords = 4 };
 constexpr size_t kLaneScheduleBytes = 32768;   // holds attn_decode.cu's DecTables
-// Default of TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: K/V rows per plane that a decode CTA asks into L2
-// beyond its shared-memory ring before its dependency wait (512 bytes per row and plane).
-constexpr uint32_t kDecodeL2PrefetchKeys = 256;
+// Default of TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: the most K/V rows per plane that a decode CTA asks
+// into L2 beyond its shared-memory ring before its dependency wait (512 bytes per row and plane); the
+// kernel asks for a quarter of its item's rows up to this cap.
+constexpr uint32_t kDecodeL2PrefetchKeys = 512;
 
 } // namespace tb
 
