@@ -373,8 +373,8 @@ class Workloads:
                 self.ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, form)
                 ms = timed(lambda i=0: self.ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk, scratch), 5, 3)
                 out[name] = {"ms": ms, "tokens_per_s": rows / (ms * 1e-3),
-                             "tflops_chunked_form": 94.5e9 / (ms * 1e-3) / 1e12,
-                             "gbs_algorithmic": 406913024 / (ms * 1e-3) / 1e9}
+                             "tflops_chunked_form": 94.5e9 * rows / 16384 / (ms * 1e-3) / 1e12,
+                             "gbs_algorithmic": (rows * 24704 + 2097152 + 65536) / (ms * 1e-3) / 1e9}
             except tb.TataraError as e:
                 out[name] = {"unavailable": str(e)}
         self.ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 0)
