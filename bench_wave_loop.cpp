@@ -5,7 +5,7 @@
 // host tables (the reference's way: re-encode every token, src/runtime/decode_step.cpp:1002-1426).
 // Prints one JSON line.  Weights and prompts are seeded synthetic data.
 //
-//   wave_bench [--lanes 8] [--context 16384] [--tokens 64] [--layers 40] [--unit 2048]
+//   bench_wave_loop [--lanes 8] [--context 16384] [--tokens 64] [--layers 40] [--unit 2048]
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -13,7 +13,7 @@
 #include <cstring>
 #include <string>
 
-#include "wave_loop.hpp"
+#include "tatara_b200/host/wave_loop.hpp"
 
 using namespace tatara::runtime;
 using namespace tatara::engine;

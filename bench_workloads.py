@@ -16,6 +16,29 @@ from tatara_b200 import sharding
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
 
+WAVE_BENCH_SRC = os.path.join(ROOT, "bench_wave_loop.cpp")
+WAVE_BENCH_EXE = os.path.join(ROOT, "bench_wave_loop")
+
+
+def build_wave_loop_bench():
+    """Compiles bench_wave_loop.cpp (the timing program of the owner's wave loop: plain C++ above the
+    C ABI and the header-only host layer) next to bench.py; a no-op when it is up to date."""
+    import subprocess
+    pkg = os.path.dirname(os.path.abspath(tb.__file__))
+    host = os.path.join(pkg, "host")
+    deps = [WAVE_BENCH_SRC, tb.LIB_PATH] + [os.path.join(host, f) for f in os.listdir(host) if f.endswith(".hpp")]
+    if os.path.exists(WAVE_BENCH_EXE) and all(os.path.getmtime(d) <= os.path.getmtime(WAVE_BENCH_EXE) for d in deps):
+        return WAVE_BENCH_EXE
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cuda = os.path.dirname(os.path.dirname(nvcc))
+    cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-o", WAVE_BENCH_EXE, WAVE_BENCH_SRC, f"-I{cuda}/include", f"-I{ROOT}",
+           f"-L{pkg}", "-ltatara_b200", f"-L{cuda}/lib64", "-lcudart", f"-Wl,-rpath,{pkg}", f"-Wl,-rpath,{cuda}/lib64"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"g++ failed for bench_wave_loop:\n{res.stdout}\n{res.stderr}")
+    return WAVE_BENCH_EXE
+
+
 def measured_peaks():
     """Roofline denominators: the driver-measured peaks of this pool, else the stated fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -565,14 +588,14 @@ class Workloads:
     # ---- single-workload runs (profiling)
     # ---- the engine's wave loop over a 40-layer stack (native program above the C ABI)
     def wave_loop(self, lanes=8, context=16384, tokens=40):
-        """Runs tatara_b200/wave_bench (host/wave_bench.cpp): 8 streams join through the owner loop to
+        """Runs bench_wave_loop (bench_wave_loop.cpp): 8 streams join through the owner loop to
         `context` positions, then full decode waves are timed with the host clock; the same waves walked
         eagerly with host tables beside them."""
         import json
         import subprocess
-        exe = os.path.join(os.path.dirname(os.path.abspath(tb.__file__)), "wave_bench")
+        exe = WAVE_BENCH_EXE
         if not os.path.exists(exe):
-            raise RuntimeError("tatara_b200/wave_bench is not built: run __graft_entry__.build()")
+            raise RuntimeError("bench_wave_loop is not built: run __graft_entry__.build()")
         self.torch.cuda.empty_cache()
         res = subprocess.run([exe, "--lanes", str(lanes), "--context", str(context), "--tokens", str(tokens)],
                              capture_output=True, text=True, timeout=150)

@@ -62,26 +62,7 @@ def build(verbose: bool = False) -> str:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    _build_wave_bench()
     return LIB
-
-
-WAVE_BENCH = os.path.join(HERE, "wave_bench")
-
-
-def _build_wave_bench():
-    """The wave-loop timing program (host/wave_bench.cpp): plain C++ above the C ABI."""
-    host = os.path.join(HERE, "host")
-    src = os.path.join(host, "wave_bench.cpp")
-    deps = [src, LIB] + [os.path.join(host, f) for f in os.listdir(host) if f.endswith(".hpp")]
-    if not _stale(WAVE_BENCH, deps):
-        return
-    cuda = os.path.dirname(os.path.dirname(NVCC))
-    cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-o", WAVE_BENCH, src, f"-I{cuda}/include", f"-L{HERE}",
-           "-ltatara_b200", f"-L{cuda}/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{cuda}/lib64"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"g++ failed for wave_bench:\n{res.stdout}\n{res.stderr}")
 
 
 if __name__ == "__main__":

@@ -1,4 +1,4 @@
-"""The wave-loop timing program (tatara_b200/host/wave_bench.cpp) on a small stack: it must join every stream
+"""The wave-loop timing program (bench_wave_loop.cpp, beside bench.py) on a small stack: it must join every stream
 through the owner loop, reach full waves and report one graph per wave size."""
 import json
 import os
@@ -12,8 +12,8 @@ pytestmark = pytest.mark.gpu
 
 
 def test_wave_bench_small_stack():
-    exe = os.path.join(os.path.dirname(os.path.abspath(tb.__file__)), "wave_bench")
-    assert os.path.exists(exe), "tatara_b200/wave_bench is not built (python -m tatara_b200.build)"
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench_wave_loop")
+    assert os.path.exists(exe), "bench_wave_loop is not built (__graft_entry__.build())"
     res = subprocess.run([exe, "--lanes", "3", "--context", "700", "--tokens", "12", "--layers", "8", "--unit", "256"],
                          capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
