@@ -74,8 +74,8 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 // matters is the number of distinct instructions fetched, not the trip count.
 constexpr uint32_t kPrKQ = 0;            // [K;Q] : 2 dim-atoms x [128 rows x 128 B]; rows 0..63 K, 64..127 Q
 constexpr uint32_t kPrV = 32768;         // V : 2 v-atoms x [64 rows x 128 B]; later U^T [128 rows x 128 B]
-constexpr uint32_t kPrA = 49152;         // A f32 [64][64], 16-byte groups swizzled by row & 7; later W^T [128 rows x 128 B]
-constexpr uint32_t kPrWs = 65536;        // T columns (f32, swizzled) during the solve; later Ws^T [128 rows x 128 B]
+constexpr uint32_t kPrA = 49152;         // A f32 [64][64] as [group][row][4]; later W^T [128 rows x 128 B]
+constexpr uint32_t kPrWs = 65536;        // T f32 as [row group][column][4] during the solve; later Ws^T [128 rows x 128 B]
 constexpr uint32_t kPrP = 81920;         // P [64 rows x 128 B]
 constexpr uint32_t kPrTW = 90112;        // T diag(beta e^G)  [64 rows x 128 B]
 constexpr uint32_t kPrTU = 98304;        // T diag(beta)      [64 rows x 128 B]
@@ -123,8 +123,10 @@ __device__ __forceinline__ void store_bf16x16(uint8_t* tile, uint32_t row, uint3
     *reinterpret_cast<uint4*>(tile + sw128(row, chunk + 1u)) =
         make_uint4(pack_bf2(v[8], v[9]), pack_bf2(v[10], v[11]), pack_bf2(v[12], v[13]), pack_bf2(v[14], v[15]));
 }
-// f32 tile of 64-float rows whose 16-byte groups are XORed with row & 7 (conflict-free row writes and column reads)
-__device__ __forceinline__ uint32_t swf(uint32_t row, uint32_t group) { return row * 256u + ((group ^ (row & 7u)) << 4); }
+// f32 [64][64] matrix stored as [16-byte group of four columns][row][4]: a warp that writes or reads one
+// group of 32 consecutive rows touches 512 contiguous bytes, and a (row, group) address is an affine
+// function of both -- the solve below steps through it with immediate offsets.
+__device__ __forceinline__ uint32_t gmat(uint32_t row, uint32_t group) { return group * 1024u + row * 16u; }
 
 __global__ void __launch_bounds__(kPrThreads, 2)
 gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_v,
@@ -242,7 +244,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
             if (row < 64u) {
 #pragma unroll
                 for (uint32_t q = 0; q < 4; ++q)
-                    *reinterpret_cast<float4*>(smem + kPrA + swf(r, c0 / 4u + q)) = make_float4(d[4 * q], d[4 * q + 1], d[4 * q + 2], d[4 * q + 3]);
+                    *reinterpret_cast<float4*>(smem + kPrA + gmat(r, c0 / 4u + q)) = make_float4(d[4 * q], d[4 * q + 1], d[4 * q + 2], d[4 * q + 3]);
             } else {
                 store_bf16x16(smem + kPrP, r, c0 / 8u, d);
             }
@@ -271,7 +273,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
             float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
             for (uint32_t q4 = 0; q4 < rr; q4 += 4) {
-                const float4 av = *reinterpret_cast<const float4*>(smem + kPrA + swf(16u * b + rr, 4u * b + q4 / 4u));   // zero at and above the diagonal
+                const float4 av = *reinterpret_cast<const float4*>(smem + kPrA + gmat(16u * b + rr, 4u * b + q4 / 4u));   // zero at and above the diagonal
                 s0 = fmaf(av.x, t[q4], s0);
                 if (q4 + 1 < rr) s1 = fmaf(av.y, t[q4 + 1], s1);
                 if (q4 + 2 < rr) s0 = fmaf(av.z, t[q4 + 2], s0);
@@ -284,48 +286,56 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
     __syncthreads();
     {
         const uint32_t j = tid & 63u, h = tid >> 6;
-        const uint8_t* amat = smem + kPrA;
-        uint8_t* tcol = smem + kPrWs;
+        uint8_t* tcol = smem + kPrWs + j * 16u;          // column j of T: group q at + q * 1024
 #pragma unroll 1
         for (uint32_t b = 0; b < 4; ++b) {
-            float mine[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint8_t* arow = smem + kPrA + (16u * b + 4u * h) * 16u;   // this thread's four rows of A: row rr at + rr * 16
+            float2 acc[4];
+#pragma unroll
+            for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = make_float2(0.0f, 0.0f);
 #pragma unroll 1
             for (uint32_t q = 0; q < 4u * b; ++q) {
-                const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
+                const float4 tv = *reinterpret_cast<const float4*>(tcol + q * 1024u);
 #pragma unroll
                 for (uint32_t rr = 0; rr < 4; ++rr) {
-                    const float4 av = *reinterpret_cast<const float4*>(amat + swf(16u * b + 4u * h + rr, q));
-                    mine[rr] = fmaf(av.x, tv.x, fmaf(av.y, tv.y, fmaf(av.z, tv.z, fmaf(av.w, tv.w, mine[rr]))));
+                    const float4 av = *reinterpret_cast<const float4*>(arow + q * 1024u + rr * 16u);
+                    acc[rr] = __ffma2_rn(make_float2(av.x, av.y), make_float2(tv.x, tv.y), acc[rr]);
+                    acc[rr] = __ffma2_rn(make_float2(av.z, av.w), make_float2(tv.z, tv.w), acc[rr]);
                 }
             }
 #pragma unroll
             for (uint32_t rr = 0; rr < 4; ++rr)
-                rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - mine[rr];
+                rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - (acc[rr].x + acc[rr].y);
             __syncthreads();
-            float t[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float2 t2[4];
+#pragma unroll
+            for (uint32_t rr = 0; rr < 4; ++rr) t2[rr] = make_float2(0.0f, 0.0f);
+            const float* drow = dsm + (b * 16u + 4u * h) * 16u;
 #pragma unroll
             for (uint32_t g4 = 0; g4 < 4; ++g4) {
-                const float r0 = rhs_s[(4u * g4) * 64u + j], r1 = rhs_s[(4u * g4 + 1u) * 64u + j];
-                const float r2 = rhs_s[(4u * g4 + 2u) * 64u + j], r3 = rhs_s[(4u * g4 + 3u) * 64u + j];
+                const float2 r01 = make_float2(rhs_s[(4u * g4) * 64u + j], rhs_s[(4u * g4 + 1u) * 64u + j]);
+                const float2 r23 = make_float2(rhs_s[(4u * g4 + 2u) * 64u + j], rhs_s[(4u * g4 + 3u) * 64u + j]);
 #pragma unroll
                 for (uint32_t rr = 0; rr < 4; ++rr) {
-                    const float4 dv = *reinterpret_cast<const float4*>(dsm + (b * 16u + 4u * h + rr) * 16u + 4u * g4);   // zero above the diagonal
-                    t[rr] = fmaf(dv.x, r0, fmaf(dv.y, r1, fmaf(dv.z, r2, fmaf(dv.w, r3, t[rr]))));
+                    const float4 dv = *reinterpret_cast<const float4*>(drow + rr * 16u + 4u * g4);   // zero above the diagonal
+                    t2[rr] = __ffma2_rn(make_float2(dv.x, dv.y), r01, t2[rr]);
+                    t2[rr] = __ffma2_rn(make_float2(dv.z, dv.w), r23, t2[rr]);
                 }
             }
-            *reinterpret_cast<float4*>(tcol + swf(j, 4u * b + h)) = make_float4(t[0], t[1], t[2], t[3]);
+            *reinterpret_cast<float4*>(tcol + (4u * b + h) * 1024u) =
+                make_float4(t2[0].x + t2[0].y, t2[1].x + t2[1].y, t2[2].x + t2[2].y, t2[3].x + t2[3].y);
             __syncthreads();
         }
     }
     if (ok) {   // (the last barrier of the sweep: everyone is done with D_b before T_U is written over it)
         // column j of T scaled by this column's factors -> the K-major B tiles T_W and T_U (row r, element j)
         const uint32_t j = tid & 63u, h = tid >> 6;
-        const uint8_t* tcol = smem + kPrWs;
+        const uint8_t* tcol = smem + kPrWs + j * 16u;
         const float bj = beta_s[j], wj = bj * e_g[j];
         const uint32_t col = (j & 7u) * 2u, chunk16 = j >> 3;
 #pragma unroll 1
         for (uint32_t q = h * 4u; q < h * 4u + 4u; ++q) {
-            const float4 tv = *reinterpret_cast<const float4*>(tcol + swf(j, q));
+            const float4 tv = *reinterpret_cast<const float4*>(tcol + q * 1024u);
             const float te[4] = {tv.x, tv.y, tv.z, tv.w};
 #pragma unroll
             for (uint32_t e = 0; e < 4; ++e) {
