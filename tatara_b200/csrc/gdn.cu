@@ -263,16 +263,6 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     const float* state_in = rec_pool + gl.rec_in;
     float* state_out = rec_pool + gl.rec_out;
 
-    // all 16 state rows of this warp go in flight first (4 batches x 4 rows, 64 KiB per CTA),
-    // so the whole state read overlaps the conv / norm prologue
-    const uint32_t row_base = warp * 16u;
-    const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
-    Rows4 rows[4];
-#pragma unroll
-    for (uint32_t batch = 0; batch < 4; ++batch)
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j)
-            rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
     // The layer's own conv taps and the weights are not written by the predecessor either: requested
     // here, with the state rows.  threads 0..127 -> q channel, 128..255 -> k channel; v channel on 0..127.
     const uint32_t l128 = threadIdx.x & 127u;
@@ -290,6 +280,16 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     const uint2 v_w = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(v_channel) * 4u);
     const __nv_bfloat16 dt_raw = dt_bias[head], alog_raw = a_log[head];
     const uint2 norm_w = *reinterpret_cast<const uint2*>(norm_weight + lane * 4u);
+    // Then all 16 state rows of this warp (4 batches x 4 rows, 64 KiB per CTA): the whole state read
+    // overlaps the conv / norm prologue, and the few small requests above are not queued behind it.
+    const uint32_t row_base = warp * 16u;
+    const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
+    Rows4 rows[4];
+#pragma unroll
+    for (uint32_t batch = 0; batch < 4; ++batch)
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j)
+            rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
     // Launched as a programmatic dependent of its predecessor in the stream (the projection that
     // produces `projection`): what is read above is this layer's own state and weights, which that
     // predecessor does not write, so those loads are in flight while the predecessor finishes; the
