@@ -391,7 +391,8 @@ class Workloads:
         y = torch.zeros((rows, 4096), dtype=bf, device="cuda")
         out = {}
         scratch = torch.empty(tb.gdn_prefill_scratch_bytes(rows), dtype=torch.uint8, device="cuda")
-        for chunk, form, name in ((64, 0, "chunk64"), (64, 1, "chunk64_register_form"), (1, 0, "sequential_scan")):
+        for chunk, form, name in ((64, 0, "chunk64"), (64, 2, "chunk64_two_launches"), (64, 1, "chunk64_register_form"),
+                                  (1, 0, "sequential_scan")):
             try:
                 self.ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, form)
                 ms = timed(lambda i=0: self.ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk, scratch), 5, 3)
@@ -402,8 +403,9 @@ class Workloads:
                 out[name] = {"unavailable": str(e)}
         self.ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 0)
         out["rows"] = rows
-        out["forms"] = ("chunk64: tcgen05 MMAs, state in tensor memory (transition form); chunk64_register_form: "
-                        "mma.sync, state in registers; same inputs, same scratch")
+        out["forms"] = ("chunk64: tcgen05 MMAs, state in tensor memory (transition form), one launch in which the scan of "
+                        "early chunks runs beside the preparation of later ones; chunk64_two_launches: the same kernels one "
+                        "after the other; chunk64_register_form: mma.sync, state in registers; same inputs, same scratch")
         return out
 
     # ---- config 2: causal prefill attention, 16384 rows from position 0

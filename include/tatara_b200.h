@@ -95,8 +95,10 @@ typedef enum tatara_policy {
      * partition up to this cap; 0 switches the requests off). */
     TATARA_POLICY_DECODE_L2_PREFETCH_KEYS = 0,
     /* Which implementation evaluates tatara_gdn_prefill with chunk 64: 0 = the tensor-memory form
-     * (tcgen05 MMAs fed by TMA, the state as an f32 accumulator in tensor memory), 1 = the
-     * register-resident mma.sync form.  Same algebra, same tolerance against the sequential scan. */
+     * (tcgen05 MMAs fed by TMA, the state as an f32 accumulator in tensor memory) as ONE launch in which
+     * the scan of early chunks runs beside the preparation of later ones, 2 = the same kernels as two
+     * launches, 1 = the register-resident mma.sync form.  Same algebra, same tolerance against the
+     * sequential scan. */
     TATARA_POLICY_GDN_CHUNK_FORM = 1
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);

@@ -116,7 +116,7 @@ tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint6
         ctx->decode_l2_prefetch_keys = static_cast<uint32_t>(value);
         return TATARA_OK;
     case TATARA_POLICY_GDN_CHUNK_FORM:
-        if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: chunk form");
+        if (value > 2) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: chunk form");
         ctx->gdn_chunk_form = static_cast<uint32_t>(value);
         return TATARA_OK;
     }

@@ -481,7 +481,8 @@ tatara_status launch_gdn_chunked_tc(tatara_ctx* ctx, cudaStream_t stream, const 
                                     void* scratch, uint64_t scratch_bytes);
 
 // The chunked form has two implementations of the same algebra, chosen by TATARA_POLICY_GDN_CHUNK_FORM:
-// 0 (default) the tensor-memory form of gdn_chunked_tc.cu, 1 the register-resident mma.sync form above.
+// 0 (default) the tensor-memory form of gdn_chunked_tc.cu as one launch, 2 the same as two launches,
+// 1 the register-resident mma.sync form above.
 tatara_status launch_gdn_chunked(tatara_ctx* ctx, cudaStream_t stream, const __nv_bfloat16* qk,
                                  const __nv_bfloat16* value, const float* decay, const float* beta,
                                  const float* state_in, __nv_bfloat16* y, float* state_out, uint32_t rows,

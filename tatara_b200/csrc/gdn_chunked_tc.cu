@@ -48,8 +48,8 @@ __host__ __device__ inline uint64_t tc_units(uint32_t rows) {
     return uint64_t((rows + kTcChunk - 1u) / kTcChunk) * kGdnValueHeads;
 }
 uint64_t gdn_tc_scratch_bytes(uint32_t rows) {
-    const uint64_t units = tc_units(rows);
-    return units * (kUnitM + kUnitU + kUnitQ + kUnitO) + ((units * 4u + 127u) & ~uint64_t(127));
+    const uint64_t units = tc_units(rows);   // four planes, then e^{G_C} per unit, then the ready word per unit
+    return units * (kUnitM + kUnitU + kUnitQ + kUnitO) + 2u * ((units * 4u + 127u) & ~uint64_t(127));
 }
 
 // kind::f16 instruction descriptor with both majors selectable (bit 15: A is MN-major, bit 16: B).
@@ -128,40 +128,41 @@ __device__ __forceinline__ void store_bf16x16(uint8_t* tile, uint32_t row, uint3
 // function of both -- the solve below steps through it with immediate offsets.
 __device__ __forceinline__ uint32_t gmat(uint32_t row, uint32_t group) { return group * 1024u + row * 16u; }
 
-__global__ void __launch_bounds__(kPrThreads, 2)
-gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_v,
-                      const TcPrepareParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+// CTA barrier over the 256 threads of one prepare group: barrier kBar (0 = the whole CTA of the
+// stand-alone kernel; 1, 2 = the two groups of a worker CTA of the fused kernel).
+template <uint32_t kBar>
+__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, 256;" ::"n"(kBar) : "memory"); }
+template <uint32_t kBar>
+__device__ __forceinline__ bool group_and(bool pred) {
+    uint32_t r;
+    asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.and.pred q, %2, 256, p;\n selp.u32 %0, 1, 0, q;\n}"
+                 : "=r"(r) : "r"(pred ? 1u : 0u), "n"(kBar) : "memory");
+    return r != 0u;
+}
+
+// The units first_unit, first_unit + unit_stride, ... by one group of 256 threads (tid = 0..255) that owns
+// kPrSmem bytes of shared memory at `smem` (its two mbarriers initialised, abort flag cleared) and
+// kPrCols columns of tensor memory at `tmem`.  `ready` (or null): one word per unit, set to `epoch` once
+// the unit's planes are complete in global memory.
+template <uint32_t kBar>
+__device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, const CUtensorMap& map_v, const TcPrepareParams& p,
+                                                 uint8_t* smem, uint32_t tmem, uint32_t tid, uint32_t first_unit,
+                                                 uint32_t unit_stride, uint32_t* ready, uint32_t epoch) {
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
     const uint32_t row = (warp & 3u) * 32u + lane, half = warp >> 2;
     const uint32_t base = s2u(smem);
     const uint32_t bar_load = base + kPrBar, bar_mma = base + kPrBar + 8;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kPrBar + 16);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kPrBar + 24);
     float* g_cum = reinterpret_cast<float*>(smem + kPrVec);
     float* beta_s = g_cum + 64;
     float* s_end = g_cum + 128;    // e^{G_C - G_r}
     float* e_g = g_cum + 192;      // e^{G_r}
-    if (tid == 0) {
-        mbar_init(bar_load, 1);
-        mbar_init(bar_mma, 1);
-        *abort_flag = 0u;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kPrCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
     const uint32_t tlane = ((warp & 3u) * 32u) << 16;
     bool ok = true;
     uint32_t mma_phase = 0;     // completions of bar_mma so far (three per unit)
 
     // Persistent CTAs: barriers and tensor memory are set up once, then the CTA walks its units.
-    for (uint32_t it = 0, unit32 = blockIdx.x; unit32 < p.n_units && ok; ++it, unit32 += gridDim.x) {
+    for (uint32_t it = 0, unit32 = first_unit; unit32 < p.n_units && ok; ++it, unit32 += unit_stride) {
     const uint32_t chunk = unit32 / kGdnValueHeads, head = unit32 % kGdnValueHeads, qkh = head >> 1;
     const uint32_t row0 = chunk * kTcChunk;
     const uint32_t live_rows = min(kTcChunk, p.rows - row0);
@@ -174,7 +175,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
             tma_load_2d(base + kPrV + a * 8192u, &map_v, bar_load, int(head * kGdnDim + a * 64u), int(row0));
         }
         // the tiles of this CTA's next unit are asked into L2 now: its loads start when this unit is done
-        const uint32_t next = unit32 + gridDim.x;
+        const uint32_t next = unit32 + unit_stride;
         if (next < p.n_units) {
             const uint32_t nh = next % kGdnValueHeads, nq = nh >> 1, nrow = (next / kGdnValueHeads) * kTcChunk;
             for (uint32_t a = 0; a < 2; ++a) {
@@ -222,7 +223,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
     }
     if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
     ++mma_phase;
-    __syncthreads();   // the decay vectors of warp 1 are visible
+    group_sync<kBar>();   // the decay vectors of warp 1 are visible
     if (ok) {
         tc_fence_after();
         const uint32_t r = row & 63u;
@@ -251,7 +252,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
         }
         tc_fence_before();
     }
-    __syncthreads();
+    group_sync<kBar>();
 
     // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), in panels of 16 rows.
     // (1) The four 16 x 16 diagonal blocks are inverted first, one column per thread (64 threads,
@@ -283,7 +284,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
             dsm[(b * 16u + rr) * 16u + c] = t[rr];
         }
     }
-    __syncthreads();
+    group_sync<kBar>();
     {
         const uint32_t j = tid & 63u, h = tid >> 6;
         uint8_t* tcol = smem + kPrWs + j * 16u;          // column j of T: group q at + q * 1024
@@ -306,7 +307,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
 #pragma unroll
             for (uint32_t rr = 0; rr < 4; ++rr)
                 rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - (acc[rr].x + acc[rr].y);
-            __syncthreads();
+            group_sync<kBar>();
             float2 t2[4];
 #pragma unroll
             for (uint32_t rr = 0; rr < 4; ++rr) t2[rr] = make_float2(0.0f, 0.0f);
@@ -324,7 +325,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
             }
             *reinterpret_cast<float4*>(tcol + (4u * b + h) * 1024u) =
                 make_float4(t2[0].x + t2[0].y, t2[1].x + t2[1].y, t2[2].x + t2[2].y, t2[3].x + t2[3].y);
-            __syncthreads();
+            group_sync<kBar>();
         }
     }
     if (ok) {   // (the last barrier of the sweep: everyone is done with D_b before T_U is written over it)
@@ -346,7 +347,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
         }
     }
     fence_async_smem();
-    __syncthreads();
+    group_sync<kBar>();
 
     // ---- MMA b: W^T = K^T T_W^T (columns 64..127), MMA c: U^T = V^T T_U^T (columns 128..191)
     if (tid == 0 && ok) {
@@ -383,7 +384,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
         tc_fence_before();
     }
     fence_async_smem();
-    __syncthreads();
+    group_sync<kBar>();
 
     // ---- MMA d: M' = Ws^T K (columns 0..127), e: X = W^T P^T (128..191), f: O0^T = U^T P^T (192..255)
     if (tid == 0 && ok) {
@@ -443,16 +444,52 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
         tc_fence_before();
     }
     fence_async_smem();
-    __syncthreads();
+    group_sync<kBar>();
     if (tid == 0 && ok) {
         bulk_store(p.planes.m + unit * kUnitM, base + kPrStM, kUnitM);
         bulk_store(p.planes.q + unit * kUnitQ, base + kPrStQ, kUnitQ);
         bulk_store(p.planes.o + unit * kUnitO, base + kPrStO, kUnitO);
         bulk_store_commit();
-        bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
+        if (ready != nullptr) {
+            // the scan of this head may be waiting for exactly this unit: the planes are complete in global
+            // memory (not only read out of shared memory) before the word that says so is released
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async;" ::: "memory");
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ready + unit32), "r"(epoch) : "memory");
+        } else {
+            bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
+        }
     }
-    ok = __syncthreads_and(ok ? 1 : 0) != 0;   // ... before the next unit's loads land on them; leave the loop together
+    ok = group_and<kBar>(ok);   // ... before the next unit's loads land on them; leave the loop together
     }   // units
+}
+
+__global__ void __launch_bounds__(kPrThreads, 2)
+gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_v,
+                      const TcPrepareParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t base = s2u(smem);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kPrBar + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kPrBar + 24);
+    if (tid == 0) {
+        mbar_init(base + kPrBar, 1);
+        mbar_init(base + kPrBar + 8, 1);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kPrCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    tc_prepare_units<0>(map_qk, map_v, p, smem, tmem, tid, blockIdx.x, gridDim.x, nullptr, 0u);
+    tc_fence_before();
+    __syncthreads();
     if (*abort_flag) {
         if (tid == 0) {
             atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
@@ -517,42 +554,55 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 }
 constexpr uint32_t kScAhead = 4;   // chunks whose plane images are asked into L2 ahead of the shared-memory ring
 
-__global__ void __launch_bounds__(kScThreads, 1)
-gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+// Bounded wait until the planes of `unit` are complete (the word carries `epoch`); true at once without flags.
+__device__ __forceinline__ bool unit_ready(const uint32_t* ready, uint64_t unit, uint32_t epoch, volatile uint32_t* abort_flag) {
+    if (ready == nullptr) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ready + unit) : "memory");
+        if (v == epoch) return true;
+        if ((spin & 15u) == 15u) {
+            if (*abort_flag) return false;
+            const unsigned long long t = now_ns();
+            if (t0 == 0) t0 = t;
+            if (t - t0 > kWaitLimitNs) {
+                *abort_flag = 1u;
+                return false;
+            }
+        }
+        __nanosleep(100);
+    }
+}
+
+__device__ __forceinline__ void tc_scan_init_barriers(uint8_t* smem) {
+    const uint32_t bars = s2u(smem) + kScBar;
+    for (uint32_t s = 0; s < kScRingA; ++s) {
+        mbar_init(bars + 8u * (kSbFullA + s), 1);
+        mbar_init(bars + 8u * (kSbEmptyA + s), 1);
+    }
+    for (uint32_t s = 0; s < 2; ++s) {
+        mbar_init(bars + 8u * (kSbFullB + s), 1);
+        mbar_init(bars + 8u * (kSbEmptyB + s), 1);
+        mbar_init(bars + 8u * (kSbOut + s), 1);
+        mbar_init(bars + 8u * (kSbOutFree + s), 128);
+    }
+    mbar_init(bars + 8u * kSbConv, 128);
+    mbar_init(bars + 8u * kSbState, 1);
+    *reinterpret_cast<volatile uint32_t*>(smem + kScBar + 8 * kSbCount) = 0u;
+}
+
+// One v-head walked by 320 threads (tid = 0..319) that own kScSmem bytes at `smem` (barriers initialised) and
+// kScCols columns of tensor memory at `tmem`.  `ready` (or null): see unit_ready.
+__device__ __forceinline__ void tc_scan_head(const CUtensorMap& map_qk, const TcScanParams& p, uint8_t* smem, uint32_t tmem,
+                                             uint32_t tid, uint32_t head, const uint32_t* ready, uint32_t epoch) {
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
     const uint32_t base = s2u(smem);
     const uint32_t bars = base + kScBar;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kScBar + 8 * kSbCount);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kScBar + 8 * kSbCount + 8);
     auto bar = [&](uint32_t slot) { return bars + 8u * slot; };
-    const uint32_t head = blockIdx.x, qkh = head >> 1;
+    const uint32_t qkh = head >> 1;
     const uint32_t nchunks = p.nchunks;
-
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kScRingA; ++s) {
-            mbar_init(bar(kSbFullA + s), 1);
-            mbar_init(bar(kSbEmptyA + s), 1);
-        }
-        for (uint32_t s = 0; s < 2; ++s) {
-            mbar_init(bar(kSbFullB + s), 1);
-            mbar_init(bar(kSbEmptyB + s), 1);
-            mbar_init(bar(kSbOut + s), 1);
-            mbar_init(bar(kSbOutFree + s), 128);
-        }
-        mbar_init(bar(kSbConv), 128);
-        mbar_init(bar(kSbState), 1);
-        *abort_flag = 0u;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kScCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -571,6 +621,8 @@ gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParam
                 const uint64_t unit = uint64_t(c) * kGdnValueHeads + head;
                 if (c + kScAhead < nchunks) prefetch(c + kScAhead);
                 if (ua > 0u && !mbar_wait(bar(kSbEmptyA + sa), (ua - 1u) & 1u, abort_flag)) break;
+                if (!unit_ready(ready, unit, epoch, abort_flag)) break;
+                if (ready != nullptr) asm volatile("fence.proxy.async;" ::: "memory");   // the planes were written through the bulk-copy engine of another SM
                 mbar_expect_tx(bar(kSbFullA + sa), kScStageA);
                 bulk_load(st + kScStageM, p.planes.m + unit * kUnitM, kUnitM, bar(kSbFullA + sa));
                 bulk_load(st + kScStageU, p.planes.u + unit * kUnitU, kUnitU, bar(kSbFullA + sa));
@@ -623,6 +675,7 @@ gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParam
         float* out_row = p.state_out + (uint64_t(head) * kGdnDim + row) * kGdnDim;
         bool ok = true;
         for (uint32_t c = 0; c <= nchunks && ok; ++c) {
+            if (c < nchunks && !unit_ready(ready, uint64_t(c) * kGdnValueHeads + head, epoch, abort_flag)) { ok = false; break; }
             const float gamma = c < nchunks ? p.planes.gamma[uint64_t(c) * kGdnValueHeads + head] : 1.0f;
             if (c > 0u) {
                 if (!mbar_wait(bar(kSbState), (c - 1u) & 1u, abort_flag)) { ok = false; break; }
@@ -668,6 +721,7 @@ gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParam
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint32_t s = c & 1u;
             const uint32_t live_rows = min(kTcChunk, p.rows - c * kTcChunk);
+            if (!unit_ready(ready, uint64_t(c) * kGdnValueHeads + head, epoch, abort_flag)) break;
             uint4 o0[8];
             const uint8_t* o_img = p.planes.o + (uint64_t(c) * kGdnValueHeads + head) * kUnitO;   // the swizzled tile image
 #pragma unroll
@@ -688,6 +742,27 @@ gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParam
         }
     }
 
+}
+
+__global__ void __launch_bounds__(kScThreads, 1)
+gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kScBar + 8 * kSbCount);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kScBar + 8 * kSbCount + 8);
+    if (threadIdx.x == 0) {
+        tc_scan_init_barriers(smem);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(tmem_slot)), "r"(kScCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    tc_scan_head(map_qk, p, smem, tmem, threadIdx.x, blockIdx.x, nullptr, 0u);
     tc_fence_before();
     __syncthreads();
     if (*abort_flag) {
@@ -701,6 +776,80 @@ gdn_tc_scan_kernel(const __grid_constant__ CUtensorMap map_qk, const TcScanParam
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kScCols) : "memory");
+    }
+}
+
+// ---- both in one launch: the scan of early chunks runs beside the preparation of later ones ---------
+// One CTA of 512 threads per SM (a cooperative launch: the scan CTAs wait for words that worker CTAs set, so
+// all of them must be resident together).  CTAs 0..31 walk one v-head each (threads 0..319); every other
+// CTA is two prepare groups of 256 threads, each with its own half of the shared and tensor memory,
+// taking units in chunk order (unit = slot, slot + slots, ...), so the planes of chunk c are complete
+// about when the scans get there.  Two launches that wait on each other's flags could not share a GPU
+// safely; one launch with roles can.
+constexpr uint32_t kFuThreads = 512;
+constexpr uint32_t kFuSmem = kScSmem > 2u * kPrSmem ? kScSmem : 2u * kPrSmem;
+static_assert(2u * kPrSmem <= 232448 && kPrSmem % 1024u == 64u, "two prepare groups per CTA");
+constexpr uint32_t kFuGroupStride = kPrSmem - 64u + 1024u;   // keeps the second group's tiles 1024-byte aligned
+
+struct TcFusedParams {
+    TcPrepareParams prep;
+    TcScanParams scan;
+    uint32_t* ready;
+    uint32_t epoch;
+};
+
+__global__ void __launch_bounds__(kFuThreads, 1)
+gdn_tc_fused_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_constant__ CUtensorMap map_v,
+                    const TcFusedParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const bool scan_role = blockIdx.x < kGdnValueHeads;
+    const uint32_t group = tid >> 8;
+    uint8_t* gsmem = smem + group * kFuGroupStride;
+    if (scan_role) {
+        if (tid == 0) {
+            tc_scan_init_barriers(smem);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    } else if ((tid & 255u) == 0u) {
+        mbar_init(s2u(gsmem) + kPrBar, 1);
+        mbar_init(s2u(gsmem) + kPrBar + 8, 1);
+        *reinterpret_cast<volatile uint32_t*>(gsmem + kPrBar + 16) = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool aborted = false;
+    if (scan_role) {
+        if (tid < kScThreads) tc_scan_head(map_qk, p.scan, smem, tmem, tid, blockIdx.x, p.ready, p.epoch);
+    } else {
+        const uint32_t slots = (gridDim.x - kGdnValueHeads) * 2u, slot = (blockIdx.x - kGdnValueHeads) * 2u + group;
+        if (group == 0u) tc_prepare_units<1>(map_qk, map_v, p.prep, gsmem, tmem, tid & 255u, slot, slots, p.ready, p.epoch);
+        else tc_prepare_units<2>(map_qk, map_v, p.prep, gsmem, tmem + kPrCols, tid & 255u, slot, slots, p.ready, p.epoch);
+    }
+    tc_fence_before();
+    __syncthreads();
+    aborted = scan_role ? *reinterpret_cast<volatile uint32_t*>(smem + kScBar + 8 * kSbCount) != 0u
+                        : (*reinterpret_cast<volatile uint32_t*>(smem + kPrBar + 16) |
+                           *reinterpret_cast<volatile uint32_t*>(smem + kFuGroupStride + kPrBar + 16)) != 0u;
+    if (aborted) {
+        if (tid == 0) {
+            atomicCAS(p.scan.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            p.scan.status[kStatusDetail] = blockIdx.x;
+        }
+        __nanosleep(200000);
+        __syncthreads();
+    }
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -739,19 +888,43 @@ tatara_status launch_gdn_chunked_tc(tatara_ctx* ctx, cudaStream_t stream, const 
     CUtensorMap map_qk, map_v;
     if (!make_map2(&map_qk, qk, kGdnQk, rows, 64) || !make_map2(&map_v, value, kGdnV, rows, 64))
         return fail(ctx, TATARA_CUDA_ERROR, "gdn_prefill: tensor map encoding failed");
+    uint32_t* ready = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(planes.gamma) + ((units * 4u + 127u) & ~uint64_t(127)));
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
         if (cudaFuncSetAttribute(gdn_tc_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrSmem) != cudaSuccess ||
-            cudaFuncSetAttribute(gdn_tc_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess)
+            cudaFuncSetAttribute(gdn_tc_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_tc_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmem) != cudaSuccess)
             return check_launch(ctx, "gdn_prefill: shared memory attribute");
         configured[ctx->device & 63] = true;
     }
     TcPrepareParams pp{decay, beta, planes, ctx->device_status, rows, uint32_t(units)};
+    TcScanParams sp{state_in, state_out, y, planes, ctx->device_status, rows, nchunks};
+    // One launch with roles (32 scan CTAs beside the prepare workers) when the device has SMs to spare for
+    // workers and the block is long enough for the overlap to matter; else, or if the cooperative launch is
+    // refused, prepare and scan as two launches.
+    if (ctx->gdn_chunk_form == 0u && ctx->sm_count >= int(kGdnValueHeads) + 32 && nchunks >= 8u) {
+        if (cudaMemsetAsync(ready, 0, units * 4u, stream) != cudaSuccess) return check_launch(ctx, "gdn_prefill(ready words)");
+        TcFusedParams fp{pp, sp, ready, 1u};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(uint32_t(ctx->sm_count));
+        cfg.blockDim = dim3(kFuThreads);
+        cfg.dynamicSmemBytes = kFuSmem;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, gdn_tc_fused_kernel, map_qk, map_v, fp) == cudaSuccess) {
+            ++ctx->launches;
+            return TATARA_OK;
+        }
+        (void)cudaGetLastError();   // not admitted as a cooperative launch (a partitioned device): two launches
+    }
     const uint32_t prep_grid = units < 2u * uint32_t(ctx->sm_count) ? uint32_t(units) : 2u * uint32_t(ctx->sm_count);
     gdn_tc_prepare_kernel<<<prep_grid, kPrThreads, kPrSmem, stream>>>(map_qk, map_v, pp);
     tatara_status st = check_launch(ctx, "gdn_prefill(prepare)");
     if (st != TATARA_OK) return st;
-    TcScanParams sp{state_in, state_out, y, planes, ctx->device_status, rows, nchunks};
     gdn_tc_scan_kernel<<<kGdnValueHeads, kScThreads, kScSmem, stream>>>(map_qk, sp);
     return check_launch(ctx, "gdn_prefill(scan)");
 }

@@ -320,12 +320,13 @@ def test_chunked_prefill_slow_decay_and_split_blocks(ctx):
 
 
 def test_chunked_prefill_both_forms_agree_with_the_oracle(ctx):
-    """The chunk-64 evaluation has two implementations behind one entry point (tensor-memory
-    transition form, the default, and the register-resident mma.sync form): both against the CPU
-    oracle's sequential scan on a block with a ragged tail, slowly forgetting heads and a non-zero
-    initial state, and against each other."""
+    """The chunk-64 evaluation has two implementations behind one entry point -- the tensor-memory
+    transition form, as one launch with roles (the default for blocks of eight chunks or more) or as two
+    launches, and the register-resident mma.sync form: each against the CPU oracle's sequential scan on a
+    block with a ragged tail, slowly forgetting heads and a non-zero initial state, the one-launch and
+    two-launch forms bit for bit, and the two algebras against each other."""
     rng = np.random.default_rng(404)
-    rows = 333
+    rows = 717
     conv_w, a_log, dt_bias, _ = syn.gdn_weights(rng)
     conv, state = syn.gdn_state(rng)
     proj = syn.gdn_projection(rng, rows)
@@ -335,7 +336,7 @@ def test_chunked_prefill_both_forms_agree_with_the_oracle(ctx):
     oy, ostate = oracle.gdn_scan(oqk, ov, od, ob, state, threads=8)
     outs = []
     try:
-        for form in (0, 1):
+        for form in (0, 2, 1):
             ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, form)
             y = torch.zeros((rows, 4096), dtype=torch.bfloat16, device="cuda")
             s = torch.zeros((32, 128, 128), dtype=torch.float32, device="cuda")
@@ -347,7 +348,8 @@ def test_chunked_prefill_both_forms_agree_with_the_oracle(ctx):
             outs.append(host_u16(y))
     finally:
         ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 0)
-    assert_close_bf16(outs[0], outs[1], "tensor-memory form vs register form")
+    assert np.array_equal(outs[0], outs[1]), "one launch with roles and two launches run the same arithmetic"
+    assert_close_bf16(outs[0], outs[2], "tensor-memory form vs register form")
 
 
 def test_chunked_prefill_config3_full_size(ctx):
