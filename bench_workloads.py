@@ -423,11 +423,19 @@ class Workloads:
                 clocks = cs.summary()
             else:
                 ms = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
+            # the one-CTA kernel on the same inputs (TATARA_POLICY_ATTN_PREFILL_FORM = 1), for comparison
+            self.ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 1)
+            try:
+                ms_single = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
+            finally:
+                self.ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 0)
         except tb.TataraError as e:
             return {"unavailable": str(e)}
         tf = prefill_flops(rows) / (ms * 1e-3) / 1e12
         return {"rows": rows, "ms": ms, "tflops": tf, "clocks": clocks, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                 "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"],
+                "kernel": "attn_prefill_pair_kernel (CTA pairs, cta_group::2)",
+                "single_cta_form": {"ms": ms_single, "tflops": prefill_flops(rows) / (ms_single * 1e-3) / 1e12},
                 "l2": "Q/gate/out 402 MB > L2"}
 
     # ---- the projections on either side of the layers (affine Q4, group 64)

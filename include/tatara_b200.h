@@ -99,7 +99,11 @@ typedef enum tatara_policy {
      * the scan of early chunks runs beside the preparation of later ones, 2 = the same kernels as two
      * launches, 1 = the register-resident mma.sync form.  Same algebra, same tolerance against the
      * sequential scan. */
-    TATARA_POLICY_GDN_CHUNK_FORM = 1
+    TATARA_POLICY_GDN_CHUNK_FORM = 1,
+    /* Which kernel evaluates tatara_attn_prefill: 0 = CTA pairs (two SMs on the same 128 query rows of two
+     * heads of a KV group, each loading half of every K and V tile), 1 = one CTA per (query tile, head).
+     * Same arithmetic in the same order: the outputs are bit-identical. */
+    TATARA_POLICY_ATTN_PREFILL_FORM = 2
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

@@ -151,6 +151,40 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0,
+                                                 int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Bounded wait on a barrier of this CTA whose arrivals may come from the peer CTA of the cluster:
+// the acquire has cluster scope, so what the peer's thread did before its release-arrive is visible.
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try_cluster(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (;;) {
+#pragma unroll 1
+        for (uint32_t i = 0; i < 32u; ++i)
+            if (mbar_try_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        const unsigned long long t = now_ns();
+        if (t0 == 0) t0 = t;
+        if (t - t0 > kWaitLimitNs) {
+            *abort_flag = 1u;
+            return false;
+        }
+    }
+}
 // One commit that arrives on the barrier at the same offset in both CTAs of the pair.
 __device__ __forceinline__ void tc_commit_both(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"

@@ -74,6 +74,26 @@ def test_prefill_matches_control_family_all_rows(ctx):
     assert np.array_equal(got, again), "prefill is not deterministic run to run"
 
 
+@pytest.mark.parametrize("base,rows", [(0, 1), (0, 129), (300, 77), (5, 513), (256, 2048)])
+def test_prefill_pair_form_equals_single_cta_form_bit_for_bit(ctx, base, rows):
+    """TATARA_POLICY_ATTN_PREFILL_FORM: the CTA-pair kernel (default) and the one-CTA kernel accumulate every
+    score and every output element over the same k-steps in the same order."""
+    rng = np.random.default_rng(base * 11 + rows)
+    cap = base + rows + 9
+    keys, values = syn.attn_cache(rng, base + rows, cap)
+    q, gate = syn.attn_query(rng, np.arange(base, base + rows))
+    assert ctx.get_policy(tb.POLICY_ATTN_PREFILL_FORM) == 0
+    pair = run_prefill(ctx, q, gate, keys, values, base, rows, cap)
+    ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 1)
+    try:
+        single = run_prefill(ctx, q, gate, keys, values, base, rows, cap)
+    finally:
+        ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 0)
+    assert np.array_equal(pair, single)
+    with pytest.raises(tb.TataraError):
+        ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 2)
+
+
 def test_prefill_config2_full_size_sampled(ctx):
     """Benchmark config 2: 16384 rows from position 0.  Row-sampled oracle (tile-boundary rows
     included) plus the control family on a slice of rows."""
