@@ -65,11 +65,28 @@ struct PrefillParams {
 // shared memory, how many P buffers there are, and the slots of the barriers they touch.
 struct SingleForm {
     static constexpr uint32_t kOffQ = tb::kOffQ, kOffP = tb::kOffP, kOffPair = tb::kOffPair, kPBufs = 1;
+    static constexpr bool kArriveAtLeader = false;
     static constexpr uint32_t kBarSFull = tb::kBarSFull, kBarSFree = tb::kBarSFree, kBarPFull = tb::kBarPFull,
                               kBarPvDone = tb::kBarPvDone;
 };
 
 // ---------------- softmax + epilogue: two threads per query row (warps 2..9 of a CTA) ----------------
+// How the softmax rows signal the MMA issuer.  One CTA: every thread arrives on its CTA's barrier.
+// CTA pair: the issuer sits in the leader CTA, so each warp of BOTH CTAs arrives once, through one
+// lane, on the leader's barrier (after __syncwarp, which orders the other lanes' tensor-memory loads
+// and shared-memory stores before it).  The arrive has CTA-scope release semantics: a cluster-scope
+// release on this path held the arriving thread for about 800 ns (timeline of a temporary build).
+template <class Form>
+__device__ __forceinline__ void rows_arrive(uint32_t bar_addr, uint32_t lane) {
+    if constexpr (Form::kArriveAtLeader) {
+        __syncwarp();
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(map_to_cta(bar_addr, 0u)) : "memory");
+    } else {
+        mbar_arrive(bar_addr);
+    }
+}
+
 template <class Form>
 __device__ __forceinline__ void softmax_rows(uint8_t* smem, uint32_t bars, uint32_t tmem, const PrefillParams& p,
                                              uint32_t warp, uint32_t lane, uint32_t head, uint32_t r0,
@@ -87,20 +104,17 @@ __device__ __forceinline__ void softmax_rows(uint8_t* smem, uint32_t bars, uint3
     bool ok = true;
     for (uint32_t j = 0; j < ntiles; ++j) {
         const uint32_t s = j % kSBufs, par = (j / kSBufs) & 1u;
-        // After a failed wait a thread keeps walking the tiles but only meets its partner at
-        // the pair barrier, so the partner can never be left waiting there.
+        // After a failed wait a thread keeps walking the tiles without waiting again (what it computes
+        // and stores from then on is never used: the CTA reports the time-out and writes no output),
+        // so every warp-wide instruction, the pair barrier and the arrivals stay convergent.
         if (ok && !mbar_wait(bar(Form::kBarSFull + s), par, abort_flag)) ok = false;
-        if (!ok) {
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            continue;
-        }
         tc_fence_after();
         float sv[64];
         tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u, sv);
         tmem_ld32(tmem + tlane + kColS + s * kBN + half * 64u + 32u, sv + 32);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(bar(Form::kBarSFree + s));   // the scores are in registers: the buffer may take tile j+2
+        rows_arrive<Form>(bar(Form::kBarSFree + s), lane);   // the scores are in registers: the buffer may take tile j+2
         const uint32_t key0 = j * kBN + half * 64u;
         if (j * kBN + kBN - 1u > p.context_base + r0) { // the tile crosses this CTA's diagonal
 #pragma unroll
@@ -127,10 +141,8 @@ __device__ __forceinline__ void softmax_rows(uint8_t* smem, uint32_t bars, uint3
             if (__any_sync(0xffffffffu, grow)) {
                 // O holds P.V of tiles < j: wait for tile j-1, then rescale this row's half of O
                 const uint32_t jp = j - 1u;
-                if (!mbar_wait(bar(Form::kBarPvDone + jp % Form::kPBufs), (jp / Form::kPBufs) & 1u, abort_flag)) {
+                if (ok && !mbar_wait(bar(Form::kBarPvDone + jp % Form::kPBufs), (jp / Form::kPBufs) & 1u, abort_flag))
                     ok = false;
-                    continue;
-                }
                 tc_fence_after();
                 const float f = grow ? ex2(m_used - mx) : 1.0f;
                 for (uint32_t ch = 0; ch < 4; ++ch) {
@@ -162,11 +174,9 @@ __device__ __forceinline__ void softmax_rows(uint8_t* smem, uint32_t bars, uint3
         // 128-byte row of atom `half`, eight 16-byte chunks under the 128-byte swizzle.  The single
         // P tile is free once P.V of the tile that used it before (j - kPBufs) has completed.
         const uint32_t pb = j % Form::kPBufs;
-        if (j >= Form::kPBufs &&
-            !mbar_wait(bar(Form::kBarPvDone + pb), (j / Form::kPBufs - 1u) & 1u, abort_flag)) {
+        if (ok && j >= Form::kPBufs &&
+            !mbar_wait(bar(Form::kBarPvDone + pb), (j / Form::kPBufs - 1u) & 1u, abort_flag))
             ok = false;
-            continue;
-        }
         {
             uint8_t* prow = smem + Form::kOffP + pb * kPBytes + half * kPAtomBytes + row * 128u;
 #pragma unroll
@@ -185,13 +195,13 @@ __device__ __forceinline__ void softmax_rows(uint8_t* smem, uint32_t bars, uint3
             __threadfence_block();
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> the MMA's async proxy
-        mbar_arrive(bar(Form::kBarPFull + pb));
+        rows_arrive<Form>(bar(Form::kBarPFull + pb), lane);
     }
     if (ok) {
         const uint32_t jl = ntiles - 1u;
         ok = mbar_wait(bar(Form::kBarPvDone + jl % Form::kPBufs), (jl / Form::kPBufs) & 1u, abort_flag);
     }
-    if (ok) {
+    if (__all_sync(0xffffffffu, ok)) {   // warp-uniform: the tensor-memory loads below are warp-wide
         tc_fence_after();
         l += reinterpret_cast<const float*>(smem + Form::kOffQ)[(half ^ 1u) * 128u + row]; // + the partner's half
         const float inv_l = 1.0f / l;
@@ -391,11 +401,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // P ready -> P.V done -> P buffer free is a chain through the leader, and with one buffer that
 // chain was the tile period.  Hand-offs: `full` barriers live in the leader (its producer arrives
 // expecting the bytes of both CTAs; both CTAs' copies complete on them); `empty`, `S full` and
-// `P.V done` are one tcgen05.commit that arrives in both CTAs; `S free` and `P full` count the
-// 256 softmax threads of the CTA they live in, and in the leader one more arrival that the
-// peer's otherwise idle warp 1 forwards when the peer's own barrier completes (a cluster-scope
-// release arrive holds its thread for about a thousand cycles, so no softmax thread makes one).
+// `P.V done` are one tcgen05.commit that arrives in both CTAs; `S free` and `P full` live in the
+// leader and count one arrival per softmax warp of both CTAs.
 constexpr uint32_t kPpKSlots = 3, kPpVSlots = 3, kPpPBufs = 2;
+constexpr uint32_t kPvWarp = 10, kPpThreads = 352;   // TMA warp, score-MMA warp, 8 softmax warps, P.V-MMA warp
 constexpr uint32_t kPpSlotBytes = 16384;   // K slot: 64 keys x 128 dims; V slot: 64 keys x 128 d
 constexpr uint32_t kPpAtomBytes = 8192;    // one 64-wide swizzle atom of a slot (64 keys x 128 B)
 constexpr uint32_t kPpOffQ = 0;
@@ -415,11 +424,12 @@ static_assert(8 * kPpBarCount + 16 <= 256, "barrier block");
 
 struct PairForm {
     static constexpr uint32_t kOffQ = kPpOffQ, kOffP = kPpOffP, kOffPair = kPpOffPair, kPBufs = kPpPBufs;
+    static constexpr bool kArriveAtLeader = true;
     static constexpr uint32_t kBarSFull = kPpBarSFull, kBarSFree = kPpBarSFree, kBarPFull = kPpBarPFull,
                               kBarPvDone = kPpBarPvDone;
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPrefillThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPpThreads, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -452,10 +462,10 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (uint32_t s = 0; s < kSBufs; ++s) {
             mbar_init(bar(kPpBarSFull + s), 1);
-            mbar_init(bar(kPpBarSFree + s), kSoftmaxThreads + (leader ? 1u : 0u));
+            mbar_init(bar(kPpBarSFree + s), 2u * kSoftmaxThreads / 32u);   // one arrival per softmax warp of both CTAs
         }
         for (uint32_t s = 0; s < kPpPBufs; ++s) {
-            mbar_init(bar(kPpBarPFull + s), kSoftmaxThreads + (leader ? 1u : 0u));
+            mbar_init(bar(kPpBarPFull + s), 2u * kSoftmaxThreads / 32u);
             mbar_init(bar(kPpBarPvDone + s), 1);
         }
         *abort_flag = 0u;
@@ -503,27 +513,33 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 return true;
             };
+            // in the order the leader's MMAs use them: S_0, S_1, S_2, P.V_0, S_3, P.V_1, ...
             bool ok = load_k(0);
+            if (ok && ntiles > 1u) ok = load_k(1);
+            if (ok && ntiles > 2u) ok = load_k(2);
             for (uint32_t j = 0; ok && j < ntiles; ++j) {
-                if (j + 1u < ntiles) ok = load_k(j + 1u);
-                if (ok) ok = load_v(j);
+                ok = load_v(j);
+                if (ok && j + 3u < ntiles) ok = load_k(j + 3u);
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            // ---------------- MMA issuer of the pair ----------------
+            // ---------------- score MMAs of the pair ----------------
             constexpr uint32_t idesc_s = instr_desc(2u * kBM, kBN, false);
-            constexpr uint32_t idesc_pv = instr_desc(2u * kBM, kHeadDim, true);
             bool ok = mbar_wait_cluster(bar(kPpBarQ), 0, abort_flag);
-            auto issue_s = [&](uint32_t j) {
+            // S_j goes out as soon as the softmax rows have taken S_{j-2} into registers (the start of
+            // their tile j-2): the score MMAs stay a full softmax tile ahead of the P.V chain.
+            for (uint32_t j = 0; ok && j < ntiles; ++j) {
                 const uint32_t b = j % kSBufs;
                 // S buffer b of BOTH CTAs is free once their softmax threads have read tile j-2 out of it
-                if (j >= kSBufs && !mbar_wait_cluster(bar(kPpBarSFree + b), (j / kSBufs - 1u) & 1u, abort_flag))
-                    return false;
+                if (j >= kSBufs && !mbar_wait_cluster(bar(kPpBarSFree + b), (j / kSBufs - 1u) & 1u, abort_flag)) break;
                 tc_fence_after();
-                for (uint32_t h = 0; h < 2; ++h) {
+                for (uint32_t h = 0; ok && h < 2; ++h) {
                     const uint32_t n = j * 2u + h, slot = n % kPpKSlots;
-                    if (!mbar_wait_cluster(bar(kPpBarKFull + slot), (n / kPpKSlots) & 1u, abort_flag)) return false;
+                    if (!mbar_wait_cluster(bar(kPpBarKFull + slot), (n / kPpKSlots) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
 #pragma unroll
                     for (uint32_t ks = 0; ks < 8; ++ks) {
@@ -534,15 +550,24 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     tc_commit_both(bar(kPpBarKEmpty + slot));
                 }
-                tc_commit_both(bar(kPpBarSFull + b));
-                return true;
-            };
-            auto issue_pv = [&](uint32_t i) {
+                if (ok) tc_commit_both(bar(kPpBarSFull + b));
+            }
+        }
+    } else if (warp == kPvWarp) {
+        if (lane == 0 && leader) {
+            // ---------------- P.V MMAs of the pair: a second issuing thread, so that the tensor pipe is fed
+            // by one thread while the other waits on a barrier or commits ----------------
+            constexpr uint32_t idesc_pv = instr_desc(2u * kBM, kHeadDim, true);
+            bool ok = true;
+            for (uint32_t i = 0; ok && i < ntiles; ++i) {
                 const uint32_t pb = i % kPpPBufs;
-                if (!mbar_wait_cluster(bar(kPpBarPFull + pb), (i / kPpPBufs) & 1u, abort_flag)) return false;
+                if (!mbar_wait_cluster(bar(kPpBarPFull + pb), (i / kPpPBufs) & 1u, abort_flag)) break;
                 for (uint32_t g = 0; g < 2; ++g) {
                     const uint32_t n = i * 2u + g, slot = n % kPpVSlots;
-                    if (!mbar_wait_cluster(bar(kPpBarVFull + slot), (n / kPpVSlots) & 1u, abort_flag)) return false;
+                    if (!mbar_wait_cluster(bar(kPpBarVFull + slot), (n / kPpVSlots) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after();
 #pragma unroll
                     for (uint32_t h = 0; h < 4; ++h) {
@@ -555,23 +580,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     tc_commit_both(bar(kPpBarVEmpty + slot));
                 }
-                tc_commit_both(bar(kPpBarPvDone + pb));
-                return true;
-            };
-            if (ok) ok = issue_s(0);
-            if (ok && ntiles > 1u) ok = issue_s(1);
-            for (uint32_t j = 0; ok && j < ntiles; ++j) {
-                ok = issue_pv(j);
-                if (ok && j + 2u < ntiles) ok = issue_s(j + 2u);
-            }
-        } else if (lane == 0) {
-            // ---------------- the peer's forwarder: its own S-free / P-full completions -> the leader ----------------
-            for (uint32_t j = 0; j < ntiles; ++j) {
-                const uint32_t b = j % kSBufs, pb = j % kPpPBufs;
-                if (!mbar_wait(bar(kPpBarSFree + b), (j / kSBufs) & 1u, abort_flag)) break;
-                mbar_arrive_cluster(map_to_cta(bar(kPpBarSFree + b), 0u));
-                if (!mbar_wait(bar(kPpBarPFull + pb), (j / kPpPBufs) & 1u, abort_flag)) break;
-                mbar_arrive_cluster(map_to_cta(bar(kPpBarPFull + pb), 0u));
+                if (ok) tc_commit_both(bar(kPpBarPvDone + pb));
             }
         }
     } else {
@@ -656,7 +665,7 @@ extern "C" tatara_status tatara_attn_prefill(tatara_ctx* ctx, void* stream, cons
     pp.rows = rows;
     pp.n_qtiles = (rows + kBM - 1u) / kBM;
     if (pair)
-        attn_prefill_pair_kernel<<<pp.n_qtiles * kQHeads, kPrefillThreads, kPpSmem, static_cast<cudaStream_t>(stream)>>>(
+        attn_prefill_pair_kernel<<<pp.n_qtiles * kQHeads, kPpThreads, kPpSmem, static_cast<cudaStream_t>(stream)>>>(
             map_q, map_k, map_v, pp);
     else
         attn_prefill_kernel<<<pp.n_qtiles * kQHeads, kPrefillThreads, kPrefillSmem, static_cast<cudaStream_t>(stream)>>>(
