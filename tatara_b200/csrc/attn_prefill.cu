@@ -24,6 +24,9 @@
 // than 2^8), which keeps the TMEM round trip of O off the steady-state path.
 // Every mbarrier wait is bounded; on a timeout the CTA latches TATARA_DEVICE_WAIT_TIMEOUT in the
 // context's status word, frees its TMEM and returns.
+// Two kernels share the softmax rows: attn_prefill_kernel (one CTA per tile and head, described
+// above) and attn_prefill_pair_kernel (two CTAs on two heads of a KV group, described at its
+// definition), selected by TATARA_POLICY_ATTN_PREFILL_FORM; their outputs are bit-identical.
 #include "tc05.cuh"
 
 namespace tb {
