@@ -370,8 +370,16 @@ class Workloads:
                                       tables[(i // reps) & 1], y, gated)
 
         ms = timed(step, max(steps, 2 * reps), max(warmup, reps))
+        # the per-lane register data path on the same inputs (TATARA_POLICY_GDN_DECODE_FORM = 1), for comparison
+        self.ctx.set_policy(tb.POLICY_GDN_DECODE_FORM, 1)
+        try:
+            ms_regs = timed(step, max(steps, 2 * reps), max(warmup, reps))
+        finally:
+            self.ctx.set_policy(tb.POLICY_GDN_DECODE_FORM, 0)
         return {"lanes": n, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
-                "l2": f"{reps} rotating state sets (> 2x L2)", "kernel": "gdn_decode_fused_kernel (1 launch per step)"}
+                "register_form_us": ms_regs * 1e3,
+                "l2": f"{reps} rotating state sets (> 2x L2)",
+                "kernel": "gdn_decode_fused_kernel<bulk copies> (1 launch per step)"}
 
     # ---- config 3: GDN prefill, 16384 rows
     def gdn_prefill(self, timed, rows=16384):

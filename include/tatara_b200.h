@@ -103,7 +103,11 @@ typedef enum tatara_policy {
     /* Which kernel evaluates tatara_attn_prefill: 0 = CTA pairs (two SMs on the same 128 query rows of two
      * heads of a KV group, each loading half of every K and V tile), 1 = one CTA per (query tile, head).
      * Same arithmetic in the same order: the outputs are bit-identical. */
-    TATARA_POLICY_ATTN_PREFILL_FORM = 2
+    TATARA_POLICY_ATTN_PREFILL_FORM = 2,
+    /* How the fused GDN decode step (tatara_gdn_decode_batch, _indirect) moves the 64 KiB of state each CTA
+     * reads and rewrites: 0 = cp.async.bulk copies through shared memory, 1 = per-lane loads into registers and
+     * streaming stores.  Same arithmetic: the outputs are bit-identical. */
+    TATARA_POLICY_GDN_DECODE_FORM = 3
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

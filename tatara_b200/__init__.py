@@ -78,6 +78,7 @@ def lib() -> ctypes.CDLL:
 POLICY_DECODE_L2_PREFETCH_KEYS = 0
 POLICY_GDN_CHUNK_FORM = 1
 POLICY_ATTN_PREFILL_FORM = 2
+POLICY_GDN_DECODE_FORM = 3
 
 
 def split_buffer_bytes(world: int) -> int:

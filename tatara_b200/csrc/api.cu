@@ -123,6 +123,10 @@ tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint6
         if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: prefill form");
         ctx->attn_prefill_form = static_cast<uint32_t>(value);
         return TATARA_OK;
+    case TATARA_POLICY_GDN_DECODE_FORM:
+        if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: decode form");
+        ctx->gdn_decode_form = static_cast<uint32_t>(value);
+        return TATARA_OK;
     }
     return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: unknown policy");
 }
@@ -132,6 +136,7 @@ uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy) {
     case TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: return ctx->decode_l2_prefetch_keys;
     case TATARA_POLICY_GDN_CHUNK_FORM: return ctx->gdn_chunk_form;
     case TATARA_POLICY_ATTN_PREFILL_FORM: return ctx->attn_prefill_form;
+    case TATARA_POLICY_GDN_DECODE_FORM: return ctx->gdn_decode_form;
     }
     return 0;
 }

@@ -43,6 +43,7 @@ struct tatara_ctx {
     uint32_t decode_l2_prefetch_keys = tb::kDecodeL2PrefetchKeys;   // TATARA_POLICY_DECODE_L2_PREFETCH_KEYS
     uint32_t gdn_chunk_form = 0;                                     // TATARA_POLICY_GDN_CHUNK_FORM
     uint32_t attn_prefill_form = 0;                                  // TATARA_POLICY_ATTN_PREFILL_FORM
+    uint32_t gdn_decode_form = 0;                                    // TATARA_POLICY_GDN_DECODE_FORM
     char error[256] = {0};
 };
 

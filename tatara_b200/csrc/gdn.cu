@@ -6,7 +6,7 @@
 // state rows: a lane holds 4 contiguous k-dim elements (one coalesced 512-byte float4 row per
 // warp), four rows are in flight per warp, and the two dot products per row are
 // adjacent-pairs shuffle trees -- the reference's reduction order.
-#include "common.cuh"
+#include "tc05.cuh"
 
 namespace tb {
 
@@ -123,9 +123,27 @@ __global__ void gdn_gates_kernel(const __nv_bfloat16* __restrict__ projection,
 struct Rows4 {
     float4 s[4];
 };
-__device__ __forceinline__ void delta_rule_rows4(Rows4& r, const float kf[4], const float qf[4],
-                                                 const float v[4], float decay, float beta,
-                                                 float out[4]) {
+// Sum over the 32 lanes of FOUR values at once, each through the adjacent-pairs tree (lane i with
+// i^1, then i^2, ... i^16): the same additions as four butterfly reductions, but after the first
+// level a lane only carries the two rows it keeps, after the second one row, so the tree takes 6
+// shuffles instead of 20.  Lane L ends with the total of row tree4_row(L); every lane of a class
+// L & 3 holds the same bits the butterfly would give.
+__device__ __forceinline__ uint32_t tree4_row(uint32_t lane) { return ((lane & 1u) << 1) | ((lane >> 1) & 1u); }
+__device__ __forceinline__ float tree4(float r0, float r1, float r2, float r3, uint32_t lane) {
+    const bool odd = (lane & 1u) != 0u, upper = (lane & 2u) != 0u;
+    // level 1: even lanes keep rows 0 and 1, odd lanes rows 2 and 3
+    const float a = (odd ? r2 : r0) + __shfl_xor_sync(0xffffffffu, odd ? r0 : r2, 1);
+    const float b = (odd ? r3 : r1) + __shfl_xor_sync(0xffffffffu, odd ? r1 : r3, 1);
+    // level 2: lanes with bit 1 clear keep the first of their two rows, the others the second
+    float t = (upper ? b : a) + __shfl_xor_sync(0xffffffffu, upper ? a : b, 2);
+    t += __shfl_xor_sync(0xffffffffu, t, 4);
+    t += __shfl_xor_sync(0xffffffffu, t, 8);
+    t += __shfl_xor_sync(0xffffffffu, t, 16);
+    return t;
+}
+// Returns, in every lane, the output of row tree4_row(lane) of the four.
+__device__ __forceinline__ float delta_rule_rows4(Rows4& r, const float kf[4], const float qf[4],
+                                                  const float v[4], float decay, float beta, uint32_t lane) {
     float kv[4];
 #pragma unroll
     for (uint32_t j = 0; j < 4; ++j) {
@@ -135,11 +153,14 @@ __device__ __forceinline__ void delta_rule_rows4(Rows4& r, const float kf[4], co
         a = fmaf(r.s[j].z, kf[2], a);
         kv[j] = fmaf(r.s[j].w, kf[3], a);
     }
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) kv[j] += __shfl_xor_sync(0xffffffffu, kv[j], off);
-    }
+    // every lane needs the four totals: rows 0, 2, 1, 3 sit in lanes 0, 1, 2, 3 of each group of four
+    const float total = tree4(kv[0], kv[1], kv[2], kv[3], lane);
+    const uint32_t quad = lane & ~3u;
+    kv[0] = __shfl_sync(0xffffffffu, total, quad);
+    kv[2] = __shfl_sync(0xffffffffu, total, quad | 1u);
+    kv[1] = __shfl_sync(0xffffffffu, total, quad | 2u);
+    kv[3] = __shfl_sync(0xffffffffu, total, quad | 3u);
+    float out[4];
 #pragma unroll
     for (uint32_t j = 0; j < 4; ++j) {
         const float delta = (v[j] - kv[j]) * beta;
@@ -152,11 +173,7 @@ __device__ __forceinline__ void delta_rule_rows4(Rows4& r, const float kf[4], co
         a = fmaf(r.s[j].z, qf[2], a);
         out[j] = fmaf(r.s[j].w, qf[3], a);
     }
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-#pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) out[j] += __shfl_xor_sync(0xffffffffu, out[j], off);
-    }
+    return tree4(out[0], out[1], out[2], out[3], lane);
 }
 
 __device__ __forceinline__ void load_bf16x4(const __nv_bfloat16* p, float out[4]) {
@@ -181,18 +198,15 @@ gdn_step_kernel(const __nv_bfloat16* __restrict__ qk, const __nv_bfloat16* __res
         r.s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + base + j * kGdnDim));
     const float decay = gdn_decay(projection[kGdnAOff + head], dt_bias[head], a_log[head]);
     const float beta = gdn_beta(projection[kGdnBOff + head]);
-    float kf[4], qf[4], v[4], out[4];
+    float kf[4], qf[4], v[4];
     load_bf16x4(qk + (head >> 1) * kGdnDim + lane * 4u, qf);
     load_bf16x4(qk + kGdnKOff + (head >> 1) * kGdnDim + lane * 4u, kf);
     load_bf16x4(value + head * kGdnDim + row0, v);
-    delta_rule_rows4(r, kf, qf, v, decay, beta, out);
+    const float mine = delta_rule_rows4(r, kf, qf, v, decay, beta, lane);
 #pragma unroll
     for (uint32_t j = 0; j < 4; ++j)
         __stcs(reinterpret_cast<float4*>(state_out + base + j * kGdnDim), r.s[j]);
-    if (lane < 4u) {
-        const float mine = lane == 0 ? out[0] : lane == 1 ? out[1] : lane == 2 ? out[2] : out[3];
-        y[head * kGdnDim + row0 + lane] = f2bf(mine);
-    }
+    if (lane < 4u) y[head * kGdnDim + row0 + tree4_row(lane)] = f2bf(mine);
 }
 
 // Weighted per-head RMSNorm of y times SiLU(z) (gdn.metal:174-207): one warp per head.
@@ -240,9 +254,37 @@ struct GdnLanes {
     tatara_gdn_lane lane[TATARA_MAX_LANES];
 };
 
+// Two data paths for the 64 KiB of state a CTA reads and rewrites (same arithmetic, same bits):
+// kBulk = false: every lane loads its float4 of a row into registers (16 rows per warp in flight) and
+// stores it back with st.global.cs.  The CTA's 512 row requests then sit in the load/store unit's
+// queue ahead of everything requested later (the projection entries that arrive after the
+// dependency wait).  kBulk = true: lane 0 of each warp asks the copy engine for its warp's 16 rows
+// as two 4 KiB cp.async.bulk copies into shared memory, completing on two mbarriers, and sends the
+// updated rows back the same way; the small requests of the prologue never queue behind them.
+constexpr uint32_t kFdStateBytes = kGdnDim * kGdnDim * 4u;      // one head's state: 64 KiB
+constexpr uint32_t kFdHalfBytes = 8u * kGdnDim * 4u;            // 8 rows of a warp: 4 KiB
+constexpr uint32_t kFdSmem = kFdStateBytes + 16u * 8u + 16u;    // + two mbarriers per warp + the abort word
+
+__device__ __forceinline__ void bulk_load_stream(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "{\n .reg .b64 pol;\n createpolicy.fractional.L2::evict_first.b64 pol, 1.0;\n"
+        " cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], pol;\n}"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_store_stream(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile(
+        "{\n .reg .b64 pol;\n createpolicy.fractional.L2::evict_first.b64 pol, 1.0;\n"
+        " cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, pol;\n}"
+        ::"l"(dst), "r"(src), "r"(bytes)
+        : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 // `projection` is NOT __restrict__: it is written by the predecessor this kernel waits for, and a
 // const __restrict__ pointer lets the compiler treat its loads as invariant and move them above
 // griddepcontrol.wait (seen once: garbage rows whenever the projection kernel was still running).
+template <bool kBulk>
 __global__ void __launch_bounds__(256)
 gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_stride,
                         const __nv_bfloat16* __restrict__ conv_weights,
@@ -250,13 +292,18 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
                         const __nv_bfloat16* __restrict__ norm_weight, __nv_bfloat16* conv_pool,
                         float* rec_pool, __nv_bfloat16* __restrict__ y_out,
                         __nv_bfloat16* __restrict__ gated, const __grid_constant__ GdnLanes lanes,
-                        const tatara_gdn_lane* lanes_device) {
+                        const tatara_gdn_lane* lanes_device, uint32_t* status, uint32_t late_half) {
+    extern __shared__ __align__(128) uint8_t fd_smem[];   // kBulk: [128 rows][128] f32, mbarriers, abort word
     __shared__ float head_q[kGdnDim], head_k[kGdnDim];
     __shared__ float qn[kGdnDim], kn[kGdnDim], vn[kGdnDim], ys[kGdnDim];
     const uint32_t head = blockIdx.x, row_lane = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     // the lane table of this call, or the one kept in device memory (CUDA-graph replay)
-    const tatara_gdn_lane gl = lanes_device != nullptr ? lanes_device[row_lane] : lanes.lane[row_lane];
+    // (both sources are read without a branch between them: the parameter table entry and the
+    // pointer sit in different lines of the cold constant bank, and a branch on the pointer would
+    // put the two misses one after the other -- 1100 cycles before the first request left the SM)
+    tatara_gdn_lane gl = lanes.lane[row_lane];
+    if (lanes_device != nullptr) gl = lanes_device[row_lane];
     const __nv_bfloat16* proj = projection + row_lane * projection_stride;
     const __nv_bfloat16* conv_in = conv_pool + gl.conv_in;
     __nv_bfloat16* conv_out = conv_pool + gl.conv_out;
@@ -284,12 +331,37 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     // overlaps the conv / norm prologue, and the few small requests above are not queued behind it.
     const uint32_t row_base = warp * 16u;
     const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
-    Rows4 rows[4];
+    Rows4 rows[kBulk ? 1 : 4];
+    float* st = reinterpret_cast<float*>(fd_smem);
+    const uint32_t fd_bars = s2u(fd_smem + kFdStateBytes) + warp * 16u;   // this warp's two mbarriers
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(fd_smem + kFdStateBytes + 128u);
+    if constexpr (kBulk) {
+        if (threadIdx.x == 0) *abort_flag = 0u;   // read only after the prologue's __syncthreads
+        if (lane == 0) {
+            mbar_init(fd_bars, 1);
+            mbar_init(fd_bars + 8u, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            // The first eight rows now.  With few lanes (one wave of CTAs, `late_half`) the other eight are
+            // asked for after the projection entries (below): behind the whole 64 KiB of every CTA
+            // those few small requests took 1.8 us to answer.  With many lanes the CTAs of a later wave
+            // overlap that wait anyway, and a CTA that asks late only holds its SM longer.
+            mbar_expect_tx(fd_bars, kFdHalfBytes);
+            bulk_load_stream(s2u(st + row_base * kGdnDim), state_in + (uint64_t(head) * kGdnDim + row_base) * kGdnDim,
+                             kFdHalfBytes, fd_bars);
+            if (!late_half) {
+                mbar_expect_tx(fd_bars + 8u, kFdHalfBytes);
+                bulk_load_stream(s2u(st + (row_base + 8u) * kGdnDim),
+                                 state_in + (uint64_t(head) * kGdnDim + row_base + 8u) * kGdnDim, kFdHalfBytes,
+                                 fd_bars + 8u);
+            }
+        }
+    } else {
 #pragma unroll
-    for (uint32_t batch = 0; batch < 4; ++batch)
+        for (uint32_t batch = 0; batch < 4; ++batch)
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j)
-            rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
+            for (uint32_t j = 0; j < 4; ++j)
+                rows[batch].s[j] = __ldcs(reinterpret_cast<const float4*>(state_in + sbase + (batch * 4u + j) * kGdnDim));
+    }
     // Launched as a programmatic dependent of its predecessor in the stream (the projection that
     // produces `projection`): what is read above is this layer's own state and weights, which that
     // predecessor does not write, so those loads are in flight while the predecessor finishes; the
@@ -306,6 +378,14 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     const __nv_bfloat16 a_raw = proj[kGdnAOff + head], b_raw = proj[kGdnBOff + head];
     float zf[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (warp == 0) load_bf16x4(proj + kGdnZOff + head * kGdnDim + lane * 4u, zf);
+    if constexpr (kBulk) {
+        if (lane == 0 && late_half) {
+            mbar_expect_tx(fd_bars + 8u, kFdHalfBytes);
+            bulk_load_stream(s2u(st + (row_base + 8u) * kGdnDim),
+                             state_in + (uint64_t(head) * kGdnDim + row_base + 8u) * kGdnDim, kFdHalfBytes,
+                             fd_bars + 8u);
+        }
+    }
     const __nv_bfloat16 act = conv_channel_apply(taps, qk_w);
     if ((head & 1u) == 0u) {
 #pragma unroll
@@ -329,20 +409,41 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
         kf[i] = kn[lane * 4u + i];
         qf[i] = qn[lane * 4u + i];
     }
+    bool ok = true;
 #pragma unroll
     for (uint32_t batch = 0; batch < 4; ++batch) {
-        Rows4& r = rows[batch];
-        float v[4], out[4];
+        if constexpr (kBulk) {
+            // rows 8h .. 8h+7 of this warp have landed (bounded wait; a warp that gives up computes nothing more)
+            if ((batch & 1u) == 0u && ok) {
+                __syncwarp();   // lane 0 initialised the barrier
+                ok = mbar_wait(fd_bars + 8u * (batch >> 1), 0, abort_flag);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j)
+                rows[0].s[j] = *reinterpret_cast<const float4*>(st + (row_base + batch * 4u + j) * kGdnDim + lane * 4u);
+        }
+        Rows4& r = rows[kBulk ? 0 : batch];
+        float v[4];
 #pragma unroll
         for (uint32_t j = 0; j < 4; ++j) v[j] = vn[row_base + batch * 4u + j];
-        delta_rule_rows4(r, kf, qf, v, decay, beta, out);
+        const float mine = delta_rule_rows4(r, kf, qf, v, decay, beta, lane);
+        if constexpr (kBulk) {
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j)
-            __stcs(reinterpret_cast<float4*>(state_out + sbase + (batch * 4u + j) * kGdnDim), r.s[j]);
-        if (lane < 4u) {
-            const float mine = lane == 0 ? out[0] : lane == 1 ? out[1] : lane == 2 ? out[2] : out[3];
-            ys[row_base + batch * 4u + lane] = bf2f(f2bf(mine));
+            for (uint32_t j = 0; j < 4; ++j)
+                *reinterpret_cast<float4*>(st + (row_base + batch * 4u + j) * kGdnDim + lane * 4u) = r.s[j];
+            if (batch & 1u) {   // eight updated rows: back to the state through the copy engine
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0 && ok)
+                    bulk_store_stream(state_out + (uint64_t(head) * kGdnDim + row_base + 8u * (batch >> 1)) * kGdnDim,
+                                      s2u(st + (row_base + 8u * (batch >> 1)) * kGdnDim), kFdHalfBytes);
+            }
+        } else {
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j)
+                __stcs(reinterpret_cast<float4*>(state_out + sbase + (batch * 4u + j) * kGdnDim), r.s[j]);
         }
+        if (lane < 4u) ys[row_base + batch * 4u + tree4_row(lane)] = bf2f(f2bf(mine));
     }
     __syncthreads();
     if (warp == 0) {
@@ -357,6 +458,14 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
             *reinterpret_cast<uint2*>(y_out + obase + lane * 4u) = *reinterpret_cast<const uint2*>(yb);
         }
         gate_norm_head_loaded(yv, zf, norm_w, gated + obase, lane);
+    }
+    if constexpr (kBulk) {
+        // the copies out of this CTA's shared memory must have completed before it is released
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (threadIdx.x == 0 && *abort_flag) {
+            atomicCAS(status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+            status[kStatusDetail] = blockIdx.y * kGdnValueHeads + blockIdx.x;
+        }
     }
 }
 
@@ -444,6 +553,40 @@ extern "C" tatara_status tatara_gdn_gate_norm(tatara_ctx* ctx, void* stream, con
     return check_launch(ctx, "gdn_gate_norm");
 }
 
+// One launch of the fused step: the form is the context's TATARA_POLICY_GDN_DECODE_FORM.
+static tatara_status launch_fused_step(tatara_ctx* ctx, void* stream, const void* projection, uint32_t projection_stride,
+                                       const void* conv_weights, const void* a_log, const void* dt_bias,
+                                       const void* norm_weight, void* conv_pool, void* rec_pool, const GdnLanes& table,
+                                       const tatara_gdn_lane* lanes_device, uint32_t n_lanes, void* y, void* gated,
+                                       const char* what) {
+    const bool bulk = ctx->gdn_decode_form == 0u;
+    static bool configured[64] = {false};
+    if (bulk && !configured[ctx->device & 63]) {
+        if (cudaFuncSetAttribute(gdn_decode_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmem) !=
+            cudaSuccess)
+            return check_launch(ctx, "gdn_decode_batch: shared memory attribute");
+        configured[ctx->device & 63] = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kGdnValueHeads, n_lanes);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = bulk ? kFdSmem : 0;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, bulk ? gdn_decode_fused_kernel<true> : gdn_decode_fused_kernel<false>,
+                             static_cast<const bf16*>(projection), uint64_t(projection_stride),
+                             static_cast<const bf16*>(conv_weights), static_cast<const bf16*>(a_log),
+                             static_cast<const bf16*>(dt_bias), static_cast<const bf16*>(norm_weight),
+                             static_cast<bf16*>(conv_pool), static_cast<float*>(rec_pool), static_cast<bf16*>(y),
+                             static_cast<bf16*>(gated), table, lanes_device, ctx->device_status,
+                             n_lanes * kGdnValueHeads <= 2u * uint32_t(ctx->sm_count) ? 1u : 0u);
+    return check_launch(ctx, what);
+}
+
 extern "C" tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, const void* projection,
                                                  uint32_t projection_stride, const void* conv_weights,
                                                  const void* a_log, const void* dt_bias,
@@ -470,22 +613,8 @@ extern "C" tatara_status tatara_gdn_decode_batch(tatara_ctx* ctx, void* stream, 
             return fail(ctx, TATARA_INVALID_BUFFER, "gdn_decode_batch: recurrent offset alignment");
         table.lane[i] = l;
     }
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(kGdnValueHeads, n_lanes);
-    cfg.blockDim = dim3(256);
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    (void)cudaLaunchKernelEx(&cfg, gdn_decode_fused_kernel, static_cast<const bf16*>(projection),
-                             uint64_t(projection_stride), static_cast<const bf16*>(conv_weights),
-                             static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
-                             static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool),
-                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), table,
-                             static_cast<const tatara_gdn_lane*>(nullptr));
-    return check_launch(ctx, "gdn_decode_batch");
+    return launch_fused_step(ctx, stream, projection, projection_stride, conv_weights, a_log, dt_bias, norm_weight,
+                             conv_pool, rec_pool, table, nullptr, n_lanes, y, gated, "gdn_decode_batch");
 }
 
 extern "C" tatara_status tatara_gdn_decode_batch_indirect(tatara_ctx* ctx, void* stream, const void* projection,
@@ -508,20 +637,6 @@ extern "C" tatara_status tatara_gdn_decode_batch_indirect(tatara_ctx* ctx, void*
     // The offsets are the caller's (written once when the table is created; tatara_lanes_advance only
     // swaps them): in != out and 16-byte alignment of the recurrent offsets are the caller's contract.
     const GdnLanes unused{};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(kGdnValueHeads, n_lanes);
-    cfg.blockDim = dim3(256);
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    (void)cudaLaunchKernelEx(&cfg, gdn_decode_fused_kernel, static_cast<const bf16*>(projection),
-                             uint64_t(projection_stride), static_cast<const bf16*>(conv_weights),
-                             static_cast<const bf16*>(a_log), static_cast<const bf16*>(dt_bias),
-                             static_cast<const bf16*>(norm_weight), static_cast<bf16*>(conv_pool),
-                             static_cast<float*>(rec_pool), static_cast<bf16*>(y), static_cast<bf16*>(gated), unused,
-                             lanes_device);
-    return check_launch(ctx, "gdn_decode_batch_indirect");
+    return launch_fused_step(ctx, stream, projection, projection_stride, conv_weights, a_log, dt_bias, norm_weight,
+                             conv_pool, rec_pool, unused, lanes_device, n_lanes, y, gated, "gdn_decode_batch_indirect");
 }

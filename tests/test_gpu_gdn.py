@@ -209,6 +209,35 @@ def test_fused_equals_unfused_ops(ctx):
     assert torch.equal(rec_pool[0, 1], s2) and torch.equal(conv_pool[0, 1], new_conv)
 
 
+@pytest.mark.parametrize("n", [3, 12])
+def test_fused_decode_forms_bit_identical(ctx, n):
+    """TATARA_POLICY_GDN_DECODE_FORM: the copy-engine data path (default; with few lanes half of the state is
+    requested after the projection entries, with many all of it first) and the per-lane register path give
+    the same bits in y, gated, the recurrent state and the conv state over two tokens."""
+    rng = np.random.default_rng(31 + n)
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    _, _, conv_pool, rec_pool = make_pools(rng, n)
+    projs = [dev_bf16(syn.gdn_projection(rng, n)) for _ in range(2)]
+    results = []
+    assert ctx.get_policy(tb.POLICY_GDN_DECODE_FORM) == 0
+    for form in (0, 1):
+        ctx.set_policy(tb.POLICY_GDN_DECODE_FORM, form)
+        try:
+            cp, rp = conv_pool.clone(), rec_pool.clone()
+            outs = []
+            for token in range(2):
+                y, gated = bf((n, 4096)), bf((n, 4096))
+                ctx.gdn_decode_batch(projs[token], w[0], w[1], w[2], w[3], cp, rp, lane_table(n, token % 2 == 1), y, gated)
+                outs += [y, gated]
+            ctx.sync()
+        finally:
+            ctx.set_policy(tb.POLICY_GDN_DECODE_FORM, 0)
+        results.append(outs + [cp, rp])
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("rows", [1, 5, 200])
 def test_sequential_scan_prefill_matches_oracle(ctx, rows):
     rng = np.random.default_rng(30 + rows)
