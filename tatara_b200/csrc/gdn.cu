@@ -176,6 +176,62 @@ __device__ __forceinline__ float delta_rule_rows4(Rows4& r, const float kf[4], c
     return tree4(out[0], out[1], out[2], out[3], lane);
 }
 
+// Two independent groups of four rows, level by level: the dependent chain is as long as for
+// one group (the shuffle unit answers in about 25 cycles per level and a warp issues in order), the
+// additions are the same.
+__device__ __forceinline__ void tree4x2(const float x[4], const float y[4], uint32_t lane, float& tx, float& ty) {
+    const bool odd = (lane & 1u) != 0u, upper = (lane & 2u) != 0u;
+    const float xa = (odd ? x[2] : x[0]) + __shfl_xor_sync(0xffffffffu, odd ? x[0] : x[2], 1);
+    const float xb = (odd ? x[3] : x[1]) + __shfl_xor_sync(0xffffffffu, odd ? x[1] : x[3], 1);
+    const float ya = (odd ? y[2] : y[0]) + __shfl_xor_sync(0xffffffffu, odd ? y[0] : y[2], 1);
+    const float yb = (odd ? y[3] : y[1]) + __shfl_xor_sync(0xffffffffu, odd ? y[1] : y[3], 1);
+    tx = (upper ? xb : xa) + __shfl_xor_sync(0xffffffffu, upper ? xa : xb, 2);
+    ty = (upper ? yb : ya) + __shfl_xor_sync(0xffffffffu, upper ? ya : yb, 2);
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        const float px = __shfl_xor_sync(0xffffffffu, tx, off), py = __shfl_xor_sync(0xffffffffu, ty, off);
+        tx += px;
+        ty += py;
+    }
+}
+// Eight rows (two groups of four) through one delta-rule step; returns the outputs of rows
+// tree4_row(lane) of the first and of the second group.
+__device__ __forceinline__ void delta_rule_rows8(Rows4& ra, Rows4& rb, const float kf[4], const float qf[4],
+                                                 const float va[4], const float vb[4], float decay, float beta,
+                                                 uint32_t lane, float& out_a, float& out_b) {
+    float ka[4], kb[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        ra.s[j].x *= decay; ra.s[j].y *= decay; ra.s[j].z *= decay; ra.s[j].w *= decay;
+        rb.s[j].x *= decay; rb.s[j].y *= decay; rb.s[j].z *= decay; rb.s[j].w *= decay;
+        float a = ra.s[j].x * kf[0], b = rb.s[j].x * kf[0];
+        a = fmaf(ra.s[j].y, kf[1], a); b = fmaf(rb.s[j].y, kf[1], b);
+        a = fmaf(ra.s[j].z, kf[2], a); b = fmaf(rb.s[j].z, kf[2], b);
+        ka[j] = fmaf(ra.s[j].w, kf[3], a); kb[j] = fmaf(rb.s[j].w, kf[3], b);
+    }
+    float ta, tb_;
+    tree4x2(ka, kb, lane, ta, tb_);
+    const uint32_t quad = lane & ~3u;
+    ka[0] = __shfl_sync(0xffffffffu, ta, quad);       kb[0] = __shfl_sync(0xffffffffu, tb_, quad);
+    ka[2] = __shfl_sync(0xffffffffu, ta, quad | 1u);  kb[2] = __shfl_sync(0xffffffffu, tb_, quad | 1u);
+    ka[1] = __shfl_sync(0xffffffffu, ta, quad | 2u);  kb[1] = __shfl_sync(0xffffffffu, tb_, quad | 2u);
+    ka[3] = __shfl_sync(0xffffffffu, ta, quad | 3u);  kb[3] = __shfl_sync(0xffffffffu, tb_, quad | 3u);
+    float oa[4], ob[4];
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        const float da = (va[j] - ka[j]) * beta, db = (vb[j] - kb[j]) * beta;
+        ra.s[j].x = fmaf(kf[0], da, ra.s[j].x); rb.s[j].x = fmaf(kf[0], db, rb.s[j].x);
+        ra.s[j].y = fmaf(kf[1], da, ra.s[j].y); rb.s[j].y = fmaf(kf[1], db, rb.s[j].y);
+        ra.s[j].z = fmaf(kf[2], da, ra.s[j].z); rb.s[j].z = fmaf(kf[2], db, rb.s[j].z);
+        ra.s[j].w = fmaf(kf[3], da, ra.s[j].w); rb.s[j].w = fmaf(kf[3], db, rb.s[j].w);
+        float a = ra.s[j].x * qf[0], b = rb.s[j].x * qf[0];
+        a = fmaf(ra.s[j].y, qf[1], a); b = fmaf(rb.s[j].y, qf[1], b);
+        a = fmaf(ra.s[j].z, qf[2], a); b = fmaf(rb.s[j].z, qf[2], b);
+        oa[j] = fmaf(ra.s[j].w, qf[3], a); ob[j] = fmaf(rb.s[j].w, qf[3], b);
+    }
+    tree4x2(oa, ob, lane, out_a, out_b);
+}
+
 __device__ __forceinline__ void load_bf16x4(const __nv_bfloat16* p, float out[4]) {
     const uint2 raw = *reinterpret_cast<const uint2*>(p);
     const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
@@ -331,7 +387,7 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     // overlaps the conv / norm prologue, and the few small requests above are not queued behind it.
     const uint32_t row_base = warp * 16u;
     const uint64_t sbase = (uint64_t(head) * kGdnDim + row_base) * kGdnDim + lane * 4u;
-    Rows4 rows[kBulk ? 1 : 4];
+    Rows4 rows[kBulk ? 1 : 4];   // the register path keeps all 16 rows of the warp here
     float* st = reinterpret_cast<float*>(fd_smem);
     const uint32_t fd_bars = s2u(fd_smem + kFdStateBytes) + warp * 16u;   // this warp's two mbarriers
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(fd_smem + kFdStateBytes + 128u);
@@ -411,39 +467,49 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     }
     bool ok = true;
 #pragma unroll
-    for (uint32_t batch = 0; batch < 4; ++batch) {
+    for (uint32_t half = 0; half < 2; ++half) {   // eight rows at a time: two groups of four, level by level
+        const uint32_t r8 = row_base + half * 8u;
+        Rows4 local[kBulk ? 2 : 1];
         if constexpr (kBulk) {
             // rows 8h .. 8h+7 of this warp have landed (bounded wait; a warp that gives up computes nothing more)
-            if ((batch & 1u) == 0u && ok) {
+            if (ok) {
                 __syncwarp();   // lane 0 initialised the barrier
-                ok = mbar_wait(fd_bars + 8u * (batch >> 1), 0, abort_flag);
+                ok = mbar_wait(fd_bars + 8u * half, 0, abort_flag);
             }
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j)
-                rows[0].s[j] = *reinterpret_cast<const float4*>(st + (row_base + batch * 4u + j) * kGdnDim + lane * 4u);
+            for (uint32_t j = 0; j < 8; ++j)
+                local[j >> 2].s[j & 3u] = *reinterpret_cast<const float4*>(st + (r8 + j) * kGdnDim + lane * 4u);
         }
-        Rows4& r = rows[kBulk ? 0 : batch];
-        float v[4];
+        Rows4& ra = kBulk ? local[0] : rows[kBulk ? 0 : half * 2u];
+        Rows4& rb = kBulk ? local[kBulk ? 1 : 0] : rows[kBulk ? 0 : half * 2u + 1u];
+        float va[4], vb[4], out_a, out_b;
 #pragma unroll
-        for (uint32_t j = 0; j < 4; ++j) v[j] = vn[row_base + batch * 4u + j];
-        const float mine = delta_rule_rows4(r, kf, qf, v, decay, beta, lane);
+        for (uint32_t j = 0; j < 4; ++j) {
+            va[j] = vn[r8 + j];
+            vb[j] = vn[r8 + 4u + j];
+        }
+        delta_rule_rows8(ra, rb, kf, qf, va, vb, decay, beta, lane, out_a, out_b);
         if constexpr (kBulk) {
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j)
-                *reinterpret_cast<float4*>(st + (row_base + batch * 4u + j) * kGdnDim + lane * 4u) = r.s[j];
-            if (batch & 1u) {   // eight updated rows: back to the state through the copy engine
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0 && ok)
-                    bulk_store_stream(state_out + (uint64_t(head) * kGdnDim + row_base + 8u * (batch >> 1)) * kGdnDim,
-                                      s2u(st + (row_base + 8u * (batch >> 1)) * kGdnDim), kFdHalfBytes);
-            }
+            for (uint32_t j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(st + (r8 + j) * kGdnDim + lane * 4u) = local[j >> 2].s[j & 3u];
+            // eight updated rows: back to the state through the copy engine
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && ok)
+                bulk_store_stream(state_out + (uint64_t(head) * kGdnDim + r8) * kGdnDim, s2u(st + r8 * kGdnDim),
+                                  kFdHalfBytes);
         } else {
 #pragma unroll
-            for (uint32_t j = 0; j < 4; ++j)
-                __stcs(reinterpret_cast<float4*>(state_out + sbase + (batch * 4u + j) * kGdnDim), r.s[j]);
+            for (uint32_t j = 0; j < 4; ++j) {
+                __stcs(reinterpret_cast<float4*>(state_out + sbase + (half * 8u + j) * kGdnDim), ra.s[j]);
+                __stcs(reinterpret_cast<float4*>(state_out + sbase + (half * 8u + 4u + j) * kGdnDim), rb.s[j]);
+            }
         }
-        if (lane < 4u) ys[row_base + batch * 4u + tree4_row(lane)] = bf2f(f2bf(mine));
+        if (lane < 4u) {
+            ys[r8 + tree4_row(lane)] = bf2f(f2bf(out_a));
+            ys[r8 + 4u + tree4_row(lane)] = bf2f(f2bf(out_b));
+        }
     }
     __syncthreads();
     if (warp == 0) {
