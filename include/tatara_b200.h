@@ -107,7 +107,13 @@ typedef enum tatara_policy {
     /* How the fused GDN decode step (tatara_gdn_decode_batch, _indirect) moves the 64 KiB of state each CTA
      * reads and rewrites: 0 = cp.async.bulk copies through shared memory, 1 = per-lane loads into registers and
      * streaming stores.  Same arithmetic: the outputs are bit-identical. */
-    TATARA_POLICY_GDN_DECODE_FORM = 3
+    TATARA_POLICY_GDN_DECODE_FORM = 3,
+    /* Where the records of a single-lane tatara_attn_decode are merged: 0 (default) = in a second kernel that is
+     * staged while the partition kernel runs, as the batched and the split calls do; 1 = in the partition kernel's
+     * own launch (its CTAs count their finished items and then take the 64 (head, quarter) pieces).  Same
+     * arithmetic in the same order: bit-identical.  Measured slower by 0.4 - 2 us at every context (the merge
+     * then runs on 4 warps per piece behind two more trips to L2), which is why it is not the default. */
+    TATARA_POLICY_DECODE_FUSED_MERGE = 4
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

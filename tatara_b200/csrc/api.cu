@@ -63,7 +63,9 @@ tatara_status tatara_ctx_create(int device, tatara_ctx** out) {
     if (cudaMalloc(&ctx->device_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
         cudaMemset(ctx->device_status, 0, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
         cudaMallocHost(&ctx->host_status, tb::kStatusWords * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMalloc(&ctx->lane_schedule, tb::kLaneScheduleBytes) != cudaSuccess) {
+        cudaMalloc(&ctx->lane_schedule, tb::kLaneScheduleBytes) != cudaSuccess ||
+        cudaMalloc(&ctx->merge_counters, tb::kMergeCounterSlots * 2 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(ctx->merge_counters, 0, tb::kMergeCounterSlots * 2 * sizeof(uint32_t)) != cudaSuccess) {
         (void)cudaGetLastError();
         tatara_ctx_destroy(ctx);
         return TATARA_CUDA_ERROR;
@@ -78,6 +80,7 @@ void tatara_ctx_destroy(tatara_ctx* ctx) {
     if (ctx->device_status != nullptr) cudaFree(ctx->device_status);
     if (ctx->host_status != nullptr) cudaFreeHost(ctx->host_status);
     if (ctx->lane_schedule != nullptr) cudaFree(ctx->lane_schedule);
+    if (ctx->merge_counters != nullptr) cudaFree(ctx->merge_counters);
     delete ctx;
 }
 
@@ -127,6 +130,10 @@ tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint6
         if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: decode form");
         ctx->gdn_decode_form = static_cast<uint32_t>(value);
         return TATARA_OK;
+    case TATARA_POLICY_DECODE_FUSED_MERGE:
+        if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: fused merge");
+        ctx->decode_fused_merge = static_cast<uint32_t>(value);
+        return TATARA_OK;
     }
     return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: unknown policy");
 }
@@ -137,6 +144,7 @@ uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy) {
     case TATARA_POLICY_GDN_CHUNK_FORM: return ctx->gdn_chunk_form;
     case TATARA_POLICY_ATTN_PREFILL_FORM: return ctx->attn_prefill_form;
     case TATARA_POLICY_GDN_DECODE_FORM: return ctx->gdn_decode_form;
+    case TATARA_POLICY_DECODE_FUSED_MERGE: return ctx->decode_fused_merge;
     }
     return 0;
 }

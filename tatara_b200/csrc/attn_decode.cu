@@ -59,6 +59,12 @@ struct DecParams {
     uint32_t n_lanes;
     uint32_t total_items;
     uint32_t l2_prefetch_keys; // K/V rows of a CTA's first item requested into L2 before the dependency wait
+    // Merge in the same launch (single lane, gated output): the CTAs count their finished items in
+    // merge_counters[0] and leave through merge_counters[1]; null = the merge is a second kernel.
+    uint32_t* merge_counters;
+    uint32_t* merge_status;
+    const __nv_bfloat16* gate;
+    __nv_bfloat16* out;
     DecLane lane[N];
 };
 
@@ -206,6 +212,163 @@ __device__ __forceinline__ void issue_slice(const SliceCursor& c, uint32_t stage
         const uint32_t dst = stage_addr + row * kRowBytes + ((lane ^ (row & 7u)) << 4);
         cp_async_16(dst, ksrc + off, live ? 16u : 0u, policy);
         cp_async_16(dst + kSliceBytes, vsrc + off, live ? 16u : 0u, policy);
+    }
+}
+
+// One CTA per (head, 64-dim quarter, lane).  The merge is defined over 32 phases: phase f sums
+// records f, f+32, ... in index order (four in flight per thread), a thread owns a float2 of the
+// quarter; then the 32 phase partials are summed in phase order.  Every order is fixed by nparts
+// alone, whatever the CTA size: a single lane runs one phase per warp (32 warps, lowest
+// latency), a batch runs four phases per warp (8 warps, many small CTAs per SM), the partition
+// kernel's own tail eight (4 warps).
+constexpr uint32_t kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
+
+// The merge of one (head, quarter): records `base + part * part_stride`, part < nparts.  Leaves the
+// 64 un-normalised sums in red_acc[0][0..63], the sum of weights in red_acc[0][64] and returns the
+// maximum; ends with a CTA barrier.  Called by every thread of a CTA of kWarps warps.
+template <uint32_t kWarps>
+__device__ __forceinline__ float merge_records(const float* base, uint64_t part_stride, uint32_t nparts,
+                                               uint32_t quarter, float* red_max,
+                                               float (*red_acc)[kCombineDims + 1]) {
+    constexpr uint32_t kCombineThreads = kWarps * 32u;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t d = quarter * kCombineDims + lane * 2u;
+    constexpr uint32_t kOwn = kCombinePhases / kWarps, kRound = kCombinePhases * kCombineUnroll;
+    // The first round of records (parts 0..127: every record of a lane cut by tb::partition_keys)
+    // is requested before the maximum is known, so the merge costs one trip to L2, not two.
+    // (ld.global.cg: the records were written by other CTAs, possibly of this same launch)
+    float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
+    float2 v[kOwn][kCombineUnroll];
+    auto load_round = [&](uint32_t round) {
+#pragma unroll
+        for (uint32_t j = 0; j < kOwn; ++j) {
+#pragma unroll
+            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+                const uint32_t part = round + (warp + j * kWarps) + u * kCombinePhases;
+                const bool live = part < nparts;
+                const float* rec = base + (live ? part : 0u) * part_stride;
+                lm[j][u] = live ? __ldcg(rec + kHeadDim) : -INFINITY;
+                ls[j][u] = __ldcg(rec + kHeadDim + 1u);
+                v[j][u] = __ldcg(reinterpret_cast<const float2*>(rec + d));
+            }
+        }
+    };
+    load_round(0);
+    float big = -INFINITY;
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j)
+#pragma unroll
+        for (uint32_t u = 0; u < kCombineUnroll; ++u) big = fmaxf(big, lm[j][u]);
+    for (uint32_t part = kRound + threadIdx.x; part < nparts; part += kCombineThreads)
+        big = fmaxf(big, __ldcg(base + part * part_stride + kHeadDim));
+#pragma unroll
+    for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    if (lane == 0) red_max[warp] = big;
+    __syncthreads();
+    big = red_max[0];
+#pragma unroll
+    for (uint32_t i = 1; i < kWarps; ++i) big = fmaxf(big, red_max[i]);
+
+    // One accumulator set per phase this warp owns.
+    float a0[kOwn], a1[kOwn], denom[kOwn];
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j) a0[j] = a1[j] = denom[j] = 0.0f;
+    for (uint32_t round = 0; round < nparts; round += kRound) {
+        if (round != 0) load_round(round);
+#pragma unroll
+        for (uint32_t j = 0; j < kOwn; ++j) {
+#pragma unroll
+            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
+                const float w = lm[j][u] == -INFINITY ? 0.0f : expf(lm[j][u] - big);
+                a0[j] = fmaf(w, v[j][u].x, a0[j]);
+                a1[j] = fmaf(w, v[j][u].y, a1[j]);
+                denom[j] = fmaf(w, ls[j][u], denom[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t j = 0; j < kOwn; ++j) {
+        const uint32_t phase = warp + j * kWarps;
+        red_acc[phase][lane * 2u] = a0[j];
+        red_acc[phase][lane * 2u + 1u] = a1[j];
+        if (lane == 0) red_acc[phase][kCombineDims] = denom[j];
+    }
+    __syncthreads();
+    if (threadIdx.x < kCombineDims + 1u) {
+        float total = 0.0f;
+#pragma unroll
+        for (uint32_t ph = 0; ph < kCombinePhases; ++ph) total += red_acc[ph][threadIdx.x];
+        red_acc[0][threadIdx.x] = total;
+    }
+    __syncthreads();
+    return big;
+}
+
+// The merge in the partition kernel's own launch (one lane, gated output).  Every CTA adds the items it
+// has finished to merge_counters[0] (its record stores made visible first); CTA c then takes the
+// (head, quarter) pieces c, c + grid, ... of the 64: waits, with a time limit, until the counter has
+// reached the lane's item count, merges with the arithmetic of attn_combine_kernel (merge_records,
+// eight phases per warp) and stores the gated output.  All CTAs of the grid are resident together
+// (at most one per SM, and the grid is never larger than the SM count), so the wait is for CTAs that
+// are running.  The last CTA to leave puts both counters back to zero for the next launch.  The
+// scratch the merge needs lies over the first warp's K/V ring, which is dead by then.
+constexpr unsigned long long kMergeWaitLimitNs = 2000000000ull;
+template <uint32_t N>
+__device__ __forceinline__ void fused_merge_tail(const DecParams<N>& p, uint8_t* smem, uint32_t total_items) {
+    __syncthreads();   // every record of this CTA's items is written, every ring slot is idle
+    float* red_max = reinterpret_cast<float*>(smem);
+    float (*red_acc)[kCombineDims + 1] = reinterpret_cast<float (*)[kCombineDims + 1]>(smem + 128);
+    volatile uint32_t* arrived = reinterpret_cast<volatile uint32_t*>(smem + 128 + kCombinePhases * (kCombineDims + 1) * 4);
+    if (threadIdx.x == 0) {
+        const uint32_t mine = blockIdx.x < total_items ? (total_items - 1u - blockIdx.x) / gridDim.x + 1u : 0u;
+        if (mine != 0u) {
+            __threadfence();
+            atomicAdd(p.merge_counters, mine);
+        }
+    }
+    const DecLane& dl = p.lane[0];
+    for (uint32_t piece = blockIdx.x; piece < kQHeads * 4u; piece += gridDim.x) {
+        const uint32_t head = piece >> 2, quarter = piece & 3u;
+        const uint64_t at = dl.row * p.query_stride + head * kHeadDim + quarter * kCombineDims + threadIdx.x;
+        float gate_logit = 0.0f;
+        if (threadIdx.x < kCombineDims) gate_logit = bf2f(p.gate[at]);
+        if (threadIdx.x == 0) {
+            unsigned long long t0 = 0;
+            uint32_t ok = 1u;
+            for (uint32_t spin = 0;; ++spin) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.merge_counters) : "memory");
+                if (v >= total_items) break;
+                __nanosleep(20);
+                if ((spin & 255u) == 255u) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > kMergeWaitLimitNs) {
+                        ok = 0u;
+                        atomicCAS(p.merge_status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+                        p.merge_status[kStatusDetail] = blockIdx.x;
+                        break;
+                    }
+                }
+            }
+            *arrived = ok;
+        }
+        __syncthreads();
+        if (*arrived == 0u) break;   // nothing more is written by this CTA
+        const float* base = p.records + dl.rec_offset + uint64_t(head) * dl.nparts * kRecordFloats;
+        (void)merge_records<kDecWarps>(base, kRecordFloats, dl.nparts, quarter, red_max, red_acc);
+        if (threadIdx.x < kCombineDims) {
+            const float acc = red_acc[0][threadIdx.x], total = red_acc[0][kCombineDims];
+            p.out[at] = f2bf((acc / total) * (1.0f / (1.0f + expf(-gate_logit))));
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (atomicAdd(p.merge_counters + 1, 1u) == gridDim.x - 1u) {   // nobody reads the counters any more
+            p.merge_counters[0] = 0u;
+            p.merge_counters[1] = 0u;
+        }
     }
 }
 
@@ -441,6 +604,9 @@ attn_decode_partition_kernel(const __grid_constant__ DecParams<N> p) {
         __syncthreads();
     }
     cp_async_wait<0>();
+    if constexpr (N == 1 && !kInd) {
+        if (p.merge_counters != nullptr) fused_merge_tail<N>(p, smem, total_items);
+    }
 }
 
 // ---- combine ---------------------------------------------------------------------------
@@ -508,19 +674,13 @@ __device__ __forceinline__ unsigned long long combine_now_ns() {
     return t;
 }
 
-// One CTA per (head, 64-dim quarter, lane).  The merge is defined over 32 phases: phase f sums
-// records f, f+32, ... in index order (four in flight per thread), a thread owns a float2 of the
-// quarter; then the 32 phase partials are summed in phase order.  Every order is fixed by nparts
-// alone, whatever the CTA size: a single lane runs one phase per warp (32 warps, lowest
-// latency), a batch runs four phases per warp (8 warps, many small CTAs per SM).
-constexpr uint32_t kCombinePhases = 32, kCombineDims = 64, kCombineUnroll = 4;
 template <uint32_t N>
 constexpr uint32_t combine_warps() { return N == 1 ? 32u : 8u; }
 
 template <uint32_t N, bool kInd = false>
 __global__ void __launch_bounds__(combine_warps<N>() * 32u)
 attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
-    constexpr uint32_t kWarps = combine_warps<N>(), kCombineThreads = kWarps * 32u;
+    constexpr uint32_t kWarps = combine_warps<N>();
     __shared__ float red_max[kCombinePhases];
     __shared__ float red_acc[kCombinePhases][kCombineDims + 1];
     // The next kernel of the stream may be staged as soon as every CTA of this grid is resident:
@@ -562,82 +722,13 @@ attn_combine_kernel(const __grid_constant__ CombineParams<N> p) {
     const CombineLane& cl = kInd ? p.tables->comb[blockIdx.y] : p.lane[blockIdx.y];
     if (kInd && cl.nparts == 0u) return;   // a lane the setup kernel rejected (context beyond capacity): status is latched
     const uint32_t head = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const float* base = cl.records + head * cl.head_stride +
                         (p.px.wait_flags != nullptr ? uint64_t(px_parity) * p.px.out_parity_floats : 0ull);
-    const uint32_t nparts = cl.nparts;
-    const uint32_t d = quarter * kCombineDims + lane * 2u;
-    constexpr uint32_t kOwn = kCombinePhases / kWarps, kRound = kCombinePhases * kCombineUnroll;
     // the gate logit of the dim this thread finishes: requested now, used after the merge
     float gate_logit = 0.0f;
     if (threadIdx.x < kCombineDims && p.out != nullptr && p.gate != nullptr)
         gate_logit = bf2f(p.gate[cl.row * p.query_stride + head * kHeadDim + quarter * kCombineDims + threadIdx.x]);
-    // The first round of records (parts 0..127: every record of a lane cut by tb::partition_keys)
-    // is requested before the maximum is known, so the merge costs one trip to L2, not two.
-    float lm[kOwn][kCombineUnroll], ls[kOwn][kCombineUnroll];
-    float2 v[kOwn][kCombineUnroll];
-    auto load_round = [&](uint32_t round) {
-#pragma unroll
-        for (uint32_t j = 0; j < kOwn; ++j) {
-#pragma unroll
-            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
-                const uint32_t part = round + (warp + j * kWarps) + u * kCombinePhases;
-                const bool live = part < nparts;
-                const float* rec = base + (live ? part : 0u) * cl.part_stride;
-                lm[j][u] = live ? rec[kHeadDim] : -INFINITY;
-                ls[j][u] = rec[kHeadDim + 1u];
-                v[j][u] = *reinterpret_cast<const float2*>(rec + d);
-            }
-        }
-    };
-    load_round(0);
-    float big = -INFINITY;
-#pragma unroll
-    for (uint32_t j = 0; j < kOwn; ++j)
-#pragma unroll
-        for (uint32_t u = 0; u < kCombineUnroll; ++u) big = fmaxf(big, lm[j][u]);
-    for (uint32_t part = kRound + threadIdx.x; part < nparts; part += kCombineThreads)
-        big = fmaxf(big, base[part * cl.part_stride + kHeadDim]);
-#pragma unroll
-    for (int off = 16; off; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-    if (lane == 0) red_max[warp] = big;
-    __syncthreads();
-    big = red_max[0];
-#pragma unroll
-    for (uint32_t i = 1; i < kWarps; ++i) big = fmaxf(big, red_max[i]);
-
-    // One accumulator set per phase this warp owns.
-    float a0[kOwn], a1[kOwn], denom[kOwn];
-#pragma unroll
-    for (uint32_t j = 0; j < kOwn; ++j) a0[j] = a1[j] = denom[j] = 0.0f;
-    for (uint32_t round = 0; round < nparts; round += kRound) {
-        if (round != 0) load_round(round);
-#pragma unroll
-        for (uint32_t j = 0; j < kOwn; ++j) {
-#pragma unroll
-            for (uint32_t u = 0; u < kCombineUnroll; ++u) {
-                const float w = lm[j][u] == -INFINITY ? 0.0f : expf(lm[j][u] - big);
-                a0[j] = fmaf(w, v[j][u].x, a0[j]);
-                a1[j] = fmaf(w, v[j][u].y, a1[j]);
-                denom[j] = fmaf(w, ls[j][u], denom[j]);
-            }
-        }
-    }
-#pragma unroll
-    for (uint32_t j = 0; j < kOwn; ++j) {
-        const uint32_t phase = warp + j * kWarps;
-        red_acc[phase][lane * 2u] = a0[j];
-        red_acc[phase][lane * 2u + 1u] = a1[j];
-        if (lane == 0) red_acc[phase][kCombineDims] = denom[j];
-    }
-    __syncthreads();
-    if (threadIdx.x < kCombineDims + 1u) {
-        float total = 0.0f;
-#pragma unroll
-        for (uint32_t ph = 0; ph < kCombinePhases; ++ph) total += red_acc[ph][threadIdx.x];
-        red_acc[0][threadIdx.x] = total;
-    }
-    __syncthreads();
+    const float big = merge_records<kWarps>(base, cl.part_stride, cl.nparts, quarter, red_max, red_acc);
     if (p.px.world != 0u && p.px.ll[0] != nullptr) {
         // ---- split-KV across GPUs in this one kernel: store this rank's merged slice into every
         // rank's buffer, wait (bounded) for every rank's slice of this (head, quarter), merge the
@@ -835,7 +926,21 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
             return check_launch(ctx, "attn_decode: shared memory attribute");
         configured[ctx->device & 63] = true;
     }
-    const uint32_t grid = items < uint32_t(ctx->sm_count) ? items : uint32_t(ctx->sm_count);
+    uint32_t grid = items < uint32_t(ctx->sm_count) ? items : uint32_t(ctx->sm_count);
+    // One lane with a gated output and no exchange: the merge runs in the partition kernel's own
+    // launch (TATARA_POLICY_DECODE_FUSED_MERGE).  At least 64 CTAs then, one per (head, quarter) piece.
+    bool fused = false;
+    if constexpr (N == 1) {
+        fused = ctx->decode_fused_merge != 0u && ctx->merge_counters != nullptr && r.out != nullptr &&
+                r.record_out == nullptr && r.px == nullptr && r.gate != nullptr && ctx->sm_count >= 64;
+        if (fused) {
+            if (grid < kQHeads * 4u) grid = kQHeads * 4u;
+            dp.merge_counters = ctx->merge_counters + 2u * (ctx->merge_slot++ % kMergeCounterSlots);
+            dp.merge_status = ctx->device_status;
+            dp.gate = static_cast<const __nv_bfloat16*>(r.gate);
+            dp.out = static_cast<__nv_bfloat16*>(r.out);
+        }
+    }
     // Both kernels are launched with programmatic stream serialization: each may be staged while
     // its predecessor in the stream drains and blocks in griddepcontrol.wait until that
     // predecessor has finished (a predecessor that never signals simply finishes first).
@@ -851,7 +956,7 @@ static tatara_status launch_decode(tatara_ctx* ctx, cudaStream_t stream, const D
     cfg.numAttrs = 1;
     (void)cudaLaunchKernelEx(&cfg, attn_decode_partition_kernel<N>, dp);
     tatara_status st = check_launch(ctx, what);
-    if (st != TATARA_OK) return st;
+    if (st != TATARA_OK || fused) return st;
     cfg.gridDim = dim3(kQHeads * 4, n_lanes);
     cfg.blockDim = dim3(combine_warps<N>() * 32u);
     cfg.dynamicSmemBytes = 0;

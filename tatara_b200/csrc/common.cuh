@@ -25,6 +25,7 @@ constexpr uint32_t kSmCount = 148; // B200; the partition function is pinned to 
 
 // Device-side status word slots (ctx->device_status).
 enum : uint32_t { kStatusCode = 0, kStatusDetail = 1, kStatusWords = 4 };
+constexpr uint32_t kMergeCounterSlots = 1024;
 constexpr size_t kLaneScheduleBytes = 32768;   // holds attn_decode.cu's DecTables
 // Default of TATARA_POLICY_DECODE_L2_PREFETCH_KEYS: the most K/V rows per plane that a decode CTA asks
 // into L2 beyond its shared-memory ring before its dependency wait (512 bytes per row and plane); the
@@ -44,6 +45,9 @@ struct tatara_ctx {
     uint32_t gdn_chunk_form = 0;                                     // TATARA_POLICY_GDN_CHUNK_FORM
     uint32_t attn_prefill_form = 0;                                  // TATARA_POLICY_ATTN_PREFILL_FORM
     uint32_t gdn_decode_form = 0;                                    // TATARA_POLICY_GDN_DECODE_FORM
+    uint32_t decode_fused_merge = 0;                                 // TATARA_POLICY_DECODE_FUSED_MERGE
+    uint32_t* merge_counters = nullptr; // kMergeCounterSlots pairs of u32 in device memory, zero between launches
+    uint32_t merge_slot = 0;            // next pair (round robin: calls in flight together use different pairs)
     char error[256] = {0};
 };
 

@@ -102,6 +102,38 @@ def test_decode_matches_oracle_long_context(ctx, context):
     assert err <= 0.015625, f"decode ctx={context}: max-abs {err} above the reference's long-context gate"
 
 
+@pytest.mark.parametrize("context", [0, 16, 200, 4500, 32767, 100000])
+def test_decode_merge_in_the_partition_launch_equals_the_two_kernel_form(ctx, context):
+    """TATARA_POLICY_DECODE_FUSED_MERGE: a single-lane decode merges its records in a second kernel (default)
+    or in the partition kernel's own launch; the bits are equal, call after call (the item counters of the
+    fused form are put back to zero by the launch that used them), and nothing past the row is written."""
+    rng = np.random.default_rng(977 + context)
+    cap = context + 3
+    keys, values = syn.attn_cache(rng, context + 1, cap)
+    q, gate = syn.attn_query(rng, [context])
+    dq, dg, dk, dv = dev_bf16(q), dev_bf16(gate), dev_bf16(keys), dev_bf16(values)
+    scratch = scratch_for(context + 1)
+    assert ctx.get_policy(tb.POLICY_DECODE_FUSED_MERGE) == 0
+    launches = ctx.launches
+    two = torch.full((2, 16, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    ctx.attn_decode(dq, dg, dk, dv, context, cap, two, scratch)
+    assert ctx.launches - launches == 2          # partition kernel + merge kernel
+    fused = []
+    ctx.set_policy(tb.POLICY_DECODE_FUSED_MERGE, 1)
+    try:
+        for _ in range(3):
+            out = torch.full((2, 16, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+            ctx.attn_decode(dq, dg, dk, dv, context, cap, out, scratch)
+            fused.append(out)
+        assert ctx.launches - launches == 5      # one kernel per call
+    finally:
+        ctx.set_policy(tb.POLICY_DECODE_FUSED_MERGE, 0)
+    ctx.sync()
+    for out in fused:
+        assert torch.equal(out, two)
+    assert (two[1].float() == 7.0).all()
+
+
 @pytest.mark.parametrize("name_inputs", list(cases.attention_cases()), ids=lambda c: c[0])
 def test_decode_matches_reference_golden(ctx, name_inputs):
     """The committed outputs of the reference's own CPU model (tests/golden)."""
