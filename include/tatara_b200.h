@@ -113,7 +113,11 @@ typedef enum tatara_policy {
      * own launch (its CTAs count their finished items and then take the 64 (head, quarter) pieces).  Same
      * arithmetic in the same order: bit-identical.  Measured slower by 0.4 - 2 us at every context (the merge
      * then runs on 4 warps per piece behind two more trips to L2), which is why it is not the default. */
-    TATARA_POLICY_DECODE_FUSED_MERGE = 4
+    TATARA_POLICY_DECODE_FUSED_MERGE = 4,
+    /* How tatara_q4_project brings the weights of one to four rows in: 0 (default) = whole column groups by
+     * cp.async.bulk copies into shared memory, asked for before the dependency wait; 1 = per-lane loads two
+     * blocks ahead of the arithmetic.  Same chains and trees: bit-identical. */
+    TATARA_POLICY_Q4_ROW_FORM = 5
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

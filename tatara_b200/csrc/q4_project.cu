@@ -35,6 +35,7 @@ struct Q4Params {
     __nv_bfloat16* out;
     uint64_t x_stride, out_stride;
     uint32_t n_rows, k, n_cols, n_mats;
+    uint32_t* status;   // the context's device status words (time-outs of the bulk-copy form)
     Q4Mat mat[kQ4MaxMats];
 };
 
@@ -181,6 +182,177 @@ __global__ void __launch_bounds__(kQ4Warps * 32) q4_project_kernel(const __grid_
             sn[c] = sf[c];
             bn[c] = bf_[c];
         }
+    }
+}
+
+// The same arithmetic with the weights brought in by the copy engine.  The rolled loop above keeps two
+// items (one 512-input block of a column group) in flight per warp, so a warp that owns one column
+// group of a 4096-input matrix walks its eight blocks at two blocks per trip to memory: 0.67 us per
+// block, 5.4 us for the single-row out projection whose whole weight stream is 0.7 us of HBM time.
+// Here lane 0 of each warp asks for the WHOLE column group at once -- C rows of words, of scales and
+// of biases, each contiguous, three cp.async.bulk copies completing on one mbarrier -- and for the
+// warp's next group into a second buffer, before the dependency wait: every byte of the matrix is
+// in flight from the start.  The pre-divided inputs and the block sums are computed once per CTA into
+// shared memory (the values and the order of the per-warp code above), and the block loop reads
+// everything from shared memory.  Same chains, same trees: bit-identical to q4_project_kernel.
+struct Q4BulkLayout {
+    uint32_t x_bytes, group_bytes, words_bytes, affine_bytes, bars_off, total;
+};
+__host__ __device__ inline Q4BulkLayout q4_bulk_layout(uint32_t rows, uint32_t cols, uint32_t k) {
+    Q4BulkLayout l;
+    l.x_bytes = rows * (k * 4u + (k >> 9) * 128u);          // [R][blocks][4][32] float4, then [R][blocks][32] sums
+    l.words_bytes = cols * (k >> 1);
+    l.affine_bytes = cols * (k >> 5);                       // one of scales / biases
+    l.group_bytes = l.words_bytes + 2u * l.affine_bytes;
+    l.bars_off = l.x_bytes + kQ4Warps * 2u * l.group_bytes;
+    l.total = l.bars_off + kQ4Warps * 16u + 16u;
+    return l;
+}
+__device__ __forceinline__ void q4_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int R, int C>
+__global__ void __launch_bounds__(kQ4Warps * 32) q4_project_bulk_kernel(const __grid_constant__ Q4Params p) {
+    extern __shared__ __align__(128) uint8_t q4s[];
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row0 = blockIdx.y * R;
+    const uint32_t blocks = p.k >> 9, wpr = p.k >> 4, gpr = p.k >> 6;
+    const Q4BulkLayout lay = q4_bulk_layout(R, C, p.k);
+    float4* xf = reinterpret_cast<float4*>(q4s);
+    float* xsum = reinterpret_cast<float*>(q4s + R * p.k * 4u);
+    uint8_t* wbuf = q4s + lay.x_bytes + warp * 2u * lay.group_bytes;
+    const uint32_t bars = s2u(q4s + lay.bars_off) + warp * 16u;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(q4s + lay.bars_off + kQ4Warps * 16u);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t n_groups = p.n_cols / C;
+    const uint32_t nwarps = gridDim.x * kQ4Warps;
+    uint32_t g = blockIdx.x * kQ4Warps + warp;
+    // lane 0: the three copies of one column group into buffer `buf`
+    auto request = [&](uint32_t group, uint32_t buf) {
+        const uint32_t col0 = group * C;
+        uint32_t m = 0;
+        while (m + 1u < p.n_mats && col0 >= p.mat[m].col_end) ++m;
+        const uint32_t local = col0 - p.mat[m].col_begin;
+        const uint32_t dst = s2u(wbuf + buf * lay.group_bytes), bar = bars + 8u * buf;
+        mbar_expect_tx(bar, lay.group_bytes);
+        q4_bulk_load(dst, p.mat[m].words + uint64_t(local) * wpr, lay.words_bytes, bar);
+        q4_bulk_load(dst + lay.words_bytes, p.mat[m].scales + uint64_t(local) * gpr, lay.affine_bytes, bar);
+        q4_bulk_load(dst + lay.words_bytes + lay.affine_bytes, p.mat[m].biases + uint64_t(local) * gpr,
+                     lay.affine_bytes, bar);
+    };
+    if (threadIdx.x == 0) *abort_flag = 0u;   // read only after the barrier below
+    if (lane == 0) {
+        mbar_init(bars, 1);
+        mbar_init(bars + 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (g < n_groups) request(g, 0);
+        if (g + nwarps < n_groups) request(g + nwarps, 1);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // inputs: (row, block, lane) -> this lane's 16 values of the block, pre-divided, and their sum
+    for (uint32_t i = threadIdx.x; i < R * blocks * 32u; i += kQ4Warps * 32u) {
+        const uint32_t l = i & 31u, rb = i >> 5, r = rb / blocks, b = rb - r * blocks;
+        const uint32_t row = min(row0 + r, p.n_rows - 1u);
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride) + b * 64u + l * 2u;
+        const uint4 v0 = src[0], v1 = src[1];
+        const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float s = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float a0 = __uint_as_float(raw[2 * q] << 16), a1 = __uint_as_float(raw[2 * q] & 0xFFFF0000u);
+            const float a2 = __uint_as_float(raw[2 * q + 1] << 16), a3 = __uint_as_float(raw[2 * q + 1] & 0xFFFF0000u);
+            s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
+            xf[(rb * 4u + q) * 32u + l] = make_float4(a0, __fmul_rn(a1, 0.0625f), __fmul_rn(a2, 0.00390625f),
+                                                      __fmul_rn(a3, 0.000244140625f));
+        }
+        xsum[rb * 32u + l] = s;
+    }
+    __syncthreads();
+
+    bool ok = true;
+    uint32_t buf = 0, phase = 0;   // bit b of `phase`: parity of buffer b's next completion
+#pragma unroll 1
+    while (g < n_groups) {
+        __syncwarp();
+        if (ok) ok = mbar_wait(bars + 8u * buf, (phase >> buf) & 1u, abort_flag);
+        const uint8_t* gb = wbuf + buf * lay.group_bytes;
+        const unsigned short* gs = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes);
+        const unsigned short* gbias = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes + lay.affine_bytes);
+        float result[R][C];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < C; ++c) result[r][c] = 0.0f;
+#pragma unroll 1
+        for (uint32_t b = 0; b < blocks; ++b) {
+            float xv[R][16], sum[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = xf[((r * blocks + b) * 4u + q) * 32u + lane];
+                    xv[r][4 * q] = v.x; xv[r][4 * q + 1] = v.y; xv[r][4 * q + 2] = v.z; xv[r][4 * q + 3] = v.w;
+                }
+                sum[r] = xsum[(r * blocks + b) * 32u + lane];
+            }
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const uint2 w = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
+                const uint32_t half[4] = {w.x & 0xFFFFu, w.x >> 16, w.y & 0xFFFFu, w.y >> 16};
+                const float scale = __uint_as_float(uint32_t(gs[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+                const float bias = __uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+                float wq[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    wq[4 * i] = small_int_to_float(half[i] & 0x000Fu);
+                    wq[4 * i + 1] = small_int_to_float(half[i] & 0x00F0u);
+                    wq[4 * i + 2] = small_int_to_float(half[i] & 0x0F00u);
+                    wq[4 * i + 3] = small_int_to_float(half[i] & 0xF000u);
+                }
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float quant = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        quant = __fmaf_rn(xv[r][4 * i + 3], wq[4 * i + 3],
+                                          __fmaf_rn(xv[r][4 * i + 2], wq[4 * i + 2],
+                                                    __fmaf_rn(xv[r][4 * i + 1], wq[4 * i + 1],
+                                                              __fmaf_rn(xv[r][4 * i], wq[4 * i], quant))));
+                    result[r][c] = __fmaf_rn(sum[r], bias, __fmaf_rn(scale, quant, result[r][c]));
+                }
+            }
+        }
+        // adjacent-pairs tree per (row, column); lane c keeps column c and stores it
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float keep = 0.0f;
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const float total = warp_sum(result[r][c]);
+                if (lane == uint32_t(c)) keep = total;
+            }
+            if (ok && lane < uint32_t(C) && row0 + uint32_t(r) < p.n_rows)
+                p.out[uint64_t(row0 + r) * p.out_stride + g * C + lane] = f2bf(keep);
+        }
+        // the buffer is read: it takes the group two rounds ahead
+        __syncwarp();
+        if (lane == 0 && ok && g + 2u * nwarps < n_groups) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            request(g + 2u * nwarps, buf);
+        }
+        phase ^= 1u << buf;
+        buf ^= 1u;
+        g += nwarps;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+        p.status[kStatusDetail] = blockIdx.x;
+        __nanosleep(200000);   // let copies still in flight land before the shared memory is released
     }
 }
 
@@ -364,6 +536,31 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
+}
+
+// The bulk-copy form of the exact-row kernel (rows <= 4): one CTA of eight warps per SM.
+template <int R, int C>
+static cudaError_t launch_q4_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+    const uint32_t groups = p.n_cols / C;
+    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
+    const Q4BulkLayout lay = q4_bulk_layout(R, C, p.k);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(q4_project_bulk_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, (p.n_rows + R - 1) / R);
+    cfg.blockDim = dim3(kQ4Warps * 32);
+    cfg.dynamicSmemBytes = lay.total;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, q4_project_bulk_kernel<R, C>, p);
 }
 
 // Up to 4 rows per warp pass (more rows run as further row tiles that re-read the weights from L2).
@@ -776,7 +973,22 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     auto s = static_cast<cudaStream_t>(stream);
     const uint32_t sms = uint32_t(ctx->sm_count);
     if (k > 6144u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "q4_project: k above 6144");
-    if (n_rows == 1) {
+    p.status = ctx->device_status;
+    // The bulk-copy form needs 16-byte aligned rows of scales and biases (k / 32 bytes each, from a
+    // 16-byte aligned base) and a column count that splits into whole groups.
+    bool bulk = ctx->q4_row_form == 0u && n_rows <= 4u && k % 512u == 0u &&
+                q4_bulk_layout(n_rows <= 2u ? n_rows : 4u, 4u, k).total <= 221184u;
+    for (uint32_t i = 0; i < n_matrices && bulk; ++i)
+        bulk = aligned(matrices[i].scales, 16) && aligned(matrices[i].biases, 16);
+    if (bulk) {
+        // narrow matrices take two columns per warp so that every warp of the grid has a group
+        const bool narrow = cols / 4u < sms * kQ4Warps;
+        cudaError_t err;
+        if (n_rows == 1) err = narrow ? launch_q4_bulk<1, 2>(p, sms, s) : launch_q4_bulk<1, 4>(p, sms, s);
+        else if (n_rows == 2) err = narrow ? launch_q4_bulk<2, 2>(p, sms, s) : launch_q4_bulk<2, 4>(p, sms, s);
+        else err = narrow ? launch_q4_bulk<4, 2>(p, sms, s) : launch_q4_bulk<4, 4>(p, sms, s);
+        (void)err;
+    } else if (n_rows == 1) {
         // few warps with many bytes in flight each; narrow matrices get narrower groups (more warps)
         if (cols >= 8192u) launch_q4<1, 8>(p, sms, 1, s);
         else launch_q4<1, 4>(p, sms, 1, s);

@@ -46,6 +46,26 @@ def test_exact_row_bits_small(ctx, rows, k):
     assert np.array_equal(host_u16(out), oracle_project(x, mats, 4))
 
 
+@pytest.mark.parametrize("rows", [1, 2, 4])
+@pytest.mark.parametrize("k", [512, 2048, 4096])
+def test_exact_row_bits_lane_load_form(ctx, rows, k):
+    """TATARA_POLICY_Q4_ROW_FORM = 1: the per-lane loads two blocks ahead (the default for one to four rows is
+    the bulk-copy form, which the other tests of this file run) give the oracle's bits too."""
+    rng = np.random.default_rng(rows * 977 + k)
+    mats = [syn.q4_matrix(rng, n, k) for n in (64, 32, 16)]
+    x = syn.hidden_rows(rng, rows, k)
+    held, arr = dev_mats(mats)
+    out = torch.zeros((rows, 112), dtype=torch.bfloat16, device="cuda")
+    assert ctx.get_policy(tb.POLICY_Q4_ROW_FORM) == 0
+    ctx.set_policy(tb.POLICY_Q4_ROW_FORM, 1)
+    try:
+        ctx.q4_project(dev_bf16(x), arr, k, out)
+        ctx.sync()
+    finally:
+        ctx.set_policy(tb.POLICY_Q4_ROW_FORM, 0)
+    assert np.array_equal(host_u16(out), oracle_project(x, mats, 4))
+
+
 @pytest.mark.parametrize("name,sizes,k", [("attn_project", (8192, 512, 512), 2048),
                                           ("gdn_project", (8192, 4096, 32, 32), 2048),
                                           ("out_projection", (2048,), 4096)])
