@@ -299,30 +299,48 @@ __global__ void __launch_bounds__(kQ4Warps * 32) q4_project_bulk_kernel(const __
                 }
                 sum[r] = xsum[(r * blocks + b) * 32u + lane];
             }
+            // Columns in PAIRS: every multiply-add of the chain is one packed fma.rn.f32x2 on {column c,
+            // column c+1} against the same input (each component rounds as the scalar fma, so the bits
+            // are those of the single-column chain), and the nibble -> float subtraction is packed too.
+            const float2 magic = make_float2(-8388608.0f, -8388608.0f);
 #pragma unroll
-            for (int c = 0; c < C; ++c) {
-                const uint2 w = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
-                const uint32_t half[4] = {w.x & 0xFFFFu, w.x >> 16, w.y & 0xFFFFu, w.y >> 16};
-                const float scale = __uint_as_float(uint32_t(gs[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
-                const float bias = __uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
-                float wq[16];
+            for (int c = 0; c < C; c += 2) {
+                const uint2 wa = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
+                const uint2 wb = *reinterpret_cast<const uint2*>(gb + uint32_t(c + 1) * (p.k >> 1) + b * 256u + lane * 8u);
+                const uint32_t ha[4] = {wa.x & 0xFFFFu, wa.x >> 16, wa.y & 0xFFFFu, wa.y >> 16};
+                const uint32_t hb[4] = {wb.x & 0xFFFFu, wb.x >> 16, wb.y & 0xFFFFu, wb.y >> 16};
+                const uint32_t gi = b * 8u + (lane >> 2);
+                const float2 scale = make_float2(__uint_as_float(uint32_t(gs[uint32_t(c) * gpr + gi]) << 16),
+                                                 __uint_as_float(uint32_t(gs[uint32_t(c + 1) * gpr + gi]) << 16));
+                const float2 bias = make_float2(__uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + gi]) << 16),
+                                                __uint_as_float(uint32_t(gbias[uint32_t(c + 1) * gpr + gi]) << 16));
+                float2 quant[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) quant[r] = make_float2(0.0f, 0.0f);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    wq[4 * i] = small_int_to_float(half[i] & 0x000Fu);
-                    wq[4 * i + 1] = small_int_to_float(half[i] & 0x00F0u);
-                    wq[4 * i + 2] = small_int_to_float(half[i] & 0x0F00u);
-                    wq[4 * i + 3] = small_int_to_float(half[i] & 0xF000u);
+                    const float2 q0 = __fadd2_rn(make_float2(__uint_as_float((ha[i] & 0x000Fu) | 0x4B000000u),
+                                                             __uint_as_float((hb[i] & 0x000Fu) | 0x4B000000u)), magic);
+                    const float2 q1 = __fadd2_rn(make_float2(__uint_as_float((ha[i] & 0x00F0u) | 0x4B000000u),
+                                                             __uint_as_float((hb[i] & 0x00F0u) | 0x4B000000u)), magic);
+                    const float2 q2 = __fadd2_rn(make_float2(__uint_as_float((ha[i] & 0x0F00u) | 0x4B000000u),
+                                                             __uint_as_float((hb[i] & 0x0F00u) | 0x4B000000u)), magic);
+                    const float2 q3 = __fadd2_rn(make_float2(__uint_as_float((ha[i] & 0xF000u) | 0x4B000000u),
+                                                             __uint_as_float((hb[i] & 0xF000u) | 0x4B000000u)), magic);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        quant[r] = __ffma2_rn(make_float2(xv[r][4 * i], xv[r][4 * i]), q0, quant[r]);
+                        quant[r] = __ffma2_rn(make_float2(xv[r][4 * i + 1], xv[r][4 * i + 1]), q1, quant[r]);
+                        quant[r] = __ffma2_rn(make_float2(xv[r][4 * i + 2], xv[r][4 * i + 2]), q2, quant[r]);
+                        quant[r] = __ffma2_rn(make_float2(xv[r][4 * i + 3], xv[r][4 * i + 3]), q3, quant[r]);
+                    }
                 }
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    float quant = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        quant = __fmaf_rn(xv[r][4 * i + 3], wq[4 * i + 3],
-                                          __fmaf_rn(xv[r][4 * i + 2], wq[4 * i + 2],
-                                                    __fmaf_rn(xv[r][4 * i + 1], wq[4 * i + 1],
-                                                              __fmaf_rn(xv[r][4 * i], wq[4 * i], quant))));
-                    result[r][c] = __fmaf_rn(sum[r], bias, __fmaf_rn(scale, quant, result[r][c]));
+                    const float2 acc = __ffma2_rn(make_float2(sum[r], sum[r]), bias,
+                                                  __ffma2_rn(scale, quant[r], make_float2(result[r][c], result[r][c + 1])));
+                    result[r][c] = acc.x;
+                    result[r][c + 1] = acc.y;
                 }
             }
         }
