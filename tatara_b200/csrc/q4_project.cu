@@ -556,12 +556,15 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
     return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
 }
 
-// The bulk-copy form of the exact-row kernel (rows <= 4): one CTA of eight warps per SM.
+// The bulk-copy form of the exact-row kernel (rows <= 4).
 template <int R, int C>
 static cudaError_t launch_q4_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C;
-    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
     const Q4BulkLayout lay = q4_bulk_layout(R, C, p.k);
+    // as many CTAs per SM as the shared memory holds (at most three): more warps to hide the latencies
+    // of the block loop, and more of the matrix asked for at once
+    const uint32_t per_sm = max(1u, min(3u, 232448u / (lay.total + 1024u)));
+    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count * per_sm);
     static bool configured = false;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(q4_project_bulk_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
