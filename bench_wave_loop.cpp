@@ -75,9 +75,11 @@ double ms_since(Clock::time_point t0) { return std::chrono::duration<double, std
 
 int main(int argc, char** argv) {
     std::uint32_t lanes = 8, context = 16384, tokens = 64, n_layers = 40, unit = 2048;
+    std::vector<std::pair<std::uint32_t, std::uint32_t>> policies;   // --policy ID*1000+VALUE: tatara_ctx_set_policy(ID, VALUE)
     for (int i = 1; i + 1 < argc; i += 2) {
         const std::string key = argv[i];
         const auto value = static_cast<std::uint32_t>(std::strtoul(argv[i + 1], nullptr, 10));
+        if (key == "--policy") { policies.emplace_back(value / 1000u, value % 1000u); continue; }
         if (key == "--lanes") lanes = value;
         else if (key == "--context") context = value;
         else if (key == "--tokens") tokens = value;
@@ -90,6 +92,11 @@ int main(int argc, char** argv) {
     const std::uint32_t capacity = context + tokens + join_waves + 16;
     tatara_ctx* ctx = nullptr;
     if (tatara_ctx_create(0, &ctx) != TATARA_OK) { std::fprintf(stderr, "no B200: %s\n", "tatara_ctx_create failed"); return 4; }
+    for (const auto& pv : policies)
+        if (tatara_ctx_set_policy(ctx, static_cast<tatara_policy>(pv.first), pv.second) != TATARA_OK) {
+            std::fprintf(stderr, "policy %u = %u refused\n", pv.first, pv.second);
+            return 2;
+        }
 
     Rng rng{0x7A7A4A5EEDull};
     Store store;
@@ -154,7 +161,8 @@ int main(int argc, char** argv) {
     double join_ms = 0, wave_ms = 0;
     std::uint64_t graphs = 0, launches_per_wave = 0;
     {
-        OwnerConfig config{0, 1, lanes, capacity, std::min<std::uint32_t>(lanes, 2), unit, 5000};
+        OwnerConfig config{0, 1, lanes, capacity, std::min<std::uint32_t>(lanes, 2), unit, 5000, {}};
+        for (const auto& pv : policies) config.policies.emplace_back(pv.first, pv.second);
         MultiStreamOwner owner(config, layers, boundary);
         if (!owner) { std::fprintf(stderr, "owner failed to build\n"); return 7; }
         if (verbose) std::fprintf(stderr, "owner built, %.1f ms since start\n", ms_since(start));

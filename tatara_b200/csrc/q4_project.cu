@@ -532,6 +532,169 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_kernel(cons
     }
 }
 
+// The row-pair kernel with the weights brought in by the copy engine (whole column groups, two buffers per
+// warp, asked for before the dependency wait: see q4_project_bulk_kernel); the arithmetic is the row-pair
+// kernel's, so are the bits.
+template <int RP, int C>
+__global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_bulk_kernel(const __grid_constant__ Q4Params p) {
+    extern __shared__ float4 xs4[];   // [RP][blocks][8][32] float4, the sums [RP][blocks][32] float2, then the weight buffers
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row0 = blockIdx.y * (2 * RP);
+    const uint32_t blocks = p.k >> 9, wpr = p.k >> 4, gpr = p.k >> 6;
+    float2* sum2 = reinterpret_cast<float2*>(xs4 + RP * blocks * 256u);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t n_groups = p.n_cols / C;
+    const uint32_t nwarps = gridDim.x * kQ4Warps;
+    uint32_t g = blockIdx.x * kQ4Warps + warp;
+
+    const Q4BulkLayout lay = q4_bulk_layout(1, C, p.k);      // (group geometry only; the inputs are laid out below)
+    const uint32_t x_bytes = RP * blocks * (256u * 16u + 32u * 8u);
+    uint8_t* smem_bytes = reinterpret_cast<uint8_t*>(xs4);
+    uint8_t* wbuf = smem_bytes + x_bytes + warp * 2u * lay.group_bytes;
+    const uint32_t bars = s2u(smem_bytes + x_bytes + kQ4Warps * 2u * lay.group_bytes) + warp * 16u;
+    volatile uint32_t* abort_flag =
+        reinterpret_cast<volatile uint32_t*>(smem_bytes + x_bytes + kQ4Warps * 2u * lay.group_bytes + kQ4Warps * 16u);
+    // lane 0: the three copies of one column group into buffer `buf` (see q4_project_bulk_kernel)
+    auto request = [&](uint32_t group, uint32_t buf) {
+        const uint32_t col0 = group * C;
+        uint32_t m = 0;
+        while (m + 1u < p.n_mats && col0 >= p.mat[m].col_end) ++m;
+        const uint32_t local = col0 - p.mat[m].col_begin;
+        const uint32_t dst = s2u(wbuf + buf * lay.group_bytes), bar = bars + 8u * buf;
+        mbar_expect_tx(bar, lay.group_bytes);
+        q4_bulk_load(dst, p.mat[m].words + uint64_t(local) * wpr, lay.words_bytes, bar);
+        q4_bulk_load(dst + lay.words_bytes, p.mat[m].scales + uint64_t(local) * gpr, lay.affine_bytes, bar);
+        q4_bulk_load(dst + lay.words_bytes + lay.affine_bytes, p.mat[m].biases + uint64_t(local) * gpr,
+                     lay.affine_bytes, bar);
+    };
+    if (threadIdx.x == 0) *abort_flag = 0u;   // read only after the barrier below
+    if (lane == 0) {
+        mbar_init(bars, 1);
+        mbar_init(bars + 8u, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (g < n_groups) request(g, 0);
+        if (g + nwarps < n_groups) request(g + nwarps, 1);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // stage the row pairs: one (row, block, lane) item = 16 inputs
+    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += kQ4Warps * 32u) {
+        const uint32_t l = item & 31u, b = (item >> 5) % blocks, r = item / (32u * blocks);
+        const uint32_t row = min(row0 + r, p.n_rows - 1u);
+        const uint4* xp = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride + b * 512u + l * 16u);
+        const uint4 v0 = xp[0], v1 = xp[1];
+        const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float* dst = reinterpret_cast<float*>(xs4 + ((r >> 1) * blocks + b) * 256u) + (r & 1u);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a0 = __uint_as_float(raw[2 * i] << 16), a1 = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
+            const float a2 = __uint_as_float(raw[2 * i + 1] << 16), a3 = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
+            s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
+            // float4 index (i4 = 2i, 2i+1), lane l: components {x0[2j], x1[2j], x0[2j+1], x1[2j+1]}
+            dst[((2 * i) * 32u + l) * 4u] = a0;
+            dst[((2 * i) * 32u + l) * 4u + 2u] = __fmul_rn(a1, 0.0625f);
+            dst[((2 * i + 1) * 32u + l) * 4u] = __fmul_rn(a2, 0.00390625f);
+            dst[((2 * i + 1) * 32u + l) * 4u + 2u] = __fmul_rn(a3, 0.000244140625f);
+        }
+        reinterpret_cast<float*>(sum2 + ((r >> 1) * blocks + b) * 32u + l)[r & 1u] = s;
+    }
+    __syncthreads();
+
+    float2 result[RP][C];
+#pragma unroll
+    for (int rp = 0; rp < RP; ++rp)
+#pragma unroll
+        for (int c = 0; c < C; ++c) result[rp][c] = make_float2(0.0f, 0.0f);
+    const float2 magic = make_float2(-8388608.0f, -8388608.0f);
+    bool ok = true;
+    uint32_t buf = 0, phase = 0;
+#pragma unroll 1
+    while (g < n_groups) {
+        __syncwarp();
+        if (ok) ok = mbar_wait(bars + 8u * buf, (phase >> buf) & 1u, abort_flag);
+        const uint8_t* gb = wbuf + buf * lay.group_bytes;
+        const unsigned short* gs = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes);
+        const unsigned short* gbias = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes + lay.affine_bytes);
+#pragma unroll 1
+      for (uint32_t b = 0; b < blocks; ++b) {
+        float4 xv[RP][8];
+        float2 sum[RP];
+#pragma unroll
+        for (int rp = 0; rp < RP; ++rp) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xv[rp][i] = xs4[((rp * blocks + b) * 8u + i) * 32u + lane];
+            sum[rp] = sum2[(rp * blocks + b) * 32u + lane];
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const uint2 wdc = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
+            const uint32_t half[4] = {wdc.x & 0xFFFFu, wdc.x >> 16, wdc.y & 0xFFFFu, wdc.y >> 16};
+            const float scale = __uint_as_float(uint32_t(gs[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+            const float bias = __uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+            float2 quant[RP];
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) quant[rp] = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // the four nibbles of half-word i, each as {w, w}; inputs 4i .. 4i+3 are xv[.][2i].xy, .zw, xv[.][2i+1].xy, .zw
+                const float w0 = __uint_as_float((half[i] & 0x000Fu) | 0x4B000000u), w1 = __uint_as_float((half[i] & 0x00F0u) | 0x4B000000u);
+                const float w2 = __uint_as_float((half[i] & 0x0F00u) | 0x4B000000u), w3 = __uint_as_float((half[i] & 0xF000u) | 0x4B000000u);
+                const float2 q0 = __fadd2_rn(make_float2(w0, w0), magic), q1 = __fadd2_rn(make_float2(w1, w1), magic);
+                const float2 q2 = __fadd2_rn(make_float2(w2, w2), magic), q3 = __fadd2_rn(make_float2(w3, w3), magic);
+#pragma unroll
+                for (int rp = 0; rp < RP; ++rp) {
+                    const float4 lo = xv[rp][2 * i], hi = xv[rp][2 * i + 1];
+                    quant[rp] = __ffma2_rn(make_float2(lo.x, lo.y), q0, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(lo.z, lo.w), q1, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(hi.x, hi.y), q2, quant[rp]);
+                    quant[rp] = __ffma2_rn(make_float2(hi.z, hi.w), q3, quant[rp]);
+                }
+            }
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp)
+                result[rp][c] = __ffma2_rn(sum[rp], make_float2(bias, bias),
+                                           __ffma2_rn(make_float2(scale, scale), quant[rp], result[rp][c]));
+        }
+      }
+        {
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) {
+                float keep0 = 0.0f, keep1 = 0.0f;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    const float t0 = warp_sum(result[rp][c].x), t1 = warp_sum(result[rp][c].y);
+                    if (lane == uint32_t(c)) {
+                        keep0 = t0;
+                        keep1 = t1;
+                    }
+                    result[rp][c] = make_float2(0.0f, 0.0f);
+                }
+                const uint32_t r0 = row0 + 2u * rp;
+                if (ok && lane < uint32_t(C)) {
+                    if (r0 < p.n_rows) p.out[uint64_t(r0) * p.out_stride + g * C + lane] = f2bf(keep0);
+                    if (r0 + 1u < p.n_rows) p.out[uint64_t(r0 + 1u) * p.out_stride + g * C + lane] = f2bf(keep1);
+                }
+            }
+        }
+        // the buffer is read: it takes the group two rounds ahead
+        __syncwarp();
+        if (lane == 0 && ok && g + 2u * nwarps < n_groups) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            request(g + 2u * nwarps, buf);
+        }
+        phase ^= 1u << buf;
+        buf ^= 1u;
+        g += nwarps;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        atomicCAS(p.status + kStatusCode, 0u, uint32_t(TATARA_DEVICE_WAIT_TIMEOUT));
+        p.status[kStatusDetail] = blockIdx.x;
+        __nanosleep(200000);   // let copies still in flight land before the shared memory is released
+    }
+}
+
 template <int RP, int C>
 static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
@@ -554,6 +717,31 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
+}
+
+template <int RP, int C>
+static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+    const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
+    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
+    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + kQ4Warps * 2u * q4_bulk_layout(1, C, p.k).group_bytes +
+                          kQ4Warps * 16u + 16u;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
+        if (err != cudaSuccess) return err;
+        configured = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas, (p.n_rows + 2 * RP - 1) / (2 * RP));
+    cfg.blockDim = dim3(kQ4Warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, q4_project_pairs_bulk_kernel<RP, C>, p);
 }
 
 // The bulk-copy form of the exact-row kernel (rows <= 4).
@@ -997,11 +1185,23 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     p.status = ctx->device_status;
     // The bulk-copy form needs 16-byte aligned rows of scales and biases (k / 32 bytes each, from a
     // 16-byte aligned base) and a column count that splits into whole groups.
-    bool bulk = ctx->q4_row_form == 0u && n_rows <= 4u && k % 512u == 0u &&
-                q4_bulk_layout(n_rows <= 2u ? n_rows : 4u, 4u, k).total <= 221184u;
-    for (uint32_t i = 0; i < n_matrices && bulk; ++i)
-        bulk = aligned(matrices[i].scales, 16) && aligned(matrices[i].biases, 16);
-    if (bulk) {
+    bool aligned16 = ctx->q4_row_form == 0u && k % 512u == 0u;
+    for (uint32_t i = 0; i < n_matrices && aligned16; ++i)
+        aligned16 = aligned(matrices[i].scales, 16) && aligned(matrices[i].biases, 16);
+    const bool bulk = aligned16 && n_rows <= 4u && q4_bulk_layout(n_rows <= 2u ? n_rows : 4u, 4u, k).total <= 221184u;
+    // more than four rows: the row-pair kernel, its weights by bulk copies when the inputs of eight rows
+    // and the buffers fit the shared memory (four columns per warp up to 2048 inputs, two up to 4096)
+    const uint32_t pairs_x = 4u * (k >> 9) * (256u * 16u + 32u * 8u);
+    const bool pairs_bulk4 = aligned16 && n_rows > 4u && pairs_x + kQ4Warps * 2u * q4_bulk_layout(1, 4, k).group_bytes + 144u <= 221184u;
+    // (two columns per warp re-read the inputs twice as often: measured 15.1 -> 10.4 us at 8 rows of the
+    // out projection but 15.1 -> 20.3 us at 16, where two row tiles share the SMs)
+    const bool pairs_bulk2 = aligned16 && n_rows > 4u && n_rows <= 8u && !pairs_bulk4 &&
+                             pairs_x + kQ4Warps * 2u * q4_bulk_layout(1, 2, k).group_bytes + 144u <= 221184u;
+    if (pairs_bulk4) {
+        (void)launch_q4_pairs_bulk<4, 4>(p, sms, s);
+    } else if (pairs_bulk2) {
+        (void)launch_q4_pairs_bulk<4, 2>(p, sms, s);
+    } else if (bulk) {
         // narrow matrices take two columns per warp so that every warp of the grid has a group
         const bool narrow = cols / 4u < sms * kQ4Warps;
         cudaError_t err;

@@ -84,6 +84,8 @@ struct OwnerConfig {
     std::uint32_t join_streams{2};      // join slots: prompts that advance side by side, one unit each per wave
     std::uint32_t join_unit_rows{256};  // prompt rows one join submission places
     std::uint32_t wait_limit_ms{30000}; // a submission that has not completed by then fails its lanes
+    // tatara_ctx_set_policy(id, value) for every context the owner creates (its lane groups' and the join slots')
+    std::vector<std::pair<std::uint32_t, std::uint64_t>> policies;
 };
 
 struct WaveStatistics {
@@ -319,6 +321,12 @@ class MultiStreamOwner {
         }
     }
 
+    bool apply_policies(tatara_ctx* ctx) const {
+        for (const auto& pv : config_.policies)
+            if (tatara_ctx_set_policy(ctx, static_cast<tatara_policy>(pv.first), pv.second) != TATARA_OK) return false;
+        return true;
+    }
+
     bool build() {
         if (layers_.empty() || config_.groups == 0 || config_.lanes_per_group == 0 ||
             config_.lanes_per_group > rt::kMaximumBatchRows || config_.join_unit_rows == 0 || !boundary_.embed ||
@@ -338,7 +346,7 @@ class MultiStreamOwner {
             OwnerLaneGroup& group = groups_[g];
             if (!rt::create_state_pool(rows, config_.capacity, schedule, group.pool, group.slots) ||
                 !rt::create_batch_scratch(rows, config_.capacity, group.batch_scratch) ||
-                tatara_ctx_create(config_.device, &group.ctx) != TATARA_OK)
+                tatara_ctx_create(config_.device, &group.ctx) != TATARA_OK || !apply_policies(group.ctx))
                 return false;
             group.stream = stream_;
             group.tables_host = PinnedBuffer(table_bytes());
@@ -362,7 +370,7 @@ class MultiStreamOwner {
         }
         joining_.resize(config_.join_streams);
         const std::uint64_t u = config_.join_unit_rows;
-        if (tatara_ctx_create(config_.device, &join_ctx_) != TATARA_OK) return false;
+        if (tatara_ctx_create(config_.device, &join_ctx_) != TATARA_OK || !apply_policies(join_ctx_)) return false;
         for (JoiningLane& j : joining_) {
             JoinStream& io = j.io;
             io.ctx = join_ctx_;
