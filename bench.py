@@ -167,6 +167,9 @@ def main():
     ap.add_argument("--rows", type=int, default=PREFILL_ROWS)
     ap.add_argument("--lanes", type=int, default=4, help="lanes of --only gdn_step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--policy", action="append", default=[], metavar="ID=VALUE",
+                    help="tatara_ctx_set_policy(ID, VALUE) on the bench's context before anything runs "
+                         "(e.g. 5=1: the per-lane-load form of the exact-row projections); may be repeated")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -186,6 +189,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ctx = tb.Context(local)
+    for item in args.policy:
+        pid, _, value = item.partition("=")
+        ctx.set_policy(int(pid), int(value))
     wl = Workloads(ctx, torch, rank=rank, world=world)
     peaks = measured_peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
