@@ -376,8 +376,16 @@ class Workloads:
             ms_regs = timed(step, max(steps, 2 * reps), max(warmup, reps))
         finally:
             self.ctx.set_policy(tb.POLICY_GDN_DECODE_FORM, 0)
+        # the step letting its successor be staged early (TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS = 1: the caller
+        # promises that the next kernels do not read this call's state before their own dependency wait; true
+        # here, every step works on another state set, and in a layer walk; the owner's wave loop sets it)
+        self.ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, 1)
+        try:
+            ms_early = timed(step, max(steps, 2 * reps), max(warmup, reps))
+        finally:
+            self.ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, 0)
         return {"lanes": n, "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
-                "register_form_us": ms_regs * 1e3,
+                "early_dependents_us": ms_early * 1e3, "register_form_us": ms_regs * 1e3,
                 "l2": f"{reps} rotating state sets (> 2x L2)",
                 "kernel": "gdn_decode_fused_kernel<bulk copies> (1 launch per step)"}
 
@@ -569,6 +577,13 @@ class Workloads:
         gb_ = nb + 14229504 + 4718592
         out["gated_delta_layer"] = {"us": ms * 1e3, "bytes": gb_, "gbs": gb_ / (ms * 1e-3) / 1e9,
                                     "kernels": "q4_project, gdn_decode_fused, q4_project"}
+        if reps >= 2:   # consecutive steps work on different state sets: the step may stage its successor early
+            self.ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, 1)
+            try:
+                ms = timed(gdn_layer, max(steps, 2 * reps), max(warmup, reps))
+            finally:
+                self.ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, 0)
+            out["gated_delta_layer"]["early_dependents_us"] = ms * 1e3
         out["l2"] = "caches / states rotate through replicas (> 2x L2 between reuse); 4 weight sets (62 MB) rotate"
         return out
 

@@ -117,7 +117,14 @@ typedef enum tatara_policy {
     /* How tatara_q4_project brings the weights of one to four rows in: 0 (default) = whole column groups by
      * cp.async.bulk copies into shared memory, asked for before the dependency wait; 1 = per-lane loads two
      * blocks ahead of the arithmetic.  Same chains and trees: bit-identical. */
-    TATARA_POLICY_Q4_ROW_FORM = 5
+    TATARA_POLICY_Q4_ROW_FORM = 5,
+    /* 1 = the fused GDN decode step lets the next kernel of its stream be staged while it computes (programmatic
+     * dependent launch).  The caller's promise: no kernel that follows within the next few launches reads, before
+     * its own dependency wait, the recurrent or conv state this call writes -- true of a layer walk (the out
+     * projection follows, then another layer), false of a loop that steps ONE state back to back, because the
+     * step asks for its state rows before it waits.  0 (default) = the step's dependents start when it has
+     * finished. */
+    TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS = 6
 } tatara_policy;
 tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint64_t value);
 uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy);

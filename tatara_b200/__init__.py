@@ -81,6 +81,7 @@ POLICY_ATTN_PREFILL_FORM = 2
 POLICY_GDN_DECODE_FORM = 3
 POLICY_DECODE_FUSED_MERGE = 4
 POLICY_Q4_ROW_FORM = 5
+POLICY_GDN_STEP_EARLY_DEPENDENTS = 6
 
 
 def split_buffer_bytes(world: int) -> int:

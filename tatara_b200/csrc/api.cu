@@ -138,6 +138,10 @@ tatara_status tatara_ctx_set_policy(tatara_ctx* ctx, tatara_policy policy, uint6
         if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: q4 row form");
         ctx->q4_row_form = static_cast<uint32_t>(value);
         return TATARA_OK;
+    case TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS:
+        if (value > 1) return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: early dependents");
+        ctx->gdn_step_early_dependents = static_cast<uint32_t>(value);
+        return TATARA_OK;
     }
     return tb::fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "set_policy: unknown policy");
 }
@@ -150,6 +154,7 @@ uint64_t tatara_ctx_get_policy(const tatara_ctx* ctx, tatara_policy policy) {
     case TATARA_POLICY_GDN_DECODE_FORM: return ctx->gdn_decode_form;
     case TATARA_POLICY_DECODE_FUSED_MERGE: return ctx->decode_fused_merge;
     case TATARA_POLICY_Q4_ROW_FORM: return ctx->q4_row_form;
+    case TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS: return ctx->gdn_step_early_dependents;
     }
     return 0;
 }

@@ -47,6 +47,7 @@ struct tatara_ctx {
     uint32_t gdn_decode_form = 0;                                    // TATARA_POLICY_GDN_DECODE_FORM
     uint32_t decode_fused_merge = 0;                                 // TATARA_POLICY_DECODE_FUSED_MERGE
     uint32_t q4_row_form = 0;                                        // TATARA_POLICY_Q4_ROW_FORM
+    uint32_t gdn_step_early_dependents = 0;                          // TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS
     uint32_t* merge_counters = nullptr; // kMergeCounterSlots pairs of u32 in device memory, zero between launches
     uint32_t merge_slot = 0;            // next pair (round robin: calls in flight together use different pairs)
     char error[256] = {0};

@@ -348,7 +348,8 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
                         const __nv_bfloat16* __restrict__ norm_weight, __nv_bfloat16* conv_pool,
                         float* rec_pool, __nv_bfloat16* __restrict__ y_out,
                         __nv_bfloat16* __restrict__ gated, const __grid_constant__ GdnLanes lanes,
-                        const tatara_gdn_lane* lanes_device, uint32_t* status, uint32_t late_half) {
+                        const tatara_gdn_lane* lanes_device, uint32_t* status, uint32_t late_half,
+                        uint32_t early_dependents) {
     extern __shared__ __align__(128) uint8_t fd_smem[];   // kBulk: [128 rows][128] f32, mbarriers, abort word
     __shared__ float head_q[kGdnDim], head_k[kGdnDim];
     __shared__ float qn[kGdnDim], kn[kGdnDim], vn[kGdnDim], ys[kGdnDim];
@@ -421,11 +422,15 @@ gdn_decode_fused_kernel(const __nv_bfloat16* projection, uint64_t projection_str
     // Launched as a programmatic dependent of its predecessor in the stream (the projection that
     // produces `projection`): what is read above is this layer's own state and weights, which that
     // predecessor does not write, so those loads are in flight while the predecessor finishes; the
-    // projection row and every store wait here.  This kernel never signals its own dependents early:
-    // the next call on the same layer reads the state written below, so it must not start before this
-    // grid has completed.
+    // projection row and every store wait here.  By default this kernel never signals its own
+    // dependents early: a following call on the SAME state would read, before its own wait, the rows
+    // written below.  A caller whose next kernels do not read this call's state or conv slots before
+    // their own dependency wait (a layer walk: the out projection follows, then another layer) may say
+    // so (TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS); the successor is then staged, and asks for its
+    // weights, while this grid computes.
     // (`proj` is an output of the statement, so no load through it can be placed above it)
     asm volatile("griddepcontrol.wait;" : "+l"(proj) : : "memory");
+    if (early_dependents) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Everything else the prologue and the epilogue read (the projection row) is requested at once:
     // one trip to L2 instead of one per dependent phase; the arithmetic keeps its order.
@@ -649,7 +654,8 @@ static tatara_status launch_fused_step(tatara_ctx* ctx, void* stream, const void
                              static_cast<const bf16*>(dt_bias), static_cast<const bf16*>(norm_weight),
                              static_cast<bf16*>(conv_pool), static_cast<float*>(rec_pool), static_cast<bf16*>(y),
                              static_cast<bf16*>(gated), table, lanes_device, ctx->device_status,
-                             n_lanes * kGdnValueHeads <= 2u * uint32_t(ctx->sm_count) ? 1u : 0u);
+                             n_lanes * kGdnValueHeads <= 2u * uint32_t(ctx->sm_count) ? 1u : 0u,
+                             ctx->gdn_step_early_dependents);
     return check_launch(ctx, what);
 }
 

@@ -322,6 +322,10 @@ class MultiStreamOwner {
     }
 
     bool apply_policies(tatara_ctx* ctx) const {
+        // A wave walks the layers in order (projection, step, out projection, next layer): no kernel reads
+        // the state a gated-delta step writes before that step's launch has completed, so the step may let
+        // its successors be staged early.  A caller's own policies come after and may undo this.
+        if (tatara_ctx_set_policy(ctx, TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS, 1) != TATARA_OK) return false;
         for (const auto& pv : config_.policies)
             if (tatara_ctx_set_policy(ctx, static_cast<tatara_policy>(pv.first), pv.second) != TATARA_OK) return false;
         return true;
