@@ -190,6 +190,51 @@ def test_projection_chained_into_step_matches_synchronised_calls(ctx):
         assert torch.equal(chained, stepped)
 
 
+def test_layer_walk_with_early_dependents_matches_synchronised_calls(ctx):
+    """TATARA_POLICY_GDN_STEP_EARLY_DEPENDENTS: in a walk over TWO gated-delta layers (projection, step, out
+    projection per layer, eight tokens, no host synchronisation) the step lets its successors be staged while
+    it computes; the bits are those of the same calls with the policy off and a synchronisation after each."""
+    rng = np.random.default_rng(78)
+    n, tokens, n_layers = 2, 8, 2
+    conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
+    w = [dev_bf16(x) for x in (conv_w, a_log, dt_bias, norm_w)]
+    layer_pools = [make_pools(rng, n)[2:] for _ in range(n_layers)]
+    proj_sets, out_sets = [], []
+    for _ in range(n_layers):
+        mats = [syn.q4_matrix(rng, m, 2048) for m in (8192, 4096, 32, 32)]
+        held = [(torch.from_numpy(a.view(np.int32)).cuda(), dev_bf16(b), dev_bf16(c)) for a, b, c in mats]
+        proj_sets.append((held, tb.Context.q4_matrices(held)))
+        om = syn.q4_matrix(rng, 2048, 4096)
+        oh = [(torch.from_numpy(om[0].view(np.int32)).cuda(), dev_bf16(om[1]), dev_bf16(om[2]))]
+        out_sets.append((oh, tb.Context.q4_matrices(oh)))
+    hidden0 = dev_bf16(syn.hidden_rows(rng, n, 2048))
+    results = []
+    for early in (1, 0):
+        pools = [(c.clone(), r.clone()) for c, r in layer_pools]
+        hidden = hidden0.clone()
+        slab, y, gated = bf((n, 12352)), bf((n, 4096)), bf((n, 4096))
+        ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, early)
+        try:
+            for token in range(tokens):
+                for layer in range(n_layers):
+                    ctx.q4_project(hidden, proj_sets[layer][1], 2048, slab)
+                    if not early:
+                        ctx.sync()
+                    ctx.gdn_decode_batch(slab, w[0], w[1], w[2], w[3], pools[layer][0], pools[layer][1],
+                                         lane_table(n, token % 2 == 1), y, gated)
+                    if not early:
+                        ctx.sync()
+                    ctx.q4_project(gated, out_sets[layer][1], 4096, hidden)
+                    if not early:
+                        ctx.sync()
+            ctx.sync()
+        finally:
+            ctx.set_policy(tb.POLICY_GDN_STEP_EARLY_DEPENDENTS, 0)
+        results.append([hidden.clone()] + [t.clone() for pair in pools for t in pair])
+    for chained, stepped in zip(results[0], results[1]):
+        assert torch.equal(chained, stepped)
+
+
 def test_fused_equals_unfused_ops(ctx):
     rng = np.random.default_rng(24)
     conv_w, a_log, dt_bias, norm_w = syn.gdn_weights(rng)
