@@ -439,10 +439,16 @@ class Workloads:
                 clocks = cs.summary()
             else:
                 ms = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
-            # the one-CTA kernel on the same inputs (TATARA_POLICY_ATTN_PREFILL_FORM = 1), for comparison
+            # the one-CTA kernel on the same inputs (TATARA_POLICY_ATTN_PREFILL_FORM = 1), timed the same way
+            # (after the same hold of its own graph when the clocks are being sampled: under the power cap
+            # the SM clock settles some 20 % below a short burst's)
             self.ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 1)
             try:
-                ms_single = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
+                if sampler is not None:
+                    ms_single = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3,
+                                      hold_s=1.0)
+                else:
+                    ms_single = timed(lambda i=0: self.ctx.attn_prefill(q, gate, keys, values, 0, rows, rows, out), steps, 3)
             finally:
                 self.ctx.set_policy(tb.POLICY_ATTN_PREFILL_FORM, 0)
         except tb.TataraError as e:
