@@ -535,8 +535,8 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_kernel(cons
 // The row-pair kernel with the weights brought in by the copy engine (whole column groups, two buffers per
 // warp, asked for before the dependency wait: see q4_project_bulk_kernel); the arithmetic is the row-pair
 // kernel's, so are the bits.
-template <int RP, int C>
-__global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_bulk_kernel(const __grid_constant__ Q4Params p) {
+template <int RP, int C, int W>
+__global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const __grid_constant__ Q4Params p) {
     extern __shared__ float4 xs4[];   // [RP][blocks][8][32] float4, the sums [RP][blocks][32] float2, then the weight buffers
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const uint32_t row0 = blockIdx.y * (2 * RP);
@@ -545,16 +545,16 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_bulk_kernel
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t n_groups = p.n_cols / C;
-    const uint32_t nwarps = gridDim.x * kQ4Warps;
-    uint32_t g = blockIdx.x * kQ4Warps + warp;
+    const uint32_t nwarps = gridDim.x * uint32_t(W);
+    uint32_t g = blockIdx.x * uint32_t(W) + warp;
 
     const Q4BulkLayout lay = q4_bulk_layout(1, C, p.k);      // (group geometry only; the inputs are laid out below)
     const uint32_t x_bytes = RP * blocks * (256u * 16u + 32u * 8u);
     uint8_t* smem_bytes = reinterpret_cast<uint8_t*>(xs4);
     uint8_t* wbuf = smem_bytes + x_bytes + warp * 2u * lay.group_bytes;
-    const uint32_t bars = s2u(smem_bytes + x_bytes + kQ4Warps * 2u * lay.group_bytes) + warp * 16u;
+    const uint32_t bars = s2u(smem_bytes + x_bytes + uint32_t(W) * 2u * lay.group_bytes) + warp * 16u;
     volatile uint32_t* abort_flag =
-        reinterpret_cast<volatile uint32_t*>(smem_bytes + x_bytes + kQ4Warps * 2u * lay.group_bytes + kQ4Warps * 16u);
+        reinterpret_cast<volatile uint32_t*>(smem_bytes + x_bytes + uint32_t(W) * 2u * lay.group_bytes + uint32_t(W) * 16u);
     // lane 0: the three copies of one column group into buffer `buf` (see q4_project_bulk_kernel)
     auto request = [&](uint32_t group, uint32_t buf) {
         const uint32_t col0 = group * C;
@@ -578,7 +578,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_bulk_kernel
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // stage the row pairs: one (row, block, lane) item = 16 inputs
-    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += kQ4Warps * 32u) {
+    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += uint32_t(W) * 32u) {
         const uint32_t l = item & 31u, b = (item >> 5) % blocks, r = item / (32u * blocks);
         const uint32_t row = min(row0 + r, p.n_rows - 1u);
         const uint4* xp = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride + b * 512u + l * 16u);
@@ -618,43 +618,53 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_bulk_kernel
         const unsigned short* gbias = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes + lay.affine_bytes);
 #pragma unroll 1
       for (uint32_t b = 0; b < blocks; ++b) {
-        float4 xv[RP][8];
-        float2 sum[RP];
-#pragma unroll
-        for (int rp = 0; rp < RP; ++rp) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) xv[rp][i] = xs4[((rp * blocks + b) * 8u + i) * 32u + lane];
-            sum[rp] = sum2[(rp * blocks + b) * 32u + lane];
-        }
+        // Half-word by half-word (four inputs of every row at a time) with the columns inside: only two
+        // float4 of inputs per row pair are live instead of eight, and the RP x C chains of one step
+        // are independent of one another (a chain still takes its inputs in order 0 .. 15).
+        uint2 wdc[C];
+        float2 quant[RP][C];
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            const uint2 wdc = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
-            const uint32_t half[4] = {wdc.x & 0xFFFFu, wdc.x >> 16, wdc.y & 0xFFFFu, wdc.y >> 16};
-            const float scale = __uint_as_float(uint32_t(gs[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
-            const float bias = __uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
-            float2 quant[RP];
+            wdc[c] = *reinterpret_cast<const uint2*>(gb + uint32_t(c) * (p.k >> 1) + b * 256u + lane * 8u);
 #pragma unroll
-            for (int rp = 0; rp < RP; ++rp) quant[rp] = make_float2(0.0f, 0.0f);
+            for (int rp = 0; rp < RP; ++rp) quant[rp][c] = make_float2(0.0f, 0.0f);
+        }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                // the four nibbles of half-word i, each as {w, w}; inputs 4i .. 4i+3 are xv[.][2i].xy, .zw, xv[.][2i+1].xy, .zw
-                const float w0 = __uint_as_float((half[i] & 0x000Fu) | 0x4B000000u), w1 = __uint_as_float((half[i] & 0x00F0u) | 0x4B000000u);
-                const float w2 = __uint_as_float((half[i] & 0x0F00u) | 0x4B000000u), w3 = __uint_as_float((half[i] & 0xF000u) | 0x4B000000u);
+        for (int i = 0; i < 4; ++i) {
+            float4 lo[RP], hi[RP];
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) {
+                lo[rp] = xs4[((rp * blocks + b) * 8u + 2 * i) * 32u + lane];
+                hi[rp] = xs4[((rp * blocks + b) * 8u + 2 * i + 1) * 32u + lane];
+            }
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const uint32_t word = (i & 2) ? wdc[c].y : wdc[c].x;
+                const uint32_t half = (i & 1) ? (word >> 16) : (word & 0xFFFFu);
+                // the four nibbles of half-word i, each as {w, w}; inputs 4i .. 4i+3 are lo.xy, lo.zw, hi.xy, hi.zw
+                const float w0 = __uint_as_float((half & 0x000Fu) | 0x4B000000u), w1 = __uint_as_float((half & 0x00F0u) | 0x4B000000u);
+                const float w2 = __uint_as_float((half & 0x0F00u) | 0x4B000000u), w3 = __uint_as_float((half & 0xF000u) | 0x4B000000u);
                 const float2 q0 = __fadd2_rn(make_float2(w0, w0), magic), q1 = __fadd2_rn(make_float2(w1, w1), magic);
                 const float2 q2 = __fadd2_rn(make_float2(w2, w2), magic), q3 = __fadd2_rn(make_float2(w3, w3), magic);
 #pragma unroll
                 for (int rp = 0; rp < RP; ++rp) {
-                    const float4 lo = xv[rp][2 * i], hi = xv[rp][2 * i + 1];
-                    quant[rp] = __ffma2_rn(make_float2(lo.x, lo.y), q0, quant[rp]);
-                    quant[rp] = __ffma2_rn(make_float2(lo.z, lo.w), q1, quant[rp]);
-                    quant[rp] = __ffma2_rn(make_float2(hi.x, hi.y), q2, quant[rp]);
-                    quant[rp] = __ffma2_rn(make_float2(hi.z, hi.w), q3, quant[rp]);
+                    quant[rp][c] = __ffma2_rn(make_float2(lo[rp].x, lo[rp].y), q0, quant[rp][c]);
+                    quant[rp][c] = __ffma2_rn(make_float2(lo[rp].z, lo[rp].w), q1, quant[rp][c]);
+                    quant[rp][c] = __ffma2_rn(make_float2(hi[rp].x, hi[rp].y), q2, quant[rp][c]);
+                    quant[rp][c] = __ffma2_rn(make_float2(hi[rp].z, hi[rp].w), q3, quant[rp][c]);
                 }
             }
+        }
 #pragma unroll
-            for (int rp = 0; rp < RP; ++rp)
-                result[rp][c] = __ffma2_rn(sum[rp], make_float2(bias, bias),
-                                           __ffma2_rn(make_float2(scale, scale), quant[rp], result[rp][c]));
+        for (int c = 0; c < C; ++c) {
+            const float scale = __uint_as_float(uint32_t(gs[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+            const float bias = __uint_as_float(uint32_t(gbias[uint32_t(c) * gpr + b * 8u + (lane >> 2)]) << 16);
+#pragma unroll
+            for (int rp = 0; rp < RP; ++rp) {
+                const float2 sum = sum2[(rp * blocks + b) * 32u + lane];
+                result[rp][c] = __ffma2_rn(sum, make_float2(bias, bias),
+                                           __ffma2_rn(make_float2(scale, scale), quant[rp][c], result[rp][c]));
+            }
         }
       }
         {
@@ -719,15 +729,15 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
     return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
 }
 
-template <int RP, int C>
+template <int RP, int C, int W>
 static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
-    const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
-    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + kQ4Warps * 2u * q4_bulk_layout(1, C, p.k).group_bytes +
-                          kQ4Warps * 16u + 16u;
+    const uint32_t ctas = min((groups + uint32_t(W) - 1u) / uint32_t(W), sm_count);
+    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + uint32_t(W) * 2u * q4_bulk_layout(1, C, p.k).group_bytes +
+                          uint32_t(W) * 16u + 16u;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
+        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
         if (err != cudaSuccess) return err;
         configured = true;
     }
@@ -736,12 +746,12 @@ static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cu
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(ctas, (p.n_rows + 2 * RP - 1) / (2 * RP));
-    cfg.blockDim = dim3(kQ4Warps * 32);
+    cfg.blockDim = dim3(uint32_t(W) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, q4_project_pairs_bulk_kernel<RP, C>, p);
+    return cudaLaunchKernelEx(&cfg, q4_project_pairs_bulk_kernel<RP, C, W>, p);
 }
 
 // The bulk-copy form of the exact-row kernel (rows <= 4).
@@ -1192,15 +1202,33 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     // more than four rows: the row-pair kernel, its weights by bulk copies when the inputs of eight rows
     // and the buffers fit the shared memory (four columns per warp up to 2048 inputs, two up to 4096)
     const uint32_t pairs_x = 4u * (k >> 9) * (256u * 16u + 32u * 8u);
-    const bool pairs_bulk4 = aligned16 && n_rows > 4u && pairs_x + kQ4Warps * 2u * q4_bulk_layout(1, 4, k).group_bytes + 144u <= 221184u;
+    auto pairs_fit = [&](uint32_t cols_per_warp, uint32_t warps) {
+        return pairs_x + warps * 2u * q4_bulk_layout(1, cols_per_warp, k).group_bytes + warps * 16u + 16u <= 221184u;
+    };
     // (two columns per warp re-read the inputs twice as often: measured 15.1 -> 10.4 us at 8 rows of the
     // out projection but 15.1 -> 20.3 us at 16, where two row tiles share the SMs)
-    const bool pairs_bulk2 = aligned16 && n_rows > 4u && n_rows <= 8u && !pairs_bulk4 &&
-                             pairs_x + kQ4Warps * 2u * q4_bulk_layout(1, 2, k).group_bytes + 144u <= 221184u;
+    const bool pairs_bulk4 = aligned16 && n_rows > 4u && pairs_fit(4, 8);
+    const bool pairs_bulk2 = aligned16 && n_rows > 4u && n_rows <= 8u && !pairs_bulk4 && pairs_fit(2, 8);
+    // Eight, eleven or twelve warps per SM (157 registers): more warps hide more latency, but what matters first is how
+    // evenly the column groups divide over the warps (2304 groups of attn_project on 8 / 12 warps: two rounds
+    // either way, 14.3 / 18.3 us; 3088 groups of gdn_project: three rounds of 8 or two of 12, 19.7 / 18.9 us).
+    auto slots = [&](uint32_t groups, uint32_t warps) { return ((groups + sms * warps - 1u) / (sms * warps)) * warps; };
+    auto best_warps = [&](uint32_t cols_per_warp) {
+        uint32_t best = 8;
+        for (uint32_t w : {11u, 12u})
+            if (pairs_fit(cols_per_warp, w) && slots(cols / cols_per_warp, w) <= slots(cols / cols_per_warp, best)) best = w;
+        return best;
+    };
     if (pairs_bulk4) {
-        (void)launch_q4_pairs_bulk<4, 4>(p, sms, s);
+        const uint32_t w = best_warps(4);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12>(p, sms, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11>(p, sms, s);
+        else (void)launch_q4_pairs_bulk<4, 4, 8>(p, sms, s);
     } else if (pairs_bulk2) {
-        (void)launch_q4_pairs_bulk<4, 2>(p, sms, s);
+        const uint32_t w = best_warps(2);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12>(p, sms, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11>(p, sms, s);
+        else (void)launch_q4_pairs_bulk<4, 2, 8>(p, sms, s);
     } else if (bulk) {
         // narrow matrices take two columns per warp so that every warp of the grid has a group
         const bool narrow = cols / 4u < sms * kQ4Warps;
