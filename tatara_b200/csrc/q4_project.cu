@@ -535,7 +535,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_kernel(cons
 // The row-pair kernel with the weights brought in by the copy engine (whole column groups, two buffers per
 // warp, asked for before the dependency wait: see q4_project_bulk_kernel); the arithmetic is the row-pair
 // kernel's, so are the bits.
-template <int RP, int C, int W>
+template <int RP, int C, int W, int NB>
 __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const __grid_constant__ Q4Params p) {
     extern __shared__ float4 xs4[];   // [RP][blocks][8][32] float4, the sums [RP][blocks][32] float2, then the weight buffers
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -551,10 +551,10 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
     const Q4BulkLayout lay = q4_bulk_layout(1, C, p.k);      // (group geometry only; the inputs are laid out below)
     const uint32_t x_bytes = RP * blocks * (256u * 16u + 32u * 8u);
     uint8_t* smem_bytes = reinterpret_cast<uint8_t*>(xs4);
-    uint8_t* wbuf = smem_bytes + x_bytes + warp * 2u * lay.group_bytes;
-    const uint32_t bars = s2u(smem_bytes + x_bytes + uint32_t(W) * 2u * lay.group_bytes) + warp * 16u;
+    uint8_t* wbuf = smem_bytes + x_bytes + warp * uint32_t(NB) * lay.group_bytes;   // NB buffers per warp
+    const uint32_t bars = s2u(smem_bytes + x_bytes + uint32_t(W) * uint32_t(NB) * lay.group_bytes) + warp * 16u;
     volatile uint32_t* abort_flag =
-        reinterpret_cast<volatile uint32_t*>(smem_bytes + x_bytes + uint32_t(W) * 2u * lay.group_bytes + uint32_t(W) * 16u);
+        reinterpret_cast<volatile uint32_t*>(smem_bytes + x_bytes + uint32_t(W) * uint32_t(NB) * lay.group_bytes + uint32_t(W) * 16u);
     // lane 0: the three copies of one column group into buffer `buf` (see q4_project_bulk_kernel)
     auto request = [&](uint32_t group, uint32_t buf) {
         const uint32_t col0 = group * C;
@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
         mbar_init(bars + 8u, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         if (g < n_groups) request(g, 0);
-        if (g + nwarps < n_groups) request(g + nwarps, 1);
+        if (NB > 1 && g + nwarps < n_groups) request(g + nwarps, 1);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // stage the row pairs: one (row, block, lane) item = 16 inputs
@@ -689,12 +689,12 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
         }
         // the buffer is read: it takes the group two rounds ahead
         __syncwarp();
-        if (lane == 0 && ok && g + 2u * nwarps < n_groups) {
+        if (lane == 0 && ok && g + uint32_t(NB) * nwarps < n_groups) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            request(g + 2u * nwarps, buf);
+            request(g + uint32_t(NB) * nwarps, buf);
         }
         phase ^= 1u << buf;
-        buf ^= 1u;
+        if (NB > 1) buf ^= 1u;
         g += nwarps;
     }
     __syncthreads();
@@ -729,15 +729,15 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
     return cudaLaunchKernelEx(&cfg, q4_project_pairs_kernel<RP, C>, p);
 }
 
-template <int RP, int C, int W>
+template <int RP, int C, int W, int NB>
 static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
     const uint32_t ctas = min((groups + uint32_t(W) - 1u) / uint32_t(W), sm_count);
-    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + uint32_t(W) * 2u * q4_bulk_layout(1, C, p.k).group_bytes +
+    const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + uint32_t(W) * uint32_t(NB) * q4_bulk_layout(1, C, p.k).group_bytes +
                           uint32_t(W) * 16u + 16u;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
+        const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C, W, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
         if (err != cudaSuccess) return err;
         configured = true;
     }
@@ -751,7 +751,7 @@ static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cu
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, q4_project_pairs_bulk_kernel<RP, C, W>, p);
+    return cudaLaunchKernelEx(&cfg, q4_project_pairs_bulk_kernel<RP, C, W, NB>, p);
 }
 
 // The bulk-copy form of the exact-row kernel (rows <= 4).
@@ -1202,13 +1202,21 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     // more than four rows: the row-pair kernel, its weights by bulk copies when the inputs of eight rows
     // and the buffers fit the shared memory (four columns per warp up to 2048 inputs, two up to 4096)
     const uint32_t pairs_x = 4u * (k >> 9) * (256u * 16u + 32u * 8u);
-    auto pairs_fit = [&](uint32_t cols_per_warp, uint32_t warps) {
-        return pairs_x + warps * 2u * q4_bulk_layout(1, cols_per_warp, k).group_bytes + warps * 16u + 16u <= 221184u;
+    auto pairs_fit = [&](uint32_t cols_per_warp, uint32_t warps, uint32_t buffers) {
+        return pairs_x + warps * buffers * q4_bulk_layout(1, cols_per_warp, k).group_bytes + warps * 16u + 16u <= 221184u;
+    };
+    auto rounds = [&](uint32_t cols_per_warp, uint32_t warps) {
+        const uint32_t groups = cols / cols_per_warp;
+        return (groups + sms * warps - 1u) / (sms * warps);
     };
     // (two columns per warp re-read the inputs twice as often: measured 15.1 -> 10.4 us at 8 rows of the
     // out projection but 15.1 -> 20.3 us at 16, where two row tiles share the SMs)
-    const bool pairs_bulk4 = aligned16 && n_rows > 4u && pairs_fit(4, 8);
-    const bool pairs_bulk2 = aligned16 && n_rows > 4u && n_rows <= 8u && !pairs_bulk4 && pairs_fit(2, 8);
+    const bool pairs_bulk4 = aligned16 && n_rows > 4u && pairs_fit(4, 8, 2);
+    const bool pairs_bulk2 = aligned16 && n_rows > 4u && n_rows <= 8u && !pairs_bulk4 && pairs_fit(2, 8, 2);
+    // EIGHT columns per warp halve the shared-memory traffic per multiply-add (the inputs of a block are read
+    // once per eight columns): taken when every warp then has exactly one column group, which also needs one
+    // buffer per warp only.
+    const bool pairs_bulk8 = pairs_bulk4 && cols % 8u == 0u && rounds(8, 8) == 1u && pairs_fit(8, 8, 1);
     // Eight, eleven or twelve warps per SM (157 registers): more warps hide more latency, but what matters first is how
     // evenly the column groups divide over the warps (2304 groups of attn_project on 8 / 12 warps: two rounds
     // either way, 14.3 / 18.3 us; 3088 groups of gdn_project: three rounds of 8 or two of 12, 19.7 / 18.9 us).
@@ -1216,19 +1224,21 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     auto best_warps = [&](uint32_t cols_per_warp) {
         uint32_t best = 8;
         for (uint32_t w : {11u, 12u})
-            if (pairs_fit(cols_per_warp, w) && slots(cols / cols_per_warp, w) <= slots(cols / cols_per_warp, best)) best = w;
+            if (pairs_fit(cols_per_warp, w, 2) && slots(cols / cols_per_warp, w) <= slots(cols / cols_per_warp, best)) best = w;
         return best;
     };
-    if (pairs_bulk4) {
+    if (pairs_bulk8) {
+        (void)launch_q4_pairs_bulk<4, 8, 8, 1>(p, sms, s);
+    } else if (pairs_bulk4) {
         const uint32_t w = best_warps(4);
-        if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12>(p, sms, s);
-        else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11>(p, sms, s);
-        else (void)launch_q4_pairs_bulk<4, 4, 8>(p, sms, s);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12, 2>(p, sms, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11, 2>(p, sms, s);
+        else (void)launch_q4_pairs_bulk<4, 4, 8, 2>(p, sms, s);
     } else if (pairs_bulk2) {
         const uint32_t w = best_warps(2);
-        if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12>(p, sms, s);
-        else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11>(p, sms, s);
-        else (void)launch_q4_pairs_bulk<4, 2, 8>(p, sms, s);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12, 2>(p, sms, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11, 2>(p, sms, s);
+        else (void)launch_q4_pairs_bulk<4, 2, 8, 2>(p, sms, s);
     } else if (bulk) {
         // narrow matrices take two columns per warp so that every warp of the grid has a group
         const bool narrow = cols / 4u < sms * kQ4Warps;
