@@ -706,15 +706,15 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
 }
 
 template <int RP, int C>
-static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, int device, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
     const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count);
     const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u);
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};   // the attribute is per device
+    if (!configured[device & 63]) {
         const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_kernel<RP, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 212992);
         if (err != cudaSuccess) return err;
-        configured = true;
+        configured[device & 63] = true;
     }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -730,16 +730,16 @@ static cudaError_t launch_q4_pairs(const Q4Params& p, uint32_t sm_count, cudaStr
 }
 
 template <int RP, int C, int W, int NB>
-static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, int device, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C, blocks = p.k >> 9;
     const uint32_t ctas = min((groups + uint32_t(W) - 1u) / uint32_t(W), sm_count);
     const uint32_t smem = RP * blocks * (256u * 16u + 32u * 8u) + uint32_t(W) * uint32_t(NB) * q4_bulk_layout(1, C, p.k).group_bytes +
                           uint32_t(W) * 16u + 16u;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};   // the attribute is per device
+    if (!configured[device & 63]) {
         const cudaError_t err = cudaFuncSetAttribute(q4_project_pairs_bulk_kernel<RP, C, W, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
         if (err != cudaSuccess) return err;
-        configured = true;
+        configured[device & 63] = true;
     }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -756,18 +756,18 @@ static cudaError_t launch_q4_pairs_bulk(const Q4Params& p, uint32_t sm_count, cu
 
 // The bulk-copy form of the exact-row kernel (rows <= 4).
 template <int R, int C>
-static cudaError_t launch_q4_bulk(const Q4Params& p, uint32_t sm_count, cudaStream_t stream) {
+static cudaError_t launch_q4_bulk(const Q4Params& p, uint32_t sm_count, int device, cudaStream_t stream) {
     const uint32_t groups = p.n_cols / C;
     const Q4BulkLayout lay = q4_bulk_layout(R, C, p.k);
     // as many CTAs per SM as the shared memory holds (at most three): more warps to hide the latencies
     // of the block loop, and more of the matrix asked for at once
     const uint32_t per_sm = max(1u, min(3u, 232448u / (lay.total + 1024u)));
     const uint32_t ctas = min((groups + kQ4Warps - 1u) / kQ4Warps, sm_count * per_sm);
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};   // the attribute is per device
+    if (!configured[device & 63]) {
         const cudaError_t err = cudaFuncSetAttribute(q4_project_bulk_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 221184);
         if (err != cudaSuccess) return err;
-        configured = true;
+        configured[device & 63] = true;
     }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1228,24 +1228,24 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
         return best;
     };
     if (pairs_bulk8) {
-        (void)launch_q4_pairs_bulk<4, 8, 8, 1>(p, sms, s);
+        (void)launch_q4_pairs_bulk<4, 8, 8, 1>(p, sms, ctx->device, s);
     } else if (pairs_bulk4) {
         const uint32_t w = best_warps(4);
-        if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12, 2>(p, sms, s);
-        else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11, 2>(p, sms, s);
-        else (void)launch_q4_pairs_bulk<4, 4, 8, 2>(p, sms, s);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12, 2>(p, sms, ctx->device, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11, 2>(p, sms, ctx->device, s);
+        else (void)launch_q4_pairs_bulk<4, 4, 8, 2>(p, sms, ctx->device, s);
     } else if (pairs_bulk2) {
         const uint32_t w = best_warps(2);
-        if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12, 2>(p, sms, s);
-        else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11, 2>(p, sms, s);
-        else (void)launch_q4_pairs_bulk<4, 2, 8, 2>(p, sms, s);
+        if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12, 2>(p, sms, ctx->device, s);
+        else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11, 2>(p, sms, ctx->device, s);
+        else (void)launch_q4_pairs_bulk<4, 2, 8, 2>(p, sms, ctx->device, s);
     } else if (bulk) {
         // narrow matrices take two columns per warp so that every warp of the grid has a group
         const bool narrow = cols / 4u < sms * kQ4Warps;
         cudaError_t err;
-        if (n_rows == 1) err = narrow ? launch_q4_bulk<1, 2>(p, sms, s) : launch_q4_bulk<1, 4>(p, sms, s);
-        else if (n_rows == 2) err = narrow ? launch_q4_bulk<2, 2>(p, sms, s) : launch_q4_bulk<2, 4>(p, sms, s);
-        else err = narrow ? launch_q4_bulk<4, 2>(p, sms, s) : launch_q4_bulk<4, 4>(p, sms, s);
+        if (n_rows == 1) err = narrow ? launch_q4_bulk<1, 2>(p, sms, ctx->device, s) : launch_q4_bulk<1, 4>(p, sms, ctx->device, s);
+        else if (n_rows == 2) err = narrow ? launch_q4_bulk<2, 2>(p, sms, ctx->device, s) : launch_q4_bulk<2, 4>(p, sms, ctx->device, s);
+        else err = narrow ? launch_q4_bulk<4, 2>(p, sms, ctx->device, s) : launch_q4_bulk<4, 4>(p, sms, ctx->device, s);
         (void)err;
     } else if (n_rows == 1) {
         // few warps with many bytes in flight each; narrow matrices get narrower groups (more warps)
@@ -1256,7 +1256,7 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
     } else if (n_rows <= 4) {
         launch_q4<4, 4>(p, sms, 1, s);
     } else {
-        (void)launch_q4_pairs<4, 4>(p, sms, s);   // 8 rows per pass; more rows run as further row tiles
+        (void)launch_q4_pairs<4, 4>(p, sms, ctx->device, s);   // 8 rows per pass; more rows run as further row tiles
     }
     return check_launch(ctx, "q4_project");
 }

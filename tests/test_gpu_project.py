@@ -66,6 +66,29 @@ def test_exact_row_bits_lane_load_form(ctx, rows, k):
     assert np.array_equal(host_u16(out), oracle_project(x, mats, 4))
 
 
+@pytest.mark.parametrize("rows", [1, 4, 8])
+def test_exact_row_bits_with_scales_off_the_16_byte_grid(ctx, rows):
+    """The bulk-copy forms need 16-byte aligned rows of scales and biases; the ABI only asks for 2-byte alignment,
+    and a matrix whose affine constants start 2 bytes off the grid runs the per-lane-load kernels: same bits."""
+    rng = np.random.default_rng(4242 + rows)
+    k = 2048
+    w, sc, bi = syn.q4_matrix(rng, 64, k)
+    x = syn.hidden_rows(rng, rows, k)
+    words = torch.from_numpy(w.view(np.int32)).cuda()
+    sbuf = torch.zeros(sc.size + 8, dtype=torch.bfloat16, device="cuda")
+    bbuf = torch.zeros(bi.size + 8, dtype=torch.bfloat16, device="cuda")
+    scales = sbuf[1:1 + sc.size].view(sc.shape)
+    biases = bbuf[1:1 + bi.size].view(bi.shape)
+    scales.copy_(dev_bf16(sc)); biases.copy_(dev_bf16(bi))
+    assert scales.data_ptr() % 16 == 2
+    held = [(words, scales, biases)]
+    arr = tb.Context.q4_matrices(held)
+    out = torch.zeros((rows, 64), dtype=torch.bfloat16, device="cuda")
+    ctx.q4_project(dev_bf16(x), arr, k, out)
+    ctx.sync()
+    assert np.array_equal(host_u16(out), oracle_project(x, [(w, sc, bi)], 4))
+
+
 @pytest.mark.parametrize("name,sizes,k", [("attn_project", (8192, 512, 512), 2048),
                                           ("gdn_project", (8192, 4096, 32, 32), 2048),
                                           ("out_projection", (2048,), 4096)])
