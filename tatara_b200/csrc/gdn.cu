@@ -105,6 +105,103 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ projection,
     }
 }
 
+// The same operator for BLOCKS of rows (prefill).  The decomposition above launches one 128-thread CTA
+// per (group, row): 196 608 CTAs for 2048 rows, each a short chain of dependent loads, a block
+// barrier and a store -- 109 us for 2048 rows where the 100 MB it moves are 16 us of HBM time, more
+// than the chunked scan it feeds.  Here a WARP owns one group of 128 channels (lane l: channels
+// 4l .. 4l+3, the reference's own split of the l2-norm: four squares per lane, then the adjacent-pairs
+// tree over the 32 lanes -- a warp reduction, no barrier) and walks a run of consecutive rows with the
+// three previous taps in registers, so every projection entry is loaded once (8 bytes per lane and row,
+// the loads of a run's next row issued before this row's arithmetic).  Same per-channel arithmetic
+// (conv_channel_apply) and the same reduction order: bit-identical to the kernel above.
+constexpr uint32_t kPrepRun = 16;         // consecutive rows per warp
+constexpr uint32_t kPrepWarps = 8;        // runs per CTA
+
+__device__ __forceinline__ void load_bf16x4_bits(const __nv_bfloat16* p, float out[4]) {
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+    out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+    out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+}
+
+__global__ void __launch_bounds__(kPrepWarps * 32)
+gdn_prepare_block_kernel(const __nv_bfloat16* __restrict__ projection,
+                         const __nv_bfloat16* __restrict__ conv_state,
+                         const __nv_bfloat16* __restrict__ conv_weights, __nv_bfloat16* __restrict__ qk,
+                         __nv_bfloat16* __restrict__ value, __nv_bfloat16* __restrict__ z,
+                         __nv_bfloat16* __restrict__ new_conv_state, uint32_t rows) {
+    const uint32_t group = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t r0 = (blockIdx.y * kPrepWarps + warp) * kPrepRun;
+    if (r0 >= rows) return;
+    const uint32_t r1 = min(rows, r0 + kPrepRun);
+    if (group >= kGdnConv / kGdnDim) {   // z: a copy
+        const uint32_t index = (group - kGdnConv / kGdnDim) * kGdnDim + lane * 4u;
+        for (uint32_t row = r0; row < r1; ++row)
+            *reinterpret_cast<uint2*>(z + uint64_t(row) * kGdnV + index) =
+                __ldg(reinterpret_cast<const uint2*>(projection + uint64_t(row) * kGdnProj + kGdnZOff + index));
+        return;
+    }
+    const uint32_t c0 = group * kGdnDim + lane * 4u;
+    // the four channels' tap weights: [channel][4] bf16, 32 bytes per lane
+    uint2 wraw[4];
+    {
+        const uint4 wa = __ldg(reinterpret_cast<const uint4*>(conv_weights + uint64_t(c0) * 4u));
+        const uint4 wb = __ldg(reinterpret_cast<const uint4*>(conv_weights + uint64_t(c0) * 4u + 8u));
+        wraw[0] = make_uint2(wa.x, wa.y); wraw[1] = make_uint2(wa.z, wa.w);
+        wraw[2] = make_uint2(wb.x, wb.y); wraw[3] = make_uint2(wb.z, wb.w);
+    }
+    // logical sequence [3 conv-state rows | projection rows]: position `row` taps logical rows row .. row+3
+    auto load_logical = [&](uint32_t logical, float out[4]) {
+        if (logical < 3u) load_bf16x4_bits(conv_state + logical * kGdnConv + c0, out);
+        else load_bf16x4_bits(projection + uint64_t(logical - 3u) * kGdnProj + c0, out);
+    };
+    float w0[4], w1[4], w2[4], cur[4], next[4];
+    load_logical(r0, w0);
+    load_logical(r0 + 1u, w1);
+    load_logical(r0 + 2u, w2);
+    load_logical(r0 + 3u, cur);
+    const bool is_qk = group < kGdnQk / kGdnDim, is_query = group < kGdnKeyHeads;
+    for (uint32_t row = r0; row < r1; ++row) {
+        if (row + 1u < r1) load_logical(row + 4u, next);   // the next row's newest tap, ahead of this row's arithmetic
+        float act[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const float taps[4] = {w0[i], w1[i], w2[i], cur[i]};
+            act[i] = bf2f(conv_channel_apply(taps, wraw[i]));
+        }
+        __nv_bfloat16 res[4];
+        if (is_qk) {
+            // head_normalise with the head's 128 channels in one warp
+            float acc = 0.0f;
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) acc += act[i] * act[i];
+            acc = warp_sum(acc);
+            const float inverse = 1.0f / sqrtf(acc / float(kGdnDim) + kRmsEps);
+            const __nv_bfloat16 scale = is_query ? f2bf(1.0f / 128.0f) : f2bf(0.08838834764831845f);
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) res[i] = bmul(f2bf(act[i] * inverse), scale);
+            *reinterpret_cast<uint2*>(qk + uint64_t(row) * kGdnQk + c0) = *reinterpret_cast<const uint2*>(res);
+        } else {
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) res[i] = f2bf(act[i]);
+            *reinterpret_cast<uint2*>(value + uint64_t(row) * kGdnV + c0 - kGdnQk) = *reinterpret_cast<const uint2*>(res);
+        }
+        if (row + 1u == rows) {   // the three newest taps become the conv state
+            __nv_bfloat16 t1[4], t2[4], t3[4];
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i) {
+                t1[i] = f2bf(w1[i]); t2[i] = f2bf(w2[i]); t3[i] = f2bf(cur[i]);
+            }
+            *reinterpret_cast<uint2*>(new_conv_state + 0u * kGdnConv + c0) = *reinterpret_cast<const uint2*>(t1);
+            *reinterpret_cast<uint2*>(new_conv_state + 1u * kGdnConv + c0) = *reinterpret_cast<const uint2*>(t2);
+            *reinterpret_cast<uint2*>(new_conv_state + 2u * kGdnConv + c0) = *reinterpret_cast<const uint2*>(t3);
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            w0[i] = w1[i]; w1[i] = w2[i]; w2[i] = cur[i]; cur[i] = next[i];
+        }
+    }
+}
+
 __global__ void gdn_gates_kernel(const __nv_bfloat16* __restrict__ projection,
                                  uint64_t projection_stride, const __nv_bfloat16* __restrict__ a_log,
                                  const __nv_bfloat16* __restrict__ dt_bias, float* __restrict__ decay,
@@ -554,6 +651,16 @@ extern "C" tatara_status tatara_gdn_prepare(tatara_ctx* ctx, void* stream, const
     if (!aligned(conv_weights, 8)) return fail(ctx, TATARA_INVALID_BUFFER, "gdn_prepare: conv weights alignment");
     if (conv_in == conv_out) return fail(ctx, TATARA_STATE_SLOT_MISMATCH, "gdn_prepare: conv_in aliases conv_out");
     if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_prepare: rows");
+    // blocks of rows: a warp per (group, run of rows), 8-byte accesses (every buffer 8-byte aligned, weights 16)
+    if (rows >= 32u && aligned(projection, 8) && aligned(conv_in, 8) && aligned(conv_weights, 16) && aligned(qk, 8) &&
+        aligned(value, 8) && aligned(z, 8) && aligned(conv_out, 8)) {
+        const uint32_t tiles = (rows + kPrepWarps * kPrepRun - 1u) / (kPrepWarps * kPrepRun);
+        gdn_prepare_block_kernel<<<dim3(96, tiles), kPrepWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const bf16*>(projection), static_cast<const bf16*>(conv_in),
+            static_cast<const bf16*>(conv_weights), static_cast<bf16*>(qk), static_cast<bf16*>(value),
+            static_cast<bf16*>(z), static_cast<bf16*>(conv_out), rows);
+        return check_launch(ctx, "gdn_prepare");
+    }
     gdn_prepare_kernel<false><<<dim3(96, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(projection), static_cast<const bf16*>(conv_in),
         static_cast<const bf16*>(conv_weights), static_cast<bf16*>(qk), static_cast<bf16*>(value),

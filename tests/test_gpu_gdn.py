@@ -42,7 +42,7 @@ def assert_bf16_steps(got, want, what, max_steps=1, max_frac=5e-3):
     assert (dist > 0).mean() <= max_frac, f"{what}: {(dist > 0).mean():.3%} elements differ"
 
 
-@pytest.mark.parametrize("rows", [1, 2, 3, 4, 7, 64])
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 7, 31, 32, 33, 64, 200])
 def test_prepare_matches_oracle(ctx, rows):
     rng = np.random.default_rng(rows)
     conv_w, *_ = syn.gdn_weights(rng)
@@ -54,6 +54,31 @@ def test_prepare_matches_oracle(ctx, rows):
     assert_bf16_steps(v, ov, "value")
     assert_bf16_steps(qk, oqk, "qk")
     assert_close_bf16(qk, oqk, "qk"); assert_close_bf16(v, ov, "value", max_abs=4e-2)
+
+
+@pytest.mark.parametrize("rows", [32, 129, 2048 + 5])
+def test_prepare_block_kernel_equals_row_kernel_bit_for_bit(ctx, rows):
+    """A block of 32 rows or more runs gdn_prepare_block_kernel (a warp per group and run of rows); the same rows
+    in calls of at most 31, the conv state carried from call to call, run the one-CTA-per-row kernel: same bits
+    in q/k, v, z and the final conv state."""
+    rng = np.random.default_rng(600 + rows)
+    conv_w, *_ = syn.gdn_weights(rng)
+    conv, _ = syn.gdn_state(rng)
+    proj = dev_bf16(syn.gdn_projection(rng, rows))
+    w = dev_bf16(conv_w)
+    qk, v, z, new_conv = bf((rows, 4096)), bf((rows, 4096)), bf((rows, 4096)), bf((3, 8192))
+    ctx.gdn_prepare(proj, dev_bf16(conv), w, qk, v, z, new_conv, rows)
+    qk2, v2, z2 = bf((rows, 4096)), bf((rows, 4096)), bf((rows, 4096))
+    state = [dev_bf16(conv), bf((3, 8192))]
+    at = 0
+    while at < rows:
+        n = min(31, rows - at)
+        ctx.gdn_prepare(proj[at:at + n], state[0], w, qk2[at:at + n], v2[at:at + n], z2[at:at + n], state[1], n)
+        state.reverse()
+        at += n
+    ctx.sync()
+    assert torch.equal(qk, qk2) and torch.equal(v, v2) and torch.equal(z, z2)
+    assert torch.equal(new_conv, state[0])
 
 
 def test_gates_match_oracle(ctx):
