@@ -42,7 +42,8 @@ def run_decode(ctx, q, gate, keys, values, context, capacity):
     return host_u16(out)
 
 
-@pytest.mark.parametrize("position,rows", [(0, 1), (1, 13), (300, 17), (4096, 1), (262143, 1), (65000, 16)])
+@pytest.mark.parametrize("position,rows", [(0, 1), (1, 13), (300, 17), (4096, 1), (262143, 1), (65000, 16),
+                                           (0, 32), (7, 77), (261900, 200)])   # 32 rows and more: the block kernel
 def test_qk_rope_matches_oracle(ctx, position, rows):
     rng = np.random.default_rng(position + rows)
     cap = position + rows
@@ -68,6 +69,33 @@ def test_qk_rope_matches_oracle(ctx, position, rows):
     # untouched cache rows stay zero (canary)
     if position > 0:
         assert not host_u16(keys[:, :min(position, 64)]).any()
+
+
+@pytest.mark.parametrize("position,rows", [(0, 32), (1000, 129), (100000, 300)])
+def test_qk_rope_block_kernel_equals_row_kernel_bit_for_bit(ctx, position, rows):
+    """A block of 32 rows or more runs attn_qk_rope_block_kernel (a warp per row, the row's angles computed once);
+    the same rows in calls of at most 31 run the 18-CTAs-per-row kernel: same bits in q, gate and the appended
+    K/V rows."""
+    rng = np.random.default_rng(4000 + position + rows)
+    cap = position + rows + 2
+    qw, kw = syn.attn_weights(rng, unit=False)
+    proj = dev_bf16(syn.attn_projection(rng, rows))
+    dq, dk = dev_bf16(qw), dev_bf16(kw)
+    outs = []
+    for chunk in (rows, 31):
+        keys = torch.zeros((2, cap, 256), dtype=torch.bfloat16, device="cuda")
+        values = torch.zeros_like(keys)
+        q = torch.zeros((rows, 16, 256), dtype=torch.bfloat16, device="cuda")
+        gate = torch.zeros_like(q)
+        at = 0
+        while at < rows:
+            n = min(chunk, rows - at)
+            ctx.attn_qk_rope(proj[at:at + n], dq, dk, q[at:at + n], gate[at:at + n], keys, values, position + at, cap, n)
+            at += n
+        ctx.sync()
+        outs.append((q, gate, keys, values))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("context", [0, 1, 15, 16, 17, 63, 64, 65, 255, 256, 257, 1000, 4095, 4096,
