@@ -28,15 +28,19 @@ __device__ __forceinline__ void conv_channel_load(const __nv_bfloat16* projectio
     }
     wraw = *reinterpret_cast<const uint2*>(conv_weights + uint64_t(channel) * 4u);
 }
-__device__ __forceinline__ __nv_bfloat16 conv_channel_apply(const float taps[4], uint2 wraw) {
-    const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
-    const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
-    float acc = __fmul_rn(bf2f(w01.x), taps[0]);
-    acc = __fadd_rn(acc, __fmul_rn(bf2f(w01.y), taps[1]));
-    acc = __fadd_rn(acc, __fmul_rn(bf2f(w23.x), taps[2]));
-    acc = __fadd_rn(acc, __fmul_rn(bf2f(w23.y), taps[3]));
+// (the four tap weights as floats: a caller that walks many rows converts them once)
+__device__ __forceinline__ __nv_bfloat16 conv_channel_apply_w(const float taps[4], const float w[4]) {
+    float acc = __fmul_rn(w[0], taps[0]);
+    acc = __fadd_rn(acc, __fmul_rn(w[1], taps[1]));
+    acc = __fadd_rn(acc, __fmul_rn(w[2], taps[2]));
+    acc = __fadd_rn(acc, __fmul_rn(w[3], taps[3]));
     const __nv_bfloat16 c = f2bf(acc);
     return bmul(c, sigmoid_bf16(c));
+}
+__device__ __forceinline__ __nv_bfloat16 conv_channel_apply(const float taps[4], uint2 wraw) {
+    const float w[4] = {__uint_as_float(wraw.x << 16), __uint_as_float(wraw.x & 0xFFFF0000u),
+                        __uint_as_float(wraw.y << 16), __uint_as_float(wraw.y & 0xFFFF0000u)};
+    return conv_channel_apply_w(taps, w);
 }
 __device__ __forceinline__ __nv_bfloat16 conv_channel(const __nv_bfloat16* projection,
                                                       uint64_t projection_stride,
@@ -142,12 +146,16 @@ gdn_prepare_block_kernel(const __nv_bfloat16* __restrict__ projection,
     }
     const uint32_t c0 = group * kGdnDim + lane * 4u;
     // the four channels' tap weights: [channel][4] bf16, 32 bytes per lane
-    uint2 wraw[4];
+    float wf[4][4];
     {
         const uint4 wa = __ldg(reinterpret_cast<const uint4*>(conv_weights + uint64_t(c0) * 4u));
         const uint4 wb = __ldg(reinterpret_cast<const uint4*>(conv_weights + uint64_t(c0) * 4u + 8u));
-        wraw[0] = make_uint2(wa.x, wa.y); wraw[1] = make_uint2(wa.z, wa.w);
-        wraw[2] = make_uint2(wb.x, wb.y); wraw[3] = make_uint2(wb.z, wb.w);
+        const uint32_t raw[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            wf[i][0] = __uint_as_float(raw[2 * i] << 16); wf[i][1] = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
+            wf[i][2] = __uint_as_float(raw[2 * i + 1] << 16); wf[i][3] = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
+        }
     }
     // logical sequence [3 conv-state rows | projection rows]: position `row` taps logical rows row .. row+3
     auto load_logical = [&](uint32_t logical, float out[4]) {
@@ -166,7 +174,7 @@ gdn_prepare_block_kernel(const __nv_bfloat16* __restrict__ projection,
 #pragma unroll
         for (uint32_t i = 0; i < 4; ++i) {
             const float taps[4] = {w0[i], w1[i], w2[i], cur[i]};
-            act[i] = bf2f(conv_channel_apply(taps, wraw[i]));
+            act[i] = bf2f(conv_channel_apply_w(taps, wf[i]));
         }
         __nv_bfloat16 res[4];
         if (is_qk) {
@@ -397,6 +405,35 @@ gdn_gate_norm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
     float yv[4];
     load_bf16x4(y + base + lane * 4u, yv);
     gate_norm_head(yv, z + base, weight, out + base, lane);
+}
+
+// Blocks of rows: a warp keeps its head and walks a run of 16 rows, the next row's y and z requested before
+// this row's arithmetic (the one-warp-per-(head, row) form above is a chain of two dependent loads, a
+// reduction and a store per 32-thread task).  Same arithmetic: bit-identical.
+constexpr uint32_t kGateNormRun = 16;
+__global__ void __launch_bounds__(128)
+gdn_gate_norm_block_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
+                           const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint32_t rows) {
+    const uint32_t head = blockIdx.x * 4u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    const uint32_t r0 = blockIdx.y * kGateNormRun;
+    const uint32_t r1 = min(rows, r0 + kGateNormRun);
+    const uint2 wraw = *reinterpret_cast<const uint2*>(weight + lane * 4u);
+    uint64_t base = uint64_t(r0) * kGdnV + head * kGdnDim + lane * 4u;
+    uint2 yraw = __ldg(reinterpret_cast<const uint2*>(y + base)), zraw = __ldg(reinterpret_cast<const uint2*>(z + base));
+    for (uint32_t row = r0; row < r1; ++row, base += kGdnV) {
+        uint2 ynext = yraw, znext = zraw;
+        if (row + 1u < r1) {
+            ynext = __ldg(reinterpret_cast<const uint2*>(y + base + kGdnV));
+            znext = __ldg(reinterpret_cast<const uint2*>(z + base + kGdnV));
+        }
+        const float yv[4] = {__uint_as_float(yraw.x << 16), __uint_as_float(yraw.x & 0xFFFF0000u),
+                             __uint_as_float(yraw.y << 16), __uint_as_float(yraw.y & 0xFFFF0000u)};
+        const float zf[4] = {__uint_as_float(zraw.x << 16), __uint_as_float(zraw.x & 0xFFFF0000u),
+                             __uint_as_float(zraw.y << 16), __uint_as_float(zraw.y & 0xFFFF0000u)};
+        gate_norm_head_loaded(yv, zf, wraw, out + base - lane * 4u, lane);
+        yraw = ynext;
+        zraw = znext;
+    }
 }
 
 // ---- fused lane-batched decode step ------------------------------------------------------
@@ -725,6 +762,13 @@ extern "C" tatara_status tatara_gdn_gate_norm(tatara_ctx* ctx, void* stream, con
     if (!aligned(y, 8) || !aligned(z, 8) || !aligned(weight, 8) || !aligned(out, 8))
         return fail(ctx, TATARA_INVALID_BUFFER, "gdn_gate_norm: misaligned buffer");
     if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_gate_norm: rows");
+    if (rows >= 32u) {
+        gdn_gate_norm_block_kernel<<<dim3(kGdnValueHeads / 4, (rows + kGateNormRun - 1u) / kGateNormRun), 128, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const bf16*>(y), static_cast<const bf16*>(z), static_cast<const bf16*>(weight),
+            static_cast<bf16*>(out), rows);
+        return check_launch(ctx, "gdn_gate_norm");
+    }
     gdn_gate_norm_kernel<<<dim3(kGdnValueHeads / 4, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(y), static_cast<const bf16*>(z), static_cast<const bf16*>(weight),
         static_cast<bf16*>(out));
