@@ -407,35 +407,6 @@ gdn_gate_norm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
     gate_norm_head(yv, z + base, weight, out + base, lane);
 }
 
-// Blocks of rows: a warp keeps its head and walks a run of 16 rows, the next row's y and z requested before
-// this row's arithmetic (the one-warp-per-(head, row) form above is a chain of two dependent loads, a
-// reduction and a store per 32-thread task).  Same arithmetic: bit-identical.
-constexpr uint32_t kGateNormRun = 16;
-__global__ void __launch_bounds__(128)
-gdn_gate_norm_block_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z,
-                           const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint32_t rows) {
-    const uint32_t head = blockIdx.x * 4u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
-    const uint32_t r0 = blockIdx.y * kGateNormRun;
-    const uint32_t r1 = min(rows, r0 + kGateNormRun);
-    const uint2 wraw = *reinterpret_cast<const uint2*>(weight + lane * 4u);
-    uint64_t base = uint64_t(r0) * kGdnV + head * kGdnDim + lane * 4u;
-    uint2 yraw = __ldg(reinterpret_cast<const uint2*>(y + base)), zraw = __ldg(reinterpret_cast<const uint2*>(z + base));
-    for (uint32_t row = r0; row < r1; ++row, base += kGdnV) {
-        uint2 ynext = yraw, znext = zraw;
-        if (row + 1u < r1) {
-            ynext = __ldg(reinterpret_cast<const uint2*>(y + base + kGdnV));
-            znext = __ldg(reinterpret_cast<const uint2*>(z + base + kGdnV));
-        }
-        const float yv[4] = {__uint_as_float(yraw.x << 16), __uint_as_float(yraw.x & 0xFFFF0000u),
-                             __uint_as_float(yraw.y << 16), __uint_as_float(yraw.y & 0xFFFF0000u)};
-        const float zf[4] = {__uint_as_float(zraw.x << 16), __uint_as_float(zraw.x & 0xFFFF0000u),
-                             __uint_as_float(zraw.y << 16), __uint_as_float(zraw.y & 0xFFFF0000u)};
-        gate_norm_head_loaded(yv, zf, wraw, out + base - lane * 4u, lane);
-        yraw = ynext;
-        zraw = znext;
-    }
-}
-
 // ---- fused lane-batched decode step ------------------------------------------------------
 // One CTA per (v-head, lane): conv + SiLU + l2-norm for this head's q, k and v channels,
 // gates, the 128-row state update and the gated RMSNorm, with the first state rows already in
@@ -762,13 +733,6 @@ extern "C" tatara_status tatara_gdn_gate_norm(tatara_ctx* ctx, void* stream, con
     if (!aligned(y, 8) || !aligned(z, 8) || !aligned(weight, 8) || !aligned(out, 8))
         return fail(ctx, TATARA_INVALID_BUFFER, "gdn_gate_norm: misaligned buffer");
     if (rows == 0 || rows > 65535u) return fail(ctx, TATARA_INVALID_DISPATCH_EXTENT, "gdn_gate_norm: rows");
-    if (rows >= 32u) {
-        gdn_gate_norm_block_kernel<<<dim3(kGdnValueHeads / 4, (rows + kGateNormRun - 1u) / kGateNormRun), 128, 0,
-                                     static_cast<cudaStream_t>(stream)>>>(
-            static_cast<const bf16*>(y), static_cast<const bf16*>(z), static_cast<const bf16*>(weight),
-            static_cast<bf16*>(out), rows);
-        return check_launch(ctx, "gdn_gate_norm");
-    }
     gdn_gate_norm_kernel<<<dim3(kGdnValueHeads / 4, rows), 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(y), static_cast<const bf16*>(z), static_cast<const bf16*>(weight),
         static_cast<bf16*>(out));

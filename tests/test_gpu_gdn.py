@@ -136,28 +136,6 @@ def lane_table(n, swapped):
                                  for i in range(n)])
 
 
-@pytest.mark.parametrize("rows", [32, 200])
-def test_gate_norm_block_kernel_equals_row_kernel_and_oracle(ctx, rows):
-    """32 rows or more run gdn_gate_norm_block_kernel (a warp per head over a run of rows); the same rows in calls of
-    at most 31 run one warp per (head, row): same bits, and the oracle's values."""
-    rng = np.random.default_rng(900 + rows)
-    _, _, _, norm_w = syn.gdn_weights(rng)
-    y = syn.to_bf16(rng.standard_normal((rows, 4096)).astype(np.float32))
-    z = syn.to_bf16(rng.standard_normal((rows, 4096)).astype(np.float32))
-    dy, dz, dw = dev_bf16(y), dev_bf16(z), dev_bf16(norm_w)
-    block = bf((rows, 4096))
-    ctx.gdn_gate_norm(dy, dz, dw, block, rows)
-    chunks = bf((rows, 4096))
-    at = 0
-    while at < rows:
-        n = min(31, rows - at)
-        ctx.gdn_gate_norm(dy[at:at + n], dz[at:at + n], dw, chunks[at:at + n], n)
-        at += n
-    ctx.sync()
-    assert torch.equal(block, chunks)
-    assert_close_bf16(host_u16(block), oracle.gdn_gate_norm(y, z, norm_w), "gate norm block", max_abs=4e-2)
-
-
 def test_fused_decode_batch_4_lanes(ctx):
     """Benchmark config 1: 4 lanes, two consecutive tokens (ping-pong), vs the oracle chain, and
     bit-identical to each lane run alone."""
