@@ -118,7 +118,7 @@ gdn_prepare_kernel(const __nv_bfloat16* __restrict__ projection,
 // three previous taps in registers, so every projection entry is loaded once (8 bytes per lane and row,
 // the loads of a run's next row issued before this row's arithmetic).  Same per-channel arithmetic
 // (conv_channel_apply) and the same reduction order: bit-identical to the kernel above.
-constexpr uint32_t kPrepRun = 16;         // consecutive rows per warp
+constexpr uint32_t kPrepRun = 8;          // consecutive rows per warp
 constexpr uint32_t kPrepWarps = 8;        // runs per CTA
 
 __device__ __forceinline__ void load_bf16x4_bits(const __nv_bfloat16* p, float out[4]) {
