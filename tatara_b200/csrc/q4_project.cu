@@ -374,6 +374,39 @@ __global__ void __launch_bounds__(kQ4Warps * 32) q4_project_bulk_kernel(const __
     }
 }
 
+// The inputs of 2 * n_pairs rows as row pairs in shared memory: float4 (pair, block, i4, lane) =
+// {x0[2 i4], x1[2 i4], x0[2 i4 + 1], x1[2 i4 + 1]} of the lane's 16 inputs of the block, each already divided by
+// the weight of its nibble position inside the half-word (1, 16, 256, 4096: exact), and the sums of the 16 raw
+// inputs per (pair, block, lane).  One item = both rows of a pair at one (block, lane): whole float4 stores
+// (the two rows as separate items wrote every other word: four wavefronts per 32-bit store).
+__device__ __forceinline__ void stage_row_pairs(const Q4Params& p, uint32_t row0, uint32_t n_pairs, uint32_t blocks,
+                                                float4* xs4, float2* sum2, uint32_t tid, uint32_t n_threads) {
+    for (uint32_t item = tid; item < n_pairs * blocks * 32u; item += n_threads) {
+        const uint32_t l = item & 31u, b = (item >> 5) % blocks, rp = item / (32u * blocks);
+        const uint32_t r0 = min(row0 + 2u * rp, p.n_rows - 1u), r1 = min(row0 + 2u * rp + 1u, p.n_rows - 1u);
+        const uint4* xp0 = reinterpret_cast<const uint4*>(p.x + uint64_t(r0) * p.x_stride + b * 512u + l * 16u);
+        const uint4* xp1 = reinterpret_cast<const uint4*>(p.x + uint64_t(r1) * p.x_stride + b * 512u + l * 16u);
+        const uint4 u0 = xp0[0], u1 = xp0[1], v0 = xp1[0], v1 = xp1[1];
+        const uint32_t raw0[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        const uint32_t raw1[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float4* dst = xs4 + (rp * blocks + b) * 256u + l;
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a0 = __uint_as_float(raw0[2 * i] << 16), a1 = __uint_as_float(raw0[2 * i] & 0xFFFF0000u);
+            const float a2 = __uint_as_float(raw0[2 * i + 1] << 16), a3 = __uint_as_float(raw0[2 * i + 1] & 0xFFFF0000u);
+            const float c0 = __uint_as_float(raw1[2 * i] << 16), c1 = __uint_as_float(raw1[2 * i] & 0xFFFF0000u);
+            const float c2 = __uint_as_float(raw1[2 * i + 1] << 16), c3 = __uint_as_float(raw1[2 * i + 1] & 0xFFFF0000u);
+            s0 = __fadd_rn(s0, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
+            s1 = __fadd_rn(s1, __fadd_rn(__fadd_rn(__fadd_rn(c0, c1), c2), c3));
+            dst[(2 * i) * 32u] = make_float4(a0, c0, __fmul_rn(a1, 0.0625f), __fmul_rn(c1, 0.0625f));
+            dst[(2 * i + 1) * 32u] = make_float4(__fmul_rn(a2, 0.00390625f), __fmul_rn(c2, 0.00390625f),
+                                                 __fmul_rn(a3, 0.000244140625f), __fmul_rn(c3, 0.000244140625f));
+        }
+        sum2[(rp * blocks + b) * 32u + l] = make_float2(s0, s1);
+    }
+}
+
 // Batched form for more than two rows: 2*RP rows per pass, rows taken in PAIRS so that every
 // multiply-add of the chain is one packed fma.rn.f32x2 (sm_100): the pair {row 2p, row 2p+1}
 // shares the decoded nibble and each component keeps the scalar kernel's exact sequence
@@ -429,28 +462,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32, 1) q4_project_pairs_kernel(cons
         if (fg < n_groups) fetch(wn, an);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // stage the row pairs: one (row, block, lane) item = 16 inputs
-    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += kQ4Warps * 32u) {
-        const uint32_t l = item & 31u, b = (item >> 5) % blocks, r = item / (32u * blocks);
-        const uint32_t row = min(row0 + r, p.n_rows - 1u);
-        const uint4* xp = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride + b * 512u + l * 16u);
-        const uint4 v0 = xp[0], v1 = xp[1];
-        const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        float* dst = reinterpret_cast<float*>(xs4 + ((r >> 1) * blocks + b) * 256u) + (r & 1u);
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float a0 = __uint_as_float(raw[2 * i] << 16), a1 = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
-            const float a2 = __uint_as_float(raw[2 * i + 1] << 16), a3 = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
-            s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
-            // float4 index (i4 = 2i, 2i+1), lane l: components {x0[2j], x1[2j], x0[2j+1], x1[2j+1]}
-            dst[((2 * i) * 32u + l) * 4u] = a0;
-            dst[((2 * i) * 32u + l) * 4u + 2u] = __fmul_rn(a1, 0.0625f);
-            dst[((2 * i + 1) * 32u + l) * 4u] = __fmul_rn(a2, 0.00390625f);
-            dst[((2 * i + 1) * 32u + l) * 4u + 2u] = __fmul_rn(a3, 0.000244140625f);
-        }
-        reinterpret_cast<float*>(sum2 + ((r >> 1) * blocks + b) * 32u + l)[r & 1u] = s;
-    }
+    stage_row_pairs(p, row0, RP, blocks, xs4, sum2, threadIdx.x, kQ4Warps * 32u);
     __syncthreads();
     if (g >= n_groups) return;
 
@@ -577,28 +589,7 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
         if (NB > 1 && g + nwarps < n_groups) request(g + nwarps, 1);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // stage the row pairs: one (row, block, lane) item = 16 inputs
-    for (uint32_t item = threadIdx.x; item < 2u * RP * blocks * 32u; item += uint32_t(W) * 32u) {
-        const uint32_t l = item & 31u, b = (item >> 5) % blocks, r = item / (32u * blocks);
-        const uint32_t row = min(row0 + r, p.n_rows - 1u);
-        const uint4* xp = reinterpret_cast<const uint4*>(p.x + uint64_t(row) * p.x_stride + b * 512u + l * 16u);
-        const uint4 v0 = xp[0], v1 = xp[1];
-        const uint32_t raw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        float* dst = reinterpret_cast<float*>(xs4 + ((r >> 1) * blocks + b) * 256u) + (r & 1u);
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float a0 = __uint_as_float(raw[2 * i] << 16), a1 = __uint_as_float(raw[2 * i] & 0xFFFF0000u);
-            const float a2 = __uint_as_float(raw[2 * i + 1] << 16), a3 = __uint_as_float(raw[2 * i + 1] & 0xFFFF0000u);
-            s = __fadd_rn(s, __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3));
-            // float4 index (i4 = 2i, 2i+1), lane l: components {x0[2j], x1[2j], x0[2j+1], x1[2j+1]}
-            dst[((2 * i) * 32u + l) * 4u] = a0;
-            dst[((2 * i) * 32u + l) * 4u + 2u] = __fmul_rn(a1, 0.0625f);
-            dst[((2 * i + 1) * 32u + l) * 4u] = __fmul_rn(a2, 0.00390625f);
-            dst[((2 * i + 1) * 32u + l) * 4u + 2u] = __fmul_rn(a3, 0.000244140625f);
-        }
-        reinterpret_cast<float*>(sum2 + ((r >> 1) * blocks + b) * 32u + l)[r & 1u] = s;
-    }
+    stage_row_pairs(p, row0, RP, blocks, xs4, sum2, threadIdx.x, uint32_t(W) * 32u);
     __syncthreads();
 
     float2 result[RP][C];
@@ -616,7 +607,7 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
         const uint8_t* gb = wbuf + buf * lay.group_bytes;
         const unsigned short* gs = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes);
         const unsigned short* gbias = reinterpret_cast<const unsigned short*>(gb + lay.words_bytes + lay.affine_bytes);
-#pragma unroll 1
+#pragma unroll 2
       for (uint32_t b = 0; b < blocks; ++b) {
         // Half-word by half-word (four inputs of every row at a time) with the columns inside: only two
         // float4 of inputs per row pair are live instead of eight, and the RP x C chains of one step
@@ -644,8 +635,9 @@ __global__ void __launch_bounds__(W * 32, 1) q4_project_pairs_bulk_kernel(const 
                 // the four nibbles of half-word i, each as {w, w}; inputs 4i .. 4i+3 are lo.xy, lo.zw, hi.xy, hi.zw
                 const float w0 = __uint_as_float((half & 0x000Fu) | 0x4B000000u), w1 = __uint_as_float((half & 0x00F0u) | 0x4B000000u);
                 const float w2 = __uint_as_float((half & 0x0F00u) | 0x4B000000u), w3 = __uint_as_float((half & 0xF000u) | 0x4B000000u);
-                const float2 q0 = __fadd2_rn(make_float2(w0, w0), magic), q1 = __fadd2_rn(make_float2(w1, w1), magic);
-                const float2 q2 = __fadd2_rn(make_float2(w2, w2), magic), q3 = __fadd2_rn(make_float2(w3, w3), magic);
+                const float n0 = __fadd_rn(w0, magic.x), n1 = __fadd_rn(w1, magic.x);
+                const float n2 = __fadd_rn(w2, magic.x), n3 = __fadd_rn(w3, magic.x);
+                const float2 q0 = make_float2(n0, n0), q1 = make_float2(n1, n1), q2 = make_float2(n2, n2), q3 = make_float2(n3, n3);
 #pragma unroll
                 for (int rp = 0; rp < RP; ++rp) {
                     quant[rp][c] = __ffma2_rn(make_float2(lo[rp].x, lo[rp].y), q0, quant[rp][c]);
@@ -1225,6 +1217,9 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
         uint32_t best = 8;
         for (uint32_t w : {11u, 12u})
             if (pairs_fit(cols_per_warp, w, 2) && slots(cols / cols_per_warp, w) <= slots(cols / cols_per_warp, best)) best = w;
+        // seven warps when they still take every group in ONE round (2048 columns in pairs: 147 CTAs of 7 warps on
+        // 148 SMs instead of 128 CTAs of 8; with several rounds fewer warps hide less: gdn_project 17.6 -> 18.3 us)
+        if (cols / cols_per_warp <= sms * 7u && slots(cols / cols_per_warp, 7) < slots(cols / cols_per_warp, best)) best = 7;
         return best;
     };
     if (pairs_bulk8) {
@@ -1233,11 +1228,13 @@ extern "C" tatara_status tatara_q4_project(tatara_ctx* ctx, void* stream, const 
         const uint32_t w = best_warps(4);
         if (w == 12) (void)launch_q4_pairs_bulk<4, 4, 12, 2>(p, sms, ctx->device, s);
         else if (w == 11) (void)launch_q4_pairs_bulk<4, 4, 11, 2>(p, sms, ctx->device, s);
+        else if (w == 7) (void)launch_q4_pairs_bulk<4, 4, 7, 2>(p, sms, ctx->device, s);
         else (void)launch_q4_pairs_bulk<4, 4, 8, 2>(p, sms, ctx->device, s);
     } else if (pairs_bulk2) {
         const uint32_t w = best_warps(2);
         if (w == 12) (void)launch_q4_pairs_bulk<4, 2, 12, 2>(p, sms, ctx->device, s);
         else if (w == 11) (void)launch_q4_pairs_bulk<4, 2, 11, 2>(p, sms, ctx->device, s);
+        else if (w == 7) (void)launch_q4_pairs_bulk<4, 2, 7, 2>(p, sms, ctx->device, s);
         else (void)launch_q4_pairs_bulk<4, 2, 8, 2>(p, sms, ctx->device, s);
     } else if (bulk) {
         // narrow matrices take two columns per warp so that every warp of the grid has a group

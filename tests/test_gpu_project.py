@@ -111,6 +111,23 @@ def test_exact_row_bits_model_geometry(ctx, name, sizes, k):
     assert 0.2 < syn.from_bf16(want).std() < 2.0
 
 
+@pytest.mark.parametrize("name,sizes,k", [("attn_project", (8192, 512, 512), 2048),
+                                          ("gdn_project", (8192, 4096, 32, 32), 2048),
+                                          ("out_projection", (2048,), 4096)])
+@pytest.mark.parametrize("rows", [5, 8])
+def test_exact_row_bits_wave_of_eight_model_geometry(ctx, name, sizes, k, rows):
+    """The three call sites at a decode wave's row counts (the row-pair kernel with bulk-copied weights: eight,
+    four or two columns per warp and 7 to 12 warps per SM, chosen per site): the oracle's chain, bit for bit."""
+    rng = np.random.default_rng(800 + rows + len(sizes))
+    mats = [syn.q4_matrix(rng, n, k) for n in sizes]
+    x = syn.hidden_rows(rng, rows, k)
+    held, arr = dev_mats(mats)
+    out = torch.zeros((rows, sum(sizes)), dtype=torch.bfloat16, device="cuda")
+    ctx.q4_project(dev_bf16(x), arr, k, out)
+    ctx.sync()
+    assert np.array_equal(host_u16(out), oracle_project(x, mats, oracle.hardware_threads()))
+
+
 def test_exact_row_batch_of_16_model_geometry(ctx):
     """gdn_project at the largest decode batch of the reference (16 rows: two passes of the row-pair kernel);
     every row has the bits of the oracle's chain, i.e. of the same row projected alone."""
