@@ -130,13 +130,13 @@ __device__ __forceinline__ uint32_t gmat(uint32_t row, uint32_t group) { return 
 
 // CTA barrier over the 256 threads of one prepare group: barrier kBar (0 = the whole CTA of the
 // stand-alone kernel; 1, 2 = the two groups of a worker CTA of the fused kernel).
-template <uint32_t kBar>
-__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, 256;" ::"n"(kBar) : "memory"); }
-template <uint32_t kBar>
-__device__ __forceinline__ bool group_and(bool pred) {
+// (the barrier number is a run-time operand: the two groups of a worker CTA run the SAME code; as a template
+// parameter it made two copies of the whole unit loop, twice the instruction-cache footprint per SM)
+__device__ __forceinline__ void group_sync(uint32_t bar_id) { asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory"); }
+__device__ __forceinline__ bool group_and(uint32_t bar_id, bool pred) {
     uint32_t r;
     asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.and.pred q, %2, 256, p;\n selp.u32 %0, 1, 0, q;\n}"
-                 : "=r"(r) : "r"(pred ? 1u : 0u), "n"(kBar) : "memory");
+                 : "=r"(r) : "r"(pred ? 1u : 0u), "r"(bar_id) : "memory");
     return r != 0u;
 }
 
@@ -144,8 +144,7 @@ __device__ __forceinline__ bool group_and(bool pred) {
 // kPrSmem bytes of shared memory at `smem` (its two mbarriers initialised, abort flag cleared) and
 // kPrCols columns of tensor memory at `tmem`.  `ready` (or null): one word per unit, set to `epoch` once
 // the unit's planes are complete in global memory.
-template <uint32_t kBar>
-__device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, const CUtensorMap& map_v, const TcPrepareParams& p,
+__device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CUtensorMap& map_qk, const CUtensorMap& map_v, const TcPrepareParams& p,
                                                  uint8_t* smem, uint32_t tmem, uint32_t tid, uint32_t first_unit,
                                                  uint32_t unit_stride, uint32_t* ready, uint32_t epoch) {
     const uint32_t warp = tid >> 5, lane = tid & 31u;
@@ -160,6 +159,25 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
     const uint32_t tlane = ((warp & 3u) * 32u) << 16;
     bool ok = true;
     uint32_t mma_phase = 0;     // completions of bar_mma so far (three per unit)
+    // thread 0: the unit whose planes have been handed to the copy engine but whose ready word is not out yet
+    uint32_t unreleased = 0xFFFFFFFFu;
+    // The ready word of a unit may only be released once its planes are COMPLETE in global memory (not only read
+    // out of shared memory).  It goes out in the middle of the group's NEXT unit, right after thread 0 has issued
+    // the last MMA group, while everyone waits for those MMAs anyway: the copies of the previous unit have long
+    // completed (`wait_group 1` leaves only this unit's Us^T copy pending), and the release store is the whole
+    // hand-over -- completed bulk copies are visible to the thread that waited for them, and a release at gpu
+    // scope is cumulative over what that thread has observed (e^{G_C}, written by warp 1 before this unit's
+    // barriers, included).  A proxy fence and a __threadfence in front of the store, at the end of the unit,
+    // held the whole group for 1 - 2 us per unit: 0.60 -> 0.56 ms for 16 384 rows together with the single copy
+    // of this loop's code (see group_sync).  The last unit's word goes out after the loop.
+    auto release_pending = [&](bool newest_group_may_pend) {
+        if (ready != nullptr && unreleased != 0xFFFFFFFFu) {
+            if (newest_group_may_pend) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ready + unreleased), "r"(epoch) : "memory");
+            unreleased = 0xFFFFFFFFu;
+        }
+    };
 
     // Persistent CTAs: barriers and tensor memory are set up once, then the CTA walks its units.
     for (uint32_t it = 0, unit32 = first_unit; unit32 < p.n_units && ok; ++it, unit32 += unit_stride) {
@@ -223,7 +241,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
     }
     if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
     ++mma_phase;
-    group_sync<kBar>();   // the decay vectors of warp 1 are visible
+    group_sync(bar_id);   // the decay vectors of warp 1 are visible
     if (ok) {
         tc_fence_after();
         const uint32_t r = row & 63u;
@@ -252,7 +270,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
         }
         tc_fence_before();
     }
-    group_sync<kBar>();
+    group_sync(bar_id);
 
     // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), in panels of 16 rows.
     // (1) The four 16 x 16 diagonal blocks are inverted first, one column per thread (64 threads,
@@ -284,7 +302,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
             dsm[(b * 16u + rr) * 16u + c] = t[rr];
         }
     }
-    group_sync<kBar>();
+    group_sync(bar_id);
     {
         const uint32_t j = tid & 63u, h = tid >> 6;
         uint8_t* tcol = smem + kPrWs + j * 16u;          // column j of T: group q at + q * 1024
@@ -307,7 +325,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
 #pragma unroll
             for (uint32_t rr = 0; rr < 4; ++rr)
                 rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - (acc[rr].x + acc[rr].y);
-            group_sync<kBar>();
+            group_sync(bar_id);
             float2 t2[4];
 #pragma unroll
             for (uint32_t rr = 0; rr < 4; ++rr) t2[rr] = make_float2(0.0f, 0.0f);
@@ -325,7 +343,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
             }
             *reinterpret_cast<float4*>(tcol + (4u * b + h) * 1024u) =
                 make_float4(t2[0].x + t2[0].y, t2[1].x + t2[1].y, t2[2].x + t2[2].y, t2[3].x + t2[3].y);
-            group_sync<kBar>();
+            group_sync(bar_id);
         }
     }
     if (ok) {   // (the last barrier of the sweep: everyone is done with D_b before T_U is written over it)
@@ -347,7 +365,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
         }
     }
     fence_async_smem();
-    group_sync<kBar>();
+    group_sync(bar_id);
 
     // ---- MMA b: W^T = K^T T_W^T (columns 64..127), MMA c: U^T = V^T T_U^T (columns 128..191)
     if (tid == 0 && ok) {
@@ -384,7 +402,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
         tc_fence_before();
     }
     fence_async_smem();
-    group_sync<kBar>();
+    group_sync(bar_id);
 
     // ---- MMA d: M' = Ws^T K (columns 0..127), e: X = W^T P^T (128..191), f: O0^T = U^T P^T (192..255)
     if (tid == 0 && ok) {
@@ -407,6 +425,7 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
                    idesc_p, ks ? 1u : 0u);
         bulk_store_wait_read();     // the Us^T image has left shared memory before anyone passes the barrier: its place takes the O0^T image
         tc_commit(bar_mma);
+        release_pending(true);      // the previous unit's ready word, while the MMAs run (this unit's Us^T copy may still be on its way)
     }
     if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
     ++mma_phase;
@@ -444,25 +463,18 @@ __device__ __forceinline__ void tc_prepare_units(const CUtensorMap& map_qk, cons
         tc_fence_before();
     }
     fence_async_smem();
-    group_sync<kBar>();
+    group_sync(bar_id);
     if (tid == 0 && ok) {
         bulk_store(p.planes.m + unit * kUnitM, base + kPrStM, kUnitM);
         bulk_store(p.planes.q + unit * kUnitQ, base + kPrStQ, kUnitQ);
         bulk_store(p.planes.o + unit * kUnitO, base + kPrStO, kUnitO);
         bulk_store_commit();
-        if (ready != nullptr) {
-            // the scan of this head may be waiting for exactly this unit: the planes are complete in global
-            // memory (not only read out of shared memory) before the word that says so is released
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-            asm volatile("fence.proxy.async;" ::: "memory");
-            __threadfence();
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ready + unit32), "r"(epoch) : "memory");
-        } else {
-            bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
-        }
+        bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
+        unreleased = unit32;
     }
-    ok = group_and<kBar>(ok);   // ... before the next unit's loads land on them; leave the loop together
+    ok = group_and(bar_id, ok);   // ... before the next unit's loads land on them; leave the loop together
     }   // units
+    if (tid == 0) release_pending(false);
 }
 
 __global__ void __launch_bounds__(kPrThreads, 2)
@@ -487,7 +499,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    tc_prepare_units<0>(map_qk, map_v, p, smem, tmem, tid, blockIdx.x, gridDim.x, nullptr, 0u);
+    tc_prepare_units(0u, map_qk, map_v, p, smem, tmem, tid, blockIdx.x, gridDim.x, nullptr, 0u);
     tc_fence_before();
     __syncthreads();
     if (*abort_flag) {
@@ -831,8 +843,8 @@ gdn_tc_fused_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
         if (tid < kScThreads) tc_scan_head(map_qk, p.scan, smem, tmem, tid, blockIdx.x, p.ready, p.epoch);
     } else {
         const uint32_t slots = (gridDim.x - kGdnValueHeads) * 2u, slot = (blockIdx.x - kGdnValueHeads) * 2u + group;
-        if (group == 0u) tc_prepare_units<1>(map_qk, map_v, p.prep, gsmem, tmem, tid & 255u, slot, slots, p.ready, p.epoch);
-        else tc_prepare_units<2>(map_qk, map_v, p.prep, gsmem, tmem + kPrCols, tid & 255u, slot, slots, p.ready, p.epoch);
+        tc_prepare_units(1u + group, map_qk, map_v, p.prep, gsmem, tmem + group * kPrCols, tid & 255u, slot, slots,
+                         p.ready, p.epoch);
     }
     tc_fence_before();
     __syncthreads();
