@@ -84,6 +84,7 @@ constexpr uint32_t kPrBar = 107520;
 constexpr uint32_t kPrSmem = kPrBar + 64;
 constexpr uint32_t kPrCols = 256;
 constexpr uint32_t kPrThreads = 256;
+constexpr uint32_t kPrStoreThread = 128;   // lane 0 of warp 4: issues the plane copies of a unit, see tc_prepare_units
 // staging of the output planes (the images the scan copies back into shared memory), over dead tiles
 constexpr uint32_t kPrStU = kPrTW;       // Us^T, written while K, Q, P, W^T, Ws^T, U^T are live
 constexpr uint32_t kPrStM = kPrV;        // -M' : two tiles, 32 KiB   (final epilogue: everything but the Q rows is dead)
@@ -150,7 +151,7 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     const uint32_t warp = tid >> 5, lane = tid & 31u;
     const uint32_t row = (warp & 3u) * 32u + lane, half = warp >> 2;
     const uint32_t base = s2u(smem);
-    const uint32_t bar_load = base + kPrBar, bar_mma = base + kPrBar + 8;
+    const uint32_t bar_load = base + kPrBar, bar_mma = base + kPrBar + 8, bar_v = base + kPrBar + 32;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kPrBar + 16);
     float* g_cum = reinterpret_cast<float*>(smem + kPrVec);
     float* beta_s = g_cum + 64;
@@ -159,41 +160,38 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     const uint32_t tlane = ((warp & 3u) * 32u) << 16;
     bool ok = true;
     uint32_t mma_phase = 0;     // completions of bar_mma so far (three per unit)
-    // thread 0: the unit whose planes have been handed to the copy engine but whose ready word is not out yet
-    uint32_t unreleased = 0xFFFFFFFFu;
-    // The ready word of a unit may only be released once its planes are COMPLETE in global memory (not only read
-    // out of shared memory).  It goes out in the middle of the group's NEXT unit, right after thread 0 has issued
-    // the last MMA group, while everyone waits for those MMAs anyway: the copies of the previous unit have long
-    // completed (`wait_group 1` leaves only this unit's Us^T copy pending), and the release store is the whole
-    // hand-over -- completed bulk copies are visible to the thread that waited for them, and a release at gpu
-    // scope is cumulative over what that thread has observed (e^{G_C}, written by warp 1 before this unit's
-    // barriers, included).  A proxy fence and a __threadfence in front of the store, at the end of the unit,
-    // held the whole group for 1 - 2 us per unit: 0.60 -> 0.56 ms for 16 384 rows together with the single copy
-    // of this loop's code (see group_sync).  The last unit's word goes out after the loop.
-    auto release_pending = [&](bool newest_group_may_pend) {
-        if (ready != nullptr && unreleased != 0xFFFFFFFFu) {
-            if (newest_group_may_pend) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
-            else asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    // Thread kPrStoreThread hands the four plane images of a unit to the copy engine (thread 0 only the Us^T image,
+    // in the middle of the unit) and owns what follows from that, each at a point where it would otherwise idle:
+    //  * the images must have LEFT shared memory before the next unit writes over them: it waits for that
+    //    (`wait_group.read`) during the next unit's first MMA group, before the barrier in front of the masks -- the
+    //    next unit's K and Q tiles load into a region that holds no image, and its V tile is asked for after that
+    //    barrier (V is not needed before the second MMA group).  Waiting at the end of the unit held the whole
+    //    group for 2.3 - 4.2 k cycles per unit.
+    //  * the unit's ready word may only be released once the images are COMPLETE in global memory: it waits for that
+    //    (`wait_group 0`) and stores the word (`st.release.gpu`) while warps 0 and 1 invert the diagonal blocks of
+    //    the next unit.  Completed bulk copies are visible to the thread that waited for them, thread 0 has
+    //    waited for its Us^T copy before the barriers in between, and a release at gpu scope is cumulative over
+    //    what the thread has observed (e^{G_C}, written by warp 1 before those barriers, included).  On thread 0,
+    //    with a proxy fence and a __threadfence in front, the release cost the group 1.5 - 3 k cycles per unit.
+    uint32_t unreleased = 0xFFFFFFFFu;   // (store thread) the unit whose ready word is not out yet
+    auto release_pending = [&]() {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (ready != nullptr && unreleased != 0xFFFFFFFFu)
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ready + unreleased), "r"(epoch) : "memory");
-            unreleased = 0xFFFFFFFFu;
-        }
+        unreleased = 0xFFFFFFFFu;
     };
 
-    // Persistent CTAs: barriers and tensor memory are set up once, then the CTA walks its units.
-    for (uint32_t it = 0, unit32 = first_unit; unit32 < p.n_units && ok; ++it, unit32 += unit_stride) {
-    const uint32_t chunk = unit32 / kGdnValueHeads, head = unit32 % kGdnValueHeads, qkh = head >> 1;
-    const uint32_t row0 = chunk * kTcChunk;
-    const uint32_t live_rows = min(kTcChunk, p.rows - row0);
-    const uint64_t unit = unit32;
-    if (tid == 0) {
-        mbar_expect_tx(bar_load, 32768u + 16384u);
+    // The K and Q tiles of a unit (one mbarrier completion per unit), and the tiles of the unit after it into L2.
+    // Issued by the store thread at the END of the previous unit, AHEAD of that unit's plane copies: the copy
+    // engine of the SM takes its work in order, and behind 64 KiB of outgoing images the loads took 3 - 5 k cycles.
+    auto issue_kq = [&](uint32_t u) {
+        const uint32_t h = u % kGdnValueHeads, q = h >> 1, r0 = (u / kGdnValueHeads) * kTcChunk;
+        mbar_expect_tx(bar_load, 32768u);
         for (uint32_t a = 0; a < 2; ++a) {
-            tma_load_2d(base + kPrKQ + a * 16384u, &map_qk, bar_load, int(kGdnKOff + qkh * kGdnDim + a * 64u), int(row0));
-            tma_load_2d(base + kPrKQ + a * 16384u + 8192u, &map_qk, bar_load, int(qkh * kGdnDim + a * 64u), int(row0));
-            tma_load_2d(base + kPrV + a * 8192u, &map_v, bar_load, int(head * kGdnDim + a * 64u), int(row0));
+            tma_load_2d(base + kPrKQ + a * 16384u, &map_qk, bar_load, int(kGdnKOff + q * kGdnDim + a * 64u), int(r0));
+            tma_load_2d(base + kPrKQ + a * 16384u + 8192u, &map_qk, bar_load, int(q * kGdnDim + a * 64u), int(r0));
         }
-        // the tiles of this CTA's next unit are asked into L2 now: its loads start when this unit is done
-        const uint32_t next = unit32 + unit_stride;
+        const uint32_t next = u + unit_stride;
         if (next < p.n_units) {
             const uint32_t nh = next % kGdnValueHeads, nq = nh >> 1, nrow = (next / kGdnValueHeads) * kTcChunk;
             for (uint32_t a = 0; a < 2; ++a) {
@@ -202,13 +200,36 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
                 tma_prefetch_2d(&map_v, int(nh * kGdnDim + a * 64u), int(nrow));
             }
         }
-    }
+    };
+    if (tid == kPrStoreThread && first_unit < p.n_units) issue_kq(first_unit);
+    // warp 1: the decay and beta of a unit's 64 steps (two per lane), loaded one unit ahead -- with the K and Q tiles
+    // already there when a unit starts, a trip to memory for these at its top was the longest wait of the unit
+    float gate_in[4] = {1.0f, 1.0f, 0.0f, 0.0f};   // decay of steps 2 lane, 2 lane + 1 (1: G stays flat), then beta
+    auto load_gates = [&](uint32_t u) {
+        const uint32_t h = u % kGdnValueHeads, r0 = (u / kGdnValueHeads) * kTcChunk + lane * 2u;
+#pragma unroll
+        for (uint32_t e = 0; e < 2; ++e) {
+            const bool live = r0 + e < p.rows;
+            gate_in[e] = live ? __ldg(p.decay + uint64_t(r0 + e) * kGdnValueHeads + h) : 1.0f;
+            gate_in[2 + e] = live ? __ldg(p.beta + uint64_t(r0 + e) * kGdnValueHeads + h) : 0.0f;
+        }
+    };
+    if (warp == 1 && first_unit < p.n_units) load_gates(first_unit);
+
+    // Persistent CTAs: barriers and tensor memory are set up once, then the CTA walks its units.
+    for (uint32_t it = 0, unit32 = first_unit; unit32 < p.n_units && ok; ++it, unit32 += unit_stride) {
+    const uint32_t chunk = unit32 / kGdnValueHeads, head = unit32 % kGdnValueHeads;
+    const uint32_t row0 = chunk * kTcChunk;
+    const uint32_t live_rows = min(kTcChunk, p.rows - row0);
+    const uint64_t unit = unit32;
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the previous unit's Us^T copy is complete (issued half a unit ago)
     if (warp == 1) {
         // inclusive cumulative log-decay over the 64 steps (two per lane); rows past the block keep G flat
-        float g0 = 0.0f, g1 = 0.0f;
         const uint32_t r0 = lane * 2u;
-        if (r0 < live_rows) g0 = fmaxf(logf(p.decay[uint64_t(row0 + r0) * kGdnValueHeads + head]), -100.0f);
-        if (r0 + 1u < live_rows) g1 = fmaxf(logf(p.decay[uint64_t(row0 + r0 + 1u) * kGdnValueHeads + head]), -100.0f);
+        const float g0 = r0 < live_rows ? fmaxf(logf(gate_in[0]), -100.0f) : 0.0f;
+        const float g1 = r0 + 1u < live_rows ? fmaxf(logf(gate_in[1]), -100.0f) : 0.0f;
+        const float b0 = gate_in[2], b1 = gate_in[3];
+        if (unit32 + unit_stride < p.n_units) load_gates(unit32 + unit_stride);
         float incl = g0 + g1;
 #pragma unroll
         for (int off = 1; off < 32; off <<= 1) {
@@ -218,8 +239,8 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         const float g_end = __shfl_sync(0xffffffffu, incl, 31);
         g_cum[r0] = incl - g1;
         g_cum[r0 + 1u] = incl;
-        beta_s[r0] = r0 < live_rows ? p.beta[uint64_t(row0 + r0) * kGdnValueHeads + head] : 0.0f;
-        beta_s[r0 + 1u] = r0 + 1u < live_rows ? p.beta[uint64_t(row0 + r0 + 1u) * kGdnValueHeads + head] : 0.0f;
+        beta_s[r0] = b0;
+        beta_s[r0 + 1u] = b1;
         s_end[r0] = __expf(g_end - (incl - g1));
         s_end[r0 + 1u] = __expf(g_end - incl);
         e_g[r0] = __expf(incl - g1);
@@ -239,9 +260,12 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         }
         tc_commit(bar_mma);
     }
+    // the previous unit's -M' image (over V, A) and its O0^T image (over P) have left shared memory: the masks write
+    // P and A; the Q~^T image (over T, written by the sweep) may still be on its way
+    if (tid == kPrStoreThread) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
     ++mma_phase;
-    group_sync(bar_id);   // the decay vectors of warp 1 are visible
+    group_sync(bar_id);   // the decay vectors of warp 1 are visible; P and A are free
     if (ok) {
         tc_fence_after();
         const uint32_t r = row & 63u;
@@ -271,6 +295,11 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         tc_fence_before();
     }
     group_sync(bar_id);
+    if (tid == 0 && ok) {   // V is not needed before the second MMA group
+        mbar_expect_tx(bar_v, 16384u);
+        for (uint32_t a = 0; a < 2; ++a)
+            tma_load_2d(base + kPrV + a * 8192u, &map_v, bar_v, int(head * kGdnDim + a * 64u), int(row0));
+    }
 
     // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), in panels of 16 rows.
     // (1) The four 16 x 16 diagonal blocks are inverted first, one column per thread (64 threads,
@@ -284,6 +313,7 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     //     of D_b is one broadcast; the columns of a warp's 32 threads are conflict-free by the swizzle.
     float* dsm = reinterpret_cast<float*>(smem + kPrTU);            // D_b [4][16][16] f32 (T_U is written after the sweep)
     float* rhs_s = reinterpret_cast<float*>(smem + kPrTU + 4096u);  // right-hand sides [16 rows of the panel][64 columns]
+    if (tid == kPrStoreThread) release_pending();   // (its warp has nothing to do until the diagonal blocks are done)
     if (ok && tid < 64u) {
         const uint32_t b = tid >> 4, c = tid & 15u;
         float t[16];
@@ -368,6 +398,7 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     group_sync(bar_id);
 
     // ---- MMA b: W^T = K^T T_W^T (columns 64..127), MMA c: U^T = V^T T_U^T (columns 128..191)
+    if (tid == 0 && ok) ok = mbar_wait(bar_v, it & 1u, abort_flag);   // (a failure reaches the others at the end of the unit)
     if (tid == 0 && ok) {
         tc_fence_after();
         constexpr uint32_t idesc = instr_desc2(128, 64, true, false);
@@ -425,25 +456,38 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
                    idesc_p, ks ? 1u : 0u);
         bulk_store_wait_read();     // the Us^T image has left shared memory before anyone passes the barrier: its place takes the O0^T image
         tc_commit(bar_mma);
-        release_pending(true);      // the previous unit's ready word, while the MMAs run (this unit's Us^T copy may still be on its way)
     }
     if (ok) ok = mbar_wait(bar_mma, mma_phase & 1u, abort_flag);
     ++mma_phase;
     if (ok) {
         tc_fence_after();
         // -M' (this thread: k-columns half*64 .. +63 = tile `half` of the image), then Q~^T and O0^T (columns half*32 .. +31)
+#pragma unroll 1
+        for (uint32_t blk = 0; blk < 4; ++blk) {
+            float v[16];
+            tmem_ld16(tmem + tlane + half * 64u + blk * 16u, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) v[i] = -v[i];
+            store_bf16x16(smem + kPrStM + half * 16384u, row, blk * 2u, v);
+        }
+    }
+    // The -M' image is half of what the unit sends out: it leaves now, while the other two images are still being
+    // made (an SM writes about 32 bytes per cycle towards L2: all 64 KiB at the end of the unit took 3.5 - 4 k
+    // cycles to leave shared memory, and the next unit needs that memory 1.2 k cycles into its run).
+    fence_async_smem();
+    group_sync(bar_id);
+    if (tid == kPrStoreThread && ok) {
+        bulk_store(p.planes.m + unit * kUnitM, base + kPrStM, kUnitM);
+        bulk_store_commit();
+    }
+    if (ok) {
         const uint8_t* q_tile = smem + kPrKQ + (row >> 6) * 16384u;
         const uint32_t qchunk = (row & 63u) >> 3, qcol = (row & 7u) * 2u;
 #pragma unroll 1
-        for (uint32_t blk = 0; blk < 8; ++blk) {
+        for (uint32_t blk = 4; blk < 8; ++blk) {
             float v[16];
-            if (blk < 4u) {
-                tmem_ld16(tmem + tlane + half * 64u + blk * 16u, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (uint32_t i = 0; i < 16; ++i) v[i] = -v[i];
-                store_bf16x16(smem + kPrStM + half * 16384u, row, blk * 2u, v);
-            } else {
+            {
                 const bool is_o = blk >= 6u;
                 const uint32_t c0 = half * 32u + (blk & 1u) * 16u;
                 tmem_ld16(tmem + tlane + (is_o ? 192u : 128u) + c0, v);
@@ -464,17 +508,20 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     }
     fence_async_smem();
     group_sync(bar_id);
-    if (tid == 0 && ok) {
-        bulk_store(p.planes.m + unit * kUnitM, base + kPrStM, kUnitM);
-        bulk_store(p.planes.q + unit * kUnitQ, base + kPrStQ, kUnitQ);
-        bulk_store(p.planes.o + unit * kUnitO, base + kPrStO, kUnitO);
+    if (tid == kPrStoreThread && ok) {
+        if (unit32 + unit_stride < p.n_units) issue_kq(unit32 + unit_stride);   // (everyone is past the Q rows)
+        // two more copy groups, in the order in which the next unit needs their shared memory back (see the waits there)
+        bulk_store(p.planes.o + unit * kUnitO, base + kPrStO, kUnitO);   // over P, T_W
         bulk_store_commit();
-        bulk_store_wait_read();   // the images have left shared memory; their global writes complete on their own
+        bulk_store(p.planes.q + unit * kUnitQ, base + kPrStQ, kUnitQ);   // over T
+        bulk_store_commit();
         unreleased = unit32;
     }
-    ok = group_and(bar_id, ok);   // ... before the next unit's loads land on them; leave the loop together
+    ok = group_and(bar_id, ok);   // everyone is done with this unit's K and Q tiles; leave the loop together
     }   // units
-    if (tid == 0) release_pending(false);
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    group_sync(bar_id);
+    if (tid == kPrStoreThread) release_pending();   // the last unit; nothing of this group is in flight when it returns
 }
 
 __global__ void __launch_bounds__(kPrThreads, 2)
@@ -488,6 +535,7 @@ gdn_tc_prepare_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_c
     if (tid == 0) {
         mbar_init(base + kPrBar, 1);
         mbar_init(base + kPrBar + 8, 1);
+        mbar_init(base + kPrBar + 32, 1);
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -827,6 +875,7 @@ gdn_tc_fused_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_con
     } else if ((tid & 255u) == 0u) {
         mbar_init(s2u(gsmem) + kPrBar, 1);
         mbar_init(s2u(gsmem) + kPrBar + 8, 1);
+        mbar_init(s2u(gsmem) + kPrBar + 32, 1);
         *reinterpret_cast<volatile uint32_t*>(gsmem + kPrBar + 16) = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -942,3 +991,4 @@ tatara_status launch_gdn_chunked_tc(tatara_ctx* ctx, cudaStream_t stream, const 
 }
 
 } // namespace tb
+
