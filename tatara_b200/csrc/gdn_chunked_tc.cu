@@ -301,19 +301,25 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
             tma_load_2d(base + kPrV + a * 8192u, &map_v, bar_v, int(head * kGdnDim + a * 64u), int(row0));
     }
 
-    // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), in panels of 16 rows.
-    // (1) The four 16 x 16 diagonal blocks are inverted first, one column per thread (64 threads,
-    //     forward substitution): D_b = (I + A_bb)^-1.
-    // (2) Column j of T belongs to four threads, one in each pair of warps (thread = (j, h), h = warp / 2),
-    //     and is built panel by panel.  Finished panels of the column live in shared memory (row j of a
-    //     swizzled f32 tile).  For a panel each of the four threads accumulates the contribution of the
-    //     finished panels to FOUR of its 16 rows, the four share the 16 right-hand sides through shared
-    //     memory, and each multiplies its four rows of D_b into them: the solve inside a panel is a
-    //     matrix-vector product with no serial chain.  h is uniform in a warp, so every read of A and
-    //     of D_b is one broadcast; the columns of a warp's 32 threads are conflict-free by the swizzle.
-    float* dsm = reinterpret_cast<float*>(smem + kPrTU);            // D_b [4][16][16] f32 (T_U is written after the sweep)
-    float* rhs_s = reinterpret_cast<float*>(smem + kPrTU + 4096u);  // right-hand sides [16 rows of the panel][64 columns]
-    if (tid == kPrStoreThread) release_pending();   // (its warp has nothing to do until the diagonal blocks are done)
+    // ---- T = (I + A)^-1 in f32 (no bf16 enters the solve), by doubling: 16 x 16 diagonal blocks, then the two
+    // 32 x 32 diagonal blocks, then the whole.  For a lower block-triangular [[P, 0], [B, Q]] the inverse is
+    // [[P^-1, 0], [-Q^-1 B P^-1, Q^-1]], so each level is two products with all the work independent inside a step:
+    //   (1) D_b = (I + A_bb)^-1, forward substitution, one column per thread (64 threads);
+    //   (2a) X = A[b1, b0] D_b0 for the two pairs (b0, b1) = (0, 1), (2, 3);   (2b) T[b1, b0] = -D_b1 X;
+    //   (3a) X = A[32.., ..32] T[..32, ..32];                                   (3b) T[32.., ..32] = -T[32.., 32..] X.
+    // Five barrier-to-barrier steps instead of the nine of a sweep over panels of 16 rows (whose steps cost ~ 1 k
+    // cycles each whatever the arithmetic in them), and a third of its shared-memory loads.  A thread owns four
+    // consecutive rows of one column of a product; the triangular zeros of the right-hand factor of (2a), (3a) and
+    // of the left-hand factor of (2b), (3b) bound its loop.
+    // Layouts: T (and with it D_b) is built in place as [row group][column][4 rows] (what the scaling pass below
+    // reads); left-hand factors are wanted as [4-column group][row][4 columns]: A is stored so, D_1 and the 32 x 32
+    // block T[32.., 32..] get a second copy in that form; the X of both levels is [row group][column][4 rows].
+    float4* tc4 = reinterpret_cast<float4*>(smem + kPrWs);               // T: float4 (row group q, column j) at q * 64 + j
+    float4* dr1 = reinterpret_cast<float4*>(smem + kPrTW);               // D_1 by rows: (column group g, row r) at g * 16 + r            1 KiB
+    float4* thr = reinterpret_cast<float4*>(smem + kPrTW + 1024u);       // T[32.., 32..] by rows: (column group g, row r) at g * 32 + r   4 KiB
+    float4* x2c = reinterpret_cast<float4*>(smem + kPrTW + 5120u);       // X of (2a): pair s, (row group q, column j) at s * 64 + q * 16 + j  2 KiB
+    float4* x3c = reinterpret_cast<float4*>(smem + kPrTW + 7168u);       // X of (3a): (row group q, column j) at q * 32 + j               4 KiB
+    if (tid == kPrStoreThread) release_pending();   // (its warp has little to do until the diagonal blocks are done)
     if (ok && tid < 64u) {
         const uint32_t b = tid >> 4, c = tid & 15u;
         float t[16];
@@ -329,54 +335,84 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
                 if (q4 + 3 < rr) s1 = fmaf(av.w, t[q4 + 3], s1);
             }
             t[rr] = (rr == c ? 1.0f : 0.0f) - (s0 + s1);
-            dsm[(b * 16u + rr) * 16u + c] = t[rr];
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < 4; ++g) tc4[(4u * b + g) * 64u + 16u * b + c] = make_float4(t[4 * g], t[4 * g + 1], t[4 * g + 2], t[4 * g + 3]);
+        if (b == 1u) {
+#pragma unroll
+            for (uint32_t rr = 0; rr < 16; ++rr) reinterpret_cast<float*>(dr1 + (c >> 2) * 16u + rr)[c & 3u] = t[rr];
+        } else if (b >= 2u) {
+            const uint32_t o = (b - 2u) * 16u;   // position of the block inside T[32.., 32..]
+#pragma unroll
+            for (uint32_t rr = 0; rr < 16; ++rr) reinterpret_cast<float*>(thr + ((o + c) >> 2) * 32u + o + rr)[c & 3u] = t[rr];
+        }
+    } else if (tid >= 64u) {
+        // the zero blocks of T above the diagonal blocks: (row block, column block) = (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+        for (uint32_t e = tid - 64u; e < 6u * 64u; e += 192u) {
+            const uint32_t blk = e >> 6, q = (e >> 4) & 3u, col = e & 15u;
+            const uint32_t rb = blk < 3u ? 0u : (blk < 5u ? 1u : 2u), cb = blk < 3u ? blk + 1u : (blk < 5u ? blk - 1u : 3u);
+            tc4[(4u * rb + q) * 64u + 16u * cb + col] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
     }
     group_sync(bar_id);
     {
-        const uint32_t j = tid & 63u, h = tid >> 6;
-        uint8_t* tcol = smem + kPrWs + j * 16u;          // column j of T: group q at + q * 1024
+        auto dot4 = [](const float4& a, const float4& b, float acc) { return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, acc)))); };
+        const float4* a4 = reinterpret_cast<const float4*>(smem + kPrA);   // A: (column group g, row r) at g * 64 + r
+        // (2a), (2b): threads 0..127 = (pair s, row group q of the 16, column j of the 16)
+        const uint32_t s2 = (tid >> 6) & 1u, q2 = (tid >> 4) & 3u, j2 = tid & 15u, b0 = 2u * s2, b1 = b0 + 1u;
+        if (tid < 128u) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
-        for (uint32_t b = 0; b < 4; ++b) {
-            const uint8_t* arow = smem + kPrA + (16u * b + 4u * h) * 16u;   // this thread's four rows of A: row rr at + rr * 16
-            float2 acc[4];
+            for (uint32_t g = j2 >> 2; g < 4u; ++g) {      // D_b0[k][j] = 0 for k < j
+                const float4 d = tc4[(4u * b0 + g) * 64u + 16u * b0 + j2];
 #pragma unroll
-            for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = make_float2(0.0f, 0.0f);
-#pragma unroll 1
-            for (uint32_t q = 0; q < 4u * b; ++q) {
-                const float4 tv = *reinterpret_cast<const float4*>(tcol + q * 1024u);
-#pragma unroll
-                for (uint32_t rr = 0; rr < 4; ++rr) {
-                    const float4 av = *reinterpret_cast<const float4*>(arow + q * 1024u + rr * 16u);
-                    acc[rr] = __ffma2_rn(make_float2(av.x, av.y), make_float2(tv.x, tv.y), acc[rr]);
-                    acc[rr] = __ffma2_rn(make_float2(av.z, av.w), make_float2(tv.z, tv.w), acc[rr]);
-                }
+                for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = dot4(a4[(4u * b0 + g) * 64u + 16u * b1 + 4u * q2 + rr], d, acc[rr]);
             }
-#pragma unroll
-            for (uint32_t rr = 0; rr < 4; ++rr)
-                rhs_s[(4u * h + rr) * 64u + j] = (16u * b + 4u * h + rr == j ? 1.0f : 0.0f) - (acc[rr].x + acc[rr].y);
-            group_sync(bar_id);
-            float2 t2[4];
-#pragma unroll
-            for (uint32_t rr = 0; rr < 4; ++rr) t2[rr] = make_float2(0.0f, 0.0f);
-            const float* drow = dsm + (b * 16u + 4u * h) * 16u;
-#pragma unroll
-            for (uint32_t g4 = 0; g4 < 4; ++g4) {
-                const float2 r01 = make_float2(rhs_s[(4u * g4) * 64u + j], rhs_s[(4u * g4 + 1u) * 64u + j]);
-                const float2 r23 = make_float2(rhs_s[(4u * g4 + 2u) * 64u + j], rhs_s[(4u * g4 + 3u) * 64u + j]);
-#pragma unroll
-                for (uint32_t rr = 0; rr < 4; ++rr) {
-                    const float4 dv = *reinterpret_cast<const float4*>(drow + rr * 16u + 4u * g4);   // zero above the diagonal
-                    t2[rr] = __ffma2_rn(make_float2(dv.x, dv.y), r01, t2[rr]);
-                    t2[rr] = __ffma2_rn(make_float2(dv.z, dv.w), r23, t2[rr]);
-                }
-            }
-            *reinterpret_cast<float4*>(tcol + (4u * b + h) * 1024u) =
-                make_float4(t2[0].x + t2[0].y, t2[1].x + t2[1].y, t2[2].x + t2[2].y, t2[3].x + t2[3].y);
-            group_sync(bar_id);
+            x2c[s2 * 64u + q2 * 16u + j2] = make_float4(acc[0], acc[1], acc[2], acc[3]);
         }
+        group_sync(bar_id);
+        if (tid < 128u) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (uint32_t g = 0; g <= q2; ++g) {           // D_b1[r][k] = 0 for k > r
+                const float4 x = x2c[s2 * 64u + g * 16u + j2];
+#pragma unroll
+                for (uint32_t rr = 0; rr < 4; ++rr)
+                    acc[rr] = dot4(s2 == 0u ? dr1[g * 16u + 4u * q2 + rr] : thr[(4u + g) * 32u + 16u + 4u * q2 + rr], x, acc[rr]);
+            }
+            tc4[(4u * b1 + q2) * 64u + 16u * b0 + j2] = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
+            if (s2 == 1u) {
+#pragma unroll
+                for (uint32_t rr = 0; rr < 4; ++rr) reinterpret_cast<float*>(thr + (j2 >> 2) * 32u + 16u + 4u * q2 + rr)[j2 & 3u] = -acc[rr];
+            }
+        }
+        group_sync(bar_id);
+        // (3a), (3b): all threads = (row group q of the 32, column j of the 32)
+        const uint32_t q3 = tid >> 5, j3 = tid & 31u;
+        {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (uint32_t g = j3 >> 2; g < 8u; ++g) {      // T[..32][k][j] = 0 for k < j
+                const float4 t = tc4[g * 64u + j3];
+#pragma unroll
+                for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = dot4(a4[g * 64u + 32u + 4u * q3 + rr], t, acc[rr]);
+            }
+            x3c[q3 * 32u + j3] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        group_sync(bar_id);
+        {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (uint32_t g = 0; g <= q3; ++g) {           // T[32.., 32..][r][k] = 0 for k > r
+                const float4 x = x3c[g * 32u + j3];
+#pragma unroll
+                for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = dot4(thr[g * 32u + 4u * q3 + rr], x, acc[rr]);
+            }
+            tc4[(8u + q3) * 64u + j3] = make_float4(-acc[0], -acc[1], -acc[2], -acc[3]);
+        }
+        group_sync(bar_id);
     }
-    if (ok) {   // (the last barrier of the sweep: everyone is done with D_b before T_U is written over it)
+    if (ok) {   // (everyone is done with the by-rows copies before T_W and T_U are written over them)
         // column j of T scaled by this column's factors -> the K-major B tiles T_W and T_U (row r, element j)
         const uint32_t j = tid & 63u, h = tid >> 6;
         const uint8_t* tcol = smem + kPrWs + j * 16u;
