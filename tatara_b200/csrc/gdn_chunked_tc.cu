@@ -16,9 +16,9 @@
 //   gdn_tc_prepare_kernel -- no state.  Persistent CTAs of 256 threads (two per SM) walk the (chunk,
 //     v-head) units: six small MMA groups ([K;Q] K^T, K^T T_W^T, V^T T_U^T, Ws^T K, W^T P^T, U^T P^T)
 //     with the f32 inverse of the unit lower-triangular (I + A) between the first and the second
-//     (panels of 16 rows: the diagonal blocks by forward substitution, the rest as matrix-vector
-//     products, one column of T per thread quad: no bf16 enters the solve).  -M', Us^T, Q~^T, O0^T leave as bf16 images of the 128-byte-swizzled shared-memory tiles
-//     the scan wants (bulk copies out of shared memory: one coalesced stream per tile).
+//     (16 x 16 diagonal blocks by forward substitution, then block doubling: no bf16 enters the solve).
+//     -M', Us^T, Q~^T, O0^T leave as bf16 images of the 128-byte-swizzled shared-memory tiles the scan
+//     wants (bulk copies out of shared memory: one coalesced stream per tile).
 //   gdn_tc_scan_kernel -- one CTA per v-head walks the chunks.  The state is the f32 accumulator of
 //     the transition MMAs in tensor memory; between two chunks four warps read it (tcgen05.ld),
 //     scale it by e^{G_C} in f32 in place (tcgen05.st) and store its bf16 copy beside it in tensor
