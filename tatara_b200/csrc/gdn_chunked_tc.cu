@@ -309,8 +309,8 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
     //   (3a) X = A[32.., ..32] T[..32, ..32];                                   (3b) T[32.., ..32] = -T[32.., 32..] X.
     // Five barrier-to-barrier steps instead of the nine of a sweep over panels of 16 rows (whose steps cost ~ 1 k
     // cycles each whatever the arithmetic in them), and a third of its shared-memory loads.  A thread owns four
-    // consecutive rows of one column of a product; the triangular zeros of the right-hand factor of (2a), (3a) and
-    // of the left-hand factor of (2b), (3b) bound its loop.
+    // consecutive rows of one column of a product; the triangular zeros of the left-hand factor of (2b), (3b) bound
+    // its loop (uniformly for a warp).
     // Layouts: T (and with it D_b) is built in place as [row group][column][4 rows] (what the scaling pass below
     // reads); left-hand factors are wanted as [4-column group][row][4 columns]: A is stored so, D_1 and the 32 x 32
     // block T[32.., 32..] get a second copy in that form; the X of both levels is [row group][column][4 rows].
@@ -363,7 +363,8 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         if (tid < 128u) {
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
-            for (uint32_t g = j2 >> 2; g < 4u; ++g) {      // D_b0[k][j] = 0 for k < j
+            for (uint32_t g = 0; g < 4u; ++g) {            // (D_b0[k][j] = 0 for k < j, but a start that differs from lane to lane
+                                                           // turns the one-address loads of A into gathers: 3.1 -> 2.0 k cycles in (3a))
                 const float4 d = tc4[(4u * b0 + g) * 64u + 16u * b0 + j2];
 #pragma unroll
                 for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = dot4(a4[(4u * b0 + g) * 64u + 16u * b1 + 4u * q2 + rr], d, acc[rr]);
@@ -392,7 +393,7 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         {
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
-            for (uint32_t g = j3 >> 2; g < 8u; ++g) {      // T[..32][k][j] = 0 for k < j
+            for (uint32_t g = 0; g < 8u; ++g) {            // (likewise: the zeros of T above its diagonal are stored zeros)
                 const float4 t = tc4[g * 64u + j3];
 #pragma unroll
                 for (uint32_t rr = 0; rr < 4; ++rr) acc[rr] = dot4(a4[g * 64u + 32u + 4u * q3 + rr], t, acc[rr]);
@@ -413,20 +414,20 @@ __device__ __forceinline__ void tc_prepare_units(const uint32_t bar_id, const CU
         group_sync(bar_id);
     }
     if (ok) {   // (everyone is done with the by-rows copies before T_W and T_U are written over them)
-        // column j of T scaled by this column's factors -> the K-major B tiles T_W and T_U (row r, element j)
-        const uint32_t j = tid & 63u, h = tid >> 6;
-        const uint8_t* tcol = smem + kPrWs + j * 16u;
-        const float bj = beta_s[j], wj = bj * e_g[j];
-        const uint32_t col = (j & 7u) * 2u, chunk16 = j >> 3;
-#pragma unroll 1
-        for (uint32_t q = h * 4u; q < h * 4u + 4u; ++q) {
-            const float4 tv = *reinterpret_cast<const float4*>(tcol + q * 1024u);
-            const float te[4] = {tv.x, tv.y, tv.z, tv.w};
+        // T scaled by its columns' factors -> the K-major B tiles T_W and T_U (row r, element j).  A thread takes the
+        // column pair 2 jp, 2 jp + 1 of eight rows: one packed conversion and one 4-byte store per row and tile.
+        const uint32_t jp = tid & 31u, rh = tid >> 5;
+        const float b0 = beta_s[2u * jp], b1 = beta_s[2u * jp + 1u], w0 = b0 * e_g[2u * jp], w1 = b1 * e_g[2u * jp + 1u];
+        const uint32_t col = (jp & 3u) * 4u, chunk16 = jp >> 2;
+#pragma unroll
+        for (uint32_t rg = 0; rg < 2; ++rg) {
+            const float4 ta = tc4[(2u * rh + rg) * 64u + 2u * jp], tb4 = tc4[(2u * rh + rg) * 64u + 2u * jp + 1u];
+            const float ca[4] = {ta.x, ta.y, ta.z, ta.w}, cb[4] = {tb4.x, tb4.y, tb4.z, tb4.w};
 #pragma unroll
             for (uint32_t e = 0; e < 4; ++e) {
-                const uint32_t at = sw128(4u * q + e, chunk16) + col;
-                *reinterpret_cast<__nv_bfloat16*>(smem + kPrTW + at) = f2bf(te[e] * wj);
-                *reinterpret_cast<__nv_bfloat16*>(smem + kPrTU + at) = f2bf(te[e] * bj);
+                const uint32_t at = sw128(8u * rh + 4u * rg + e, chunk16) + col;
+                *reinterpret_cast<uint32_t*>(smem + kPrTW + at) = pack_bf2(ca[e] * w0, cb[e] * w1);
+                *reinterpret_cast<uint32_t*>(smem + kPrTU + at) = pack_bf2(ca[e] * b0, cb[e] * b1);
             }
         }
     }
