@@ -451,6 +451,39 @@ def test_chunked_prefill_both_forms_agree_with_the_oracle(ctx):
     assert_close_bf16(outs[0], outs[2], "tensor-memory form vs register form")
 
 
+def test_chunked_prefill_one_launch_hand_over_on_poisoned_scratch(ctx):
+    """The one-launch form hands every unit's planes from the preparation groups to the scan through a ready
+    word.  Run it repeatedly on scratch filled with 0xFF (a NaN wherever a plane is read before it was
+    written) and require the bits of the two-launch form, where the planes are complete before the scan starts."""
+    rows = 4096
+    g = torch.Generator(device="cuda").manual_seed(77)
+    x = torch.randn((rows, 32, 128), generator=g, device="cuda")
+    x = x / x.norm(dim=-1, keepdim=True)
+    qk = torch.cat([(x[:, :16] / 128 ** 0.5).reshape(rows, 2048), x[:, 16:].reshape(rows, 2048)], 1).to(torch.bfloat16).contiguous()
+    v = torch.randn((rows, 4096), generator=g, device="cuda").to(torch.bfloat16)
+    a = torch.randn((rows, 32), generator=g, device="cuda")
+    a_log = torch.log(1 + 15 * torch.rand(32, generator=g, device="cuda"))
+    decay = torch.exp(-torch.exp(a_log)[None, :] * torch.nn.functional.softplus(a)).contiguous()
+    beta = torch.sigmoid(torch.randn((rows, 32), generator=g, device="cuda")).contiguous()
+    s0 = torch.randn((32, 128, 128), generator=g, device="cuda") * 0.05
+    want = None
+    try:
+        for it in range(13):
+            ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 2 if it == 0 else 0)
+            scratch = torch.full((tb.gdn_prefill_scratch_bytes(rows),), 0xFF, dtype=torch.uint8, device="cuda")
+            y = torch.zeros((rows, 4096), dtype=torch.bfloat16, device="cuda")
+            s1 = torch.zeros_like(s0)
+            ctx.gdn_prefill(qk, v, decay, beta, s0, y, s1, rows, chunk=64, scratch=scratch)
+            ctx.sync()
+            if want is None:
+                assert torch.isfinite(y.float()).all() and torch.isfinite(s1).all()
+                want = (y, s1)
+            else:
+                assert torch.equal(y, want[0]) and torch.equal(s1, want[1]), f"one-launch run {it} differs from the two-launch form"
+    finally:
+        ctx.set_policy(tb.POLICY_GDN_CHUNK_FORM, 0)
+
+
 def test_chunked_prefill_config3_full_size(ctx):
     """Benchmark config 3: 16384 rows, chunk 64, initial state zero; per-token outputs and the
     final f32 state against the sequential oracle."""
